@@ -1,0 +1,381 @@
+// The C ABI of libdsmoe: handle, argument checks, tier-1 launch wrappers and the tier-2 layer call.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+#include "launch.h"
+
+using namespace dsmoe;
+
+struct dsmoe_layer_slot {
+    const uint8_t *gate, *up, *down;
+    int layout;
+    bool set;
+};
+
+struct dsmoe_handle {
+    dsmoe_config cfg;
+    int device;
+    mutable char err[512];
+    uint64_t launches;
+    dsmoe_layer_slot *layers;
+    // library-owned scratch for the tier-2 call, sized by cfg.max_tokens
+    float *probs, *weights, *mid;
+    int32_t *selected;
+    uint8_t *xq, *midq;
+    // staging for the host-buffer call
+    cudaStream_t hstream;
+    float *d_x, *d_logits, *d_out;
+};
+
+namespace {
+
+int fail(const dsmoe_handle *h, int code, const char *fmt, ...)
+{
+    if (h) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(h->err, sizeof(h->err), fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+
+int check_launch(dsmoe_handle *h, const char *what, int n_launched)
+{
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(h, DSMOE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    h->launches += (uint64_t)n_launched;
+    return DSMOE_OK;
+}
+
+bool aligned(const void *p, size_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
+
+int check_layout(const dsmoe_handle *h, int layout)
+{
+    if (layout != DSMOE_LAYOUT_NATIVE && layout != DSMOE_LAYOUT_ROWSOA)
+        return fail(h, DSMOE_ERR_ARG, "unknown layout %d", layout);
+    return DSMOE_OK;
+}
+
+template <typename T>
+cudaError_t dev_alloc(T **p, size_t n)
+{
+    *p = nullptr;
+    return n ? cudaMalloc((void **)p, n * sizeof(T)) : cudaSuccess;
+}
+
+#define DSMOE_REQUIRE(h, cond, ...) \
+    do {                            \
+        if (!(cond)) return fail((h), DSMOE_ERR_ARG, __VA_ARGS__); \
+    } while (0)
+
+}  // namespace
+
+extern "C" {
+
+const char *dsmoe_version(void) { return "dsmoe 0.1 (sm_100a)"; }
+
+void dsmoe_default_config(dsmoe_config *cfg)
+{
+    if (!cfg) return;
+    cfg->n_embd = 4096;
+    cfg->n_ff = 2048;
+    cfg->n_expert = 256;
+    cfg->n_expert_used = 6;
+    cfg->swiglu_clamp = 10.0f;
+    cfg->route_scale = 1.5f;
+    cfg->f16_ieee = 0;
+    cfg->max_tokens = 64;
+    cfg->max_layers = 1;
+}
+
+int dsmoe_create(const dsmoe_config *cfg, int device, dsmoe_handle **out)
+{
+    if (!cfg || !out) return DSMOE_ERR_ARG;
+    *out = nullptr;
+    if (cfg->n_embd == 0 || cfg->n_embd % QK_K || cfg->n_ff == 0 || cfg->n_ff % QK_K) return DSMOE_ERR_ARG;
+    if (cfg->n_expert == 0 || cfg->n_expert % 32 || cfg->n_expert > 512) return DSMOE_ERR_ARG;
+    if (cfg->n_expert_used == 0 || cfg->n_expert_used > MAX_K || cfg->n_expert_used > cfg->n_expert) return DSMOE_ERR_ARG;
+    if (!(cfg->route_scale > 0.0f)) return DSMOE_ERR_ARG;
+
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) return DSMOE_ERR_CUDA;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return DSMOE_ERR_CUDA;
+    if (prop.major != 10) return DSMOE_ERR_CUDA;  // the kernels are sm_100a machine code only
+    if (cudaSetDevice(device) != cudaSuccess) return DSMOE_ERR_CUDA;
+
+    dsmoe_handle *h = new (std::nothrow) dsmoe_handle();
+    if (!h) return DSMOE_ERR_NOMEM;
+    memset(h, 0, sizeof(*h));
+    h->cfg = *cfg;
+    h->device = device;
+    const size_t T = cfg->max_tokens, k = cfg->n_expert_used;
+    const size_t L = cfg->max_layers ? cfg->max_layers : 1;
+    h->layers = new (std::nothrow) dsmoe_layer_slot[L]();
+    bool ok = h->layers != nullptr;
+    ok = ok && dev_alloc(&h->probs, T * cfg->n_expert) == cudaSuccess;
+    ok = ok && dev_alloc(&h->weights, T * k) == cudaSuccess;
+    ok = ok && dev_alloc(&h->selected, T * k) == cudaSuccess;
+    ok = ok && dev_alloc(&h->xq, T * (cfg->n_embd / QK_K) * Q8K_BYTES) == cudaSuccess;
+    ok = ok && dev_alloc(&h->mid, T * k * cfg->n_ff) == cudaSuccess;
+    ok = ok && dev_alloc(&h->midq, T * k * (cfg->n_ff / QK_K) * Q8K_BYTES) == cudaSuccess;
+    ok = ok && dev_alloc(&h->d_x, T * cfg->n_embd) == cudaSuccess;
+    ok = ok && dev_alloc(&h->d_logits, T * cfg->n_expert) == cudaSuccess;
+    ok = ok && dev_alloc(&h->d_out, T * cfg->n_embd) == cudaSuccess;
+    ok = ok && cudaStreamCreateWithFlags(&h->hstream, cudaStreamNonBlocking) == cudaSuccess;
+    if (!ok) {
+        cudaGetLastError();
+        dsmoe_destroy(h);
+        return DSMOE_ERR_NOMEM;
+    }
+    *out = h;
+    return DSMOE_OK;
+}
+
+int dsmoe_destroy(dsmoe_handle *h)
+{
+    if (!h) return DSMOE_OK;
+    cudaSetDevice(h->device);
+    if (h->hstream) cudaStreamDestroy(h->hstream);
+    cudaFree(h->probs);
+    cudaFree(h->weights);
+    cudaFree(h->selected);
+    cudaFree(h->xq);
+    cudaFree(h->mid);
+    cudaFree(h->midq);
+    cudaFree(h->d_x);
+    cudaFree(h->d_logits);
+    cudaFree(h->d_out);
+    delete[] h->layers;
+    delete h;
+    return DSMOE_OK;
+}
+
+const char *dsmoe_last_error(const dsmoe_handle *h) { return h ? h->err : "null handle"; }
+uint64_t dsmoe_launch_count(const dsmoe_handle *h) { return h ? h->launches : 0; }
+
+// ---------------------------------------------------------------------------------------------------------------
+// tier 1
+// ---------------------------------------------------------------------------------------------------------------
+
+int dsmoe_q8k_quantize(dsmoe_handle *h, dsmoe_stream stream, const float *x, uint8_t *out, uint32_t in_dim,
+                       uint32_t n_rows)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_REQUIRE(h, in_dim % QK_K == 0, "q8k_quantize: in_dim %u is not a multiple of 256", in_dim);
+    if (n_rows == 0 || in_dim == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, x && out, "q8k_quantize: null pointer");
+    DSMOE_REQUIRE(h, aligned(x, 16) && aligned(out, 4), "q8k_quantize: x must be 16-byte and out 4-byte aligned");
+    launch_q8k_quantize((cudaStream_t)stream, x, out, in_dim, n_rows);
+    return check_launch(h, "q8k_quantize", 1);
+}
+
+int dsmoe_router_select(dsmoe_handle *h, dsmoe_stream stream, const float *logits, const float *bias,
+                        const int32_t *hash, const int32_t *tokens, float *probs, int32_t *selected, float *weights,
+                        int32_t token_scalar, uint32_t hash_rows, uint32_t n_tokens, uint32_t has_bias,
+                        uint32_t hash_mode)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    if (n_tokens == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, logits && probs && selected && weights, "router_select: null pointer");
+    DSMOE_REQUIRE(h, !has_bias || bias, "router_select: has_bias set but bias is null");
+    DSMOE_REQUIRE(h, !hash_mode || (hash && hash_rows > 0), "router_select: hash_mode set but no hash table");
+    launch_router_select((cudaStream_t)stream, logits, has_bias ? bias : nullptr, hash_mode ? hash : nullptr, tokens,
+                         probs, selected, weights, token_scalar, hash_rows, n_tokens, has_bias != 0, hash_mode != 0,
+                         (int)h->cfg.n_expert_used, (int)h->cfg.n_expert, h->cfg.route_scale);
+    return check_launch(h, "router_select", 1);
+}
+
+int dsmoe_gate_up_mid(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *gate_base, const uint8_t *up_base,
+                      const uint8_t *xq, const int32_t *selected, const float *weights, float *gate_out, float *up_out,
+                      float *mid_out, uint64_t gate_expert_bytes, uint64_t gate_row_bytes, uint32_t xq_blocks,
+                      uint32_t expert_mid_dim, uint32_t n_expert_used, uint32_t n_tokens, float clamp, int layout)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    if (int rc = check_layout(h, layout)) return rc;
+    if (n_tokens == 0 || expert_mid_dim == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, gate_base && up_base && xq && selected && weights && mid_out, "gate_up_mid: null pointer");
+    DSMOE_REQUIRE(h, n_expert_used >= 1 && n_expert_used <= MAX_K, "gate_up_mid: n_expert_used %u out of 1..8", n_expert_used);
+    DSMOE_REQUIRE(h, xq_blocks >= 1 && gate_row_bytes >= (uint64_t)xq_blocks * IQ2XXS_BYTES,
+                  "gate_up_mid: row stride %llu shorter than %u blocks", (unsigned long long)gate_row_bytes, xq_blocks);
+    DSMOE_REQUIRE(h, aligned(gate_base, 2) && aligned(up_base, 2) && gate_row_bytes % 2 == 0 && gate_expert_bytes % 2 == 0,
+                  "gate_up_mid: packed rows must be 2-byte aligned");
+    DSMOE_REQUIRE(h, aligned(xq, 4), "gate_up_mid: xq must be 4-byte aligned");
+    GateUpArgs a = {gate_base, up_base, xq, selected, weights, gate_out, up_out, mid_out, gate_expert_bytes,
+                    gate_row_bytes, xq_blocks, expert_mid_dim, n_expert_used, n_tokens, clamp, layout,
+                    (int)h->cfg.f16_ieee};
+    DSMOE_REQUIRE(h, (uint64_t)n_tokens * n_expert_used <= 65535u, "gate_up_mid: n_tokens*k exceeds 65535");
+    int n = launch_gate_up_mid((cudaStream_t)stream, a);
+    return check_launch(h, "gate_up_mid", n);
+}
+
+static int down_common(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *down_base, const uint8_t *midq,
+                       const int32_t *selected, float *out, uint64_t down_expert_bytes, uint64_t down_row_bytes,
+                       uint32_t midq_blocks, uint32_t out_dim, uint32_t n_expert_used, uint32_t n_tokens, int layout,
+                       int sum_slots)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    if (int rc = check_layout(h, layout)) return rc;
+    if (n_tokens == 0 || out_dim == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, down_base && midq && selected && out, "down: null pointer");
+    DSMOE_REQUIRE(h, n_expert_used >= 1 && n_expert_used <= MAX_K, "down: n_expert_used %u out of 1..8", n_expert_used);
+    DSMOE_REQUIRE(h, midq_blocks >= 1 && down_row_bytes >= (uint64_t)midq_blocks * Q2K_BYTES,
+                  "down: row stride %llu shorter than %u blocks", (unsigned long long)down_row_bytes, midq_blocks);
+    DSMOE_REQUIRE(h, aligned(down_base, 4) && down_row_bytes % 4 == 0 && down_expert_bytes % 4 == 0 && aligned(midq, 4),
+                  "down: packed rows and midq must be 4-byte aligned");
+    DSMOE_REQUIRE(h, n_tokens <= 65535u, "down: n_tokens exceeds 65535");
+    DownArgs a = {down_base, midq, selected, out, down_expert_bytes, down_row_bytes, midq_blocks, out_dim,
+                  n_expert_used, n_tokens, layout, (int)h->cfg.f16_ieee, sum_slots};
+    int n = launch_down((cudaStream_t)stream, a);
+    return check_launch(h, sum_slots ? "down_sum" : "down", n);
+}
+
+int dsmoe_down(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *down_base, const uint8_t *midq,
+               const int32_t *selected, float *down_out, uint64_t down_expert_bytes, uint64_t down_row_bytes,
+               uint32_t midq_blocks, uint32_t out_dim, uint32_t n_expert_used, uint32_t n_tokens, int layout)
+{
+    return down_common(h, stream, down_base, midq, selected, down_out, down_expert_bytes, down_row_bytes, midq_blocks,
+                       out_dim, n_expert_used, n_tokens, layout, 0);
+}
+
+int dsmoe_down_sum(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *down_base, const uint8_t *midq,
+                   const int32_t *selected, float *out, uint64_t down_expert_bytes, uint64_t down_row_bytes,
+                   uint32_t midq_blocks, uint32_t out_dim, uint32_t n_expert_used, uint32_t n_tokens, int layout)
+{
+    return down_common(h, stream, down_base, midq, selected, out, down_expert_bytes, down_row_bytes, midq_blocks,
+                       out_dim, n_expert_used, n_tokens, layout, 1);
+}
+
+int dsmoe_moe_sum(dsmoe_handle *h, dsmoe_stream stream, const float *down, float *out, uint32_t out_dim,
+                  uint32_t n_expert_used, uint32_t n_tokens)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    if (n_tokens == 0 || out_dim == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, down && out, "moe_sum: null pointer");
+    launch_moe_sum((cudaStream_t)stream, down, out, out_dim, n_expert_used, n_tokens);
+    return check_launch(h, "moe_sum", 1);
+}
+
+int dsmoe_dequant_iq2xxs(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *blocks, uint64_t n_blocks, float *out)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    if (n_blocks == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, blocks && out && aligned(blocks, 2), "dequant_iq2xxs: null or misaligned pointer");
+    launch_dequant_iq2xxs((cudaStream_t)stream, blocks, n_blocks, out, (int)h->cfg.f16_ieee);
+    return check_launch(h, "dequant_iq2xxs", 1);
+}
+
+int dsmoe_dequant_q2k(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *blocks, uint64_t n_blocks, float *out)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    if (n_blocks == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, blocks && out && aligned(blocks, 2), "dequant_q2k: null or misaligned pointer");
+    launch_dequant_q2k((cudaStream_t)stream, blocks, n_blocks, out, (int)h->cfg.f16_ieee);
+    return check_launch(h, "dequant_q2k", 1);
+}
+
+int dsmoe_relayout_iq2xxs(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *src, uint8_t *dst, uint64_t n_rows,
+                          uint32_t blocks_per_row, int inverse)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    if (n_rows == 0 || blocks_per_row == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, src && dst && src != dst && aligned(src, 2) && aligned(dst, 2),
+                  "relayout_iq2xxs: null, aliased or misaligned pointer");
+    launch_relayout_iq2xxs((cudaStream_t)stream, src, dst, n_rows, blocks_per_row, inverse);
+    return check_launch(h, "relayout_iq2xxs", 1);
+}
+
+int dsmoe_relayout_q2k(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *src, uint8_t *dst, uint64_t n_rows,
+                       uint32_t blocks_per_row, int inverse)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    if (n_rows == 0 || blocks_per_row == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, src && dst && src != dst && aligned(src, 4) && aligned(dst, 4),
+                  "relayout_q2k: null, aliased or misaligned pointer");
+    launch_relayout_q2k((cudaStream_t)stream, src, dst, n_rows, blocks_per_row, inverse);
+    return check_launch(h, "relayout_q2k", 1);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// tier 2
+// ---------------------------------------------------------------------------------------------------------------
+
+int dsmoe_layer_register(dsmoe_handle *h, uint32_t layer, const uint8_t *gate, const uint8_t *up, const uint8_t *down,
+                         int layout)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    if (int rc = check_layout(h, layout)) return rc;
+    const uint32_t L = h->cfg.max_layers ? h->cfg.max_layers : 1;
+    DSMOE_REQUIRE(h, layer < L, "layer_register: layer %u beyond max_layers %u", layer, L);
+    DSMOE_REQUIRE(h, gate && up && down, "layer_register: null tensor");
+    const size_t al = layout == DSMOE_LAYOUT_ROWSOA ? 16 : 4;
+    DSMOE_REQUIRE(h, aligned(gate, al) && aligned(up, al) && aligned(down, al),
+                  "layer_register: tensors must be %zu-byte aligned for this layout", al);
+    h->layers[layer] = {gate, up, down, layout, true};
+    return DSMOE_OK;
+}
+
+int dsmoe_moe_forward(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, const float *x, const float *logits,
+                      uint32_t n_tokens, float *out, int32_t *selected_out, float *weights_out)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    const dsmoe_config &c = h->cfg;
+    const uint32_t L = c.max_layers ? c.max_layers : 1;
+    if (layer >= L || !h->layers[layer].set) return fail(h, DSMOE_ERR_STATE, "moe_forward: layer %u not registered", layer);
+    if (n_tokens > c.max_tokens)
+        return fail(h, DSMOE_ERR_BOUNDS, "moe_forward: n_tokens %u exceeds max_tokens %u", n_tokens, c.max_tokens);
+    if (n_tokens == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, x && logits && out, "moe_forward: null pointer");
+    DSMOE_REQUIRE(h, aligned(x, 16), "moe_forward: x must be 16-byte aligned");
+    DSMOE_REQUIRE(h, (uint64_t)n_tokens * c.n_expert_used <= 65535u, "moe_forward: n_tokens*k exceeds 65535");
+    const dsmoe_layer_slot &ly = h->layers[layer];
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint32_t k = c.n_expert_used, xb = c.n_embd / QK_K, mb = c.n_ff / QK_K;
+    int32_t *sel = selected_out ? selected_out : h->selected;
+    float *wts = weights_out ? weights_out : h->weights;
+
+    launch_router_select(st, logits, nullptr, nullptr, nullptr, h->probs, sel, wts, 0, 0, n_tokens, 0, 0, (int)k,
+                         (int)c.n_expert, c.route_scale);
+    launch_q8k_quantize(st, x, h->xq, c.n_embd, n_tokens);
+    GateUpArgs g = {ly.gate, ly.up, h->xq, sel, wts, nullptr, nullptr, h->mid, (uint64_t)c.n_ff * xb * IQ2XXS_BYTES,
+                    (uint64_t)xb * IQ2XXS_BYTES, xb, c.n_ff, k, n_tokens, c.swiglu_clamp, ly.layout, (int)c.f16_ieee};
+    int n = 2 + launch_gate_up_mid(st, g);
+    launch_q8k_quantize(st, h->mid, h->midq, c.n_ff, n_tokens * k);
+    DownArgs d = {ly.down, h->midq, sel, out, (uint64_t)c.n_embd * mb * Q2K_BYTES, (uint64_t)mb * Q2K_BYTES, mb,
+                  c.n_embd, k, n_tokens, ly.layout, (int)c.f16_ieee, 1};
+    n += 1 + launch_down(st, d);
+    return check_launch(h, "moe_forward", n);
+}
+
+int dsmoe_moe_forward_host(dsmoe_handle *h, uint32_t layer, const float *x_host, const float *logits_host,
+                           uint32_t n_tokens, float *out_host, int32_t *selected_out_host, float *weights_out_host)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    const dsmoe_config &c = h->cfg;
+    if (n_tokens > c.max_tokens)
+        return fail(h, DSMOE_ERR_BOUNDS, "moe_forward_host: n_tokens %u exceeds max_tokens %u", n_tokens, c.max_tokens);
+    if (n_tokens == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, x_host && logits_host && out_host, "moe_forward_host: null pointer");
+    cudaStream_t st = h->hstream;
+    const size_t k = c.n_expert_used;
+    cudaError_t e = cudaMemcpyAsync(h->d_x, x_host, (size_t)n_tokens * c.n_embd * 4, cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(h->d_logits, logits_host, (size_t)n_tokens * c.n_expert * 4, cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) return fail(h, DSMOE_ERR_CUDA, "moe_forward_host: copy in: %s", cudaGetErrorString(e));
+    int rc = dsmoe_moe_forward(h, st, layer, h->d_x, h->d_logits, n_tokens, h->d_out, h->selected, h->weights);
+    if (rc != DSMOE_OK) return rc;
+    e = cudaMemcpyAsync(out_host, h->d_out, (size_t)n_tokens * c.n_embd * 4, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess && selected_out_host)
+        e = cudaMemcpyAsync(selected_out_host, h->selected, n_tokens * k * 4, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess && weights_out_host)
+        e = cudaMemcpyAsync(weights_out_host, h->weights, n_tokens * k * 4, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return fail(h, DSMOE_ERR_CUDA, "moe_forward_host: copy out: %s", cudaGetErrorString(e));
+    return DSMOE_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,46 @@
+// Host-side launchers shared between the kernel files and the C ABI. Each launches on the given stream and returns
+// without synchronising; the caller checks cudaGetLastError().
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace dsmoe {
+
+void launch_q8k_quantize(cudaStream_t st, const float *x, uint8_t *out, uint32_t in_dim, uint32_t n_rows);
+
+void launch_router_select(cudaStream_t st, const float *logits, const float *bias, const int32_t *hash,
+                          const int32_t *tokens, float *probs, int32_t *selected, float *weights, int32_t token_scalar,
+                          uint32_t hash_rows, uint32_t n_tokens, int has_bias, int hash_mode, int k, int n_expert,
+                          float route_scale);
+
+void launch_dequant_iq2xxs(cudaStream_t st, const uint8_t *blocks, uint64_t n_blocks, float *out, int ieee);
+void launch_dequant_q2k(cudaStream_t st, const uint8_t *blocks, uint64_t n_blocks, float *out, int ieee);
+void launch_relayout_iq2xxs(cudaStream_t st, const uint8_t *src, uint8_t *dst, uint64_t n_rows, uint32_t xb, int inverse);
+void launch_relayout_q2k(cudaStream_t st, const uint8_t *src, uint8_t *dst, uint64_t n_rows, uint32_t mb, int inverse);
+void launch_moe_sum(cudaStream_t st, const float *down, float *out, uint32_t out_dim, uint32_t k, uint32_t n_tokens);
+
+struct GateUpArgs {
+    const uint8_t *gate_base, *up_base, *xq;
+    const int32_t *selected;
+    const float *weights;
+    float *gate_out, *up_out, *mid_out;
+    uint64_t expert_bytes, row_bytes;
+    uint32_t xq_blocks, mid_dim, k, n_tokens;
+    float clamp;
+    int layout, ieee;
+};
+// Returns the number of kernels launched.
+int launch_gate_up_mid(cudaStream_t st, const GateUpArgs &a);
+
+struct DownArgs {
+    const uint8_t *down_base, *midq;
+    const int32_t *selected;
+    float *out;  // [n_tokens*k][out_dim] when sum_slots == 0, [n_tokens][out_dim] otherwise
+    uint64_t expert_bytes, row_bytes;
+    uint32_t midq_blocks, out_dim, k, n_tokens;
+    int layout, ieee, sum_slots;
+};
+int launch_down(cudaStream_t st, const DownArgs &a);
+
+}  // namespace dsmoe

@@ -1,0 +1,326 @@
+// Q8_K activation quantiser, router top-k, dequantisers, upload-time re-layout and the slot sum.
+#include "common.cuh"
+#include "launch.h"
+
+namespace dsmoe {
+
+// ---------------------------------------------------------------------------------------------------------------
+// Q8_K quantiser: one warp per 256-element block, lane l owns elements 8l..8l+7.
+//
+// Result is bit-identical to the reference kernel (engine/src/kernels/quantize.rs:309-417). Its shared-memory
+// halving tree keeps the lower slot on equal magnitudes, level by level from stride 128 down to 1, so among equal
+// maxima the element with the smallest bit-reversed index wins; using (|x|, bit-reversed index) as the reduction key
+// reproduces that choice (and hence the sign of d) in any reduction order.
+// ---------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) q8k_quantize_kernel(const float *__restrict__ x, uint8_t *__restrict__ out,
+                                                            uint64_t n_blocks_total)
+{
+    const int lane = threadIdx.x & 31;
+    const uint64_t blk = (uint64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (blk >= n_blocks_total) return;
+    const float4 *src = reinterpret_cast<const float4 *>(x + blk * QK_K + 8 * lane);
+    float4 v0 = src[0], v1 = src[1];
+    float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+
+    float best_abs = -1.0f, best_val = 0.0f;
+    uint32_t best_rev = 0xFFFFFFFFu;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float a = v[i] < 0.0f ? -v[i] : v[i];
+        uint32_t rev = __brev((uint32_t)(8 * lane + i)) >> 24;
+        if (a > best_abs || (a == best_abs && rev < best_rev)) {
+            best_abs = a;
+            best_val = v[i];
+            best_rev = rev;
+        }
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+        float oa = __shfl_xor_sync(FULL, best_abs, m);
+        float ov = __shfl_xor_sync(FULL, best_val, m);
+        uint32_t orv = __shfl_xor_sync(FULL, best_rev, m);
+        if (oa > best_abs || (oa == best_abs && orv < best_rev)) {
+            best_abs = oa;
+            best_val = ov;
+            best_rev = orv;
+        }
+    }
+
+    uint8_t *yb = out + blk * Q8K_BYTES;
+    uint32_t *qdst = reinterpret_cast<uint32_t *>(yb + 4 + 8 * lane);
+    if (!(best_abs > 0.0f)) {  // amax == 0 (or no finite maximum): all-zero block
+        if (lane == 0) *reinterpret_cast<float *>(yb) = 0.0f;
+        qdst[0] = 0u;
+        qdst[1] = 0u;
+        if (lane < 16) reinterpret_cast<uint16_t *>(yb + 260)[lane] = 0;
+        return;
+    }
+    const float iscale = __fdiv_rn(-127.0f, best_val);
+    if (lane == 0) *reinterpret_cast<float *>(yb) = __fdiv_rn(1.0f, iscale);
+
+    int q[8], s = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float raw = __fmul_rn(iscale, v[i]);
+        int qi = raw >= 0.0f ? __float2int_rz(__fadd_rn(raw, 0.5f)) : __float2int_rz(__fadd_rn(raw, -0.5f));
+        qi = max(-128, min(127, qi));
+        q[i] = qi;
+        s += qi;
+    }
+    qdst[0] = (uint32_t)(q[0] & 255) | ((uint32_t)(q[1] & 255) << 8) | ((uint32_t)(q[2] & 255) << 16) |
+              ((uint32_t)(q[3] & 255) << 24);
+    qdst[1] = (uint32_t)(q[4] & 255) | ((uint32_t)(q[5] & 255) << 8) | ((uint32_t)(q[6] & 255) << 16) |
+              ((uint32_t)(q[7] & 255) << 24);
+    s += __shfl_xor_sync(FULL, s, 1);  // bsums cover 16 elements = two lanes
+    if ((lane & 1) == 0) reinterpret_cast<int16_t *>(yb + 260)[lane >> 1] = (int16_t)s;
+}
+
+void launch_q8k_quantize(cudaStream_t st, const float *x, uint8_t *out, uint32_t in_dim, uint32_t n_rows)
+{
+    uint64_t nb = (uint64_t)(in_dim / QK_K) * n_rows;
+    if (nb == 0) return;
+    q8k_quantize_kernel<<<(unsigned)((nb + 7) / 8), 256, 0, st>>>(x, out, nb);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Router: one warp per token. probs = sqrt(softplus(logit)); k rounds of warp arg-max with the reference's order
+// (higher score first, lower index on equal scores), which yields the same list as its insertion scan
+// (engine/src/kernels/moe.rs:239-263). Scores that are not greater than -inf (NaN, -inf) are never selected, as in
+// the reference, and leave -1 in the list.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int ROUTER_MAX_PER_LANE = 16;  // up to 512 experts
+
+__global__ void __launch_bounds__(128) router_select_kernel(const float *__restrict__ logits,
+                                                             const float *__restrict__ bias,
+                                                             const int32_t *__restrict__ hash,
+                                                             const int32_t *__restrict__ tokens,
+                                                             float *__restrict__ probs, int32_t *__restrict__ selected,
+                                                             float *__restrict__ weights, int32_t token_scalar,
+                                                             uint32_t hash_rows, uint32_t n_tokens, int has_bias,
+                                                             int hash_mode, int k, int n_expert, float route_scale)
+{
+    const int lane = threadIdx.x & 31;
+    const uint32_t t = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (t >= n_tokens) return;
+    const int per_lane = n_expert >> 5;
+    float p[ROUTER_MAX_PER_LANE], sc[ROUTER_MAX_PER_LANE];
+#pragma unroll
+    for (int j = 0; j < ROUTER_MAX_PER_LANE; ++j) {
+        p[j] = 0.0f;
+        sc[j] = -INFINITY;
+        if (j < per_lane) {
+            int e = lane + 32 * j;
+            float pe = sqrtf(softplus_ref(logits[(size_t)t * n_expert + e]));
+            p[j] = pe;
+            sc[j] = has_bias ? __fadd_rn(pe, bias[e]) : pe;
+            probs[(size_t)t * n_expert + e] = pe;
+        }
+    }
+
+    int sel_mine = -1;     // lane j keeps the j-th selection
+    float w_mine = 0.0f;   // and its un-biased probability
+    if (hash_mode) {
+        int32_t raw = tokens ? tokens[t] : token_scalar;
+        size_t tok = (raw < 0 || (uint32_t)raw >= hash_rows) ? 0 : (size_t)raw;
+        if (lane < k) sel_mine = hash[tok * k + lane];
+        // fetch the probability of an arbitrary expert id from the lane that owns it
+        for (int j = 0; j < k; ++j) {
+            int e = __shfl_sync(FULL, sel_mine, j);
+            bool ok = e >= 0 && e < n_expert;
+            int owner = ok ? (e & 31) : 0, slot = ok ? (e >> 5) : 0;
+            float mine = 0.0f;
+#pragma unroll
+            for (int q = 0; q < ROUTER_MAX_PER_LANE; ++q)
+                if (q == slot) mine = p[q];
+            float pv = __shfl_sync(FULL, mine, owner);
+            if (lane == j) w_mine = ok ? pv : 0.0f;
+        }
+    } else {
+        for (int r = 0; r < k; ++r) {
+            float bs = -INFINITY, bp = 0.0f;
+            int bi = -1;
+#pragma unroll
+            for (int j = 0; j < ROUTER_MAX_PER_LANE; ++j)
+                if (j < per_lane && sc[j] > -INFINITY) {
+                    int e = lane + 32 * j;
+                    if (bi < 0 || sc[j] > bs) {  // ascending e within the lane: strict > keeps the lower index
+                        bs = sc[j];
+                        bp = p[j];
+                        bi = e;
+                    }
+                }
+#pragma unroll
+            for (int m = 16; m > 0; m >>= 1) {
+                float os = __shfl_xor_sync(FULL, bs, m);
+                float op = __shfl_xor_sync(FULL, bp, m);
+                int oi = __shfl_xor_sync(FULL, bi, m);
+                bool take = oi >= 0 && (bi < 0 || os > bs || (os == bs && oi < bi));
+                if (take) {
+                    bs = os;
+                    bp = op;
+                    bi = oi;
+                }
+            }
+            if (bi >= 0 && (bi & 31) == lane) {
+#pragma unroll
+                for (int j = 0; j < ROUTER_MAX_PER_LANE; ++j)
+                    if (j == (bi >> 5)) sc[j] = -INFINITY;
+            }
+            if (lane == r) {
+                sel_mine = bi;
+                w_mine = bi >= 0 ? bp : 0.0f;
+            }
+        }
+    }
+    // sum in slot order, floor at 2^-14, w /= (sum / route_scale)   (engine/src/kernels/moe.rs:266-286)
+    float sum = 0.0f;
+    for (int j = 0; j < k; ++j) sum = __fadd_rn(sum, __shfl_sync(FULL, w_mine, j));
+    if (sum < 6.103515625e-5f) sum = 6.103515625e-5f;
+    float div = __fdiv_rn(sum, route_scale);
+    if (lane < k) {
+        selected[(size_t)t * k + lane] = sel_mine;
+        weights[(size_t)t * k + lane] = __fdiv_rn(w_mine, div);
+    }
+}
+
+void launch_router_select(cudaStream_t st, const float *logits, const float *bias, const int32_t *hash,
+                          const int32_t *tokens, float *probs, int32_t *selected, float *weights, int32_t token_scalar,
+                          uint32_t hash_rows, uint32_t n_tokens, int has_bias, int hash_mode, int k, int n_expert,
+                          float route_scale)
+{
+    if (n_tokens == 0) return;
+    router_select_kernel<<<(n_tokens + 3) / 4, 128, 0, st>>>(logits, bias, hash, tokens, probs, selected, weights,
+                                                             token_scalar, hash_rows, n_tokens, has_bias, hash_mode, k,
+                                                             n_expert, route_scale);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Dequantisers (NATIVE block order). One thread per 8 weights.
+// ---------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) dequant_iq2xxs_kernel(const uint8_t *__restrict__ blocks, uint64_t n_units,
+                                                              float *__restrict__ out, int ieee)
+{
+    uint64_t u = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;  // unit = (block, ib32, k)
+    if (u >= n_units) return;
+    uint64_t b = u >> 5;
+    int ib32 = (int)(u >> 2) & 7, k = (int)u & 3;
+    const uint8_t *blk = blocks + b * IQ2XXS_BYTES;
+    const uint16_t *q2 = reinterpret_cast<const uint16_t *>(blk + 2 + 8 * ib32);
+    uint32_t aux0 = (uint32_t)q2[0] | ((uint32_t)q2[1] << 16);
+    uint32_t aux1 = (uint32_t)q2[2] | ((uint32_t)q2[3] << 16);
+    float d = __fmul_rn(0.125f, f16_bits_to_f32(ld_u16(blk), ieee != 0));
+    int ls = (int)(2u * (aux1 >> 28) + 1u);
+    uint64_t g = c_iq2xxs_grid[(aux0 >> (8 * k)) & 255u];
+    uint32_t sb = dsmoe_iq2_sign_byte((aux1 >> (7 * k)) & 127u);
+    float *o = out + b * QK_K + 32 * ib32 + 8 * k;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        int mag = (int)((g >> (8 * j)) & 0xFFu);
+        int code = ls * (((sb >> j) & 1u) ? -mag : mag);
+        o[j] = __fmul_rn(d, (float)code);
+    }
+}
+
+__global__ void __launch_bounds__(256) dequant_q2k_kernel(const uint8_t *__restrict__ blocks, uint64_t n_elems,
+                                                           float *__restrict__ out, int ieee)
+{
+    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_elems) return;
+    uint64_t b = i >> 8;
+    int e = (int)i & 255, h = e >> 7, j = (e >> 5) & 3, ii = e & 31;
+    const uint8_t *blk = blocks + b * Q2K_BYTES;
+    int sb = 8 * h + 2 * j + (ii >> 4);
+    int q = (blk[16 + 32 * h + ii] >> (2 * j)) & 3;
+    float d = f16_bits_to_f32(ld_u16(blk + 80), ieee != 0), dmin = f16_bits_to_f32(ld_u16(blk + 82), ieee != 0);
+    float a = __fmul_rn(d, (float)((blk[sb] & 0x0F) * q));
+    float m = __fmul_rn(dmin, (float)(blk[sb] >> 4));
+    out[i] = __fsub_rn(a, m);
+}
+
+void launch_dequant_iq2xxs(cudaStream_t st, const uint8_t *blocks, uint64_t n_blocks, float *out, int ieee)
+{
+    uint64_t units = n_blocks * 32;
+    if (units == 0) return;
+    dequant_iq2xxs_kernel<<<(unsigned)((units + 255) / 256), 256, 0, st>>>(blocks, units, out, ieee);
+}
+
+void launch_dequant_q2k(cudaStream_t st, const uint8_t *blocks, uint64_t n_blocks, float *out, int ieee)
+{
+    uint64_t n = n_blocks * QK_K;
+    if (n == 0) return;
+    dequant_q2k_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(blocks, n, out, ieee);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Row re-layout NATIVE <-> ROWSOA: a byte permutation inside each row, done once at upload.
+// IQ2_XXS rows move in 2-byte units (33 per block), Q2_K rows in 4-byte units (21 per block).
+// ---------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) relayout_iq2xxs_kernel(const uint16_t *__restrict__ src,
+                                                               uint16_t *__restrict__ dst, uint64_t n_rows, uint32_t xb,
+                                                               int inverse)
+{
+    const uint64_t per_row = 33ull * xb, total = n_rows * per_row;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t row = i / per_row;
+        uint32_t s = (uint32_t)(i - row * per_row);  // position in ROWSOA order
+        uint32_t n = s < xb ? 33u * s : 33u * ((s - xb) >> 5) + 1u + ((s - xb) & 31u);  // position in NATIVE order
+        if (inverse) dst[row * per_row + n] = src[row * per_row + s];
+        else dst[row * per_row + s] = src[row * per_row + n];
+    }
+}
+
+__global__ void __launch_bounds__(256) relayout_q2k_kernel(const uint32_t *__restrict__ src, uint32_t *__restrict__ dst,
+                                                            uint64_t n_rows, uint32_t mb, int inverse)
+{
+    const uint64_t per_row = 21ull * mb, total = n_rows * per_row;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t row = i / per_row;
+        uint32_t s = (uint32_t)(i - row * per_row), n;
+        if (s < 4u * mb) n = 21u * (s >> 2) + (s & 3u);
+        else if (s < 20u * mb) n = 21u * ((s - 4u * mb) >> 4) + 4u + ((s - 4u * mb) & 15u);
+        else n = 21u * (s - 20u * mb) + 20u;
+        if (inverse) dst[row * per_row + n] = src[row * per_row + s];
+        else dst[row * per_row + s] = src[row * per_row + n];
+    }
+}
+
+void launch_relayout_iq2xxs(cudaStream_t st, const uint8_t *src, uint8_t *dst, uint64_t n_rows, uint32_t xb, int inverse)
+{
+    uint64_t total = n_rows * 33ull * xb;
+    if (total == 0) return;
+    unsigned grid = (unsigned)(((total + 255) / 256) < 148ull * 64 ? ((total + 255) / 256) : 148ull * 64);
+    relayout_iq2xxs_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const uint16_t *>(src),
+                                                 reinterpret_cast<uint16_t *>(dst), n_rows, xb, inverse);
+}
+
+void launch_relayout_q2k(cudaStream_t st, const uint8_t *src, uint8_t *dst, uint64_t n_rows, uint32_t mb, int inverse)
+{
+    uint64_t total = n_rows * 21ull * mb;
+    if (total == 0) return;
+    unsigned grid = (unsigned)(((total + 255) / 256) < 148ull * 64 ? ((total + 255) / 256) : 148ull * 64);
+    relayout_q2k_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const uint32_t *>(src), reinterpret_cast<uint32_t *>(dst),
+                                              n_rows, mb, inverse);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Slot sum (engine/src/kernels/moe.rs:983-1005): out[t][row] = sum over slots, in slot order, starting from 0.
+// ---------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) moe_sum_kernel(const float *__restrict__ down, float *__restrict__ out,
+                                                       uint32_t out_dim, uint32_t k, uint64_t n)
+{
+    uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= n) return;
+    uint64_t tok = gid / out_dim, row = gid - tok * out_dim;
+    float acc = 0.0f;
+    for (uint32_t e = 0; e < k; ++e) acc = __fadd_rn(acc, down[(tok * k + e) * out_dim + row]);
+    out[gid] = acc;
+}
+
+void launch_moe_sum(cudaStream_t st, const float *down, float *out, uint32_t out_dim, uint32_t k, uint32_t n_tokens)
+{
+    uint64_t n = (uint64_t)n_tokens * out_dim;
+    if (n == 0) return;
+    moe_sum_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(down, out, out_dim, k, n);
+}
+
+}  // namespace dsmoe

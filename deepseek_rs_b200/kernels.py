@@ -1,0 +1,202 @@
+"""Host-side mirror of the reference's kernel call surface for the routed-expert path, over torch CUDA tensors.
+
+Method names and operand order follow the reference's generated launch methods (``engine.kernels.moe.<kernel>`` and
+``engine.kernels.quantize.q8k_quantize``; engine/src/session.rs:2038-2153) minus the LaunchConfig, which the library
+chooses itself, and minus the lookup tables, which live inside the library. Every call goes through the C ABI of
+libdsmoe.so on the current torch stream and raises ``DsmoeError`` on a non-zero status. torch is only the owner of
+device memory and streams here.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from .formats import IQ2XXS_BYTES, Q2K_BYTES, Q8K_BYTES, QK_K
+
+LAYOUT_NATIVE, LAYOUT_ROWSOA = _lib.LAYOUT_NATIVE, _lib.LAYOUT_ROWSOA
+
+
+class DsmoeError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"dsmoe status {code}: {msg}")
+        self.code = code
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    assert t.is_cuda and t.is_contiguous(), "dsmoe operands must be contiguous CUDA tensors"
+    return C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class MoeKernels:
+    """One library handle on one device: the counterpart of ``Kernels::load`` (engine/src/engine.rs:31-54)."""
+
+    def __init__(self, device: int = 0, n_embd: int = 4096, n_ff: int = 2048, n_expert: int = 256,
+                 n_expert_used: int = 6, swiglu_clamp: float = 10.0, route_scale: float = 1.5, f16_ieee: bool = False,
+                 max_tokens: int = 64, max_layers: int = 1):
+        self.lib = _lib.load()
+        if not torch.cuda.is_available():
+            raise RuntimeError("dsmoe needs a CUDA device; there is no CPU path")
+        self.cfg = _lib.Config(n_embd, n_ff, n_expert, n_expert_used, swiglu_clamp, route_scale, int(f16_ieee),
+                               max_tokens, max_layers)
+        self.device = device
+        torch.cuda.set_device(device)
+        h = C.c_void_p()
+        rc = self.lib.dsmoe_create(C.byref(self.cfg), device, C.byref(h))
+        if rc != 0:
+            raise DsmoeError(rc, "dsmoe_create failed (needs a compute-capability 10.x device)")
+        self.h = h
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.dsmoe_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc: int):
+        if rc != 0:
+            raise DsmoeError(rc, self.lib.dsmoe_last_error(self.h).decode())
+
+    @property
+    def launch_count(self) -> int:
+        return int(self.lib.dsmoe_launch_count(self.h))
+
+    # ---- tier 1: one method per reference kernel ---------------------------------------------------------------
+
+    def q8k_quantize(self, x, out, in_dim: int, n_rows: int):
+        """engine/src/kernels/quantize.rs:309 — x f32 [n_rows, in_dim] -> out uint8 Q8_K blocks."""
+        self._check(self.lib.dsmoe_q8k_quantize(self.h, _stream(), _ptr(x), _ptr(out), in_dim, n_rows))
+
+    def router_select_parallel(self, logits, bias, hash, tokens, probs, selected, weights, token_scalar: int,
+                               hash_rows: int, n_tokens: int, has_bias: int, hash_mode: int):
+        """engine/src/kernels/moe.rs:177"""
+        self._check(self.lib.dsmoe_router_select(self.h, _stream(), _ptr(logits), _ptr(bias), _ptr(hash), _ptr(tokens),
+                                                 _ptr(probs), _ptr(selected), _ptr(weights), token_scalar, hash_rows,
+                                                 n_tokens, has_bias, hash_mode))
+
+    def moe_gate_up_mid_qwarp32(self, gate_base, up_base, xq, selected, weights, gate_out, up_out, mid_out,
+                                gate_expert_bytes: int, gate_row_bytes: int, xq_blocks: int, expert_mid_dim: int,
+                                n_expert: int, clamp: float, n_tokens: int | None = None, layout: int = LAYOUT_NATIVE):
+        """engine/src/kernels/moe.rs:622 — the pair count comes from the launch grid in the reference; here it is
+        n_tokens (default: rows of ``selected``)."""
+        if n_tokens is None:
+            n_tokens = selected.numel() // n_expert
+        self._check(self.lib.dsmoe_gate_up_mid(self.h, _stream(), _ptr(gate_base), _ptr(up_base), _ptr(xq),
+                                               _ptr(selected), _ptr(weights), _ptr(gate_out), _ptr(up_out),
+                                               _ptr(mid_out), gate_expert_bytes, gate_row_bytes, xq_blocks,
+                                               expert_mid_dim, n_expert, n_tokens, clamp, layout))
+
+    def moe_down_qwarp32(self, down_base, midq, selected, down_out, down_expert_bytes: int, down_row_bytes: int,
+                         midq_blocks: int, out_dim: int, n_expert: int, n_tokens: int | None = None,
+                         layout: int = LAYOUT_NATIVE):
+        """engine/src/kernels/moe.rs:821"""
+        if n_tokens is None:
+            n_tokens = selected.numel() // n_expert
+        self._check(self.lib.dsmoe_down(self.h, _stream(), _ptr(down_base), _ptr(midq), _ptr(selected), _ptr(down_out),
+                                        down_expert_bytes, down_row_bytes, midq_blocks, out_dim, n_expert, n_tokens,
+                                        layout))
+
+    def moe_down_sum6_qwarp32(self, down_base, midq, selected, out, down_expert_bytes: int, down_row_bytes: int,
+                              midq_blocks: int, out_dim: int, n_expert: int | None = None, n_tokens: int = 1,
+                              layout: int = LAYOUT_NATIVE):
+        """engine/src/kernels/moe.rs:922 — the reference sums six slots of one token; n_expert / n_tokens generalise."""
+        if n_expert is None:
+            n_expert = self.cfg.n_expert_used
+        self._check(self.lib.dsmoe_down_sum(self.h, _stream(), _ptr(down_base), _ptr(midq), _ptr(selected), _ptr(out),
+                                            down_expert_bytes, down_row_bytes, midq_blocks, out_dim, n_expert, n_tokens,
+                                            layout))
+
+    def moe_sum(self, down, out, out_dim: int, n_expert: int, n_tokens: int):
+        """engine/src/kernels/moe.rs:983"""
+        self._check(self.lib.dsmoe_moe_sum(self.h, _stream(), _ptr(down), _ptr(out), out_dim, n_expert, n_tokens))
+
+    # ---- helpers with no reference kernel ------------------------------------------------------------------------
+
+    def dequant_iq2xxs(self, blocks, n_blocks: int, out):
+        self._check(self.lib.dsmoe_dequant_iq2xxs(self.h, _stream(), _ptr(blocks), n_blocks, _ptr(out)))
+
+    def dequant_q2k(self, blocks, n_blocks: int, out):
+        self._check(self.lib.dsmoe_dequant_q2k(self.h, _stream(), _ptr(blocks), n_blocks, _ptr(out)))
+
+    def relayout_iq2xxs(self, src, dst, n_rows: int, blocks_per_row: int, inverse: bool = False):
+        self._check(self.lib.dsmoe_relayout_iq2xxs(self.h, _stream(), _ptr(src), _ptr(dst), n_rows, blocks_per_row,
+                                                   int(inverse)))
+
+    def relayout_q2k(self, src, dst, n_rows: int, blocks_per_row: int, inverse: bool = False):
+        self._check(self.lib.dsmoe_relayout_q2k(self.h, _stream(), _ptr(src), _ptr(dst), n_rows, blocks_per_row,
+                                                int(inverse)))
+
+    # ---- tier 2 ---------------------------------------------------------------------------------------------------
+
+    def layer_register(self, layer: int, gate, up, down, layout: int):
+        self._check(self.lib.dsmoe_layer_register(self.h, layer, _ptr(gate), _ptr(up), _ptr(down), layout))
+
+    def moe_forward(self, layer: int, x, logits, n_tokens: int, out, selected_out=None, weights_out=None):
+        self._check(self.lib.dsmoe_moe_forward(self.h, _stream(), layer, _ptr(x), _ptr(logits), n_tokens, _ptr(out),
+                                               _ptr(selected_out), _ptr(weights_out)))
+
+    def moe_forward_host(self, layer: int, x_host, logits_host, n_tokens: int, out_host, selected_host=None,
+                         weights_host=None):
+        """Host (ideally pinned) tensors in and out; copies and a stream wait happen inside the call."""
+        def hp(t):
+            if t is None:
+                return None
+            assert (not t.is_cuda) and t.is_contiguous()
+            return C.c_void_p(t.data_ptr())
+        self._check(self.lib.dsmoe_moe_forward_host(self.h, layer, hp(x_host), hp(logits_host), n_tokens, hp(out_host),
+                                                    hp(selected_host), hp(weights_host)))
+
+
+class MoeLayer:
+    """One layer's routed experts resident on the device, with the upload-time re-layout applied.
+
+    Counterpart of the expert-tensor upload (engine/src/engine.rs:77-90) plus step "h" of
+    Session::decode_attn_out_and_ffn (engine/src/session.rs:1989-2155)."""
+
+    def __init__(self, kernels: MoeKernels, gate_bytes, up_bytes, down_bytes, layout: int = LAYOUT_ROWSOA,
+                 layer: int = 0):
+        self.k = kernels
+        cfg = kernels.cfg
+        dev = torch.device("cuda", kernels.device)
+        self.xq_blocks, self.mid_blocks = cfg.n_embd // QK_K, cfg.n_ff // QK_K
+        as_dev = lambda a: (a if isinstance(a, torch.Tensor) else torch.from_numpy(a)).to(dev).contiguous().view(-1)
+        gate, up, down = as_dev(gate_bytes), as_dev(up_bytes), as_dev(down_bytes)
+        assert gate.numel() == cfg.n_expert * cfg.n_ff * self.xq_blocks * IQ2XXS_BYTES
+        assert down.numel() == cfg.n_expert * cfg.n_embd * self.mid_blocks * Q2K_BYTES
+        if layout == LAYOUT_ROWSOA:
+            g2, u2, d2 = torch.empty_like(gate), torch.empty_like(up), torch.empty_like(down)
+            kernels.relayout_iq2xxs(gate, g2, cfg.n_expert * cfg.n_ff, self.xq_blocks)
+            kernels.relayout_iq2xxs(up, u2, cfg.n_expert * cfg.n_ff, self.xq_blocks)
+            kernels.relayout_q2k(down, d2, cfg.n_expert * cfg.n_embd, self.mid_blocks)
+            torch.cuda.synchronize()
+            gate, up, down = g2, u2, d2
+        self.gate, self.up, self.down, self.layout, self.layer = gate, up, down, layout, layer
+        kernels.layer_register(layer, gate, up, down, layout)
+
+    @property
+    def packed_bytes_per_expert(self) -> int:
+        c = self.k.cfg
+        return 2 * c.n_ff * self.xq_blocks * IQ2XXS_BYTES + c.n_embd * self.mid_blocks * Q2K_BYTES
+
+    def forward(self, x, logits, out=None, selected_out=None, weights_out=None):
+        n = x.shape[0]
+        if out is None:
+            out = torch.empty((n, self.k.cfg.n_embd), dtype=torch.float32, device=x.device)
+        self.k.moe_forward(self.layer, x, logits, n, out, selected_out, weights_out)
+        return out
+
+
+def q8k_empty(n_rows: int, blocks: int, device) -> torch.Tensor:
+    return torch.empty((n_rows, blocks, Q8K_BYTES), dtype=torch.uint8, device=device)

@@ -1,0 +1,173 @@
+/*
+ * dsmoe — B200-native (sm_100a) kernels for the quantized routed-expert path of the deepseek-rs engine, behind a
+ * plain C ABI.
+ *
+ * Every entry point replaces one kernel launch (tier 1) or one group of launches (tier 2) that the reference's Rust
+ * host code makes through its generated `engine.kernels.<module>.<kernel>(&stream, LaunchConfig, args...)` methods
+ * (engine/src/engine.rs:16-55). Operand meaning and order follow the reference kernel's parameter list; launch
+ * geometry and lookup tables are internal. The reference file:line each one stands in for is cited on its
+ * declaration.
+ *
+ * Conventions
+ *   - All pointers are device pointers unless the name ends in `_host`. The library never frees caller memory.
+ *   - All calls are asynchronous on the caller's stream (a cudaStream_t passed as void*; NULL = the legacy default
+ *     stream) and perform no host synchronisation, except the `_host` calls and create/destroy.
+ *   - Every function returns DSMOE_OK or a negative dsmoe_status; dsmoe_last_error() gives the text. Nothing aborts
+ *     and nothing throws across the boundary.
+ *   - Packed weight pointers must be 16-byte aligned for the ROWSOA layout and 2-byte (IQ2_XXS) / 4-byte (Q2_K)
+ *     aligned for the NATIVE layout; Q8_K buffers must be 4-byte aligned.
+ *   - A handle belongs to one device and one host thread at a time.
+ *
+ * Block formats (little-endian): IQ2_XXS 66 B, Q2_K 84 B, Q8_K 292 B per 256 values
+ * (engine/src/kernels/moe.rs:601-611).
+ */
+#ifndef DSMOE_H
+#define DSMOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define DSMOE_API
+#else
+#define DSMOE_API __attribute__((visibility("default")))
+#endif
+
+typedef struct dsmoe_handle dsmoe_handle;
+typedef void *dsmoe_stream; /* cudaStream_t */
+
+typedef enum dsmoe_status {
+    DSMOE_OK = 0,
+    DSMOE_ERR_ARG = -1,     /* bad pointer, size, alignment or enum */
+    DSMOE_ERR_CUDA = -2,    /* a CUDA runtime call or launch failed */
+    DSMOE_ERR_NCCL = -3,    /* reserved for the expert-parallel path */
+    DSMOE_ERR_TIMEOUT = -4, /* a bounded device-side wait expired */
+    DSMOE_ERR_BOUNDS = -5,  /* a size exceeds what the handle was created for */
+    DSMOE_ERR_NOMEM = -6,
+    DSMOE_ERR_STATE = -7    /* e.g. layer not registered */
+} dsmoe_status;
+
+/*
+ * Byte order of packed expert rows in device memory. A row keeps its byte count and stride in both layouts, so the
+ * expert/row byte strides the reference passes (engine/src/session.rs:2079-2080, 2130-2131) stay valid.
+ *   NATIVE: the GGUF order the reference uploads verbatim (engine/src/engine.rs:81-89): block after block.
+ *   ROWSOA: a per-row permutation made once at upload by dsmoe_relayout_*: for IQ2_XXS
+ *           [d x blocks][qs(64 B) x blocks]; for Q2_K [scales(16 B) x blocks][qs(64 B) x blocks][d,dmin x blocks].
+ *           It makes every 16-byte load aligned. Dequantised values are unchanged.
+ */
+typedef enum dsmoe_layout { DSMOE_LAYOUT_NATIVE = 0, DSMOE_LAYOUT_ROWSOA = 1 } dsmoe_layout;
+
+typedef struct dsmoe_config {
+    uint32_t n_embd;        /* hidden size, multiple of 256 (reference: 4096, engine/src/model.rs:4) */
+    uint32_t n_ff;          /* expert width, multiple of 256 (2048, model.rs:18) */
+    uint32_t n_expert;      /* routed experts, multiple of 32, <= 512 (256, model.rs:15) */
+    uint32_t n_expert_used; /* top-k, 1..8 (6, model.rs:16) */
+    float swiglu_clamp;     /* 10.0 (engine/src/session.rs:21); <= 1e-6 disables clamping */
+    float route_scale;      /* selected weights are renormalised to this sum (1.5, moe.rs:279-285) */
+    uint32_t f16_ieee;      /* 0: f16 subnormal scales flush to zero as the reference device code does
+                               (engine/src/kernels/utils.rs:16-29); 1: IEEE conversion */
+    uint32_t max_tokens;    /* largest n_tokens the tier-2 calls will see; sizes library-owned scratch */
+    uint32_t max_layers;    /* layer slots for dsmoe_layer_register */
+} dsmoe_config;
+
+DSMOE_API const char *dsmoe_version(void);
+DSMOE_API void dsmoe_default_config(dsmoe_config *cfg);
+
+/* Replaces Kernels::load (engine/src/engine.rs:31-54): the kernels are prebuilt sm_100a code inside this library,
+ * so nothing is JIT-compiled. Fails with DSMOE_ERR_CUDA when the device is not compute capability 10.x. */
+DSMOE_API int dsmoe_create(const dsmoe_config *cfg, int device, dsmoe_handle **out);
+DSMOE_API int dsmoe_destroy(dsmoe_handle *h);
+DSMOE_API const char *dsmoe_last_error(const dsmoe_handle *h);
+/* Number of kernels this handle has launched since creation (bookkeeping for benchmarks). */
+DSMOE_API uint64_t dsmoe_launch_count(const dsmoe_handle *h);
+
+/* ------------------------------------------------------------------------------------------------------------ */
+/* Tier 1: kernel-for-kernel                                                                                      */
+/* ------------------------------------------------------------------------------------------------------------ */
+
+/* q8k_quantize (engine/src/kernels/quantize.rs:309-417; calls engine/src/session.rs:2062-2073, 2115-2126).
+ * x: f32 [n_rows][in_dim]; out: Q8_K blocks [n_rows][in_dim/256][292]. Bit-exact. */
+DSMOE_API int dsmoe_q8k_quantize(dsmoe_handle *h, dsmoe_stream stream, const float *x, uint8_t *out, uint32_t in_dim,
+                                 uint32_t n_rows);
+
+/* router_select_parallel (engine/src/kernels/moe.rs:177-287; call engine/src/session.rs:2038-2057); the serial and
+ * warp variants (:64-169, :376-537) compute the same thing. bias, hash, tokens may be NULL. k and the expert count
+ * come from the handle's config. logits, probs: f32 [n_tokens][n_expert]; selected: i32 [n_tokens][k];
+ * weights: f32 [n_tokens][k]. */
+DSMOE_API int dsmoe_router_select(dsmoe_handle *h, dsmoe_stream stream, const float *logits, const float *bias,
+                                  const int32_t *hash, const int32_t *tokens, float *probs, int32_t *selected,
+                                  float *weights, int32_t token_scalar, uint32_t hash_rows, uint32_t n_tokens,
+                                  uint32_t has_bias, uint32_t hash_mode);
+
+/* moe_gate_up_mid_qwarp32 (engine/src/kernels/moe.rs:622-715; call engine/src/session.rs:2088-2111).
+ * xq: Q8_K [n_tokens][xq_blocks]; outputs f32 [n_tokens*k][expert_mid_dim]; gate_out / up_out may be NULL (the
+ * reference never reads them back). */
+DSMOE_API int dsmoe_gate_up_mid(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *gate_base, const uint8_t *up_base,
+                                const uint8_t *xq, const int32_t *selected, const float *weights, float *gate_out,
+                                float *up_out, float *mid_out, uint64_t gate_expert_bytes, uint64_t gate_row_bytes,
+                                uint32_t xq_blocks, uint32_t expert_mid_dim, uint32_t n_expert_used, uint32_t n_tokens,
+                                float clamp, int layout);
+
+/* moe_down_qwarp32 (engine/src/kernels/moe.rs:821-865). midq: Q8_K [n_tokens*k][midq_blocks];
+ * down_out: f32 [n_tokens*k][out_dim]. */
+DSMOE_API int dsmoe_down(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *down_base, const uint8_t *midq,
+                         const int32_t *selected, float *down_out, uint64_t down_expert_bytes, uint64_t down_row_bytes,
+                         uint32_t midq_blocks, uint32_t out_dim, uint32_t n_expert_used, uint32_t n_tokens, int layout);
+
+/* moe_down_sum6_qwarp32 (engine/src/kernels/moe.rs:922-970; call engine/src/session.rs:2138-2153), generalised to
+ * n_tokens rows and k slots: out f32 [n_tokens][out_dim] = slots summed in slot order. */
+DSMOE_API int dsmoe_down_sum(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *down_base, const uint8_t *midq,
+                             const int32_t *selected, float *out, uint64_t down_expert_bytes, uint64_t down_row_bytes,
+                             uint32_t midq_blocks, uint32_t out_dim, uint32_t n_expert_used, uint32_t n_tokens,
+                             int layout);
+
+/* moe_sum (engine/src/kernels/moe.rs:983-1005). down: f32 [n_tokens*n_expert_used][out_dim]. */
+DSMOE_API int dsmoe_moe_sum(dsmoe_handle *h, dsmoe_stream stream, const float *down, float *out, uint32_t out_dim,
+                            uint32_t n_expert_used, uint32_t n_tokens);
+
+/* Dequantised weights. The reference has no such kernel; the values are defined by its block dots
+ * (engine/src/kernels/quantize.rs:811, :900): IQ2_XXS w = (0.125*d) * (ls * +/-g); Q2_K w = d*(sc*q) - dmin*m.
+ * blocks are in NATIVE order; out: f32 [n_blocks][256]. Bit-exact against the CPU oracle. */
+DSMOE_API int dsmoe_dequant_iq2xxs(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *blocks, uint64_t n_blocks,
+                                   float *out);
+DSMOE_API int dsmoe_dequant_q2k(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *blocks, uint64_t n_blocks,
+                                float *out);
+
+/* Upload-time row permutation NATIVE -> ROWSOA (replaces the verbatim upload of engine/src/engine.rs:81-89).
+ * src and dst must not overlap. inverse != 0 converts back. */
+DSMOE_API int dsmoe_relayout_iq2xxs(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *src, uint8_t *dst,
+                                    uint64_t n_rows, uint32_t blocks_per_row, int inverse);
+DSMOE_API int dsmoe_relayout_q2k(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *src, uint8_t *dst,
+                                 uint64_t n_rows, uint32_t blocks_per_row, int inverse);
+
+/* ------------------------------------------------------------------------------------------------------------ */
+/* Tier 2: the routed-expert step as one call                                                                     */
+/* ------------------------------------------------------------------------------------------------------------ */
+
+/* Registers one layer's expert tensors (blk.{il}.ffn_{gate,up,down}_exps.weight, engine/src/engine.rs:180-182),
+ * already in device memory in the given layout. The pointers are borrowed for the handle's lifetime. */
+DSMOE_API int dsmoe_layer_register(dsmoe_handle *h, uint32_t layer, const uint8_t *gate, const uint8_t *up,
+                                   const uint8_t *down, int layout);
+
+/* Steps 2-6 of the routed-expert block of Session::decode_attn_out_and_ffn (engine/src/session.rs:2010-2155) for
+ * n_tokens rows: router_select -> q8k(x) -> gate/up/SwiGLU -> q8k(mid) -> down + slot sum.
+ * x: f32 [n_tokens][n_embd]; logits: f32 [n_tokens][n_expert]; out: f32 [n_tokens][n_embd];
+ * selected_out / weights_out: optional [n_tokens][k]. Scratch is library-owned, sized by max_tokens. */
+DSMOE_API int dsmoe_moe_forward(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, const float *x,
+                                const float *logits, uint32_t n_tokens, float *out, int32_t *selected_out,
+                                float *weights_out);
+
+/* Same with host buffers: copies x and logits in, runs dsmoe_moe_forward on an internal stream, copies out (and the
+ * optional routing) back and waits. Host buffers should be page-locked for full copy speed. */
+DSMOE_API int dsmoe_moe_forward_host(dsmoe_handle *h, uint32_t layer, const float *x_host, const float *logits_host,
+                                     uint32_t n_tokens, float *out_host, int32_t *selected_out_host,
+                                     float *weights_out_host);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DSMOE_H */

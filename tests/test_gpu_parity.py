@@ -1,0 +1,390 @@
+"""GPU parity: every kernel of the routed-expert path, called through the C ABI, against the CPU oracle on the same
+seeded inputs.
+
+Bars: dequantised weights, Q8_K blocks and router indices bit-exact; expert outputs within rel 1e-3 / abs 1e-4
+(they are in fact bit-identical to the oracle, which the tests also record, because the kernels keep the reference's
+f32 summation order)."""
+import numpy as np
+import pytest
+
+from deepseek_rs_b200 import formats as F
+
+pytestmark = pytest.mark.gpu
+
+REL, ABS = 1e-3, 1e-4  # tolerance for expert outputs (f32 accumulate)
+
+
+@pytest.fixture(scope="module")
+def torch_cuda():
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    return torch
+
+
+@pytest.fixture(scope="module")
+def K(torch_cuda):
+    from deepseek_rs_b200.kernels import MoeKernels
+
+    return MoeKernels(device=0, max_tokens=64)
+
+
+def dev(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def assert_close(got, ref):
+    err = np.abs(got - ref)
+    assert np.all(err <= ABS + REL * np.abs(ref)), f"max abs err {err.max()}"
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# dequantised weights: bit-exact
+# ---------------------------------------------------------------------------------------------------------------
+
+def test_dequant_iq2xxs_bit_exact(torch_cuda, K, oracle):
+    torch = torch_cuda
+    rng = np.random.default_rng(1)
+    blocks = F.random_iq2xxs(rng, 4096)
+    blocks[:64, 0:2] = np.frombuffer(np.arange(1, 65, dtype=np.uint16).tobytes(), np.uint8).reshape(64, 2)  # subnormal d
+    out = torch.empty(4096 * 256, dtype=torch.float32, device="cuda")
+    K.dequant_iq2xxs(dev(torch, blocks.reshape(-1)), 4096, out)
+    ref = oracle.dequant_iq2xxs(blocks)
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), ref.view(np.uint32))
+    assert np.all(ref[:64 * 256] == 0.0)  # subnormal scales are flushed
+
+
+def test_dequant_q2k_bit_exact(torch_cuda, K, oracle):
+    torch = torch_cuda
+    rng = np.random.default_rng(2)
+    blocks = F.random_q2k(rng, 4096)
+    blocks[:32, 80:82] = np.frombuffer(np.arange(1, 33, dtype=np.uint16).tobytes(), np.uint8).reshape(32, 2)
+    out = torch.empty(4096 * 256, dtype=torch.float32, device="cuda")
+    K.dequant_q2k(dev(torch, blocks.reshape(-1)), 4096, out)
+    ref = oracle.dequant_q2k(blocks)
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), ref.view(np.uint32))
+
+
+def test_ieee_f16_switch(torch_cuda, oracle):
+    torch = torch_cuda
+    from deepseek_rs_b200.kernels import MoeKernels
+
+    Ki = MoeKernels(device=0, f16_ieee=True, max_tokens=1)
+    rng = np.random.default_rng(3)
+    blocks = F.random_iq2xxs(rng, 256)
+    blocks[:, 0:2] = np.frombuffer(rng.integers(1, 0x400, 256, dtype=np.uint16).tobytes(), np.uint8).reshape(256, 2)
+    out = torch.empty(256 * 256, dtype=torch.float32, device="cuda")
+    Ki.dequant_iq2xxs(dev(torch, blocks.reshape(-1)), 256, out)
+    ref = oracle.dequant_iq2xxs(blocks, ieee=True)
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), ref.view(np.uint32))
+    assert np.any(ref != 0.0)
+    Ki.close()
+
+
+@pytest.mark.parametrize("xb", [1, 3, 16])
+def test_relayout_iq2xxs_is_a_row_permutation(torch_cuda, K, xb):
+    torch = torch_cuda
+    rng = np.random.default_rng(4)
+    rows = 37
+    src = rng.integers(0, 256, rows * xb * 66, dtype=np.uint8)
+    s = dev(torch, src)
+    d = torch.zeros_like(s)
+    back = torch.zeros_like(s)
+    K.relayout_iq2xxs(s, d, rows, xb)
+    K.relayout_iq2xxs(d, back, rows, xb, inverse=True)
+    assert torch.equal(back, s)
+    dn = d.cpu().numpy().reshape(rows, xb * 66)
+    sn = src.reshape(rows, xb, 66)
+    assert np.array_equal(dn[:, :2 * xb].reshape(rows, xb, 2), sn[:, :, :2])
+    assert np.array_equal(dn[:, 2 * xb:].reshape(rows, xb, 64), sn[:, :, 2:])
+
+
+@pytest.mark.parametrize("mb", [1, 5, 8])
+def test_relayout_q2k_is_a_row_permutation(torch_cuda, K, mb):
+    torch = torch_cuda
+    rng = np.random.default_rng(5)
+    rows = 29
+    src = rng.integers(0, 256, rows * mb * 84, dtype=np.uint8)
+    s = dev(torch, src)
+    d = torch.zeros_like(s)
+    back = torch.zeros_like(s)
+    K.relayout_q2k(s, d, rows, mb)
+    K.relayout_q2k(d, back, rows, mb, inverse=True)
+    assert torch.equal(back, s)
+    dn = d.cpu().numpy().reshape(rows, mb * 84)
+    sn = src.reshape(rows, mb, 84)
+    assert np.array_equal(dn[:, :16 * mb].reshape(rows, mb, 16), sn[:, :, :16])
+    assert np.array_equal(dn[:, 16 * mb:80 * mb].reshape(rows, mb, 64), sn[:, :, 16:80])
+    assert np.array_equal(dn[:, 80 * mb:].reshape(rows, mb, 4), sn[:, :, 80:])
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Q8_K quantiser: bit-exact
+# ---------------------------------------------------------------------------------------------------------------
+
+def _q8k_gpu(torch, K, x):
+    rows, in_dim = x.shape
+    out = torch.zeros((rows, in_dim // 256, 292), dtype=torch.uint8, device="cuda")
+    K.q8k_quantize(dev(torch, x), out, in_dim, rows)
+    return out.cpu().numpy()
+
+
+def test_q8k_quantize_bit_exact_random(torch_cuda, K, oracle):
+    rng = np.random.default_rng(6)
+    x = rng.standard_normal((48, 4096)).astype(np.float32)
+    x[3] *= 1e-30
+    x[4] *= 1e30
+    x[5, 256:512] = 0.0  # an all-zero block
+    x[6] = 0.0
+    assert np.array_equal(_q8k_gpu(torch_cuda, K, x), oracle.q8k_quantize(x))
+
+
+def test_q8k_quantize_ties_and_signs(torch_cuda, K, oracle):
+    rng = np.random.default_rng(7)
+    # many equal magnitudes with both signs: the winner of the reference's tree decides the sign of d
+    x = rng.choice(np.array([-2.0, 2.0, -1.0, 1.0, 0.5], np.float32), size=(64, 512)).astype(np.float32)
+    x[0, :256] = -3.0
+    x[1, :256] = 3.0
+    x[2, 255] = -7.0
+    x[3, 0] = 7.0
+    got, ref = _q8k_gpu(torch_cuda, K, x), oracle.q8k_quantize(x)
+    assert np.array_equal(got, ref)
+    # rounding is half away from zero: 0.5 * iscale lands on .5 boundaries often in this set
+    vals = np.linspace(-1.0, 1.0, 256, dtype=np.float32)[None, :].repeat(4, 0)
+    assert np.array_equal(_q8k_gpu(torch_cuda, K, vals), oracle.q8k_quantize(vals))
+
+
+def test_q8k_quantize_empty(torch_cuda, K):
+    torch = torch_cuda
+    K.q8k_quantize(torch.empty((0, 256), device="cuda"), torch.empty((0,), dtype=torch.uint8, device="cuda"), 256, 0)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# router: indices and weights bit-exact
+# ---------------------------------------------------------------------------------------------------------------
+
+def _router_gpu(torch, K, logits, bias=None, hash_table=None, tokens=None, token_scalar=0):
+    T, E = logits.shape
+    k = K.cfg.n_expert_used
+    probs = torch.zeros((T, E), dtype=torch.float32, device="cuda")
+    sel = torch.zeros((T, k), dtype=torch.int32, device="cuda")
+    w = torch.zeros((T, k), dtype=torch.float32, device="cuda")
+    K.router_select_parallel(dev(torch, logits), None if bias is None else dev(torch, bias),
+                             None if hash_table is None else dev(torch, hash_table),
+                             None if tokens is None else dev(torch, tokens), probs, sel, w, token_scalar,
+                             0 if hash_table is None else hash_table.shape[0], T, int(bias is not None),
+                             int(hash_table is not None))
+    return probs.cpu().numpy(), sel.cpu().numpy(), w.cpu().numpy()
+
+
+def _assert_router_equal(got, ref):
+    assert np.array_equal(got[1], ref[1]), "selected experts differ"
+    assert np.array_equal(got[0].view(np.uint32), ref[0].view(np.uint32)), "probs differ"
+    assert np.array_equal(got[2].view(np.uint32), ref[2].view(np.uint32)), "weights differ"
+
+
+def test_router_random_and_zipf(torch_cuda, K, oracle):
+    rng = np.random.default_rng(8)
+    logits = rng.standard_normal((64, 256)).astype(np.float32)
+    _assert_router_equal(_router_gpu(torch_cuda, K, logits), oracle.router_select(logits, k=6))
+    z = F.zipf_logits(rng, 4096)
+    got, ref = _router_gpu(torch_cuda, K, z), oracle.router_select(z, k=6)
+    _assert_router_equal(got, ref)
+    assert np.allclose(got[2].sum(axis=1), 1.5, atol=1e-5)
+
+
+def test_router_ties_extremes_bias_hash(torch_cuda, K, oracle):
+    rng = np.random.default_rng(9)
+    logits = rng.standard_normal((16, 256)).astype(np.float32)
+    logits[0] = 0.25                      # all equal: lowest indices win
+    logits[1, ::2] = 1.0                  # half equal
+    logits[2] = -40.0                     # softplus underflow branch
+    logits[3, 5] = 30.0                   # identity branch
+    logits[4, 10:20] = np.nan             # never selected
+    logits[5] = np.nan                    # nothing selectable -> -1, weights 0
+    _assert_router_equal(_router_gpu(torch_cuda, K, logits), oracle.router_select(logits, k=6))
+    bias = rng.standard_normal(256).astype(np.float32)
+    bias[7] = -np.inf
+    _assert_router_equal(_router_gpu(torch_cuda, K, logits, bias=bias), oracle.router_select(logits, k=6, bias=bias))
+    table = rng.integers(0, 256, (50, 6)).astype(np.int32)
+    table[3, 2] = -1
+    tokens = rng.integers(-2, 60, 16).astype(np.int32)  # out-of-range ids fall back to row 0
+    _assert_router_equal(_router_gpu(torch_cuda, K, logits, hash_table=table, tokens=tokens),
+                         oracle.router_select(logits, k=6, hash_table=table, tokens=tokens))
+    _assert_router_equal(_router_gpu(torch_cuda, K, logits[:1], hash_table=table, token_scalar=7),
+                         oracle.router_select(logits[:1], k=6, hash_table=table, token_scalar=7))
+
+
+def test_router_top8_variant(torch_cuda, oracle):
+    from deepseek_rs_b200.kernels import MoeKernels
+
+    K8 = MoeKernels(device=0, n_expert_used=8, max_tokens=1)
+    logits = np.random.default_rng(10).standard_normal((33, 256)).astype(np.float32)
+    _assert_router_equal(_router_gpu(torch_cuda, K8, logits), oracle.router_select(logits, k=8))
+    K8.close()
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# gate / up / mid and down
+# ---------------------------------------------------------------------------------------------------------------
+
+def _relaid(torch, K, w_np, n_rows, blocks, kind):
+    s = dev(torch, w_np)
+    d = torch.empty_like(s)
+    (K.relayout_iq2xxs if kind == "iq2" else K.relayout_q2k)(s, d, n_rows, blocks)
+    return d
+
+
+@pytest.mark.parametrize("layout", ["native", "rowsoa"])
+@pytest.mark.parametrize("xb,n_ff,T,n_e", [(16, 2048, 3, 4), (16, 200, 2, 3), (1, 40, 2, 3), (3, 17, 1, 2), (8, 64, 4, 5),
+                                           (20, 24, 2, 2)])
+def test_gate_up_mid(torch_cuda, K, oracle, layout, xb, n_ff, T, n_e):
+    torch = torch_cuda
+    from deepseek_rs_b200.kernels import LAYOUT_NATIVE, LAYOUT_ROWSOA
+
+    rng = np.random.default_rng(100 + xb + n_ff)
+    k = 6
+    gate = F.random_iq2xxs(rng, n_e * n_ff * xb).reshape(-1)
+    up = F.random_iq2xxs(rng, n_e * n_ff * xb).reshape(-1)
+    x = rng.standard_normal((T, xb * 256)).astype(np.float32) * 30.0  # large enough that the clamp at 10 bites
+    xq = oracle.q8k_quantize(x)
+    sel = rng.integers(0, n_e, (T, k)).astype(np.int32)
+    sel[0, 1] = -1  # clamped to expert 0 as in the reference
+    w = rng.random((T, k)).astype(np.float32)
+    rg, ru, rm = oracle.gate_up_mid(gate, up, xq, sel, w, n_ff, xb, clamp=10.0)
+    if layout == "rowsoa":
+        dg, du = _relaid(torch, K, gate, n_e * n_ff, xb, "iq2"), _relaid(torch, K, up, n_e * n_ff, xb, "iq2")
+        lay = LAYOUT_ROWSOA
+    else:
+        dg, du, lay = dev(torch, gate), dev(torch, up), LAYOUT_NATIVE
+    outs = [torch.zeros((T * k, n_ff), dtype=torch.float32, device="cuda") for _ in range(3)]
+    K.moe_gate_up_mid_qwarp32(dg, du, dev(torch, xq), dev(torch, sel), dev(torch, w), outs[0], outs[1], outs[2],
+                              n_ff * xb * 66, xb * 66, xb, n_ff, k, 10.0, n_tokens=T, layout=lay)
+    g, u, m = (o.cpu().numpy() for o in outs)
+    for got, ref in ((g, rg), (u, ru), (m, rm)):
+        assert_close(got, ref)
+    assert rg.max() <= 10.0 and np.abs(ru).max() <= 10.0
+    bit_exact = all(np.array_equal(a.view(np.uint32), b.view(np.uint32)) for a, b in ((g, rg), (u, ru), (m, rm)))
+    assert bit_exact, "within tolerance but not bit-identical to the oracle's summation order"
+    # gate_out / up_out are optional
+    m2 = torch.zeros_like(outs[2])
+    K.moe_gate_up_mid_qwarp32(dg, du, dev(torch, xq), dev(torch, sel), dev(torch, w), None, None, m2, n_ff * xb * 66,
+                              xb * 66, xb, n_ff, k, 10.0, n_tokens=T, layout=lay)
+    assert torch.equal(m2, outs[2])
+
+
+@pytest.mark.parametrize("layout", ["native", "rowsoa"])
+@pytest.mark.parametrize("mb,out_dim,T,n_e,k", [(8, 4096, 2, 4, 6), (8, 100, 3, 3, 6), (1, 33, 2, 2, 6), (5, 20, 1, 3, 4),
+                                                (16, 64, 4, 2, 1), (9, 31, 2, 2, 8)])
+def test_down_and_down_sum(torch_cuda, K, oracle, layout, mb, out_dim, T, n_e, k):
+    torch = torch_cuda
+    from deepseek_rs_b200.kernels import LAYOUT_NATIVE, LAYOUT_ROWSOA
+
+    rng = np.random.default_rng(200 + mb + out_dim)
+    down = F.random_q2k(rng, n_e * out_dim * mb).reshape(-1)
+    mid = rng.standard_normal((T * k, mb * 256)).astype(np.float32)
+    midq = oracle.q8k_quantize(mid)
+    sel = rng.integers(0, n_e, (T, k)).astype(np.int32)
+    ref_pair = oracle.down(down, midq, sel, out_dim, mb)
+    ref_sum = oracle.down_sum(down, midq, sel, out_dim, mb)
+    if layout == "rowsoa":
+        dd, lay = _relaid(torch, K, down, n_e * out_dim, mb, "q2k"), LAYOUT_ROWSOA
+    else:
+        dd, lay = dev(torch, down), LAYOUT_NATIVE
+    o_pair = torch.zeros((T * k, out_dim), dtype=torch.float32, device="cuda")
+    o_sum = torch.zeros((T, out_dim), dtype=torch.float32, device="cuda")
+    K.moe_down_qwarp32(dd, dev(torch, midq), dev(torch, sel), o_pair, out_dim * mb * 84, mb * 84, mb, out_dim, k,
+                       n_tokens=T, layout=lay)
+    K.moe_down_sum6_qwarp32(dd, dev(torch, midq), dev(torch, sel), o_sum, out_dim * mb * 84, mb * 84, mb, out_dim,
+                            n_expert=k, n_tokens=T, layout=lay)
+    assert_close(o_pair.cpu().numpy(), ref_pair)
+    assert_close(o_sum.cpu().numpy(), ref_sum)
+    assert np.array_equal(o_pair.cpu().numpy().view(np.uint32), ref_pair.view(np.uint32))
+    assert np.array_equal(o_sum.cpu().numpy().view(np.uint32), ref_sum.view(np.uint32))
+    # moe_sum over the per-pair rows gives the same numbers as the fused sum
+    o2 = torch.zeros_like(o_sum)
+    K.moe_sum(o_pair, o2, out_dim, k, T)
+    assert torch.equal(o2, o_sum)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# the benchmark's single-matrix configurations
+# ---------------------------------------------------------------------------------------------------------------
+
+def test_config_iq2xxs_matvec_2048x4096_seed0(torch_cuda, K, oracle):
+    """Single IQ2_XXS matvec, W 2048 x 4096, x ~ N(0,1), one token, seed 0."""
+    torch = torch_cuda
+    rng = np.random.default_rng(0)
+    W = F.random_iq2xxs(rng, 2048 * 16).reshape(-1)
+    x = rng.standard_normal((1, 4096)).astype(np.float32)
+    xq = oracle.q8k_quantize(x)
+    ref = oracle.matvec_iq2xxs(W, xq, 2048, 16)
+    dW = dev(torch, W)
+    sel = torch.zeros((1, 1), dtype=torch.int32, device="cuda")
+    w1 = torch.ones((1, 1), dtype=torch.float32, device="cuda")
+    y, u, m = (torch.zeros((1, 2048), dtype=torch.float32, device="cuda") for _ in range(3))
+    K.moe_gate_up_mid_qwarp32(dW, dW, dev(torch, xq), sel, w1, y, u, m, 2048 * 16 * 66, 16 * 66, 16, 2048, 1, 0.0,
+                              n_tokens=1)
+    assert_close(y.cpu().numpy(), ref)
+    assert np.array_equal(y.cpu().numpy(), ref)
+    # and the device-side quantiser feeds it the same blocks
+    xq_gpu = torch.zeros((1, 16, 292), dtype=torch.uint8, device="cuda")
+    K.q8k_quantize(dev(torch, x), xq_gpu, 4096, 1)
+    assert np.array_equal(xq_gpu.cpu().numpy(), xq)
+
+
+@pytest.mark.parametrize("batch", [1, 4, 16])
+def test_config_q2k_matvec_2048x4096(torch_cuda, K, oracle, batch):
+    """Q2_K matvec, W 2048 x 4096, batch 1 / 4 / 16 tokens, seed 0."""
+    torch = torch_cuda
+    rng = np.random.default_rng(0)
+    W = F.random_q2k(rng, 2048 * 16).reshape(-1)
+    x = rng.standard_normal((batch, 4096)).astype(np.float32)
+    xq = oracle.q8k_quantize(x)
+    ref = oracle.matvec_q2k(W, xq, 2048, 16)
+    sel = torch.zeros((batch, 1), dtype=torch.int32, device="cuda")
+    y = torch.zeros((batch, 2048), dtype=torch.float32, device="cuda")
+    K.moe_down_qwarp32(dev(torch, W), dev(torch, xq), sel, y, 2048 * 16 * 84, 16 * 84, 16, 2048, 1, n_tokens=batch)
+    assert_close(y.cpu().numpy(), ref)
+    assert np.array_equal(y.cpu().numpy(), ref)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# the whole routed-expert step (tier 2)
+# ---------------------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("layout", ["native", "rowsoa"])
+@pytest.mark.parametrize("T", [1, 8])
+def test_moe_forward_layer(torch_cuda, oracle, layout, T):
+    """hidden 4096, width 2048, top-6, 32 experts (full-size experts, fewer of them so the CPU oracle stays quick)."""
+    torch = torch_cuda
+    from deepseek_rs_b200.kernels import LAYOUT_NATIVE, LAYOUT_ROWSOA, MoeKernels, MoeLayer
+
+    n_e = 32
+    Kl = MoeKernels(device=0, n_expert=n_e, max_tokens=8)
+    layer_w = F.ExpertLayer(seed=11, n_expert=n_e)
+    rng = np.random.default_rng(12)
+    x = F.bf16_round(rng.standard_normal((T, 4096)).astype(np.float32))
+    logits = rng.standard_normal((T, n_e)).astype(np.float32)
+    ref_out, ref_sel, ref_w = oracle.moe_layer(x, logits, layer_w.gate, layer_w.up, layer_w.down, k=6)
+    layer = MoeLayer(Kl, layer_w.gate, layer_w.up, layer_w.down,
+                     layout=LAYOUT_ROWSOA if layout == "rowsoa" else LAYOUT_NATIVE)
+    sel = torch.zeros((T, 6), dtype=torch.int32, device="cuda")
+    w = torch.zeros((T, 6), dtype=torch.float32, device="cuda")
+    out = layer.forward(dev(torch, x), dev(torch, logits), selected_out=sel, weights_out=w)
+    assert np.array_equal(sel.cpu().numpy(), ref_sel)
+    assert np.array_equal(w.cpu().numpy(), ref_w)
+    assert_close(out.cpu().numpy(), ref_out)
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), ref_out.view(np.uint32))
+    # host-buffer entry point gives the same result
+    xh, lh = torch.from_numpy(x).pin_memory(), torch.from_numpy(logits).pin_memory()
+    oh = torch.zeros((T, 4096), dtype=torch.float32).pin_memory()
+    Kl.moe_forward_host(0, xh, lh, T, oh)
+    assert np.array_equal(oh.numpy(), out.cpu().numpy())
+    # bounds and state errors come back as statuses, not crashes
+    from deepseek_rs_b200.kernels import DsmoeError
+    with pytest.raises(DsmoeError):
+        Kl.moe_forward(0, dev(torch, np.zeros((9, 4096), np.float32)), dev(torch, np.zeros((9, n_e), np.float32)), 9,
+                       torch.zeros((9, 4096), device="cuda"))
+    Kl.close()

@@ -1,0 +1,150 @@
+"""The oracle against an independent numpy restatement and against structural properties of the formats."""
+import numpy as np
+
+from deepseek_rs_b200 import formats as F
+
+
+def _grid_table():
+    import re, os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    text = open(os.path.join(root, "include", "dsmoe_iq2_tables.h")).read()
+    vals = [int(v, 16) for v in re.findall(r"0x([0-9a-fA-F]{16})ULL", text)]
+    assert len(vals) == 256
+    return np.array(vals, dtype=np.uint64)
+
+
+def _np_dequant_iq2xxs(blocks):
+    """Vectorised numpy decode written from the format description, independent of the C code."""
+    grid = _grid_table()
+    blocks = blocks.reshape(-1, 66)
+    d = blocks[:, 0:2].copy().view(np.float16).astype(np.float32).reshape(-1)
+    d[np.abs(d) < 2.0 ** -14] = 0.0  # device conversion flushes subnormals
+    grp = blocks[:, 2:].copy().view("<u4").reshape(-1, 8, 2)
+    aux0, aux1 = grp[..., 0], grp[..., 1]
+    ls = (2 * (aux1 >> 28) + 1).astype(np.int64)
+    out = np.zeros((blocks.shape[0], 8, 4, 8), np.float64)
+    for k in range(4):
+        g = grid[(aux0 >> (8 * k)) & 255]
+        si = (aux1 >> (7 * k)) & 127
+        par = np.zeros_like(si)
+        for b in range(7):
+            par ^= (si >> b) & 1
+        sb = si | (par << 7)
+        for j in range(8):
+            mag = ((g >> np.uint64(8 * j)) & np.uint64(0xFF)).astype(np.int64)
+            sign = np.where((sb >> j) & 1, -1, 1)
+            out[:, :, k, j] = mag * sign * ls
+    return (out.reshape(blocks.shape[0], 256) * (0.125 * d.astype(np.float64))[:, None]).astype(np.float32)
+
+
+def _np_dequant_q2k(blocks):
+    blocks = blocks.reshape(-1, 84)
+    sc = blocks[:, :16].astype(np.int64)
+    qs = blocks[:, 16:80].astype(np.int64)
+    d = blocks[:, 80:82].copy().view(np.float16).astype(np.float32).reshape(-1)
+    dmin = blocks[:, 82:84].copy().view(np.float16).astype(np.float32).reshape(-1)
+    d[np.abs(d) < 2.0 ** -14] = 0.0
+    dmin[np.abs(dmin) < 2.0 ** -14] = 0.0
+    out = np.zeros((blocks.shape[0], 256), np.float32)
+    for h in range(2):
+        for j in range(4):
+            for i in range(32):
+                sb = 8 * h + 2 * j + i // 16
+                q = (qs[:, 32 * h + i] >> (2 * j)) & 3
+                a = d * ((sc[:, sb] & 15) * q).astype(np.float32)
+                m = dmin * (sc[:, sb] >> 4).astype(np.float32)
+                out[:, 128 * h + 32 * j + i] = a - m
+    return out
+
+
+def test_dequant_matches_numpy_decode(oracle):
+    rng = np.random.default_rng(0)
+    b = F.random_iq2xxs(rng, 300)
+    assert np.array_equal(oracle.dequant_iq2xxs(b).reshape(-1, 256), _np_dequant_iq2xxs(b))
+    b = F.random_q2k(rng, 300)
+    assert np.array_equal(oracle.dequant_q2k(b).reshape(-1, 256), _np_dequant_q2k(b))
+
+
+def test_block_dots_equal_dequant_times_q8(oracle):
+    """The integer block dot equals sum(dequantised weight * d_x * q8) up to f32 rounding."""
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((1, 256)).astype(np.float32)
+    q8k = oracle.q8k_quantize(x)[0, 0]
+    dx = q8k[0:4].view(np.float32)[0]
+    q = q8k[4:260].view(np.int8).astype(np.float64)
+    for _ in range(20):
+        b = F.random_iq2xxs(rng, 1)
+        w = oracle.dequant_iq2xxs(b).astype(np.float64)
+        ref = float((w * q).sum() * dx)
+        got = oracle.dot_iq2xxs_q8k(b[0], q8k)
+        assert abs(got - ref) <= 1e-6 * max(1.0, abs(ref)) + 1e-9
+        b = F.random_q2k(rng, 1)
+        w = oracle.dequant_q2k(b).astype(np.float64)
+        ref = float((w * q).sum() * dx)
+        got = oracle.dot_q2k_q8k(b[0], q8k)
+        assert abs(got - ref) <= 2e-5 * max(abs(ref), float(np.abs(w * q).sum() * abs(dx)))
+
+
+def test_q8k_properties(oracle):
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((5, 1024)).astype(np.float32)
+    blk = oracle.q8k_quantize(x)
+    d = blk[:, :, 0:4].copy().view(np.float32).reshape(5, 4)
+    q = blk[:, :, 4:260].copy().view(np.int8).reshape(5, 4, 256)
+    bs = blk[:, :, 260:].copy().view(np.int16).reshape(5, 4, 16)
+    assert np.array_equal(bs, q.astype(np.int32).reshape(5, 4, 16, 16).sum(-1))
+    assert np.abs(q.astype(np.int32)).max() <= 128
+    # the largest-magnitude element maps to -127 exactly (iscale = -127/max)
+    xr = x.reshape(5, 4, 256)
+    idx = np.abs(xr).argmax(-1)
+    assert np.all(np.take_along_axis(q, idx[..., None], -1)[..., 0] == -127)
+    assert np.allclose(q * d[..., None], xr, atol=np.abs(d).max() * 0.5001)
+    # empty and zero inputs
+    assert oracle.q8k_quantize(np.zeros((0, 256), np.float32)).shape == (0, 1, 292)
+    assert not oracle.q8k_quantize(np.zeros((2, 256), np.float32)).any()
+
+
+def test_router_matches_numpy_topk(oracle):
+    rng = np.random.default_rng(3)
+    logits = rng.standard_normal((200, 256)).astype(np.float32)
+    probs, sel, w = oracle.router_select(logits, k=6)
+    order = np.argsort(-probs, axis=1, kind="stable")[:, :6]  # stable: ties keep the lower index
+    assert np.array_equal(sel, order.astype(np.int32))
+    assert np.allclose(w.sum(1), 1.5, atol=1e-5)
+    p64 = np.sqrt(np.log1p(np.exp(logits.astype(np.float64))))
+    assert np.allclose(probs, p64, rtol=5e-6)  # f32 1+exp(x) loses bits for negative logits, as in the reference
+
+
+def test_layer_equals_its_parts(oracle):
+    rng = np.random.default_rng(4)
+    lw = F.ExpertLayer(seed=5, n_expert=4, n_embd=512, n_ff=256)
+    x = rng.standard_normal((3, 512)).astype(np.float32)
+    logits = np.full((3, 256), -30.0, np.float32)
+    logits[:, :4] = rng.standard_normal((3, 4))
+    out, sel, w, mid = oracle.moe_layer(x, logits, lw.gate, lw.up, lw.down, k=3, n_ff=256, return_mid=True)
+    assert sel.max() < 4
+    xq = oracle.q8k_quantize(x)
+    _, _, mid2 = oracle.gate_up_mid(lw.gate, lw.up, xq, sel, w, 256, 2)
+    assert np.array_equal(mid, mid2)
+    out2 = oracle.down_sum(lw.down, oracle.q8k_quantize(mid2), sel, 512, 1)
+    assert np.array_equal(out, out2)
+    # thread count does not change results
+    n = oracle.num_threads()
+    oracle.set_num_threads(1)
+    out3, _, _ = oracle.moe_layer(x, logits, lw.gate, lw.up, lw.down, k=3, n_ff=256)
+    oracle.set_num_threads(n)
+    assert np.array_equal(out, out3)
+
+
+def test_e4m3_codes(oracle):
+    assert oracle.e4m3_decode(oracle.e4m3_encode(448.0)) == 448.0
+    assert oracle.e4m3_decode(oracle.e4m3_encode(1e9)) == 448.0
+    assert oracle.e4m3_decode(oracle.e4m3_encode(-0.3)) == -0.3125
+    # every code round-trips; ties go to the even code
+    for c in range(127):
+        v = oracle.e4m3_decode(c)
+        assert oracle.e4m3_encode(v) == c
+    mid = (oracle.e4m3_decode(8) + oracle.e4m3_decode(9)) / 2
+    assert oracle.e4m3_encode(mid) == 8
+    mid = (oracle.e4m3_decode(9) + oracle.e4m3_decode(10)) / 2
+    assert oracle.e4m3_encode(mid) == 10
