@@ -81,7 +81,7 @@ def _declare(L: C.CDLL) -> None:
     L.orc_swiglu.argtypes = [_f32p, _f32p, _f32p, C.c_int64, C.c_float, C.c_float]
     L.orc_moe_layer.restype = C.c_int
     L.orc_moe_layer.argtypes = [_f32p, _f32p, _u8p, _u8p, _u8p, _f32p, _i32p, _f32p, _f32p, C.c_int64, C.c_uint32,
-                                C.c_uint32, C.c_int, C.c_float, C.c_int]
+                                C.c_uint32, C.c_int, C.c_int, C.c_float, C.c_int]
     L.orc_quantize_q8_0.argtypes = [_f32p, _i8p, _f32p, C.c_int64, C.c_int64]
     L.orc_matmul_q8_0.argtypes = [_u8p, _i8p, _f32p, _f32p, C.c_int64, C.c_int64, C.c_int64]
     L.orc_e4m3_value.restype = C.c_float
@@ -275,8 +275,8 @@ def moe_layer(x: np.ndarray, logits: np.ndarray, gate: np.ndarray, up: np.ndarra
     mid = np.empty((T * k, n_ff), np.float32) if return_mid else None
     if T:
         rc = lib().orc_moe_layer(_p(x, _f32p), _p(logits, _f32p), _p(gate, _u8p), _p(up, _u8p), _p(down_w, _u8p),
-                                 _p(out, _f32p), _p(sel, _i32p), _p(w, _f32p), _p(mid, _f32p), T, n_embd, n_ff, k,
-                                 clamp, int(ieee))
+                                 _p(out, _f32p), _p(sel, _i32p), _p(w, _f32p), _p(mid, _f32p), T, n_embd, n_ff,
+                                 logits.shape[1], k, clamp, int(ieee))
         if rc != 0:
             raise MemoryError("oracle scratch allocation failed")
     return (out, sel, w, mid) if return_mid else (out, sel, w)

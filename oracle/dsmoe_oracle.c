@@ -34,7 +34,6 @@
 #define ORC_Q2K_BYTES 84
 #define ORC_Q8K_BYTES 292
 #define ORC_MAX_K 8
-#define ORC_N_EXPERT 256
 
 static const uint64_t orc_grid[DSMOE_IQ2XXS_GRID_ENTRIES] = {DSMOE_IQ2XXS_GRID_VALUES};
 
@@ -564,25 +563,25 @@ void orc_swiglu(const float *gate, const float *up, float *out, int64_t n, float
 
 /*
  * The routed-expert step of Session::decode_attn_out_and_ffn (engine/src/session.rs:2010-2155) for n_tokens rows
- * of x: router_select -> q8k(x) -> gate/up/mid -> q8k(mid) -> down + slot sum. Router logits are an input (the
+ * of x (logits are [n_tokens][n_expert]): router_select -> q8k(x) -> gate/up/mid -> q8k(mid) -> down + slot sum. Router logits are an input (the
  * reference computes them with matmul_f16 just before, session.rs:1995-2008). Scratch is allocated here.
  * Returns 0, or -1 when memory runs out.
  */
 int orc_moe_layer(const float *x, const float *logits, const uint8_t *gate_base, const uint8_t *up_base,
                   const uint8_t *down_base, float *out, int32_t *selected, float *weights, float *mid_opt,
-                  int64_t n_tokens, uint32_t n_embd, uint32_t n_ff, int k, float clamp, int ieee)
+                  int64_t n_tokens, uint32_t n_embd, uint32_t n_ff, int n_expert, int k, float clamp, int ieee)
 {
     uint32_t xb = n_embd / ORC_QK_K, mb = n_ff / ORC_QK_K;
     uint64_t gate_row = (uint64_t)xb * ORC_IQ2XXS_BYTES, gate_exp = (uint64_t)n_ff * gate_row;
     uint64_t down_row = (uint64_t)mb * ORC_Q2K_BYTES, down_exp = (uint64_t)n_embd * down_row;
     int64_t n_pairs = n_tokens * k;
-    float *probs = (float *)malloc((size_t)n_tokens * ORC_N_EXPERT * sizeof(float));
+    float *probs = (float *)malloc((size_t)n_tokens * (size_t)n_expert * sizeof(float));
     uint8_t *xq = (uint8_t *)malloc((size_t)n_tokens * xb * ORC_Q8K_BYTES);
     float *mid = mid_opt ? mid_opt : (float *)malloc((size_t)n_pairs * n_ff * sizeof(float));
     uint8_t *midq = (uint8_t *)malloc((size_t)n_pairs * mb * ORC_Q8K_BYTES);
     int rc = -1;
     if (probs && xq && mid && midq) {
-        orc_router_select(logits, NULL, NULL, NULL, probs, selected, weights, 0, 0, n_tokens, 0, 0, k, ORC_N_EXPERT);
+        orc_router_select(logits, NULL, NULL, NULL, probs, selected, weights, 0, 0, n_tokens, 0, 0, k, n_expert);
         orc_q8k_quantize(x, xq, n_embd, n_tokens);
         orc_gate_up_mid(gate_base, up_base, xq, selected, weights, NULL, NULL, mid, gate_exp, gate_row, xb, n_ff,
                         (uint32_t)k, n_tokens, clamp, ieee);
