@@ -1,0 +1,377 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized routed-expert layer (router top-6 -> Q8_K -> IQ2_XXS gate/up + SwiGLU -> Q8_K -> Q2_K
+down -> slot sum) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+Prints ONE JSON line. A step is one pass of the layer over one batch of synthetic tokens. Inputs are synthetic with
+the distributions of the benchmark configurations (f16 scales |N(0,1)|*1e-3, uniform codebook/sign/scale/quant fields,
+hidden states N(0,1) rounded to bf16, router logits N(0,1)); weights are random, no dataset or checkpoint is involved.
+
+Timing: CUDA events on the launching stream, W >= 3 warm-up steps, max over ranks. Every step uses another layer's
+weights and another routing, so the packed bytes of a step are never in L2 from the step before (the rotation covers
+several times the 126 MB L2). `value` is device-timed with inputs resident in HBM; `e2e` goes through the host-buffer
+C-ABI call with pinned host memory, copies inside the timed region. `roofline` is the dominant kernel (gate/up)
+timed by CUDA events around its launches. `--impl reference` times the CPU oracle (a C port of the reference's CPU
+semantics; the reference's Rust cannot be built here) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_EMBD, N_FF, N_EXPERT, TOP_K = 4096, 2048, 256, 6
+GATE_EXPERT_BYTES = N_FF * (N_EMBD // 256) * 66       # 2 162 688
+DOWN_EXPERT_BYTES = N_EMBD * (N_FF // 256) * 84       # 2 752 512
+EXPERT_BYTES = 2 * GATE_EXPERT_BYTES + DOWN_EXPERT_BYTES  # 7 077 888
+
+WORKLOADS = {
+    # name: (tokens per step, layers rotated, routing variants)
+    "moe_decode_b1": dict(tokens=1, layers=8, zipf=False),
+    "moe_decode_b8": dict(tokens=8, layers=4, zipf=False),
+    "moe_decode_b64": dict(tokens=64, layers=2, zipf=False),
+}
+DEFAULT_WORKLOAD = "moe_decode_b64"
+METRIC, UNIT = "moe_expert_layer_tokens_per_s", "tokens/s"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def ncu_traffic(workload: str):
+    """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if one exists for this workload."""
+    p = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    if os.path.exists(p):
+        try:
+            return json.load(open(p)).get(workload, {}).get("gate_up_dram_bytes_per_launch")
+        except Exception:
+            return None
+    return None
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed regions run."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+                for n, v in zip(names, r[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except Exception:
+                continue
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def gen_layer_gpu(torch, device, seed: int):
+    """One layer's expert tensors generated on the device: uniform bytes give uniform codebook / sign / scale /
+    quant fields; the f16 scales are |N(0,1)| * 1e-3."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+
+    def scales(n):
+        return (torch.randn(n, device=device, generator=g).abs() * 1e-3).to(torch.float16).view(torch.uint8).view(n, 2)
+
+    def iq2(n):
+        t = torch.randint(0, 256, (n, 66), dtype=torch.uint8, device=device, generator=g)
+        t[:, 0:2] = scales(n)
+        return t.view(-1)
+
+    def q2k(n):
+        t = torch.randint(0, 256, (n, 84), dtype=torch.uint8, device=device, generator=g)
+        t[:, 80:82] = scales(n)
+        t[:, 82:84] = scales(n)
+        return t.view(-1)
+
+    nb_gate, nb_down = N_EXPERT * N_FF * (N_EMBD // 256), N_EXPERT * N_EMBD * (N_FF // 256)
+    return iq2(nb_gate), iq2(nb_gate), q2k(nb_down)
+
+
+def run_reference(args, rank: int, world: int):
+    """CPU arm: the oracle's routed-expert layer on all host threads, a bounded sample of the workload per step."""
+    if rank != 0:
+        return
+    import numpy as np
+
+    import oracle
+    from deepseek_rs_b200 import formats as F
+
+    oracle.build()
+    wl = WORKLOADS[args.workload]
+    cores = oracle.num_threads()
+    sample_tokens = min(wl["tokens"], max(1, 2 * cores))
+    n_exp = 32  # full-size experts, fewer of them: the CPU path's cost per token does not depend on the expert count
+    lw = F.ExpertLayer(seed=1, n_expert=n_exp)
+    rng = np.random.default_rng(0)
+    x = F.bf16_round(rng.standard_normal((sample_tokens, N_EMBD)).astype(np.float32))
+    logits = rng.standard_normal((sample_tokens, n_exp)).astype(np.float32)
+    for _ in range(max(1, min(args.warmup, 2))):
+        oracle.moe_layer(x, logits, lw.gate, lw.up, lw.down, k=TOP_K)
+    steps = max(1, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.moe_layer(x, logits, lw.gate, lw.up, lw.down, k=TOP_K)
+    dt = time.perf_counter() - t0
+    tps = sample_tokens * steps / dt
+    sample = f"{sample_tokens} tokens/step x {steps} steps, {n_exp} full-size experts, oracle port, OpenMP"
+    line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * dt / steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8 x 2-bit codes, f32 accumulate", "data": "synthetic",
+            "config": {"workload": args.workload, "tokens_per_step": sample_tokens, "top_k": TOP_K,
+                       "n_embd": N_EMBD, "n_ff": N_FF},
+            "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def cpu_baseline(workload: str):
+    import numpy as np
+
+    import oracle
+    from deepseek_rs_b200 import formats as F
+
+    oracle.build()
+    cores = oracle.num_threads()
+    n_tok, n_exp = max(4, 4 * cores), 32
+    lw = F.ExpertLayer(seed=1, n_expert=n_exp)
+    rng = np.random.default_rng(0)
+    x = F.bf16_round(rng.standard_normal((n_tok, N_EMBD)).astype(np.float32))
+    logits = rng.standard_normal((n_tok, n_exp)).astype(np.float32)
+    oracle.moe_layer(x[:2], logits[:2], lw.gate, lw.up, lw.down, k=TOP_K)
+    t0 = time.perf_counter()
+    reps = 0
+    while time.perf_counter() - t0 < 10.0:
+        oracle.moe_layer(x, logits, lw.gate, lw.up, lw.down, k=TOP_K)
+        reps += 1
+    dt = time.perf_counter() - t0
+    return {"value": n_tok * reps / dt, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{n_tok} tokens x {reps} passes of the layer ({n_exp} full-size experts), {dt:.1f} s"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layout", default="rowsoa", choices=["rowsoa", "native"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from deepseek_rs_b200.kernels import LAYOUT_NATIVE, LAYOUT_ROWSOA, MoeKernels
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    wl = WORKLOADS[args.workload]
+    T, L = wl["tokens"], wl["layers"]
+    K = MoeKernels(device=local_rank, max_tokens=T, max_layers=L)
+    layout = LAYOUT_ROWSOA if args.layout == "rowsoa" else LAYOUT_NATIVE
+    layers = []
+    for il in range(L):
+        gate, up, down = gen_layer_gpu(torch, device, seed=1000 * rank + il)
+        if layout == LAYOUT_ROWSOA:
+            g2, u2, d2 = torch.empty_like(gate), torch.empty_like(up), torch.empty_like(down)
+            K.relayout_iq2xxs(gate, g2, N_EXPERT * N_FF, N_EMBD // 256)
+            K.relayout_iq2xxs(up, u2, N_EXPERT * N_FF, N_EMBD // 256)
+            K.relayout_q2k(down, d2, N_EXPERT * N_EMBD, N_FF // 256)
+            torch.cuda.synchronize()
+            gate, up, down = g2, u2, d2
+        K.layer_register(il, gate, up, down, layout)
+        layers.append((gate, up, down))
+
+    # routing / activation variants: enough of them that (layer, routing) pairs repeat only after far more than the
+    # L2 capacity has streamed through
+    V = 16
+    gen = torch.Generator(device=device)
+    gen.manual_seed(7 + rank)
+    xs = torch.randn((V, T, N_EMBD), device=device, generator=gen).to(torch.bfloat16).to(torch.float32).contiguous()
+    lgs = torch.randn((V, T, N_EXPERT), device=device, generator=gen).contiguous()
+    out = torch.empty((T, N_EMBD), device=device)
+    sel = torch.empty((T, TOP_K), dtype=torch.int32, device=device)
+    wts = torch.empty((T, TOP_K), device=device)
+
+    # distinct experts per variant (for the algorithmic byte count)
+    distinct = []
+    for v in range(V):
+        K.moe_forward(v % L, xs[v], lgs[v], T, out, sel, wts)
+        distinct.append(int(torch.unique(sel).numel()))
+    torch.cuda.synchronize()
+
+    def step(i):
+        K.moe_forward(i % L, xs[i % V], lgs[i % V], T, out, None, None)
+
+    sampler = ClockSampler(local_rank)
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler.start()
+    launches0 = K.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    launches = K.launch_count - launches0
+    ms_total = e0.elapsed_time(e1)
+    u_mean = sum(distinct[(args.warmup + i) % V] for i in range(args.steps)) / args.steps
+
+    # dominant kernels timed one by one with events (same inputs, same rotation), tier-1 calls
+    xb, mb = N_EMBD // 256, N_FF // 256
+    xq = torch.empty((T, xb, 292), dtype=torch.uint8, device=device)
+    mid = torch.empty((T * TOP_K, N_FF), device=device)
+    midq = torch.empty((T * TOP_K, mb, 292), dtype=torch.uint8, device=device)
+    probs = torch.empty((T, N_EXPERT), device=device)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    for i in range(args.warmup + args.steps):
+        j = i - args.warmup
+        gate, up, down = layers[i % L]
+        K.router_select_parallel(lgs[i % V], None, None, None, probs, sel, wts, 0, 0, T, 0, 0)
+        K.q8k_quantize(xs[i % V], xq, N_EMBD, T)
+        if j >= 0:
+            ev[j][0].record()
+        K.moe_gate_up_mid_qwarp32(gate, up, xq, sel, wts, None, None, mid, GATE_EXPERT_BYTES, xb * 66, xb, N_FF, TOP_K,
+                                  10.0, n_tokens=T, layout=layout)
+        if j >= 0:
+            ev[j][1].record()
+        K.q8k_quantize(mid, midq, N_FF, T * TOP_K)
+        if j >= 0:
+            ev[j][2].record()
+        K.moe_down_sum6_qwarp32(down, midq, sel, out, DOWN_EXPERT_BYTES, mb * 84, mb, N_EMBD, n_expert=TOP_K,
+                                n_tokens=T, layout=layout)
+        if j >= 0:
+            ev[j][3].record()
+    torch.cuda.synchronize()
+    dn_ms_mean = sum(ev[j][2].elapsed_time(ev[j][3]) for j in range(args.steps)) / args.steps
+    gu_ms = [ev[j][0].elapsed_time(ev[j][1]) for j in range(args.steps)]
+    gu_ms_mean = sum(gu_ms) / len(gu_ms)
+    clocks = sampler.stop()
+
+    # end to end through the host-buffer C-ABI call
+    xh = xs.cpu().pin_memory()
+    lh = lgs.cpu().pin_memory()
+    oh = torch.empty((T, N_EMBD)).pin_memory()
+    for i in range(3):
+        K.moe_forward_host(i % L, xh[i % V], lh[i % V], T, oh)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        K.moe_forward_host(i % L, xh[i % V], lh[i % V], T, oh)
+    e2e_s = time.perf_counter() - t0
+
+    # max over ranks
+    times = torch.tensor([ms_total, e2e_s * 1e3, gu_ms_mean], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms, gu_ms_mean = (float(v) for v in times.tolist())
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        tokens = T * args.steps * world
+        value = tokens / (ms_total * 1e-3)
+        gu_bytes = u_mean * 2 * GATE_EXPERT_BYTES
+        achieved = gu_bytes / (gu_ms_mean * 1e-3) / 1e9
+        layer_gbs = u_mean * EXPERT_BYTES * world / (ms_total / args.steps * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8 x 2-bit codes, f32 accumulate", "data": "synthetic",
+            "config": {"workload": args.workload, "tokens_per_step_per_gpu": T, "top_k": TOP_K, "n_expert": N_EXPERT,
+                       "n_embd": N_EMBD, "n_ff": N_FF, "layout": args.layout,
+                       "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
+                       "l2": f"inputs rotate over {L} layers x {V} routings; packed bytes between reuse >> 126 MB L2",
+                       "distinct_experts_per_step": u_mean},
+            "packed_weight_gbs": layer_gbs,
+            "packed_weight_frac_of_measured_hbm": layer_gbs / world / peak,
+            "packed_weight_frac_of_8000": layer_gbs / world / 8000.0,
+            "roofline": {"bound": "hbm", "kernel": "gate_up_x16_kernel (IQ2_XXS gate+up+SwiGLU)", "achieved": achieved,
+                         "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": ncu_traffic(args.workload), "algorithmic_bytes_per_launch": gu_bytes,
+                         "avg_launch_ms": gu_ms_mean},
+            "roofline_down": {"bound": "hbm", "kernel": "down_m8_kernel (Q2_K down + slot sum)",
+                              "achieved": u_mean * DOWN_EXPERT_BYTES / (dn_ms_mean * 1e-3) / 1e9, "peak": peak,
+                              "unit": "GB/s", "frac": u_mean * DOWN_EXPERT_BYTES / (dn_ms_mean * 1e-3) / 1e9 / peak,
+                              "avg_launch_ms": dn_ms_mean},
+            "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": T * (N_EMBD + N_EXPERT) * 4, "d2h_bytes_per_step": T * N_EMBD * 4},
+            "gpu_launches": launches,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(args.workload)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
