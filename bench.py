@@ -203,6 +203,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layout", default="rowsoa", choices=["rowsoa", "native"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=0, help="layers to rotate over (0 = the workload's default; 1 keeps "
+                    "device memory small for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
@@ -225,7 +227,7 @@ def main():
         dist.init_process_group("nccl", device_id=device)
 
     wl = WORKLOADS[args.workload]
-    T, L = wl["tokens"], wl["layers"]
+    T, L = wl["tokens"], (args.layers if args.layers > 0 else wl["layers"])
     K = MoeKernels(device=local_rank, max_tokens=T, max_layers=L)
     layout = LAYOUT_ROWSOA if args.layout == "rowsoa" else LAYOUT_NATIVE
     layers = []
