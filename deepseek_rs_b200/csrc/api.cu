@@ -1,6 +1,7 @@
 // The C ABI of libdsmoe: handle, argument checks, tier-1 launch wrappers and the tier-2 layer call.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -28,6 +29,8 @@ struct dsmoe_handle {
     // staging for the host-buffer call
     cudaStream_t hstream;
     float *d_x, *d_logits, *d_out;
+    int *d_status;  // device status word: 0, or the first device-side error code (a bounded wait that expired)
+    bool use_tma;   // stage packed rows with bulk asynchronous copies where the shapes allow (default on)
 };
 
 namespace {
@@ -127,6 +130,9 @@ int dsmoe_create(const dsmoe_config *cfg, int device, dsmoe_handle **out)
     ok = ok && dev_alloc(&h->d_logits, T * cfg->n_expert) == cudaSuccess;
     ok = ok && dev_alloc(&h->d_out, T * cfg->n_embd) == cudaSuccess;
     ok = ok && cudaStreamCreateWithFlags(&h->hstream, cudaStreamNonBlocking) == cudaSuccess;
+    ok = ok && dev_alloc(&h->d_status, 1) == cudaSuccess && cudaMemset(h->d_status, 0, sizeof(int)) == cudaSuccess;
+    const char *no_tma = getenv("DSMOE_DISABLE_TMA");
+    h->use_tma = !(no_tma && no_tma[0] == '1');
     if (!ok) {
         cudaGetLastError();
         dsmoe_destroy(h);
@@ -150,12 +156,23 @@ int dsmoe_destroy(dsmoe_handle *h)
     cudaFree(h->d_x);
     cudaFree(h->d_logits);
     cudaFree(h->d_out);
+    cudaFree(h->d_status);
     delete[] h->layers;
     delete h;
     return DSMOE_OK;
 }
 
 const char *dsmoe_last_error(const dsmoe_handle *h) { return h ? h->err : "null handle"; }
+
+int dsmoe_device_status(dsmoe_handle *h, dsmoe_stream stream, int *code_out)
+{
+    if (!h || !code_out) return DSMOE_ERR_ARG;
+    cudaError_t e = cudaMemcpyAsync(code_out, h->d_status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(h, DSMOE_ERR_CUDA, "device_status: %s", cudaGetErrorString(e));
+    if (*code_out != 0) return fail(h, DSMOE_ERR_TIMEOUT, "a bounded device-side wait expired (code %d)", *code_out);
+    return DSMOE_OK;
+}
 uint64_t dsmoe_launch_count(const dsmoe_handle *h) { return h ? h->launches : 0; }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -209,7 +226,8 @@ int dsmoe_gate_up_mid(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *gate_
                     gate_row_bytes, xq_blocks, expert_mid_dim, n_expert_used, n_tokens, clamp, layout,
                     (int)h->cfg.f16_ieee};
     DSMOE_REQUIRE(h, (uint64_t)n_tokens * n_expert_used <= 65535u, "gate_up_mid: n_tokens*k exceeds 65535");
-    int n = launch_gate_up_mid((cudaStream_t)stream, a);
+    int n = (h->use_tma && gate_up_tma_eligible(a)) ? launch_gate_up_mid_tma((cudaStream_t)stream, a, h->d_status)
+                                                    : launch_gate_up_mid((cudaStream_t)stream, a);
     return check_launch(h, "gate_up_mid", n);
 }
 
@@ -230,7 +248,8 @@ static int down_common(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *down
     DSMOE_REQUIRE(h, n_tokens <= 65535u, "down: n_tokens exceeds 65535");
     DownArgs a = {down_base, midq, selected, out, down_expert_bytes, down_row_bytes, midq_blocks, out_dim,
                   n_expert_used, n_tokens, layout, (int)h->cfg.f16_ieee, sum_slots};
-    int n = launch_down((cudaStream_t)stream, a);
+    int n = (h->use_tma && down_tma_eligible(a)) ? launch_down_tma((cudaStream_t)stream, a, h->d_status)
+                                                 : launch_down((cudaStream_t)stream, a);
     return check_launch(h, sum_slots ? "down_sum" : "down", n);
 }
 
@@ -343,11 +362,12 @@ int dsmoe_moe_forward(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, cons
     launch_q8k_quantize(st, x, h->xq, c.n_embd, n_tokens);
     GateUpArgs g = {ly.gate, ly.up, h->xq, sel, wts, nullptr, nullptr, h->mid, (uint64_t)c.n_ff * xb * IQ2XXS_BYTES,
                     (uint64_t)xb * IQ2XXS_BYTES, xb, c.n_ff, k, n_tokens, c.swiglu_clamp, ly.layout, (int)c.f16_ieee};
-    int n = 2 + launch_gate_up_mid(st, g);
+    int n = 2 + ((h->use_tma && gate_up_tma_eligible(g)) ? launch_gate_up_mid_tma(st, g, h->d_status)
+                                                         : launch_gate_up_mid(st, g));
     launch_q8k_quantize(st, h->mid, h->midq, c.n_ff, n_tokens * k);
     DownArgs d = {ly.down, h->midq, sel, out, (uint64_t)c.n_embd * mb * Q2K_BYTES, (uint64_t)mb * Q2K_BYTES, mb,
                   c.n_embd, k, n_tokens, ly.layout, (int)c.f16_ieee, 1};
-    n += 1 + launch_down(st, d);
+    n += 1 + ((h->use_tma && down_tma_eligible(d)) ? launch_down_tma(st, d, h->d_status) : launch_down(st, d));
     return check_launch(h, "moe_forward", n);
 }
 

@@ -307,22 +307,6 @@ __device__ __forceinline__ float q2k_block_dot(const DnRow &r, const int (&q)[4]
     return __fsub_rn(__fmul_rn(dall, (float)isum), __fmul_rn(dmin, (float)summs));
 }
 
-__device__ __forceinline__ void q2k_load_acts(const uint8_t *mq_blk, int c, int (&q)[4][4], uint32_t &bs01,
-                                              uint32_t &bs23, float &yd)
-{
-    const int h = c >> 1, half = c & 1;
-    yd = *reinterpret_cast<const float *>(mq_blk);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const int *p = reinterpret_cast<const int *>(mq_blk + 4 + 128 * h + 32 * j + 16 * half);
-#pragma unroll
-        for (int w = 0; w < 4; ++w) q[j][w] = p[w];
-    }
-    const uint16_t *bs = reinterpret_cast<const uint16_t *>(mq_blk + 260);
-    const int s0 = 8 * h + half;
-    bs01 = (uint32_t)bs[s0] | ((uint32_t)bs[s0 + 2] << 16);
-    bs23 = (uint32_t)bs[s0 + 4] | ((uint32_t)bs[s0 + 6] << 16);
-}
 
 constexpr int DOWN_ROWS_MAX = 32;
 

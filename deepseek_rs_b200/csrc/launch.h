@@ -43,4 +43,11 @@ struct DownArgs {
 };
 int launch_down(cudaStream_t st, const DownArgs &a);
 
+// Variants that stage the packed rows through shared memory with bulk asynchronous copies (reference shapes only).
+// status points at a device int that receives a non-zero code if a bounded wait expires.
+bool gate_up_tma_eligible(const GateUpArgs &a);
+int launch_gate_up_mid_tma(cudaStream_t st, const GateUpArgs &a, int *status);
+bool down_tma_eligible(const DownArgs &a);
+int launch_down_tma(cudaStream_t st, const DownArgs &a, int *status);
+
 }  // namespace dsmoe

@@ -69,6 +69,13 @@ class MoeKernels:
         if rc != 0:
             raise DsmoeError(rc, self.lib.dsmoe_last_error(self.h).decode())
 
+    def device_status(self) -> int:
+        """Synchronises the current stream and returns the device status word (0 = no bounded wait ever expired);
+        raises DsmoeError otherwise."""
+        code = C.c_int(0)
+        self._check(self.lib.dsmoe_device_status(self.h, _stream(), C.byref(code)))
+        return code.value
+
     @property
     def launch_count(self) -> int:
         return int(self.lib.dsmoe_launch_count(self.h))

@@ -82,6 +82,11 @@ DSMOE_API void dsmoe_default_config(dsmoe_config *cfg);
 DSMOE_API int dsmoe_create(const dsmoe_config *cfg, int device, dsmoe_handle **out);
 DSMOE_API int dsmoe_destroy(dsmoe_handle *h);
 DSMOE_API const char *dsmoe_last_error(const dsmoe_handle *h);
+/* Waits for the stream and reads the handle's device status word. Kernels that wait on asynchronous copies bound the
+ * wait; if one ever expires the kernel records a code and returns instead of hanging. Returns DSMOE_OK with
+ * *code_out == 0, or DSMOE_ERR_TIMEOUT with the code. The reference has no device-side error reporting
+ * (launch errors only, engine/src/session.rs `?` propagation). */
+DSMOE_API int dsmoe_device_status(dsmoe_handle *h, dsmoe_stream stream, int *code_out);
 /* Number of kernels this handle has launched since creation (bookkeeping for benchmarks). */
 DSMOE_API uint64_t dsmoe_launch_count(const dsmoe_handle *h);
 

@@ -23,11 +23,31 @@ def torch_cuda():
     return torch
 
 
-@pytest.fixture(scope="module")
-def K(torch_cuda):
+def _make_kernels(tma: bool, **kw):
+    """A handle with the bulk-copy (TMA) staging kernels on or off; the switch is read at handle creation."""
+    import os
+
     from deepseek_rs_b200.kernels import MoeKernels
 
-    return MoeKernels(device=0, max_tokens=64)
+    old = os.environ.get("DSMOE_DISABLE_TMA")
+    os.environ["DSMOE_DISABLE_TMA"] = "0" if tma else "1"
+    try:
+        return MoeKernels(device=0, **kw)
+    finally:
+        if old is None:
+            del os.environ["DSMOE_DISABLE_TMA"]
+        else:
+            os.environ["DSMOE_DISABLE_TMA"] = old
+
+
+@pytest.fixture(scope="module")
+def K(torch_cuda):
+    return _make_kernels(True, max_tokens=64)
+
+
+@pytest.fixture(scope="module")
+def K_plain(torch_cuda):
+    return _make_kernels(False, max_tokens=64)
 
 
 def dev(torch, a):
@@ -240,11 +260,14 @@ def _relaid(torch, K, w_np, n_rows, blocks, kind):
     return d
 
 
+@pytest.mark.parametrize("path", ["tma", "plain"])
 @pytest.mark.parametrize("layout", ["native", "rowsoa"])
 @pytest.mark.parametrize("xb,n_ff,T,n_e", [(16, 2048, 3, 4), (16, 200, 2, 3), (1, 40, 2, 3), (3, 17, 1, 2), (8, 64, 4, 5),
                                            (20, 24, 2, 2)])
-def test_gate_up_mid(torch_cuda, K, oracle, layout, xb, n_ff, T, n_e):
+def test_gate_up_mid(torch_cuda, K, K_plain, oracle, path, layout, xb, n_ff, T, n_e):
     torch = torch_cuda
+    if path == "plain":
+        K = K_plain
     from deepseek_rs_b200.kernels import LAYOUT_NATIVE, LAYOUT_ROWSOA
 
     rng = np.random.default_rng(100 + xb + n_ff)
@@ -278,11 +301,14 @@ def test_gate_up_mid(torch_cuda, K, oracle, layout, xb, n_ff, T, n_e):
     assert torch.equal(m2, outs[2])
 
 
+@pytest.mark.parametrize("path", ["tma", "plain"])
 @pytest.mark.parametrize("layout", ["native", "rowsoa"])
 @pytest.mark.parametrize("mb,out_dim,T,n_e,k", [(8, 4096, 2, 4, 6), (8, 100, 3, 3, 6), (1, 33, 2, 2, 6), (5, 20, 1, 3, 4),
-                                                (16, 64, 4, 2, 1), (9, 31, 2, 2, 8)])
-def test_down_and_down_sum(torch_cuda, K, oracle, layout, mb, out_dim, T, n_e, k):
+                                                (16, 64, 4, 2, 1), (9, 31, 2, 2, 8), (8, 4096, 20, 3, 8)])
+def test_down_and_down_sum(torch_cuda, K, K_plain, oracle, path, layout, mb, out_dim, T, n_e, k):
     torch = torch_cuda
+    if path == "plain":
+        K = K_plain
     from deepseek_rs_b200.kernels import LAYOUT_NATIVE, LAYOUT_ROWSOA
 
     rng = np.random.default_rng(200 + mb + out_dim)
@@ -381,6 +407,7 @@ def test_moe_forward_layer(torch_cuda, oracle, layout, T):
     assert np.array_equal(w.cpu().numpy(), ref_w)
     assert_close(out.cpu().numpy(), ref_out)
     assert np.array_equal(out.cpu().numpy().view(np.uint32), ref_out.view(np.uint32))
+    assert Kl.device_status() == 0  # no bounded wait expired
     # host-buffer entry point gives the same result
     xh, lh = torch.from_numpy(x).pin_memory(), torch.from_numpy(logits).pin_memory()
     oh = torch.zeros((T, 4096), dtype=torch.float32).pin_memory()
