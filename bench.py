@@ -12,7 +12,7 @@ Timing: CUDA events on the launching stream, W >= 3 warm-up steps, max over rank
 weights and another routing, so the packed bytes of a step are never in L2 from the step before (the rotation covers
 several times the 126 MB L2). `value` is device-timed with inputs resident in HBM; `e2e` goes through the host-buffer
 C-ABI call with pinned host memory, copies inside the timed region. `roofline` is the dominant kernel (gate/up)
-timed by CUDA events around its launches. `--impl reference` times the CPU oracle (a C port of the reference's CPU
+timed alone: K back-to-back launches between two CUDA events. `--impl reference` times the CPU oracle (a C port of the reference's CPU
 semantics; the reference's Rust cannot be built here) on the host cores.
 """
 from __future__ import annotations
@@ -69,7 +69,7 @@ class ClockSampler:
     """Samples SM clock and throttle reasons with nvidia-smi while the timed regions run."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,utilization.gpu")
 
     def __init__(self, index: int):
         self.index, self.rows, self.proc = index, [], None
@@ -85,9 +85,10 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
 
-    def stop(self):
+    def stop(self, window=None):
+        """window = (t0, t1) in host time: only samples taken while the measured load ran are kept."""
         if self.proc:
             self.proc.terminate()
             try:
@@ -96,7 +97,9 @@ class ClockSampler:
                 pass
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for ts, r in self.rows:
+            if window and not (window[0] <= ts <= window[1]):
+                continue
             try:
                 sm.append(float(r[0]))
                 mx.append(float(r[1]))
@@ -226,6 +229,8 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()  # started early (nvidia-smi takes a while to come up); samples are filtered to the load window
     wl = WORKLOADS[args.workload]
     T, L = wl["tokens"], (args.layers if args.layers > 0 else wl["layers"])
     K = MoeKernels(device=local_rank, max_tokens=T, max_layers=L)
@@ -264,57 +269,98 @@ def main():
     def step(i):
         K.moe_forward(i % L, xs[i % V], lgs[i % V], T, out, None, None)
 
-    sampler = ClockSampler(local_rank)
+    t_load0 = time.time()
     for i in range(args.warmup):
         step(i)
     torch.cuda.synchronize()
+
+    # The timed steps are replayed from a CUDA graph holding G consecutive steps (G divides K), so that the host's
+    # launch cost (several microseconds per ctypes call) does not sit between kernels of a 40-microsecond step.
+    G = max(g for g in range(1, min(args.steps, 32) + 1) if args.steps % g == 0)
+    launches0 = K.launch_count
+    graph = torch.cuda.CUDAGraph()
+    cap_stream = torch.cuda.Stream()
+    cap_stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(cap_stream):
+        step(args.warmup)  # the capture stream's first use of every kernel happens outside the capture
+        torch.cuda.synchronize()
+        launches0 = K.launch_count
+        with torch.cuda.graph(graph, stream=cap_stream):
+            for i in range(G):
+                step(args.warmup + i)
+    launches = (K.launch_count - launches0) * (args.steps // G)
+    torch.cuda.current_stream().wait_stream(cap_stream)
+    graph.replay()  # one untimed replay
+    torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    sampler.start()
-    launches0 = K.launch_count
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     e0.record()
-    for i in range(args.steps):
-        step(args.warmup + i)
+    for _ in range(args.steps // G):
+        graph.replay()
     e1.record()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    launches = K.launch_count - launches0
     ms_total = e0.elapsed_time(e1)
-    u_mean = sum(distinct[(args.warmup + i) % V] for i in range(args.steps)) / args.steps
+    u_mean = sum(distinct[(args.warmup + i) % V] for i in range(G)) / G
+    assert K.device_status() == 0
 
-    # dominant kernels timed one by one with events (same inputs, same rotation), tier-1 calls
+    # The two dominant kernels timed alone: K back-to-back launches each (inputs prepared beforehand, same rotation
+    # over layers and routings), CUDA events around the batch.
     xb, mb = N_EMBD // 256, N_FF // 256
-    xq = torch.empty((T, xb, 292), dtype=torch.uint8, device=device)
-    mid = torch.empty((T * TOP_K, N_FF), device=device)
-    midq = torch.empty((T * TOP_K, mb, 292), dtype=torch.uint8, device=device)
     probs = torch.empty((T, N_EXPERT), device=device)
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
-    for i in range(args.warmup + args.steps):
-        j = i - args.warmup
-        gate, up, down = layers[i % L]
-        K.router_select_parallel(lgs[i % V], None, None, None, probs, sel, wts, 0, 0, T, 0, 0)
-        K.q8k_quantize(xs[i % V], xq, N_EMBD, T)
-        if j >= 0:
-            ev[j][0].record()
-        K.moe_gate_up_mid_qwarp32(gate, up, xq, sel, wts, None, None, mid, GATE_EXPERT_BYTES, xb * 66, xb, N_FF, TOP_K,
+    pre = []
+    for v in range(V):
+        xq = torch.empty((T, xb, 292), dtype=torch.uint8, device=device)
+        mid = torch.empty((T * TOP_K, N_FF), device=device)
+        midq = torch.empty((T * TOP_K, mb, 292), dtype=torch.uint8, device=device)
+        sv, wv = torch.empty_like(sel), torch.empty_like(wts)
+        gate, up, down = layers[v % L]
+        K.router_select_parallel(lgs[v], None, None, None, probs, sv, wv, 0, 0, T, 0, 0)
+        K.q8k_quantize(xs[v], xq, N_EMBD, T)
+        K.moe_gate_up_mid_qwarp32(gate, up, xq, sv, wv, None, None, mid, GATE_EXPERT_BYTES, xb * 66, xb, N_FF, TOP_K,
                                   10.0, n_tokens=T, layout=layout)
-        if j >= 0:
-            ev[j][1].record()
         K.q8k_quantize(mid, midq, N_FF, T * TOP_K)
-        if j >= 0:
-            ev[j][2].record()
-        K.moe_down_sum6_qwarp32(down, midq, sel, out, DOWN_EXPERT_BYTES, mb * 84, mb, N_EMBD, n_expert=TOP_K,
-                                n_tokens=T, layout=layout)
-        if j >= 0:
-            ev[j][3].record()
+        pre.append((xq, sv, wv, midq))
+    mid = torch.empty((T * TOP_K, N_FF), device=device)
     torch.cuda.synchronize()
-    dn_ms_mean = sum(ev[j][2].elapsed_time(ev[j][3]) for j in range(args.steps)) / args.steps
-    gu_ms = [ev[j][0].elapsed_time(ev[j][1]) for j in range(args.steps)]
-    gu_ms_mean = sum(gu_ms) / len(gu_ms)
-    clocks = sampler.stop()
+
+    def run_gate_up(i):
+        gate, up, _ = layers[i % L]
+        xq, sv, wv, _ = pre[i % V]
+        K.moe_gate_up_mid_qwarp32(gate, up, xq, sv, wv, None, None, mid, GATE_EXPERT_BYTES, xb * 66, xb, N_FF, TOP_K,
+                                  10.0, n_tokens=T, layout=layout)
+
+    def run_down(i):
+        _, _, down = layers[i % L]
+        _, sv, _, midq = pre[i % V]
+        K.moe_down_sum6_qwarp32(down, midq, sv, out, DOWN_EXPERT_BYTES, mb * 84, mb, N_EMBD, n_expert=TOP_K,
+                                n_tokens=T, layout=layout)
+
+    def time_alone(fn):
+        # L must divide V for (layer, routing) pairs to stay matched; replay from a graph for the same reason as above
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(cap_stream):
+            fn(0)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g2, stream=cap_stream):
+                for i in range(G):
+                    fn(i)
+        torch.cuda.current_stream().wait_stream(cap_stream)
+        g2.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps // G):
+            g2.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / args.steps
+
+    gu_ms_mean = time_alone(run_gate_up)
+    dn_ms_mean = time_alone(run_down)
 
     # end to end through the host-buffer C-ABI call
     xh = xs.cpu().pin_memory()
@@ -329,6 +375,12 @@ def main():
     for i in range(args.steps):
         K.moe_forward_host(i % L, xh[i % V], lh[i % V], T, oh)
     e2e_s = time.perf_counter() - t0
+    # nvidia-smi samples every 100 ms: keep the same load running (untimed) until the window holds enough samples
+    while time.time() - t_load0 < 2.0:
+        for _ in range(8):
+            graph.replay()
+        torch.cuda.synchronize()
+    clocks = sampler.stop(window=(t_load0, time.time()))
 
     # max over ranks
     times = torch.tensor([ms_total, e2e_s * 1e3, gu_ms_mean], dtype=torch.float64, device=device)
@@ -365,7 +417,7 @@ def main():
                               "avg_launch_ms": dn_ms_mean},
             "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": T * (N_EMBD + N_EXPERT) * 4, "d2h_bytes_per_step": T * N_EMBD * 4},
-            "gpu_launches": launches,
+            "gpu_launches": launches, "timed_with": f"CUDA graph of {G} steps replayed {args.steps // G} times",
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:

@@ -357,12 +357,20 @@ int dsmoe_moe_forward(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, cons
     int32_t *sel = selected_out ? selected_out : h->selected;
     float *wts = weights_out ? weights_out : h->weights;
 
-    launch_router_select(st, logits, nullptr, nullptr, nullptr, h->probs, sel, wts, 0, 0, n_tokens, 0, 0, (int)k,
-                         (int)c.n_expert, c.route_scale);
-    launch_q8k_quantize(st, x, h->xq, c.n_embd, n_tokens);
+    int n = 0;
+    if (c.n_expert <= 256) {
+        launch_router_q8k_fused(st, logits, x, h->probs, sel, wts, h->xq, n_tokens, (int)k, (int)c.n_expert, c.n_embd,
+                                c.route_scale);
+        n = 1;
+    } else {
+        launch_router_select(st, logits, nullptr, nullptr, nullptr, h->probs, sel, wts, 0, 0, n_tokens, 0, 0, (int)k,
+                             (int)c.n_expert, c.route_scale);
+        launch_q8k_quantize(st, x, h->xq, c.n_embd, n_tokens);
+        n = 2;
+    }
     GateUpArgs g = {ly.gate, ly.up, h->xq, sel, wts, nullptr, nullptr, h->mid, (uint64_t)c.n_ff * xb * IQ2XXS_BYTES,
                     (uint64_t)xb * IQ2XXS_BYTES, xb, c.n_ff, k, n_tokens, c.swiglu_clamp, ly.layout, (int)c.f16_ieee};
-    int n = 2 + ((h->use_tma && gate_up_tma_eligible(g)) ? launch_gate_up_mid_tma(st, g, h->d_status)
+    n += ((h->use_tma && gate_up_tma_eligible(g)) ? launch_gate_up_mid_tma(st, g, h->d_status)
                                                          : launch_gate_up_mid(st, g));
     launch_q8k_quantize(st, h->mid, h->midq, c.n_ff, n_tokens * k);
     DownArgs d = {ly.down, h->midq, sel, out, (uint64_t)c.n_embd * mb * Q2K_BYTES, (uint64_t)mb * Q2K_BYTES, mb,

@@ -2,16 +2,27 @@
 // by bulk asynchronous copies (TMA, untiled), so that every SM keeps tens of kilobytes of HBM reads in flight
 // without holding them in registers.
 //
-//   gate/up: persistent CTAs, one per SM. Each warp owns a contiguous run of (pair, row) items and a private ring of
-//            GU_STAGES stages; lane 0 issues two 1056-byte bulk copies (gate row, up row) per stage onto the stage's
-//            mbarrier, the warp consumes the stage two items later. The codebook and the sign masks are replicated
-//            16x in shared memory, one copy per lane of a half-warp, which makes every 64-bit lookup conflict-free.
-//   down:    one CTA per (token, chunk of output rows), one warp per routed slot; lane 0 fetches the warp's whole
-//            chunk of that expert's rows (contiguous) with a single bulk copy while the other lanes load the int8
-//            activations of their K-slice into registers.
+// Both kernels are limited by instruction issue, not by HBM, at small batch: B200 delivers about 5.8 packed bytes per
+// issued warp instruction at full bandwidth, i.e. about 22 IQ2_XXS or 18 Q2_K weights. The mapping therefore gives
+// each lane a whole 256-weight block (as the reference's quarter-warp kernels do), which removes every integer
+// cross-lane reduction; only the reference's own f32 butterfly remains. The int8 activations of the lane's block
+// live in registers for the lifetime of the (token, slot) pair.
 //
-// Arithmetic and summation order are those of experts.cu (and of the reference kernels), so results stay
-// bit-identical to the CPU oracle.
+//   gate/up: persistent CTAs, one per SM. A warp item is two consecutive rows (half-warp per row, lane = block).
+//            Lane 0 issues the four 1056-byte bulk copies of an item onto the stage's mbarrier; the warp consumes the
+//            stage one item later (the kernel is issue-bound, a depth of one item per warp keeps ~60 KB in flight). Codebook and sign masks are replicated in shared memory so that every 64-bit
+//            lookup is conflict-free. Clamp, SwiGLU and the stores run once per 32 finished rows, one row per lane.
+//   down:    one CTA per (token, chunk of output rows), one warp per routed slot, four rows per warp step (quarter-warp
+//            per row, lane = block); lane 0 fetches the warp's whole chunk of that expert's rows (contiguous) with
+//            one bulk copy and the pair's Q8_K activations with another. Slot results meet in shared memory and
+//            are summed in slot order.
+//
+// Lanes read their 64-byte block from the staged row in a rotated 16-byte order ((j + block/2) mod 4) so that the
+// eight lanes of a shared-memory wavefront hit eight different bank groups; the activation registers are loaded in
+// the same rotated order, which keeps all register indexing static.
+//
+// Arithmetic and summation order are those of the reference kernels (engine/src/kernels/moe.rs:622-715, 922-970), so
+// results stay bit-identical to the CPU oracle.
 #include "async.cuh"
 #include "common.cuh"
 #include "launch.h"
@@ -22,21 +33,32 @@ namespace dsmoe {
 // per-thread indices).
 __device__ const uint64_t g_iq2xxs_grid[DSMOE_IQ2XXS_GRID_ENTRIES] = {DSMOE_IQ2XXS_GRID_VALUES};
 
-constexpr int GU_STAGES = 3;
+constexpr int GU_STAGES = 2;
 constexpr int GU_ROW_BYTES = 16 * IQ2XXS_BYTES;  // 1056
-constexpr int GU_STAGE_BYTES = 2 * GU_ROW_BYTES; // gate row + up row
-constexpr int GU_TABLE_BYTES = (DSMOE_IQ2XXS_GRID_ENTRIES + DSMOE_IQ2_SIGN_ENTRIES) * 16 * 8;  // 49152
-constexpr int GU_MAX_WARPS = 16;
+constexpr int GU_STAGE_BYTES = 2 * GU_ROW_BYTES; // gate row + up row of one output row
+// Lookup tables, replicated so that every lane of a warp (codebook, 32 copies, 256-byte entry stride) or of a
+// half-warp (sign masks, 16 copies, 128-byte stride) reads its own bank pair: each 64-bit lookup costs the minimum of
+// two shared-memory wavefronts, and the codebook address is assembled from the packed index byte by one PRMT.
+constexpr int GU_GRID_TABLE_BYTES = DSMOE_IQ2XXS_GRID_ENTRIES * 256;  // 65536
+constexpr int GU_SIGN_TABLE_BYTES = DSMOE_IQ2_SIGN_ENTRIES * 128;     // 16384
+constexpr int GU_TABLE_BYTES = GU_GRID_TABLE_BYTES + GU_SIGN_TABLE_BYTES;
+constexpr int GU_MAX_WARPS = 14;  // register file: 14 warps x 146 registers; 80 KB tables + 14 rings of 2 x 4224 B
 
-// conflict-free variant of iq2_group_dot: tg / ts point at this lane's copy (entry stride 16 uint2)
-__device__ __forceinline__ int iq2_group_dot_rep(uint32_t aux0, uint32_t aux1, const int *q, const uint2 *tg,
-                                                 const uint2 *ts)
+// Integer dot of one 32-weight group; tables addressed as described above. lane8 = 8 * lane,
+// sbase = GU_GRID_TABLE_BYTES + 8 * (lane & 15). Signs by the identity sum(+/-g*q) = dp4a(g^m, q) - dp4a(m, q).
+__device__ __forceinline__ int iq2_group_dot_rep(uint32_t aux0, uint32_t aux1, const int *q, const uint8_t *tbl,
+                                                 uint32_t lane8, uint32_t sbase)
 {
     int pos = 0, neg = 0;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-        uint2 g = tg[((aux0 >> (8 * k)) & 255u) * 16];
-        uint2 m = ts[((aux1 >> (7 * k)) & 127u) * 16];
+        // (index byte k) << 8 | 8*lane: byte 0 from lane8, byte 1 from aux0, bytes 2-3 zero (lane8 bytes 1, 2)
+        const uint32_t goff = __byte_perm(aux0, lane8, 0x6504u | ((uint32_t)k << 4));
+        const int sh = 7 - 7 * k;  // bring the 7-bit sign index to bits 7..13
+        const uint32_t sraw = sh >= 0 ? (aux1 << sh) : (aux1 >> (-sh));
+        const uint32_t soff = (sraw & 0x3F80u) + sbase;
+        const uint2 g = *reinterpret_cast<const uint2 *>(tbl + goff);
+        const uint2 m = *reinterpret_cast<const uint2 *>(tbl + soff);
         pos = __dp4a((int)(g.x ^ m.x), q[2 * k], pos);
         pos = __dp4a((int)(g.y ^ m.y), q[2 * k + 1], pos);
         neg = __dp4a((int)m.x, q[2 * k], neg);
@@ -45,25 +67,33 @@ __device__ __forceinline__ int iq2_group_dot_rep(uint32_t aux0, uint32_t aux1, c
     return (pos - neg) * (int)(2u * (aux1 >> 28) + 1u);
 }
 
+constexpr int GU_ITEM_ROWS = 2;
+constexpr int GU_ITEM_BYTES = GU_ITEM_ROWS * GU_STAGE_BYTES;  // gate,up of row r then gate,up of row r+1
+
+// 16-byte piece c (groups 2c, 2c+1) of block blk of a staged row
 template <int LAYOUT>
-__device__ __forceinline__ uint4 gu_smem_chunk(const uint8_t *row, int c)
+__device__ __forceinline__ uint4 gu_smem_piece(const uint8_t *row, int blk, int c)
 {
-    if (LAYOUT == DSMOE_LAYOUT_ROWSOA) return *reinterpret_cast<const uint4 *>(row + 32 + 16 * c);
-    return ld_16B_align2(row + IQ2XXS_BYTES * (c >> 2) + 2 + 16 * (c & 3));
+    if (LAYOUT == DSMOE_LAYOUT_ROWSOA) return *reinterpret_cast<const uint4 *>(row + 32 + 64 * blk + 16 * c);
+    return ld_16B_align2(row + IQ2XXS_BYTES * blk + 2 + 16 * c);
 }
 
-__device__ __forceinline__ float gu_reduce(int s0, int s1, uint32_t d0, uint32_t d1, float yd0, float yd1, bool ieee)
+// ((0.125 * d_w) * d_x) * (float)bsum, engine/src/kernels/quantize.rs:811
+__device__ __forceinline__ float iq2_block_scale(uint32_t dbits, float yd, int bsum, bool ieee)
 {
-    s0 += __shfl_xor_sync(FULL, s0, 1);
-    s1 += __shfl_xor_sync(FULL, s1, 1);
-    s0 += __shfl_xor_sync(FULL, s0, 2);
-    s1 += __shfl_xor_sync(FULL, s1, 2);
-    float p0 = __fmul_rn(__fmul_rn(__fmul_rn(0.125f, f16_bits_to_f32(d0, ieee)), yd0), (float)s0);
-    float p1 = __fmul_rn(__fmul_rn(__fmul_rn(0.125f, f16_bits_to_f32(d1, ieee)), yd1), (float)s1);
-    float a = __fadd_rn(__fadd_rn(0.0f, p0), p1);
-    a = __fadd_rn(a, __shfl_xor_sync(FULL, a, 16));
-    a = __fadd_rn(a, __shfl_xor_sync(FULL, a, 8));
+    return __fmul_rn(__fmul_rn(__fmul_rn(0.125f, f16_bits_to_f32(dbits, ieee)), yd), (float)bsum);
+}
+
+// lane partial a_l = (0 + dot_l) + dot_(l+8), then the butterfly xor 4, 2, 1 (engine/src/kernels/moe.rs:37-42,
+// 661-690), over the 16 lanes of a half-warp (lane = block)
+__device__ __forceinline__ float gu_row_total(float dot)
+{
+    const float other = __shfl_xor_sync(FULL, dot, 8);
+    const bool low = (threadIdx.x & 8) == 0;
+    float a = __fadd_rn(__fadd_rn(0.0f, low ? dot : other), low ? other : dot);
     a = __fadd_rn(a, __shfl_xor_sync(FULL, a, 4));
+    a = __fadd_rn(a, __shfl_xor_sync(FULL, a, 2));
+    a = __fadd_rn(a, __shfl_xor_sync(FULL, a, 1));
     return a;
 }
 
@@ -76,20 +106,20 @@ __global__ void __launch_bounds__(32 * GU_MAX_WARPS, 1)
                            uint32_t n_items, float clamp, int ieee_i, int *status)
 {
     extern __shared__ __align__(128) uint8_t smem[];
-    uint2 *s_grid = reinterpret_cast<uint2 *>(smem);
-    uint2 *s_sign = s_grid + DSMOE_IQ2XXS_GRID_ENTRIES * 16;
     const int wpc = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    uint8_t *ring = smem + GU_TABLE_BYTES + (size_t)warp * GU_STAGES * GU_STAGE_BYTES;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + GU_TABLE_BYTES + (size_t)wpc * GU_STAGES * GU_STAGE_BYTES) +
+    uint8_t *ring = smem + GU_TABLE_BYTES + (size_t)warp * GU_STAGES * GU_ITEM_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + GU_TABLE_BYTES + (size_t)wpc * GU_STAGES * GU_ITEM_BYTES) +
                      warp * GU_STAGES;
 
-    for (int i = threadIdx.x; i < DSMOE_IQ2XXS_GRID_ENTRIES * 16; i += blockDim.x) {
-        uint64_t g = g_iq2xxs_grid[i >> 4];
-        s_grid[i] = make_uint2((uint32_t)g, (uint32_t)(g >> 32));
+    // fill the replicated tables, 16 bytes (two copies of one entry) per store
+    for (int i = threadIdx.x; i < GU_GRID_TABLE_BYTES / 16; i += blockDim.x) {
+        const uint64_t g = g_iq2xxs_grid[i >> 4];
+        reinterpret_cast<uint4 *>(smem)[i] = make_uint4((uint32_t)g, (uint32_t)(g >> 32), (uint32_t)g, (uint32_t)(g >> 32));
     }
-    for (int i = threadIdx.x; i < DSMOE_IQ2_SIGN_ENTRIES * 16; i += blockDim.x) {
-        uint32_t sb = dsmoe_iq2_sign_byte((uint32_t)(i >> 4));
-        s_sign[i] = make_uint2(nibble_to_bytemask(sb), nibble_to_bytemask(sb >> 4));
+    for (int i = threadIdx.x; i < GU_SIGN_TABLE_BYTES / 16; i += blockDim.x) {
+        const uint32_t sb = dsmoe_iq2_sign_byte((uint32_t)(i >> 3));
+        const uint32_t lo = nibble_to_bytemask(sb), hi = nibble_to_bytemask(sb >> 4);
+        reinterpret_cast<uint4 *>(smem + GU_GRID_TABLE_BYTES)[i] = make_uint4(lo, hi, lo, hi);
     }
     if (lane == 0) {
 #pragma unroll
@@ -98,81 +128,105 @@ __global__ void __launch_bounds__(32 * GU_MAX_WARPS, 1)
     }
     __syncthreads();
 
-    // this warp's run of items; item = pair * mid_dim + row
+    // this warp's run of items; item i covers rows 2i, 2i+1 of the flattened [pair][row] space (mid_dim is even)
     const uint32_t n_warps = gridDim.x * wpc, gw = blockIdx.x * wpc + warp;
     const uint32_t chunk = (n_items + n_warps - 1) / n_warps;
     const uint32_t begin = min(n_items, gw * chunk), end = min(n_items, begin + chunk);
     if (begin >= end) return;
     const bool ieee = ieee_i != 0;
-    const uint2 *tg = s_grid + (lane & 15), *ts = s_sign + (lane & 15);
-    const int b = lane >> 2, part = lane & 3;
+    const uint32_t lane8 = 8u * lane, sbase = GU_GRID_TABLE_BYTES + 8u * (lane & 15);
+    const int sub = lane >> 4, blk = lane & 15, rot = blk >> 1;
+    const uint32_t items_per_pair = mid_dim / GU_ITEM_ROWS;
 
-    auto issue = [&](uint32_t item, int stage) {
+    uint32_t f_item = begin, f_pair = begin / items_per_pair, f_row = (begin - f_pair * items_per_pair) * GU_ITEM_ROWS;
+    auto issue_next = [&](int stage) {
         if (lane == 0) {
-            const uint32_t pair = item / mid_dim, row = item - pair * mid_dim;
-            const int32_t e = selected[pair];
-            const uint64_t off = (e < 0 ? 0u : (uint64_t)e) * expert_bytes + (uint64_t)row * GU_ROW_BYTES;
-            uint8_t *dst = ring + stage * GU_STAGE_BYTES;
-            mbar_expect_tx(&bars[stage], GU_STAGE_BYTES);
-            bulk_g2s(dst, gate_base + off, GU_ROW_BYTES, &bars[stage]);
-            bulk_g2s(dst + GU_ROW_BYTES, up_base + off, GU_ROW_BYTES, &bars[stage]);
+            const int32_t e = selected[f_pair];
+            const uint64_t off = (e < 0 ? 0u : (uint64_t)e) * expert_bytes + (uint64_t)f_row * GU_ROW_BYTES;
+            uint8_t *dst = ring + stage * GU_ITEM_BYTES;
+            mbar_expect_tx(&bars[stage], GU_ITEM_BYTES);
+            // rows f_row and f_row+1 are adjacent in each tensor: one copy per tensor; gate rows first, then up rows
+            bulk_g2s(dst, gate_base + off, GU_ITEM_ROWS * GU_ROW_BYTES, &bars[stage]);
+            bulk_g2s(dst + GU_ITEM_ROWS * GU_ROW_BYTES, up_base + off, GU_ITEM_ROWS * GU_ROW_BYTES, &bars[stage]);
+        }
+        ++f_item;
+        f_row += GU_ITEM_ROWS;
+        if (f_row == mid_dim) {
+            f_row = 0;
+            ++f_pair;
         }
     };
 #pragma unroll
     for (int j = 0; j < GU_STAGES - 1; ++j)
-        if (begin + j < end) issue(begin + j, j);
+        if (f_item < end) issue_next(j);
 
-    int qa[16], qb[16];
-    float yd0 = 0.0f, yd1 = 0.0f, w = 0.0f;
-    uint32_t cur_pair = 0xFFFFFFFFu;
+    int q[64];  // activations of block blk, 16-byte pieces in rotated order: q[16j ..] belongs to piece (j + rot) & 3
+    float yd = 0.0f;
+    uint32_t pair = begin / items_per_pair, row = (begin - pair * items_per_pair) * GU_ITEM_ROWS, cur_tok = 0xFFFFFFFFu;
+    float keep_g = 0.0f, keep_u = 0.0f;  // lane L keeps row (2 * flush_base + L) of the flattened output
+    uint32_t flush_base = begin;
     uint32_t it = 0;
     for (uint32_t item = begin; item < end; ++item, ++it) {
         const int stage = it % GU_STAGES;
-        const uint32_t pair = item / mid_dim, row = item - pair * mid_dim;
-        if (pair != cur_pair) {  // new (token, slot): reload this lane's slice of the token's Q8_K row
-            cur_pair = pair;
-            const uint8_t *xt = xq + (size_t)(pair / k) * 16 * Q8K_BYTES;
-            const int *pa = reinterpret_cast<const int *>(xt + Q8K_BYTES * b + 4 + 64 * part);
-            const int *pb = reinterpret_cast<const int *>(xt + Q8K_BYTES * (b + 8) + 4 + 64 * part);
+        const uint32_t tok = pair / k;
+        if (tok != cur_tok) {  // new token: reload this lane's block of its Q8_K row
+            cur_tok = tok;
+            const uint8_t *xb = xq + ((size_t)tok * 16 + blk) * Q8K_BYTES;
+            yd = *reinterpret_cast<const float *>(xb);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                qa[i] = pa[i];
-                qb[i] = pb[i];
+            for (int j = 0; j < 4; ++j) {
+                const int *pq = reinterpret_cast<const int *>(xb + 4 + 64 * ((j + rot) & 3));
+#pragma unroll
+                for (int i = 0; i < 16; ++i) q[16 * j + i] = pq[i];
             }
-            yd0 = *reinterpret_cast<const float *>(xt + Q8K_BYTES * b);
-            yd1 = *reinterpret_cast<const float *>(xt + Q8K_BYTES * (b + 8));
-            w = weights[pair];
         }
-        // refill the stage consumed one iteration ago (all lanes finished reading it before the __syncwarp below)
-        if (item + GU_STAGES - 1 < end) {
+        if (f_item < end) {  // refill the stage consumed one iteration ago
             fence_async_smem();
-            issue(item + GU_STAGES - 1, (it + GU_STAGES - 1) % GU_STAGES);
+            issue_next((it + GU_STAGES - 1) % GU_STAGES);
         }
         if (!mbar_wait_bounded(&bars[stage], (it / GU_STAGES) & 1, status)) return;
-        const uint8_t *grow = ring + stage * GU_STAGE_BYTES, *urow = grow + GU_ROW_BYTES;
-        const uint4 g0 = gu_smem_chunk<LAYOUT>(grow, lane), g1 = gu_smem_chunk<LAYOUT>(grow, lane + 32);
-        const uint4 u0 = gu_smem_chunk<LAYOUT>(urow, lane), u1 = gu_smem_chunk<LAYOUT>(urow, lane + 32);
+        const uint8_t *grow = ring + stage * GU_ITEM_BYTES + sub * GU_ROW_BYTES;
+        const uint8_t *urow = grow + GU_ITEM_ROWS * GU_ROW_BYTES;
+        int sg = 0, su = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = (j + rot) & 3;
+            const uint4 gp = gu_smem_piece<LAYOUT>(grow, blk, c), up = gu_smem_piece<LAYOUT>(urow, blk, c);
+            sg += iq2_group_dot_rep(gp.x, gp.y, q + 16 * j, smem, lane8, sbase);
+            sg += iq2_group_dot_rep(gp.z, gp.w, q + 16 * j + 8, smem, lane8, sbase);
+            su += iq2_group_dot_rep(up.x, up.y, q + 16 * j, smem, lane8, sbase);
+            su += iq2_group_dot_rep(up.z, up.w, q + 16 * j + 8, smem, lane8, sbase);
+        }
         const uint32_t dstep = LAYOUT == DSMOE_LAYOUT_ROWSOA ? 2 : IQ2XXS_BYTES;
-        const uint32_t dg0 = ld_u16(grow + dstep * b), dg1 = ld_u16(grow + dstep * (b + 8));
-        const uint32_t du0 = ld_u16(urow + dstep * b), du1 = ld_u16(urow + dstep * (b + 8));
-        __syncwarp();
-
-        int sg0 = iq2_group_dot_rep(g0.x, g0.y, qa, tg, ts) + iq2_group_dot_rep(g0.z, g0.w, qa + 8, tg, ts);
-        int sg1 = iq2_group_dot_rep(g1.x, g1.y, qb, tg, ts) + iq2_group_dot_rep(g1.z, g1.w, qb + 8, tg, ts);
-        int su0 = iq2_group_dot_rep(u0.x, u0.y, qa, tg, ts) + iq2_group_dot_rep(u0.z, u0.w, qa + 8, tg, ts);
-        int su1 = iq2_group_dot_rep(u1.x, u1.y, qb, tg, ts) + iq2_group_dot_rep(u1.z, u1.w, qb + 8, tg, ts);
-        float g = gu_reduce(sg0, sg1, dg0, dg1, yd0, yd1, ieee);
-        float u = gu_reduce(su0, su1, du0, du1, yd0, yd1, ieee);
-        if (lane == 0) {
-            if (clamp > 1.0e-6f) {
-                if (g > clamp) g = clamp;
-                if (u > clamp) u = clamp;
-                if (u < -clamp) u = -clamp;
+        const uint32_t dg = ld_u16(grow + dstep * blk), du = ld_u16(urow + dstep * blk);
+        __syncwarp();  // every lane has finished reading the stage
+        const float g = gu_row_total(iq2_block_scale(dg, yd, sg, ieee));  // all 16 lanes of the half hold the row total
+        const float u = gu_row_total(iq2_block_scale(du, yd, su, ieee));
+        const float g_o = __shfl_xor_sync(FULL, g, 16), u_o = __shfl_xor_sync(FULL, u, 16);
+        if ((uint32_t)(lane >> 1) == item - flush_base) {  // lane L keeps sub-row L & 1 of this item
+            keep_g = (lane & 1) == sub ? g : g_o;
+            keep_u = (lane & 1) == sub ? u : u_o;
+        }
+        if (item - flush_base == 15 || item + 1 == end) {
+            // clamp + SwiGLU + stores for up to 32 finished rows at once, one per lane
+            const uint32_t mine = GU_ITEM_ROWS * flush_base + lane;  // flattened [pair][row] output index
+            if (mine < GU_ITEM_ROWS * (item + 1)) {
+                float gg = keep_g, uu = keep_u;
+                if (clamp > 1.0e-6f) {
+                    if (gg > clamp) gg = clamp;
+                    if (uu > clamp) uu = clamp;
+                    if (uu < -clamp) uu = -clamp;
+                }
+                if (gate_out) gate_out[mine] = gg;
+                if (up_out) up_out[mine] = uu;
+                mid_out[mine] = swiglu_weighted(gg, uu, weights[mine / mid_dim]);
             }
-            const size_t off = (size_t)pair * mid_dim + row;
-            if (gate_out) gate_out[off] = g;
-            if (up_out) up_out[off] = u;
-            mid_out[off] = swiglu_weighted(g, u, w);
+            flush_base = item + 1;
+        }
+        row += GU_ITEM_ROWS;
+        if (row == mid_dim) {
+            row = 0;
+            ++pair;
         }
     }
 }
@@ -181,15 +235,20 @@ __global__ void __launch_bounds__(32 * GU_MAX_WARPS, 1)
 
 constexpr int DN_ROW_BYTES = 8 * Q2K_BYTES;  // 672
 constexpr int DN_ROWS_MAX = 16;
+constexpr int DN_STAGES = DN_ROWS_MAX / 4;
+constexpr int DN_ACT_BYTES = 8 * Q8K_BYTES;  // 2336: one (token, slot) mid row as Q8_K blocks
 
-struct DnRowS {
-    uint4 qs;
-    uint2 sc;
-    uint32_t dd;
-};
+// 16 quant bytes (piece c = 2h + half: sub-blocks 8h + half + {0,2,4,6}) of block blk of a staged Q2_K row
+template <int LAYOUT>
+__device__ __forceinline__ uint4 dn_smem_piece(const uint8_t *row, int blk, int c)
+{
+    const uint8_t *p = q2k_qs_ptr<LAYOUT>(row, 8, blk) + 16 * c;
+    if (LAYOUT == DSMOE_LAYOUT_ROWSOA) return *reinterpret_cast<const uint4 *>(p);
+    return ld_16B_align4(p);
+}
 
 template <int LAYOUT, bool SUM>
-__global__ void __launch_bounds__(256) down_m8_tma_kernel(const uint8_t *__restrict__ down_base,
+__global__ void __launch_bounds__(256, 2) down_m8_tma_kernel(const uint8_t *__restrict__ down_base,
                                                            const uint8_t *__restrict__ midq,
                                                            const int32_t *__restrict__ selected, float *__restrict__ out,
                                                            uint64_t expert_bytes, uint32_t out_dim, uint32_t k, int ieee_i,
@@ -199,8 +258,9 @@ __global__ void __launch_bounds__(256) down_m8_tma_kernel(const uint8_t *__restr
     const bool ieee = ieee_i != 0;
     const int lane = threadIdx.x & 31, slot = threadIdx.x >> 5;
     uint8_t *wbuf = smem + (size_t)slot * rows_per_cta * DN_ROW_BYTES;
-    float *s_part = reinterpret_cast<float *>(smem + (size_t)k * rows_per_cta * DN_ROW_BYTES);
-    uint64_t *bar = reinterpret_cast<uint64_t *>(s_part + MAX_K * DN_ROWS_MAX) + slot;
+    uint8_t *abuf = smem + (size_t)k * rows_per_cta * DN_ROW_BYTES + (size_t)slot * DN_ACT_BYTES;  // this pair's Q8_K row
+    float *s_part = reinterpret_cast<float *>(smem + (size_t)k * (rows_per_cta * DN_ROW_BYTES + DN_ACT_BYTES));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(s_part + MAX_K * DN_ROWS_MAX) + slot * DN_STAGES;
 
     const uint32_t tok = blockIdx.y, pair = tok * k + slot;
     const uint32_t row_begin = blockIdx.x * rows_per_cta;
@@ -208,47 +268,80 @@ __global__ void __launch_bounds__(256) down_m8_tma_kernel(const uint8_t *__restr
     if (lane == 0) {
         const int32_t e = selected[pair];
         const uint64_t ex = e < 0 ? 0u : (uint64_t)e;
-        mbar_init(bar, 1);
+        const uint8_t *src = down_base + ex * expert_bytes + (uint64_t)row_begin * DN_ROW_BYTES;
+#pragma unroll
+        for (int s = 0; s < DN_STAGES; ++s) mbar_init(&bars[s], 1);
         fence_async_smem();
-        mbar_expect_tx(bar, n_rows * DN_ROW_BYTES);
-        bulk_g2s(wbuf, down_base + ex * expert_bytes + (uint64_t)row_begin * DN_ROW_BYTES, n_rows * DN_ROW_BYTES, bar);
-    }
-    const int b = lane >> 2, c = lane & 3;
-    int q[4][4];
-    uint32_t bs01, bs23;
-    float yd;
-    q2k_load_acts(midq + ((size_t)pair * 8 + b) * Q8K_BYTES, c, q, bs01, bs23, yd);
-    __syncwarp();  // the barrier lane 0 initialised is now visible to the whole warp
-    const bool ok = mbar_wait_bounded(bar, 0, status);
-
-    for (uint32_t r = 0; ok && r < n_rows; ++r) {
-        const uint8_t *rowp = wbuf + r * DN_ROW_BYTES;
-        DnRowS d;
-        const uint8_t *qp = q2k_qs_ptr<LAYOUT>(rowp, 8, b) + 16 * c;
-        const uint8_t *sp = q2k_scales_ptr<LAYOUT>(rowp, 8, b) + 8 * (c >> 1);
-        if (LAYOUT == DSMOE_LAYOUT_ROWSOA) {
-            d.qs = *reinterpret_cast<const uint4 *>(qp);
-            d.sc = *reinterpret_cast<const uint2 *>(sp);
-        } else {
-            d.qs = ld_16B_align4(qp);
-            d.sc = make_uint2(ld_u32(sp), ld_u32(sp + 4));
+        // everything is requested up front, four rows per mbarrier, so that the first rows can be consumed while
+        // the later ones are still arriving
+        for (uint32_t s = 0; 4 * s < n_rows; ++s) {
+            const uint32_t rows = min(4u, n_rows - 4 * s), bytes = rows * DN_ROW_BYTES + (s == 0 ? DN_ACT_BYTES : 0);
+            mbar_expect_tx(&bars[s], bytes);
+            if (s == 0) bulk_g2s(abuf, midq + (size_t)pair * DN_ACT_BYTES, DN_ACT_BYTES, &bars[0]);
+            bulk_g2s(wbuf + 4 * s * DN_ROW_BYTES, src + (uint64_t)4 * s * DN_ROW_BYTES, rows * DN_ROW_BYTES, &bars[s]);
         }
-        d.dd = ld_u32(q2k_dd_ptr<LAYOUT>(rowp, 8, b));
+    }
+    // lane = (row of the current group of four, block): the block's 256 activations stay in registers, 16-byte
+    // pieces in rotated order (piece (j + rot) & 3 at step j), bsums likewise
+    const int sub = lane >> 3, blk = lane & 7, rot = blk >> 1;
+    __syncwarp();  // the barrier lane 0 initialised is now visible to the whole warp
+    bool ok = mbar_wait_bounded(&bars[0], 0, status);
+    const uint8_t *mq = abuf + blk * Q8K_BYTES;
+    const float yd = *reinterpret_cast<const float *>(mq);
+    int q[4][4][4];      // [step j][sub-block jj][word]
+    uint32_t bs[4][2];   // [step j]: bsums of sub-blocks (jj = 0,1) and (2,3) as int16 pairs
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int c = (j + rot) & 3, h = c >> 1, half = c & 1;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+            const int *pq = reinterpret_cast<const int *>(mq + 4 + 128 * h + 32 * jj + 16 * half);
+#pragma unroll
+            for (int w = 0; w < 4; ++w) q[j][jj][w] = pq[w];
+        }
+        const uint16_t *pb = reinterpret_cast<const uint16_t *>(mq + 260) + 8 * h + half;
+        bs[j][0] = (uint32_t)pb[0] | ((uint32_t)pb[2] << 16);
+        bs[j][1] = (uint32_t)pb[4] | ((uint32_t)pb[6] << 16);
+    }
 
-        uint32_t sc4 = __byte_perm(d.sc.x, d.sc.y, (c & 1) ? 0x7531u : 0x6420u);
-        int isum, summs;
-        q2k_quarter_dot(d.qs, q, sc4, bs01, bs23, isum, summs);
-        isum += __shfl_xor_sync(FULL, isum, 1);
-        summs += __shfl_xor_sync(FULL, summs, 1);
-        isum += __shfl_xor_sync(FULL, isum, 2);
-        summs += __shfl_xor_sync(FULL, summs, 2);
-        float dall = __fmul_rn(yd, f16_bits_to_f32(d.dd & 0xFFFFu, ieee));
-        float dmin = __fmul_rn(yd, f16_bits_to_f32(d.dd >> 16, ieee));
+    for (uint32_t r0 = 0; ok && r0 < n_rows; r0 += 4) {
+        if (r0 > 0 && !(ok = mbar_wait_bounded(&bars[r0 >> 2], 0, status))) break;
+        const uint32_t r = r0 + sub;
+        const bool valid = r < n_rows;
+        const uint8_t *rowp = wbuf + (valid ? r : r0) * DN_ROW_BYTES;
+        // the 16 scale bytes of the block
+        uint32_t sc[4];
+        {
+            const uint8_t *sp = q2k_scales_ptr<LAYOUT>(rowp, 8, blk);
+            if (LAYOUT == DSMOE_LAYOUT_ROWSOA) {
+                const uint4 v = *reinterpret_cast<const uint4 *>(sp);
+                sc[0] = v.x, sc[1] = v.y, sc[2] = v.z, sc[3] = v.w;
+            } else {
+                sc[0] = ld_u32(sp), sc[1] = ld_u32(sp + 4), sc[2] = ld_u32(sp + 8), sc[3] = ld_u32(sp + 12);
+            }
+        }
+        const uint32_t dd = ld_u32(q2k_dd_ptr<LAYOUT>(rowp, 8, blk));
+        int isum = 0, summs = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = (j + rot) & 3;
+            const uint4 qs = dn_smem_piece<LAYOUT>(rowp, blk, c);
+            const uint32_t lo_w = (c & 2) ? sc[2] : sc[0], hi_w = (c & 2) ? sc[3] : sc[1];
+            const uint32_t sc4 = __byte_perm(lo_w, hi_w, (c & 1) ? 0x7531u : 0x6420u);
+            int is, sm;
+            q2k_quarter_dot(qs, q[j], sc4, bs[j][0], bs[j][1], is, sm);
+            isum += is;
+            summs += sm;
+        }
+        // dall * isum - dmin * summs (engine/src/kernels/quantize.rs:856-900); one block per lane = the reference's
+        // lane partial, then its butterfly xor 4, 2, 1 over the quarter-warp
+        const float dall = __fmul_rn(yd, f16_bits_to_f32(dd & 0xFFFFu, ieee));
+        const float dmin = __fmul_rn(yd, f16_bits_to_f32(dd >> 16, ieee));
         float a = __fadd_rn(0.0f, __fsub_rn(__fmul_rn(dall, (float)isum), __fmul_rn(dmin, (float)summs)));
-        a = __fadd_rn(a, __shfl_xor_sync(FULL, a, 16));
-        a = __fadd_rn(a, __shfl_xor_sync(FULL, a, 8));
         a = __fadd_rn(a, __shfl_xor_sync(FULL, a, 4));
-        if (lane == 0) {
+        a = __fadd_rn(a, __shfl_xor_sync(FULL, a, 2));
+        a = __fadd_rn(a, __shfl_xor_sync(FULL, a, 1));
+        if (blk == 0 && valid) {
             if (SUM) s_part[slot * DN_ROWS_MAX + r] = a;
             else out[(size_t)pair * out_dim + row_begin + r] = a;
         }
@@ -282,31 +375,28 @@ static int sm_count()
 
 bool gate_up_tma_eligible(const GateUpArgs &a)
 {
-    return a.xq_blocks == 16 && a.row_bytes == (uint64_t)GU_ROW_BYTES &&
+    return a.xq_blocks == 16 && a.row_bytes == (uint64_t)GU_ROW_BYTES && a.mid_dim % GU_ITEM_ROWS == 0 &&
            (((uintptr_t)a.gate_base | (uintptr_t)a.up_base | a.expert_bytes) & 15) == 0;
 }
 
 template <int LAYOUT>
 static void launch_gu_tma(cudaStream_t st, const GateUpArgs &a, int *status)
 {
-    const uint32_t n_items = a.n_tokens * a.k * a.mid_dim;
+    const uint32_t n_items = a.n_tokens * a.k * (a.mid_dim / GU_ITEM_ROWS);
     const int sms = sm_count();
-    // warps per CTA: the count in 8..16 that leaves the fewest idle warp-slots in the last round of items
-    int best_w = 16;
-    double best_eff = 0.0;
-    for (int w = 16; w >= 8; --w) {
+    // warps per CTA: as many as fit, unless a smaller count wastes clearly fewer warp-slots in the last round of items
+    auto eff_of = [&](int w) {
         const uint32_t nw = (uint32_t)sms * w, chunk = (n_items + nw - 1) / nw;
-        const double eff = (double)n_items / ((double)chunk * nw);
-        if (eff > best_eff + 1e-9) {
-            best_eff = eff;
-            best_w = w;
-        }
-    }
-    const size_t smem = GU_TABLE_BYTES + (size_t)best_w * GU_STAGES * GU_STAGE_BYTES + (size_t)best_w * GU_STAGES * 8;
+        return (double)n_items / ((double)chunk * nw);
+    };
+    int best_w = GU_MAX_WARPS;
+    for (int w = GU_MAX_WARPS - 1; w >= 8; --w)
+        if (eff_of(w) > eff_of(best_w) + 0.08) best_w = w;
+    const size_t smem = GU_TABLE_BYTES + (size_t)best_w * GU_STAGES * GU_ITEM_BYTES + (size_t)best_w * GU_STAGES * 8;
     static bool attr_set[2] = {false, false};
     if (!attr_set[LAYOUT]) {
         cudaFuncSetAttribute(gate_up_x16_tma_kernel<LAYOUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             GU_TABLE_BYTES + GU_MAX_WARPS * GU_STAGES * (GU_STAGE_BYTES + 8));
+                             GU_TABLE_BYTES + GU_MAX_WARPS * GU_STAGES * (GU_ITEM_BYTES + 8));
         attr_set[LAYOUT] = true;
     }
     const uint32_t want = (n_items + best_w - 1) / best_w;
@@ -327,19 +417,19 @@ int launch_gate_up_mid_tma(cudaStream_t st, const GateUpArgs &a, int *status)
 bool down_tma_eligible(const DownArgs &a)
 {
     return a.midq_blocks == 8 && a.row_bytes == (uint64_t)DN_ROW_BYTES &&
-           (((uintptr_t)a.down_base | a.expert_bytes) & 15) == 0;
+           (((uintptr_t)a.down_base | (uintptr_t)a.midq | a.expert_bytes) & 15) == 0;
 }
 
 template <int LAYOUT, bool SUM>
 static void launch_dn_tma(cudaStream_t st, const DownArgs &a, int *status)
 {
     // small batches: short chunks so that one wave of CTAs covers all rows; large batches: longer chunks
-    const int rows_per_cta = a.n_tokens <= 2 ? 6 : (a.n_tokens <= 16 ? 8 : 16);
-    const size_t smem = (size_t)a.k * rows_per_cta * DN_ROW_BYTES + MAX_K * DN_ROWS_MAX * 4 + MAX_K * 8;
+    const int rows_per_cta = 16;  // 256 CTAs per token at out_dim 4096: one wave at two CTAs per SM
+    const size_t smem = (size_t)a.k * (rows_per_cta * DN_ROW_BYTES + DN_ACT_BYTES) + MAX_K * DN_ROWS_MAX * 4 + MAX_K * DN_STAGES * 8;
     static bool attr_set = false;
     if (!attr_set) {
         cudaFuncSetAttribute(down_m8_tma_kernel<LAYOUT, SUM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             MAX_K * DN_ROWS_MAX * DN_ROW_BYTES + MAX_K * DN_ROWS_MAX * 4 + MAX_K * 8);
+                             MAX_K * (DN_ROWS_MAX * DN_ROW_BYTES + DN_ACT_BYTES) + MAX_K * DN_ROWS_MAX * 4 + MAX_K * DN_STAGES * 8);
         attr_set = true;
     }
     dim3 grid((a.out_dim + rows_per_cta - 1) / rows_per_cta, a.n_tokens);

@@ -14,6 +14,11 @@ void launch_router_select(cudaStream_t st, const float *logits, const float *bia
                           uint32_t hash_rows, uint32_t n_tokens, int has_bias, int hash_mode, int k, int n_expert,
                           float route_scale);
 
+// Router (no bias / hash) and Q8_K of x in one launch; n_expert <= 256.
+void launch_router_q8k_fused(cudaStream_t st, const float *logits, const float *x, float *probs, int32_t *selected,
+                             float *weights, uint8_t *xq, uint32_t n_tokens, int k, int n_expert, uint32_t n_embd,
+                             float route_scale);
+
 void launch_dequant_iq2xxs(cudaStream_t st, const uint8_t *blocks, uint64_t n_blocks, float *out, int ieee);
 void launch_dequant_q2k(cudaStream_t st, const uint8_t *blocks, uint64_t n_blocks, float *out, int ieee);
 void launch_relayout_iq2xxs(cudaStream_t st, const uint8_t *src, uint8_t *dst, uint64_t n_rows, uint32_t xb, int inverse);

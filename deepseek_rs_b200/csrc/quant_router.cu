@@ -12,13 +12,9 @@ namespace dsmoe {
 // maxima the element with the smallest bit-reversed index wins; using (|x|, bit-reversed index) as the reduction key
 // reproduces that choice (and hence the sign of d) in any reduction order.
 // ---------------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) q8k_quantize_kernel(const float *__restrict__ x, uint8_t *__restrict__ out,
-                                                            uint64_t n_blocks_total)
+__device__ __forceinline__ void q8k_quantize_block(const float *__restrict__ xb, uint8_t *__restrict__ yb, int lane)
 {
-    const int lane = threadIdx.x & 31;
-    const uint64_t blk = (uint64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (blk >= n_blocks_total) return;
-    const float4 *src = reinterpret_cast<const float4 *>(x + blk * QK_K + 8 * lane);
+    const float4 *src = reinterpret_cast<const float4 *>(xb + 8 * lane);
     float4 v0 = src[0], v1 = src[1];
     float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
 
@@ -46,7 +42,6 @@ __global__ void __launch_bounds__(256) q8k_quantize_kernel(const float *__restri
         }
     }
 
-    uint8_t *yb = out + blk * Q8K_BYTES;
     uint32_t *qdst = reinterpret_cast<uint32_t *>(yb + 4 + 8 * lane);
     if (!(best_abs > 0.0f)) {  // amax == 0 (or no finite maximum): all-zero block
         if (lane == 0) *reinterpret_cast<float *>(yb) = 0.0f;
@@ -73,6 +68,15 @@ __global__ void __launch_bounds__(256) q8k_quantize_kernel(const float *__restri
               ((uint32_t)(q[7] & 255) << 24);
     s += __shfl_xor_sync(FULL, s, 1);  // bsums cover 16 elements = two lanes
     if ((lane & 1) == 0) reinterpret_cast<int16_t *>(yb + 260)[lane >> 1] = (int16_t)s;
+}
+
+__global__ void __launch_bounds__(256) q8k_quantize_kernel(const float *__restrict__ x, uint8_t *__restrict__ out,
+                                                            uint64_t n_blocks_total)
+{
+    const int lane = threadIdx.x & 31;
+    const uint64_t blk = (uint64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (blk >= n_blocks_total) return;
+    q8k_quantize_block(x + blk * QK_K, out + blk * Q8K_BYTES, lane);
 }
 
 void launch_q8k_quantize(cudaStream_t st, const float *x, uint8_t *out, uint32_t in_dim, uint32_t n_rows)
@@ -192,6 +196,87 @@ void launch_router_select(cudaStream_t st, const float *logits, const float *bia
     router_select_kernel<<<(n_tokens + 3) / 4, 128, 0, st>>>(logits, bias, hash, tokens, probs, selected, weights,
                                                              token_scalar, hash_rows, n_tokens, has_bias, hash_mode, k,
                                                              n_expert, route_scale);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Router and Q8_K of the same token in one launch (no bias, no hash table): one 256-thread CTA per token, one expert
+// per thread, so the double-precision exp/ln of all experts run side by side; the eight warps then quantise the
+// token's hidden row. Same results as router_select_kernel + q8k_quantize_kernel.
+// Selection key: order-preserving integer image of the score in the high word, inverted expert index in the low
+// word, so an integer maximum picks the highest score and, among equals, the lowest index; key 0 = not selectable.
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned long long router_key(float score, int e)
+{
+    if (!(score > -INFINITY)) return 0ull;
+    uint32_t b = __float_as_uint(score);
+    b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+    return ((unsigned long long)b << 32) | (uint32_t)(0xFFFFFFFFu - (uint32_t)e);
+}
+
+__global__ void __launch_bounds__(256) router_q8k_fused_kernel(const float *__restrict__ logits,
+                                                                const float *__restrict__ x, float *__restrict__ probs,
+                                                                int32_t *__restrict__ selected, float *__restrict__ weights,
+                                                                uint8_t *__restrict__ xq, int k, int n_expert,
+                                                                uint32_t n_embd, float route_scale)
+{
+    __shared__ unsigned long long s_warp_best[8];
+    __shared__ float s_w[MAX_K];
+    __shared__ int s_sel[MAX_K];
+    const uint32_t t = blockIdx.x;
+    const int e = threadIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float p = 0.0f;
+    unsigned long long key = 0ull;
+    if (e < n_expert) {
+        p = sqrtf(softplus_ref(logits[(size_t)t * n_expert + e]));
+        probs[(size_t)t * n_expert + e] = p;
+        key = router_key(p, e);
+    }
+    for (int r = 0; r < k; ++r) {
+        unsigned long long best = key;
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) {
+            unsigned long long o = __shfl_xor_sync(FULL, best, m);
+            best = o > best ? o : best;
+        }
+        if (lane == 0) s_warp_best[warp] = best;
+        __syncthreads();
+        unsigned long long top = s_warp_best[0];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) top = s_warp_best[w] > top ? s_warp_best[w] : top;
+        if (top == 0ull) {
+            if (e == 0) {
+                s_sel[r] = -1;
+                s_w[r] = 0.0f;
+            }
+        } else if (key == top) {
+            s_sel[r] = e;
+            s_w[r] = p;
+            key = 0ull;  // taken
+        }
+        __syncthreads();
+    }
+    if (e == 0) {
+        float sum = 0.0f;
+        for (int j = 0; j < k; ++j) sum = __fadd_rn(sum, s_w[j]);
+        if (sum < 6.103515625e-5f) sum = 6.103515625e-5f;
+        const float div = __fdiv_rn(sum, route_scale);
+        for (int j = 0; j < k; ++j) {
+            selected[(size_t)t * k + j] = s_sel[j];
+            weights[(size_t)t * k + j] = __fdiv_rn(s_w[j], div);
+        }
+    }
+    const uint32_t n_blocks = n_embd / QK_K;
+    for (uint32_t b = warp; b < n_blocks; b += 8)
+        q8k_quantize_block(x + (size_t)t * n_embd + (size_t)b * QK_K, xq + ((size_t)t * n_blocks + b) * Q8K_BYTES, lane);
+}
+
+void launch_router_q8k_fused(cudaStream_t st, const float *logits, const float *x, float *probs, int32_t *selected,
+                             float *weights, uint8_t *xq, uint32_t n_tokens, int k, int n_expert, uint32_t n_embd,
+                             float route_scale)
+{
+    if (n_tokens == 0) return;
+    router_q8k_fused_kernel<<<n_tokens, 256, 0, st>>>(logits, x, probs, selected, weights, xq, k, n_expert, n_embd,
+                                                      route_scale);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
