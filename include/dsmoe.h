@@ -172,6 +172,33 @@ DSMOE_API int dsmoe_moe_forward_host(dsmoe_handle *h, uint32_t layer, const floa
                                      uint32_t n_tokens, float *out_host, int32_t *selected_out_host,
                                      float *weights_out_host);
 
+/* ------------------------------------------------------------------------------------------------------------ */
+/* For callers that cannot allocate device memory                                                                 */
+/* ------------------------------------------------------------------------------------------------------------ */
+
+#define DSMOE_NOALLOC_MAX_TOKENS 8
+
+/* No counterpart in the reference (its Session owns cudaMalloc'd scratch, engine/src/session.rs:224-271).
+ *
+ * The routed-expert step of dsmoe_moe_forward without a handle and without any device allocation, for hosts where
+ * cudaMalloc is not an option: an engine that has already given the whole device to its own arena, a plugin inside a
+ * process whose allocator forbids side allocations, a real-time thread that must not take the driver's allocation
+ * lock. The intermediates (probabilities, Q8_K blocks, the f32 mid rows) live in a fixed array of about 0.55 MB inside
+ * the library's device image; every GPU that loads the library holds that array until the process exits.
+ *
+ * Fixed to the reference model: n_embd 4096, n_ff 2048, 256 experts, top-6, clamp 10, weights renormalised to 1.5,
+ * f16 subnormals flushed. n_tokens above DSMOE_NOALLOC_MAX_TOKENS returns DSMOE_ERR_BOUNDS. gate / up / down are one
+ * layer's expert tensors in `layout`; the other operands are as in dsmoe_moe_forward; selected_out / weights_out may
+ * be NULL. Runs on the CURRENT device, asynchronously on `stream`.
+ *
+ * The first call on a device looks the array's address up (cudaGetSymbolAddress); make that first call outside any
+ * stream capture. All calls on a device share the one array, which keeps the previous call's contents: the call
+ * clears the one word that must start at zero and overwrites the rest before reading it, but two calls whose kernels
+ * overlap on the GPU (different streams, or different host threads) race on it — serialise them. */
+DSMOE_API int dsmoe_moe_forward_noalloc(dsmoe_stream stream, const uint8_t *gate, const uint8_t *up,
+                                        const uint8_t *down, int layout, const float *x, const float *logits,
+                                        uint32_t n_tokens, float *out, int32_t *selected_out, float *weights_out);
+
 #ifdef __cplusplus
 }
 #endif
