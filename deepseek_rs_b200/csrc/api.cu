@@ -31,6 +31,10 @@ struct dsmoe_handle {
     float *d_x, *d_logits, *d_out;
     int *d_status;  // device status word: 0, or the first device-side error code (a bounded wait that expired)
     bool use_tma;   // stage packed rows with bulk asynchronous copies where the shapes allow (default on)
+    // batched (tcgen05 grouped GEMM) path: used by the tier-2 call from prefill_min_tokens tokens upwards
+    uint8_t *pf_scratch;
+    PrefillScratch pf_lay;
+    uint32_t prefill_min_tokens;
 };
 
 namespace {
@@ -131,6 +135,13 @@ int dsmoe_create(const dsmoe_config *cfg, int device, dsmoe_handle **out)
     ok = ok && dev_alloc(&h->d_out, T * cfg->n_embd) == cudaSuccess;
     ok = ok && cudaStreamCreateWithFlags(&h->hstream, cudaStreamNonBlocking) == cudaSuccess;
     ok = ok && dev_alloc(&h->d_status, 1) == cudaSuccess && cudaMemset(h->d_status, 0, sizeof(int)) == cudaSuccess;
+    {
+        const size_t pf_bytes = prefill_scratch_bytes(cfg->max_tokens, cfg->n_expert_used, cfg->n_expert, cfg->n_embd,
+                                                      cfg->n_ff, &h->pf_lay);
+        ok = ok && dev_alloc(&h->pf_scratch, pf_bytes) == cudaSuccess;
+        const char *pm = getenv("DSMOE_PREFILL_MIN_TOKENS");
+        h->prefill_min_tokens = pm ? (uint32_t)strtoul(pm, nullptr, 10) : 48u;
+    }
     const char *no_tma = getenv("DSMOE_DISABLE_TMA");
     h->use_tma = !(no_tma && no_tma[0] == '1');
     if (!ok) {
@@ -157,6 +168,7 @@ int dsmoe_destroy(dsmoe_handle *h)
     cudaFree(h->d_logits);
     cudaFree(h->d_out);
     cudaFree(h->d_status);
+    cudaFree(h->pf_scratch);
     delete[] h->layers;
     delete h;
     return DSMOE_OK;
@@ -367,6 +379,13 @@ int dsmoe_moe_forward(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, cons
                              (int)c.n_expert, c.route_scale);
         launch_q8k_quantize(st, x, h->xq, c.n_embd, n_tokens);
         n = 2;
+    }
+    if (n_tokens >= h->prefill_min_tokens && prefill_eligible(c.n_embd, c.n_ff, ly.gate, ly.up, ly.down, ly.layout)) {
+        PrefillArgs p = {ly.gate, ly.up, ly.down, h->xq, sel, wts, h->mid, h->midq, out, h->pf_scratch, h->pf_lay,
+                         n_tokens, k, c.n_expert, c.n_embd, c.n_ff, c.swiglu_clamp, ly.layout, (int)c.f16_ieee,
+                         h->d_status};
+        n += launch_prefill_experts(st, p);
+        return check_launch(h, "moe_forward (batched)", n);
     }
     GateUpArgs g = {ly.gate, ly.up, h->xq, sel, wts, nullptr, nullptr, h->mid, (uint64_t)c.n_ff * xb * IQ2XXS_BYTES,
                     (uint64_t)xb * IQ2XXS_BYTES, xb, c.n_ff, k, n_tokens, c.swiglu_clamp, ly.layout, (int)c.f16_ieee};

@@ -55,4 +55,31 @@ int launch_gate_up_mid_tma(cudaStream_t st, const GateUpArgs &a, int *status);
 bool down_tma_eligible(const DownArgs &a);
 int launch_down_tma(cudaStream_t st, const DownArgs &a, int *status);
 
+// Batched path (tcgen05 grouped GEMM). Scratch is one device buffer carved up by prefill_scratch_bytes().
+struct PrefillScratch {
+    uint32_t r_cap, tile_cap;
+    size_t counts, offsets, sorted, tile_expert, tile_start, tile_rows, tile_boff, plan, bx, sx, bm, sm, bs, down_pair;
+};
+size_t prefill_scratch_bytes(uint32_t max_tokens, uint32_t k, uint32_t n_expert, uint32_t n_embd, uint32_t n_ff,
+                             PrefillScratch *lay);
+bool prefill_eligible(uint32_t n_embd, uint32_t n_ff, const uint8_t *gate, const uint8_t *up, const uint8_t *down,
+                      int layout);
+struct PrefillArgs {
+    const uint8_t *gate, *up, *down;   // one layer's expert tensors
+    const uint8_t *xq;                 // Q8_K of x, [n_tokens][n_embd/256]
+    const int32_t *selected;           // [n_tokens][k]
+    const float *weights;              // [n_tokens][k]
+    float *mid;                        // [n_tokens*k][n_ff] f32 (scratch, also an output)
+    uint8_t *midq;                     // [n_tokens*k][n_ff/256] Q8_K (scratch)
+    float *out;                        // [n_tokens][n_embd]
+    uint8_t *scratch;
+    PrefillScratch lay;
+    uint32_t n_tokens, k, n_expert, n_embd, n_ff;
+    float clamp;
+    int layout, ieee;
+    int *status;
+};
+// Everything after the router and the Q8_K of x. Returns the number of kernels launched.
+int launch_prefill_experts(cudaStream_t st, const PrefillArgs &p);
+
 }  // namespace dsmoe

@@ -1,0 +1,639 @@
+// Batched (prefill) routed experts: pairs grouped by expert, then one grouped GEMM per projection on the tcgen05
+// tensor cores.
+//
+// The reference runs the expert FFN one token at a time even in prefill (engine/src/session.rs:795-895); its
+// sorted-pair and tile-list helpers (engine/src/kernels/moe.rs:299-362, 547-596) were written for a grouped GEMM that
+// was never added. This file is that GEMM. To stay within rel 1e-3 of the reference, the contraction consumes what
+// the reference's integer block dots consume: the Q8_K int8 activations and the integer weight codes
+// (IQ2_XXS: ls * (+/-g), |code| <= 1333; Q2_K: sc_lo * q <= 45), both exact in f16, accumulated in f32 in TMEM per
+// 256-wide superblock and scaled by d_w * d_x when the accumulator is drained — the same factorisation as
+// engine/src/kernels/quantize.rs:811 and :900.
+//
+// Pipeline (all on the caller's stream, no host synchronisation):
+//   1 pair_count / pair_plan / pair_place   stable counting sort of (token, slot) pairs by expert + token-tile list
+//   2 gather_acts                           Q8_K rows of each tile -> f16 operand tiles in the tensor-core layout
+//   3 grouped_gemm<IQ2>                     gate & up (64 + 64 rows per tile) -> clamp, SwiGLU, weight -> mid f32
+//   4 q8k_quantize(mid), gather_acts        as in decode
+//   5 grouped_gemm<Q2K>                     down, min-term as a second K=16 MMA -> per-pair rows
+//   6 moe_sum                               slots summed in slot order
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "launch.h"
+#include "tc05.cuh"
+
+namespace dsmoe {
+
+constexpr int PF_TN = 128;       // token rows per tile (MMA N), padded to a multiple of 16
+constexpr int PF_KS = 128;       // K elements per pipeline stage (half a superblock)
+constexpr int PF_STAGE_A = 128 * PF_KS * 2;  // 32 KB: 128 weight rows
+constexpr int PF_SBO = (PF_KS / 8) * 128;    // 2048: byte distance between 8-row groups in a stage
+
+// ---------------------------------------------------------------------------------------------------------------
+// 1. grouping: deterministic and stable (pairs of an expert keep ascending pair order), unlike the reference's
+//    atomic-cursor scatter (engine/src/kernels/moe.rs:341-362)
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ int pf_expert_of(const int32_t *selected, uint32_t p)
+{
+    const int32_t e = selected[p];
+    return e < 0 ? 0 : e;  // engine/src/kernels/moe.rs:645-648
+}
+
+// counts[e] = number of pairs routed to e. One CTA per expert.
+__global__ void __launch_bounds__(256) pf_count_kernel(const int32_t *__restrict__ selected, uint32_t n_pairs,
+                                                        uint32_t *__restrict__ counts)
+{
+    __shared__ uint32_t s_warp[8];
+    const int e = blockIdx.x;
+    uint32_t c = 0;
+    for (uint32_t p = threadIdx.x; p < n_pairs; p += 256) c += pf_expert_of(selected, p) == e;
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) c += __shfl_xor_sync(FULL, c, m);
+    if ((threadIdx.x & 31) == 0) s_warp[threadIdx.x >> 5] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t t = 0;
+        for (int w = 0; w < 8; ++w) t += s_warp[w];
+        counts[e] = t;
+    }
+}
+
+// offsets (exclusive prefix of counts) and the tile list: expert e contributes ceil(count / PF_TN) tiles.
+// plan[0] = n_tiles, plan[1] = total padded rows. One thread: 256 experts.
+__global__ void pf_plan_kernel(const uint32_t *__restrict__ counts, int n_expert, uint32_t *__restrict__ offsets,
+                               uint32_t *__restrict__ tile_expert, uint32_t *__restrict__ tile_start,
+                               uint32_t *__restrict__ tile_rows, uint32_t *__restrict__ tile_boff,
+                               uint32_t *__restrict__ plan)
+{
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    uint32_t sum = 0, nt = 0, boff = 0;
+    for (int e = 0; e < n_expert; ++e) {
+        offsets[e] = sum;
+        const uint32_t c = counts[e];
+        for (uint32_t s = 0; s < c; s += PF_TN) {
+            const uint32_t rows = min((uint32_t)PF_TN, c - s);
+            tile_expert[nt] = (uint32_t)e;
+            tile_start[nt] = sum + s;
+            tile_rows[nt] = rows;
+            tile_boff[nt] = boff;
+            boff += (rows + 15u) & ~15u;
+            ++nt;
+        }
+        sum += c;
+    }
+    offsets[n_expert] = sum;
+    tile_boff[nt] = boff;
+    plan[0] = nt;
+    plan[1] = boff;
+}
+
+// sorted[offsets[e] + rank] = pair, rank = number of earlier pairs of the same expert. One CTA per expert.
+__global__ void __launch_bounds__(256) pf_place_kernel(const int32_t *__restrict__ selected, uint32_t n_pairs,
+                                                        const uint32_t *__restrict__ offsets,
+                                                        uint32_t *__restrict__ sorted)
+{
+    __shared__ uint32_t s_warp[8];
+    __shared__ uint32_t s_base;
+    const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) s_base = offsets[e];
+    __syncthreads();
+    for (uint32_t p0 = 0; p0 < n_pairs; p0 += 256) {
+        const uint32_t p = p0 + threadIdx.x;
+        const bool hit = p < n_pairs && pf_expert_of(selected, p) == e;
+        const uint32_t ballot = __ballot_sync(FULL, hit);
+        if (lane == 0) s_warp[warp] = __popc(ballot);
+        __syncthreads();
+        uint32_t before = 0, total = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            before += w < warp ? s_warp[w] : 0u;
+            total += s_warp[w];
+        }
+        if (hit) sorted[s_base + before + __popc(ballot & ((1u << lane) - 1u))] = p;
+        __syncthreads();
+        if (threadIdx.x == 0) s_base += total;
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// 2. activation tiles. For tile t (rows16 = padded row count, boff = first padded row) the f16 operand occupies
+//    rows16 * kblocks * 512 bytes at B + boff * kblocks * 512, ordered [stage = k / 128][row / 8][k % 128 / 8][row % 8]
+//    [k % 8] so that one stage is one contiguous block in the layout the MMA descriptor describes.
+//    Scales: S[kb * r_cap + boff + row] = d of the row's Q8_K block kb. bsums (Q2_K min term) as f16:
+//    BS[(kb * r_cap + boff + row) * 16 + j], stored per tile in core-matrix order [kb][row / 8][j / 8][row % 8][j % 8].
+//    src_row(p) = p / div_k (gate/up: the token's row) or p (down: the pair's row).
+// ---------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) pf_gather_kernel(const uint8_t *__restrict__ q8k, uint32_t kblocks,
+                                                         uint32_t div_k, const uint32_t *__restrict__ sorted,
+                                                         const uint32_t *__restrict__ tile_start,
+                                                         const uint32_t *__restrict__ tile_rows,
+                                                         const uint32_t *__restrict__ tile_boff,
+                                                         const uint32_t *__restrict__ plan, uint8_t *__restrict__ B,
+                                                         float *__restrict__ S, __half *__restrict__ BS, uint32_t r_cap)
+{
+    const uint32_t n_tiles = plan[0];
+    // one warp per (tile, padded row, Q8_K block); lane l converts elements 8l..8l+7 of the block
+    const uint32_t lane = threadIdx.x & 31;
+    for (uint32_t t = blockIdx.y; t < n_tiles; t += gridDim.y) {
+        const uint32_t rows = tile_rows[t], rows16 = (rows + 15u) & ~15u, boff = tile_boff[t], start = tile_start[t];
+        const uint32_t units = rows16 * kblocks;
+        for (uint32_t u = blockIdx.x * 8 + (threadIdx.x >> 5); u < units; u += gridDim.x * 8) {
+            const uint32_t r = u / kblocks, kb = u - r * kblocks;
+            uint32_t w0 = 0, w1 = 0;
+            float d = 0.0f;
+            uint32_t bsum = 0;
+            if (r < rows) {
+                const uint8_t *blk = q8k + ((size_t)(sorted[start + r] / div_k) * kblocks + kb) * Q8K_BYTES;
+                const uint32_t *qs = reinterpret_cast<const uint32_t *>(blk + 4);
+                w0 = qs[2 * lane];
+                w1 = qs[2 * lane + 1];
+                d = *reinterpret_cast<const float *>(blk);
+                if (lane < 16) bsum = reinterpret_cast<const uint16_t *>(blk + 260)[lane];
+            }
+            // int8 -> f16 exactly: byte ^ 0x80 is the value + 128; 0x6400 | b is 1024 + b as f16
+            w0 ^= 0x80808080u;
+            w1 ^= 0x80808080u;
+            const __half2 off = __floats2half2_rn(1152.0f, 1152.0f);
+            uint32_t h[4] = {__byte_perm(w0, 0x64646464u, 0x4140u), __byte_perm(w0, 0x64646464u, 0x4342u),
+                             __byte_perm(w1, 0x64646464u, 0x4140u), __byte_perm(w1, 0x64646464u, 0x4342u)};
+            uint4 o;
+            uint32_t *op = reinterpret_cast<uint32_t *>(&o);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                __half2 v = __hsub2(*reinterpret_cast<__half2 *>(&h[i]), off);
+                op[i] = *reinterpret_cast<uint32_t *>(&v);
+            }
+            // element k = 256 kb + 8 lane: stage 2 kb + lane / 16, core column lane % 16
+            const size_t tile_base = (size_t)boff * kblocks * 512;
+            const size_t off_b = tile_base + (size_t)(2 * kb + (lane >> 4)) * rows16 * 256 + (size_t)(r >> 3) * PF_SBO +
+                                 (lane & 15) * 128 + (r & 7) * 16;
+            *reinterpret_cast<uint4 *>(B + off_b) = o;
+            if (lane == 0) S[(size_t)kb * r_cap + boff + r] = d;
+            if (BS && lane < 16) {
+                const size_t bs_tile = ((size_t)kb * r_cap + boff) * 16;
+                BS[bs_tile + (size_t)(r >> 3) * 128 + (lane >> 3) * 64 + (r & 7) * 8 + (lane & 7)] =
+                    __short2half_rn((short)(int16_t)(uint16_t)bsum);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// 3 / 5. grouped GEMM on tcgen05
+//
+// One persistent CTA per SM (256 threads) walks items = (token tile, M tile). D (128 x N f32, N = padded token rows)
+// lives in TMEM, two buffers so that the accumulator of superblock j is drained (tcgen05.ld -> scale by d_w * d_x ->
+// add to 64 f32 registers per thread) while the MMAs of superblock j+1 run. A stage is half a superblock (K = 128):
+//   all threads  decode 128 weight rows x 128 K into shared memory as exact f16 integers (the producer side),
+//   thread 0     bulk-copies the matching activation block (already f16, already in operand layout) onto an mbarrier,
+//                then issues eight K=16 MMAs and commits them to the stage's second mbarrier,
+//   all threads  drain the previous superblock.
+// IQ2_XXS tile rows: 0-63 gate rows, 64-127 the same rows of up, so that SwiGLU meets both halves in one tile.
+// Q2_K: the min term -dmin * d_x * sum_j bsums[j] * sc_hi[j] is a second accumulator fed by one K=16 MMA per
+// superblock (A = sc_hi, B = bsums, both exact in f16).
+// Every wait is bounded; on expiry all threads leave through the common exit that frees TMEM.
+// ---------------------------------------------------------------------------------------------------------------
+struct PfGemmArgs {
+    const uint8_t *w0, *w1;  // IQ2: gate, up tensors; Q2K: down tensor (w1 unused)
+    uint64_t expert_bytes;
+    const uint8_t *B;        // f16 activation tiles
+    const float *S;          // [kblocks][r_cap] Q8_K scales
+    const __half *BS;        // Q2K: bsums tiles
+    uint32_t r_cap;
+    const uint32_t *sorted, *tile_expert, *tile_start, *tile_rows, *tile_boff, *plan;
+    const float *weights;    // IQ2: router weight per pair
+    float *out;              // IQ2: mid [pair][out_dim]; Q2K: per-pair down rows [pair][out_dim]
+    uint32_t out_dim, kblocks;
+    float clamp;
+    int ieee, layout;
+    int *status;
+};
+
+constexpr int PF_SMEM_A = 0;                          // 2 x 32 KB
+constexpr int PF_SMEM_B = 2 * PF_STAGE_A;             // 2 x 32 KB
+constexpr int PF_SMEM_LUT = PF_SMEM_B + 2 * PF_STAGE_A;        // 4 KB codebook (f16) + 2 KB signs (f16)
+constexpr int PF_SMEM_A2 = PF_SMEM_LUT + 6144;        // 2 x 4 KB: sc_hi tile (Q2K), one per TMEM buffer
+constexpr int PF_SMEM_B2 = PF_SMEM_A2 + 8192;         // 2 x 4 KB: bsums tile (Q2K)
+constexpr int PF_SMEM_S = PF_SMEM_B2 + 8192;          // 16 x 128 f32 scales
+constexpr int PF_SMEM_BAR = PF_SMEM_S + 16 * PF_TN * 4;
+constexpr int PF_SMEM_TOTAL = PF_SMEM_BAR + 64;
+constexpr int PF_XSTRIDE = 129;                       // f32 stride of the epilogue exchange buffer (aliases A and B)
+static_assert(128 * PF_XSTRIDE * 4 <= PF_SMEM_LUT, "exchange buffer must fit in the A and B stages");
+
+enum { PF_IQ2 = 0, PF_Q2K = 1 };
+
+// 8 unsigned bytes (two words) -> 8 exact f16 integers; 0x6400 | b is 1024 + b
+__device__ __forceinline__ uint4 pf_bytes_to_f16x8(uint32_t lo, uint32_t hi)
+{
+    const __half2 off = __floats2half2_rn(1024.0f, 1024.0f);
+    uint32_t h[4] = {__byte_perm(lo, 0x64646464u, 0x4140u), __byte_perm(lo, 0x64646464u, 0x4342u),
+                     __byte_perm(hi, 0x64646464u, 0x4140u), __byte_perm(hi, 0x64646464u, 0x4342u)};
+    uint4 o;
+    uint32_t *op = reinterpret_cast<uint32_t *>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __half2 v = __hsub2(*reinterpret_cast<__half2 *>(&h[i]), off);
+        op[i] = *reinterpret_cast<uint32_t *>(&v);
+    }
+    return o;
+}
+
+__device__ __forceinline__ uint32_t pf_hmul2(uint32_t a, uint32_t b)
+{
+    __half2 r = __hmul2(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b));
+    return *reinterpret_cast<uint32_t *>(&r);
+}
+
+// packed bytes of one (row, stage, quarter): IQ2: one 32-weight group (aux0, aux1); Q2K: 8 quant bytes
+template <int KIND>
+__device__ __forceinline__ uint2 pf_load_packed(const uint8_t *row, int layout, uint32_t kb, uint32_t half, uint32_t c)
+{
+    if (KIND == PF_IQ2) {
+        if (layout == DSMOE_LAYOUT_ROWSOA) return *reinterpret_cast<const uint2 *>(row + 32 + 64 * kb + 8 * (4 * half + c));
+        const uint16_t *p = reinterpret_cast<const uint16_t *>(row + IQ2XXS_BYTES * kb + 2 + 8 * (4 * half + c));
+        return make_uint2((uint32_t)p[0] | ((uint32_t)p[1] << 16), (uint32_t)p[2] | ((uint32_t)p[3] << 16));
+    }
+    if (layout == DSMOE_LAYOUT_ROWSOA) return *reinterpret_cast<const uint2 *>(row + 128 + 64 * kb + 32 * half + 8 * c);
+    const uint32_t *p = reinterpret_cast<const uint32_t *>(row + Q2K_BYTES * kb + 16 + 32 * half + 8 * c);
+    return make_uint2(p[0], p[1]);
+}
+
+// the 8 scale bytes of sub-blocks 8*half .. 8*half+7 of Q2_K block kb
+__device__ __forceinline__ uint2 pf_load_q2k_scales(const uint8_t *row, int layout, uint32_t kb, uint32_t half)
+{
+    const uint8_t *p = layout == DSMOE_LAYOUT_ROWSOA ? row + 16 * kb + 8 * half : row + Q2K_BYTES * kb + 8 * half;
+    const uint32_t *q = reinterpret_cast<const uint32_t *>(p);
+    return make_uint2(q[0], q[1]);
+}
+
+// IQ2_XXS: decode one 32-weight group into four core-matrix rows (8 f16 each) at dst + u * 128, u = 0..3
+__device__ __forceinline__ void pf_decode_iq2(uint2 pk, uint8_t *dst, const uint4 *lut_grid, const uint4 *lut_sign)
+{
+    const uint32_t aux0 = pk.x, aux1 = pk.y;
+    const __half2 ls = __float2half2_rn((float)(2u * (aux1 >> 28) + 1u));
+    const uint32_t ls2 = *reinterpret_cast<const uint32_t *>(&ls);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const uint4 g = lut_grid[(aux0 >> (8 * u)) & 255u];   // magnitudes as f16
+        const uint4 s = lut_sign[(aux1 >> (7 * u)) & 127u];   // +1 / -1 as f16
+        uint4 w;
+        w.x = pf_hmul2(g.x, pf_hmul2(s.x, ls2));
+        w.y = pf_hmul2(g.y, pf_hmul2(s.y, ls2));
+        w.z = pf_hmul2(g.z, pf_hmul2(s.z, ls2));
+        w.w = pf_hmul2(g.w, pf_hmul2(s.w, ls2));
+        *reinterpret_cast<uint4 *>(dst + u * 128) = w;
+    }
+}
+
+// Q2_K: 8 quant bytes (quarter c of half-block `half`) -> units j = 0..3 (k = 32 j + 8 c + i), value sc_lo[j] * q,
+// at dst + j * 512. sc8 = the 8 scale bytes of sub-blocks 8*half .. +7; sub-block of unit j is 2 j + c / 2.
+__device__ __forceinline__ void pf_decode_q2k(uint2 pk, uint2 sc8, uint32_t c, uint8_t *dst)
+{
+    const uint32_t sc4 = __byte_perm(sc8.x, sc8.y, (c & 2) ? 0x7531u : 0x6420u) & 0x0F0F0F0Fu;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t sc = (sc4 >> (8 * j)) & 0xFFu;
+        const uint32_t lo = ((pk.x >> (2 * j)) & 0x03030303u) * sc, hi = ((pk.y >> (2 * j)) & 0x03030303u) * sc;
+        *reinterpret_cast<uint4 *>(dst + j * 512) = pf_bytes_to_f16x8(lo, hi);
+    }
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(256, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
+{
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint64_t *bar_full = reinterpret_cast<uint64_t *>(smem + PF_SMEM_BAR);       // [2] activation stage landed
+    uint64_t *bar_mma = bar_full + 2;                                             // [2] stage's MMAs retired
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_mma + 2);
+    uint4 *lut_grid = reinterpret_cast<uint4 *>(smem + PF_SMEM_LUT);
+    uint4 *lut_sign = lut_grid + 256;
+    float *sS = reinterpret_cast<float *>(smem + PF_SMEM_S);
+    float *sX = reinterpret_cast<float *>(smem);  // epilogue exchange buffer, aliases the A and B stages
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    constexpr uint32_t TMEM_COLS = KIND == PF_Q2K ? 512u : 256u;
+    constexpr uint32_t M_OUT = KIND == PF_IQ2 ? 64u : 128u;  // output rows per tile
+    const bool ieee = a.ieee != 0;
+
+    if (KIND == PF_IQ2) {
+        for (int i = tid; i < 256; i += 256) {
+            const uint64_t g = c_iq2xxs_grid[i];
+            lut_grid[i] = pf_bytes_to_f16x8((uint32_t)g, (uint32_t)(g >> 32));
+        }
+        if (tid < 128) {
+            const uint32_t sb = dsmoe_iq2_sign_byte((uint32_t)tid);
+            uint32_t h[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                h[i] = (((sb >> (2 * i)) & 1u) ? 0xBC00u : 0x3C00u) | ((((sb >> (2 * i + 1)) & 1u) ? 0xBC00u : 0x3C00u) << 16);
+            lut_sign[tid] = make_uint4(h[0], h[1], h[2], h[3]);
+        }
+    }
+    if (warp == 0) tc05_alloc(tmem_slot, TMEM_COLS);
+    if (tid == 0) {
+        mbar_init(&bar_full[0], 1);
+        mbar_init(&bar_full[1], 1);
+        mbar_init(&bar_mma[0], 1);
+        mbar_init(&bar_mma[1], 1);
+        fence_async_smem();
+    }
+    tc05_fence_before_sync();
+    __syncthreads();
+    tc05_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    const uint32_t n_tiles = a.plan[0], n_mtiles = a.out_dim / M_OUT, n_items = n_tiles * n_mtiles;
+    const uint32_t n_stages = 2 * a.kblocks;
+    // this thread in the decode phase: lane = c * 8 + r8 -> quarter c of the stage, row 16 warp + 8 pass + r8
+    const uint32_t dc = lane >> 3, dr8 = lane & 7;
+    // this thread in the drain phase: accumulator row and column half
+    const uint32_t arow = 32 * (warp & 3) + lane, acol0 = 64 * (warp >> 2);
+    const uint32_t tlane = (32u * (warp & 3)) << 16;
+
+    uint32_t gs = 0, gsb = 0;  // stages / superblocks issued so far by this CTA (mbarrier and TMEM phase tracking)
+    bool ok = true;
+
+    for (uint32_t item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+        const uint32_t tile = item / n_mtiles, mt = item - tile * n_mtiles;
+        const uint32_t rows = a.tile_rows[tile], rows16 = (rows + 15u) & ~15u, boff = a.tile_boff[tile];
+        const uint32_t start = a.tile_start[tile];
+        const uint64_t ebase = (uint64_t)a.tile_expert[tile] * a.expert_bytes;
+        const uint32_t row_bytes = (KIND == PF_IQ2 ? IQ2XXS_BYTES : Q2K_BYTES) * a.kblocks;
+        const uint32_t idesc = tc05_idesc_f16(128, rows16);
+        const uint8_t *btile = a.B + (size_t)boff * a.kblocks * 512;
+
+        // weight rows this thread decodes (two passes) and the row it drains
+        const uint8_t *drow[2];
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+            const uint32_t rl = 16 * warp + 8 * p + dr8;
+            if (KIND == PF_IQ2) drow[p] = (rl < 64 ? a.w0 : a.w1) + ebase + (uint64_t)(mt * 64 + (rl & 63)) * row_bytes;
+            else drow[p] = a.w0 + ebase + (uint64_t)(mt * 128 + rl) * row_bytes;
+        }
+        const uint8_t *srow;  // the row whose scales this thread applies when draining
+        if (KIND == PF_IQ2) srow = (arow < 64 ? a.w0 : a.w1) + ebase + (uint64_t)(mt * 64 + (arow & 63)) * row_bytes;
+        else srow = a.w0 + ebase + (uint64_t)(mt * 128 + arow) * row_bytes;
+
+        for (uint32_t i = tid; i < a.kblocks * rows16; i += 256) {
+            const uint32_t kb = i / rows16, c = i - kb * rows16;
+            sS[kb * PF_TN + c] = a.S[(size_t)kb * a.r_cap + boff + c];
+        }
+        float acc[64];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+
+        uint2 pk[2] = {pf_load_packed<KIND>(drow[0], a.layout, 0, 0, dc), pf_load_packed<KIND>(drow[1], a.layout, 0, 0, dc)};
+
+        auto drain = [&](uint32_t kb, uint32_t buf) {
+            // scales of this row for superblock kb
+            float dw, dmin = 0.0f;
+            if (KIND == PF_IQ2) {
+                const uint32_t bits = a.layout == DSMOE_LAYOUT_ROWSOA ? ld_u16(srow + 2 * kb) : ld_u16(srow + IQ2XXS_BYTES * kb);
+                dw = __fmul_rn(0.125f, f16_bits_to_f32(bits, ieee));
+            } else {
+                const uint32_t dd = a.layout == DSMOE_LAYOUT_ROWSOA ? ld_u32(srow + 80 * a.kblocks + 4 * kb)
+                                                                    : ld_u32(srow + Q2K_BYTES * kb + 80);
+                dw = f16_bits_to_f32(dd & 0xFFFFu, ieee);
+                dmin = f16_bits_to_f32(dd >> 16, ieee);
+            }
+            const float *sx = sS + kb * PF_TN + acol0;
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 16) {
+                if (acol0 + c0 >= rows16) break;  // warp-uniform: columns beyond the padded tile hold nothing
+                float v[16], v2[16];
+                tc05_ld16(tmem + tlane + buf * PF_TN + acol0 + c0, v);
+                if (KIND == PF_Q2K) tc05_ld16(tmem + tlane + 256u + buf * PF_TN + acol0 + c0, v2);
+                tc05_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float dx = sx[c0 + i];
+                    if (KIND == PF_IQ2) {
+                        acc[c0 + i] = __fadd_rn(acc[c0 + i], __fmul_rn(__fmul_rn(dw, dx), v[i]));
+                    } else {
+                        const float t = __fsub_rn(__fmul_rn(__fmul_rn(dx, dw), v[i]), __fmul_rn(__fmul_rn(dx, dmin), v2[i]));
+                        acc[c0 + i] = __fadd_rn(acc[c0 + i], t);
+                    }
+                }
+            }
+        };
+
+        for (uint32_t s = 0; s < n_stages; ++s, ++gs) {
+            const uint32_t b = gs & 1, kb = s >> 1, half = s & 1;
+            // 1. the stage buffer is free once the MMAs of the stage issued two stages ago have retired
+            if (gs >= 2) ok = ok && mbar_wait_bounded(&bar_mma[b], ((gs >> 1) - 1) & 1, a.status);
+            // 2. activation block of this stage (and, for Q2_K, the superblock's bsums tile)
+            if (tid == 0) {
+                uint32_t bytes = rows16 * 256u;
+                if (KIND == PF_Q2K && half == 0) bytes += rows16 * 32u;
+                mbar_expect_tx(&bar_full[b], bytes);
+                bulk_g2s(smem + PF_SMEM_B + b * PF_STAGE_A, btile + (size_t)s * rows16 * 256, rows16 * 256u, &bar_full[b]);
+                if (KIND == PF_Q2K && half == 0)
+                    bulk_g2s(smem + PF_SMEM_B2 + (gsb & 1) * 4096, a.BS + ((size_t)kb * a.r_cap + boff) * 16, rows16 * 32u,
+                             &bar_full[b]);
+            }
+            // 3. decode this stage's weights; fetch the next stage's packed bytes meanwhile
+            uint2 nx[2] = {pk[0], pk[1]};
+            if (s + 1 < n_stages) {
+                nx[0] = pf_load_packed<KIND>(drow[0], a.layout, (s + 1) >> 1, (s + 1) & 1, dc);
+                nx[1] = pf_load_packed<KIND>(drow[1], a.layout, (s + 1) >> 1, (s + 1) & 1, dc);
+            }
+            uint8_t *sA = smem + PF_SMEM_A + b * PF_STAGE_A;
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {
+                const uint32_t rl = 16 * warp + 8 * p + dr8;
+                uint8_t *dst = sA + (rl >> 3) * PF_SBO + (rl & 7) * 16;
+                if (KIND == PF_IQ2) {
+                    pf_decode_iq2(pk[p], dst + dc * 512, lut_grid, lut_sign);
+                } else {
+                    const uint2 sc8 = pf_load_q2k_scales(drow[p], a.layout, kb, half);
+                    pf_decode_q2k(pk[p], sc8, dc, dst + dc * 128);
+                    if (half == 0 && dc < 2) {  // sc_hi of sub-blocks 8 dc .. 8 dc + 7 -> min-term operand, core dc
+                        const uint2 sh = pf_load_q2k_scales(drow[p], a.layout, kb, dc);
+                        *reinterpret_cast<uint4 *>(smem + PF_SMEM_A2 + (gsb & 1) * 4096 + (rl >> 3) * 256 + dc * 128 + (rl & 7) * 16) =
+                            pf_bytes_to_f16x8((sh.x >> 4) & 0x0F0F0F0Fu, (sh.y >> 4) & 0x0F0F0F0Fu);
+                    }
+                }
+            }
+            pk[0] = nx[0];
+            pk[1] = nx[1];
+            // 4. generic-proxy writes -> visible to the tensor core (async proxy); everyone has finished draining
+            fence_async_smem();
+            tc05_fence_before_sync();
+            ok = __syncthreads_and(ok);
+            if (!ok) break;
+            // 5. issue
+            if (tid == 0) {
+                if (mbar_wait_bounded(&bar_full[b], (gs >> 1) & 1, a.status)) {
+                    tc05_fence_after_sync();
+                    const uint32_t d_tmem = tmem + (gsb & 1) * PF_TN;
+                    const uint32_t sa = smem_u32(sA), sb = smem_u32(smem + PF_SMEM_B + b * PF_STAGE_A);
+#pragma unroll
+                    for (int ks = 0; ks < PF_KS / 16; ++ks)
+                        tc05_mma_f16(d_tmem, tc05_smem_desc(sa + ks * 256, 128, PF_SBO),
+                                     tc05_smem_desc(sb + ks * 256, 128, PF_SBO), idesc, (half | ks) != 0);
+                    if (KIND == PF_Q2K && half == 1)
+                        tc05_mma_f16(tmem + 256u + (gsb & 1) * PF_TN,
+                                     tc05_smem_desc(smem_u32(smem + PF_SMEM_A2 + (gsb & 1) * 4096), 128, 256),
+                                     tc05_smem_desc(smem_u32(smem + PF_SMEM_B2 + (gsb & 1) * 4096), 128, 256), idesc, 0);
+                }
+                tc05_commit(&bar_mma[b]);  // also arrives when the wait above gave up, so nobody waits on it for ever
+            }
+            // 6. drain the previous superblock while this stage's MMAs run (its last stage retired at step 1)
+            if (half == 1) {
+                if (s >= 3) {
+                    tc05_fence_after_sync();
+                    drain(kb - 1, (gsb + 1) & 1);
+                }
+                ++gsb;
+            }
+        }
+        if (!ok) break;
+        // last superblock: wait for the final stage (commits retire in order, so the one before is done too)
+        ok = mbar_wait_bounded(&bar_mma[(gs - 1) & 1], ((gs - 1) >> 1) & 1, a.status);
+        tc05_fence_after_sync();
+        if (ok) drain(a.kblocks - 1, (gsb + 1) & 1);
+        tc05_fence_before_sync();
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
+
+        // epilogue
+        if (KIND == PF_IQ2) {
+#pragma unroll
+            for (int i = 0; i < 64; ++i) sX[arow * PF_XSTRIDE + acol0 + i] = acc[i];
+            __syncthreads();
+            for (uint32_t i = tid; i < 64u * rows; i += 256) {
+                const uint32_t col = i >> 6, r = i & 63;
+                float g = sX[r * PF_XSTRIDE + col], u = sX[(64 + r) * PF_XSTRIDE + col];
+                if (a.clamp > 1.0e-6f) {
+                    if (g > a.clamp) g = a.clamp;
+                    if (u > a.clamp) u = a.clamp;
+                    if (u < -a.clamp) u = -a.clamp;
+                }
+                const uint32_t pair = a.sorted[start + col];
+                a.out[(size_t)pair * a.out_dim + mt * 64 + r] = swiglu_weighted(g, u, a.weights[pair]);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+                const uint32_t col = acol0 + i;
+                if (col < rows) a.out[(size_t)a.sorted[start + col] * a.out_dim + mt * 128 + arow] = acc[i];
+            }
+        }
+        __syncthreads();  // the exchange buffer and the scale table are reused by the next item
+    }
+
+    tc05_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tc05_dealloc(tmem, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// launchers
+// ---------------------------------------------------------------------------------------------------------------
+size_t prefill_scratch_bytes(uint32_t max_tokens, uint32_t k, uint32_t n_expert, uint32_t n_embd, uint32_t n_ff,
+                             PrefillScratch *lay)
+{
+    const size_t P = (size_t)max_tokens * k;
+    const size_t tl = P / PF_TN + n_expert + 1;          // tiles: full ones plus one partial per expert
+    const size_t r_cap = ((P + 15 * (tl < P ? tl : P) + 15) & ~(size_t)15) + 16;  // padded rows over all tiles
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t o = off;
+        off += (bytes + 255) & ~(size_t)255;
+        return o;
+    };
+    PrefillScratch L;
+    L.r_cap = (uint32_t)r_cap;
+    L.tile_cap = (uint32_t)tl;
+    L.counts = take(4 * (size_t)n_expert);
+    L.offsets = take(4 * ((size_t)n_expert + 1));
+    L.sorted = take(4 * P);
+    L.tile_expert = take(4 * tl);
+    L.tile_start = take(4 * tl);
+    L.tile_rows = take(4 * tl);
+    L.tile_boff = take(4 * (tl + 1));
+    L.plan = take(16);
+    L.bx = take(r_cap * (size_t)n_embd * 2);
+    L.sx = take(r_cap * (size_t)(n_embd / QK_K) * 4);
+    L.bm = take(r_cap * (size_t)n_ff * 2);
+    L.sm = take(r_cap * (size_t)(n_ff / QK_K) * 4);
+    L.bs = take(r_cap * (size_t)(n_ff / QK_K) * 16 * 2);
+    L.down_pair = take(P * (size_t)n_embd * 4);
+    if (lay) *lay = L;
+    return off;
+}
+
+bool prefill_eligible(uint32_t n_embd, uint32_t n_ff, const uint8_t *gate, const uint8_t *up, const uint8_t *down,
+                      int layout)
+{
+    const uintptr_t al = layout == DSMOE_LAYOUT_ROWSOA ? 15 : 3;
+    return n_embd % QK_K == 0 && n_ff % QK_K == 0 && n_ff % 64 == 0 && n_embd % 128 == 0 && n_embd / QK_K <= 16 &&
+           n_ff / QK_K <= 16 && (((uintptr_t)gate | (uintptr_t)up | (uintptr_t)down) & al) == 0 &&
+           (layout == DSMOE_LAYOUT_NATIVE || ((n_embd / QK_K * IQ2XXS_BYTES) % 16 == 0 && (n_ff / QK_K * Q2K_BYTES) % 16 == 0));
+}
+
+static int pf_sm_count()
+{
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+int launch_prefill_experts(cudaStream_t st, const PrefillArgs &p)
+{
+    uint8_t *w = p.scratch;
+    const PrefillScratch &L = p.lay;
+    auto u32p = [&](size_t o) { return reinterpret_cast<uint32_t *>(w + o); };
+    const uint32_t P = p.n_tokens * p.k, xb = p.n_embd / QK_K, mb = p.n_ff / QK_K;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(pf_grouped_gemm_kernel<PF_IQ2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM_TOTAL);
+        cudaFuncSetAttribute(pf_grouped_gemm_kernel<PF_Q2K>, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM_TOTAL);
+        attr_set = true;
+    }
+    const int sms = pf_sm_count();
+    int n = 0;
+    // 1. group pairs by expert
+    pf_count_kernel<<<p.n_expert, 256, 0, st>>>(p.selected, P, u32p(L.counts));
+    pf_plan_kernel<<<1, 32, 0, st>>>(u32p(L.counts), (int)p.n_expert, u32p(L.offsets), u32p(L.tile_expert),
+                                     u32p(L.tile_start), u32p(L.tile_rows), u32p(L.tile_boff), u32p(L.plan));
+    pf_place_kernel<<<p.n_expert, 256, 0, st>>>(p.selected, P, u32p(L.offsets), u32p(L.sorted));
+    n += 3;
+    // 2. activation tiles of x
+    const dim3 ggrid(32, (unsigned)(L.tile_cap < 1024u ? L.tile_cap : 1024u));
+    pf_gather_kernel<<<ggrid, 256, 0, st>>>(p.xq, xb, p.k, u32p(L.sorted), u32p(L.tile_start), u32p(L.tile_rows),
+                                            u32p(L.tile_boff), u32p(L.plan), w + L.bx,
+                                            reinterpret_cast<float *>(w + L.sx), nullptr, L.r_cap);
+    // 3. gate / up / SwiGLU
+    PfGemmArgs g = {};
+    g.w0 = p.gate, g.w1 = p.up, g.expert_bytes = (uint64_t)p.n_ff * xb * IQ2XXS_BYTES;
+    g.B = w + L.bx, g.S = reinterpret_cast<const float *>(w + L.sx), g.BS = nullptr, g.r_cap = L.r_cap;
+    g.sorted = u32p(L.sorted), g.tile_expert = u32p(L.tile_expert), g.tile_start = u32p(L.tile_start);
+    g.tile_rows = u32p(L.tile_rows), g.tile_boff = u32p(L.tile_boff), g.plan = u32p(L.plan);
+    g.weights = p.weights, g.out = p.mid, g.out_dim = p.n_ff, g.kblocks = xb, g.clamp = p.clamp, g.ieee = p.ieee;
+    g.layout = p.layout, g.status = p.status;
+    pf_grouped_gemm_kernel<PF_IQ2><<<sms, 256, PF_SMEM_TOTAL, st>>>(g);
+    // 4. Q8_K of mid, tiles of it (with bsums)
+    launch_q8k_quantize(st, p.mid, p.midq, p.n_ff, P);
+    pf_gather_kernel<<<ggrid, 256, 0, st>>>(p.midq, mb, 1, u32p(L.sorted), u32p(L.tile_start), u32p(L.tile_rows),
+                                            u32p(L.tile_boff), u32p(L.plan), w + L.bm,
+                                            reinterpret_cast<float *>(w + L.sm), reinterpret_cast<__half *>(w + L.bs),
+                                            L.r_cap);
+    // 5. down
+    PfGemmArgs d = g;
+    d.w0 = p.down, d.w1 = nullptr, d.expert_bytes = (uint64_t)p.n_embd * mb * Q2K_BYTES;
+    d.B = w + L.bm, d.S = reinterpret_cast<const float *>(w + L.sm), d.BS = reinterpret_cast<const __half *>(w + L.bs);
+    d.weights = nullptr, d.out = reinterpret_cast<float *>(w + L.down_pair), d.out_dim = p.n_embd, d.kblocks = mb;
+    pf_grouped_gemm_kernel<PF_Q2K><<<sms, 256, PF_SMEM_TOTAL, st>>>(d);
+    // 6. slots summed in slot order
+    launch_moe_sum(st, reinterpret_cast<const float *>(w + L.down_pair), p.out, p.n_embd, p.k, p.n_tokens);
+    return n + 6;
+}
+
+}  // namespace dsmoe

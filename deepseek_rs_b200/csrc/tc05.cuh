@@ -1,0 +1,111 @@
+// tcgen05 (5th-generation tensor core) helpers for sm_100a: TMEM allocation, shared-memory matrix descriptors,
+// MMA issue, commit and accumulator loads. cta_group::1 only, no multicast.
+//
+// Shared-memory operand layout used throughout ("K-major, no swizzle"): a tile of R rows x KT elements of 2 bytes is
+// stored as 8-row x 16-byte core matrices; element (r, k) lives at
+//     (r / 8) * SBO + (k / 8) * 128 + (r % 8) * 16 + (k % 8) * 2,        SBO = (KT / 8) * 128 bytes,
+// i.e. the core matrices of one 8-row group are contiguous along K (leading byte offset 128) and consecutive row
+// groups are SBO apart (stride byte offset). One MMA of K = 16 consumes two consecutive core matrices per row group,
+// so advancing K by 16 elements advances the descriptor start address by 256 bytes.
+#pragma once
+
+#include <stdint.h>
+
+#include "async.cuh"
+
+namespace dsmoe {
+
+// 64-bit shared-memory matrix descriptor: start address, leading / stride byte offsets (all >> 4), version 1
+// (Blackwell) in bits 46-47, no swizzle (layout type 0 in bits 61-63), base offset 0.
+__device__ __forceinline__ uint64_t tc05_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= 1ull << 46;
+    return d;
+}
+
+// 32-bit instruction descriptor for kind::f16 with f16 A and B (both K-major) and f32 accumulation:
+// c_format = 1 (F32) at bits 4-5, a/b_format = 0 (F16), N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+__host__ __device__ constexpr uint32_t tc05_idesc_f16(uint32_t m, uint32_t n)
+{
+    return (1u << 4) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// kind::f8f6f4 with E4M3 A and B (format code 0), f32 accumulation, both K-major.
+__host__ __device__ constexpr uint32_t tc05_idesc_e4m3(uint32_t m, uint32_t n)
+{
+    return (1u << 4) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// Allocates ncols (power of two >= 32) TMEM columns; one full warp must call it. The base address is written to
+// *slot (shared memory). The permit is relinquished so that no later allocation in this CTA can stall another CTA.
+__device__ __forceinline__ void tc05_alloc(uint32_t *slot, uint32_t ncols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc05_dealloc(uint32_t taddr, uint32_t ncols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+__device__ __forceinline__ void tc05_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc05_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] * B[smem]; accumulate = 0 overwrites D. Issued by ONE thread.
+__device__ __forceinline__ void tc05_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc05_mma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Makes the mbarrier track completion of every MMA this thread has issued so far (arrives once when they are done).
+__device__ __forceinline__ void tc05_commit(uint64_t *bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Loads 16 consecutive f32 columns of this thread's TMEM lane (lane = 32 * (warp % 4) + lane id). taddr carries the
+// lane base in bits 16-31 and the column in bits 0-15.
+__device__ __forceinline__ void tc05_ld16(uint32_t taddr, float (&v)[16])
+{
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void tc05_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+}  // namespace dsmoe

@@ -419,3 +419,52 @@ def test_moe_forward_layer(torch_cuda, oracle, layout, T):
         Kl.moe_forward(0, dev(torch, np.zeros((9, 4096), np.float32)), dev(torch, np.zeros((9, n_e), np.float32)), 9,
                        torch.zeros((9, 4096), device="cuda"))
     Kl.close()
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# batched path (tcgen05 grouped GEMM)
+# ---------------------------------------------------------------------------------------------------------------
+
+def _batched_kernels(n_e, max_tokens):
+    """A handle whose tier-2 call takes the batched path from one token upwards."""
+    import os
+
+    from deepseek_rs_b200.kernels import MoeKernels
+
+    old = os.environ.get("DSMOE_PREFILL_MIN_TOKENS")
+    os.environ["DSMOE_PREFILL_MIN_TOKENS"] = "1"
+    try:
+        return MoeKernels(device=0, n_expert=n_e, max_tokens=max_tokens)
+    finally:
+        if old is None:
+            del os.environ["DSMOE_PREFILL_MIN_TOKENS"]
+        else:
+            os.environ["DSMOE_PREFILL_MIN_TOKENS"] = old
+
+
+@pytest.mark.parametrize("layout", ["rowsoa", "native"])
+@pytest.mark.parametrize("T,n_e,zipf", [(5, 32, False), (70, 32, False), (200, 32, True)])
+def test_moe_forward_batched_tcgen05(torch_cuda, oracle, layout, T, n_e, zipf):
+    """The grouped-GEMM path against the oracle: routing bit-exact, outputs within rel 1e-3 / abs 1e-4 (the tensor-core
+    f32 accumulation order differs from the reference's, and a mid value on a Q8_K rounding boundary may flip by one
+    code, so this path is held to the stated tolerance, not to bit identity). Zipf routing makes one expert span
+    more than one 128-row tile and leaves others empty."""
+    torch = torch_cuda
+    from deepseek_rs_b200.kernels import LAYOUT_NATIVE, LAYOUT_ROWSOA, MoeLayer
+
+    Kb = _batched_kernels(n_e, T)
+    lw = F.ExpertLayer(seed=31, n_expert=n_e)
+    rng = np.random.default_rng(32 + T)
+    x = F.bf16_round(rng.standard_normal((T, 4096)).astype(np.float32))
+    logits = F.zipf_logits(rng, T, n_e, s=2.0) if zipf else rng.standard_normal((T, n_e)).astype(np.float32)
+    ref_out, ref_sel, ref_w = oracle.moe_layer(x, logits, lw.gate, lw.up, lw.down, k=6)
+    layer = MoeLayer(Kb, lw.gate, lw.up, lw.down, layout=LAYOUT_ROWSOA if layout == "rowsoa" else LAYOUT_NATIVE)
+    sel = torch.zeros((T, 6), dtype=torch.int32, device="cuda")
+    out = layer.forward(dev(torch, x), dev(torch, logits), selected_out=sel)
+    assert Kb.device_status() == 0
+    assert np.array_equal(sel.cpu().numpy(), ref_sel)
+    got = out.cpu().numpy()
+    err = np.abs(got - ref_out)
+    bad = err > ABS + REL * np.abs(ref_out)
+    assert not bad.any(), f"{bad.sum()} of {bad.size} outside tolerance, max abs err {err.max()}, ref scale {np.abs(ref_out).max()}"
+    Kb.close()
