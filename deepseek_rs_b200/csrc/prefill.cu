@@ -299,6 +299,20 @@ __device__ __forceinline__ void pf_decode_q2k(uint2 pk, uint2 sc8, uint32_t c, u
     }
 }
 
+// Order in which the superblocks of a row are contracted. Q2_K: ascending. IQ2_XXS: the post-order of the reference's
+// reduction tree, so that the f32 partial sums can be folded exactly as the reference folds them
+// (engine/src/kernels/moe.rs:37-42, 661-690: lane partial a_l = (0 + dot_l) + dot_(l+8), then
+// ((a0+a4)+(a2+a6)) + ((a1+a5)+(a3+a7))) with only two live register sets. Leaf order l = 0,4,2,6,1,5,3,7; with 16
+// blocks per row visit j covers block l(j/2) + 8 (j%2), with 8 blocks visit j covers block l(j).
+template <int KIND>
+__device__ __forceinline__ uint32_t pf_visit_block(uint32_t kblocks, uint32_t j)
+{
+    if (KIND == PF_Q2K) return j;
+    const uint32_t leaf = kblocks == 16 ? (j >> 1) : j;
+    const uint32_t l = (0x73516240u >> (4 * leaf)) & 7u;
+    return kblocks == 16 ? l + 8 * (j & 1) : l;
+}
+
 template <int KIND>
 __global__ void __launch_bounds__(256, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
 {
@@ -312,7 +326,7 @@ __global__ void __launch_bounds__(256, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
     float *sX = reinterpret_cast<float *>(smem);  // epilogue exchange buffer, aliases the A and B stages
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    constexpr uint32_t TMEM_COLS = KIND == PF_Q2K ? 512u : 256u;
+    constexpr uint32_t TMEM_COLS = 512u;  // D x2 at 0/128; Q2K: D2 x2 at 256/384; IQ2: spill sets P2 at 256, P3 at 384
     constexpr uint32_t M_OUT = KIND == PF_IQ2 ? 64u : 128u;  // output rows per tile
     const bool ieee = a.ieee != 0;
 
@@ -379,13 +393,20 @@ __global__ void __launch_bounds__(256, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
             const uint32_t kb = i / rows16, c = i - kb * rows16;
             sS[kb * PF_TN + c] = a.S[(size_t)kb * a.r_cap + boff + c];
         }
-        float acc[64];
+        float acc[64];                          // Q2K: running sum. IQ2: the current leaf's partial a_l
+        float p1[64];                           // IQ2: pair level of the reduction tree, finally the row total
 #pragma unroll
         for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
 
-        uint2 pk[2] = {pf_load_packed<KIND>(drow[0], a.layout, 0, 0, dc), pf_load_packed<KIND>(drow[1], a.layout, 0, 0, dc)};
+        const uint32_t kb0 = pf_visit_block<KIND>(a.kblocks, 0);
+        uint2 pk[2] = {pf_load_packed<KIND>(drow[0], a.layout, kb0, 0, dc), pf_load_packed<KIND>(drow[1], a.layout, kb0, 0, dc)};
 
-        auto drain = [&](uint32_t kb, uint32_t buf) {
+        auto drain = [&](uint32_t j, uint32_t buf) {
+            const uint32_t kb = pf_visit_block<KIND>(a.kblocks, j);
+            // IQ2: position of this block in the reference's reduction tree
+            const uint32_t leaf = a.kblocks == 16 ? (j >> 1) : j;
+            const bool first_of_leaf = a.kblocks == 16 ? (j & 1) == 0 : true;
+            const bool last_of_leaf = a.kblocks == 16 ? (j & 1) == 1 : true;
             // scales of this row for superblock kb
             float dw, dmin = 0.0f;
             if (KIND == PF_IQ2) {
@@ -409,17 +430,57 @@ __global__ void __launch_bounds__(256, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
                 for (int i = 0; i < 16; ++i) {
                     const float dx = sx[c0 + i];
                     if (KIND == PF_IQ2) {
-                        acc[c0 + i] = __fadd_rn(acc[c0 + i], __fmul_rn(__fmul_rn(dw, dx), v[i]));
+                        // ((0.125 d_w) d_x) bsum, added to 0 or to the leaf's first block
+                        const float t = __fmul_rn(__fmul_rn(dw, dx), v[i]);
+                        acc[c0 + i] = __fadd_rn(first_of_leaf ? 0.0f : acc[c0 + i], t);
                     } else {
                         const float t = __fsub_rn(__fmul_rn(__fmul_rn(dx, dw), v[i]), __fmul_rn(__fmul_rn(dx, dmin), v2[i]));
                         acc[c0 + i] = __fadd_rn(acc[c0 + i], t);
                     }
                 }
             }
+            if (KIND == PF_IQ2 && last_of_leaf) {
+                // fold the finished leaf a_l (in acc) into the tree: P1 = pair sums (registers), P2 = quad sums and
+                // P3 = the even half (TMEM columns 256.. and 384.., used as spill space)
+#pragma unroll
+                for (int c0 = 0; c0 < 64; c0 += 16) {
+                    if (acol0 + c0 >= rows16) break;
+                    const uint32_t t2 = tmem + tlane + 256u + acol0 + c0, t3 = tmem + tlane + 384u + acol0 + c0;
+                    float w[16];
+                    if ((leaf & 1) == 0) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) p1[c0 + i] = acc[c0 + i];
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) p1[c0 + i] = __fadd_rn(p1[c0 + i], acc[c0 + i]);
+                        if (leaf == 1 || leaf == 5) {          // P2 = first pair sum of this half
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) w[i] = p1[c0 + i];
+                            tc05_st16(t2, w);
+                            tc05_wait_st();
+                        } else {                               // leaf 3 or 7: quad sum = P2 + P1
+                            tc05_ld16(t2, w);
+                            tc05_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) w[i] = __fadd_rn(w[i], p1[c0 + i]);
+                            if (leaf == 3) {                   // even half done: park it in P3
+                                tc05_st16(t3, w);
+                                tc05_wait_st();
+                            } else {                           // total = even half + odd half
+                                float e[16];
+                                tc05_ld16(t3, e);
+                                tc05_wait_ld();
+#pragma unroll
+                                for (int i = 0; i < 16; ++i) p1[c0 + i] = __fadd_rn(e[i], w[i]);
+                            }
+                        }
+                    }
+                }
+            }
         };
 
         for (uint32_t s = 0; s < n_stages; ++s, ++gs) {
-            const uint32_t b = gs & 1, kb = s >> 1, half = s & 1;
+            const uint32_t b = gs & 1, kb = pf_visit_block<KIND>(a.kblocks, s >> 1), half = s & 1;
             // 1. the stage buffer is free once the MMAs of the stage issued two stages ago have retired
             if (gs >= 2) ok = ok && mbar_wait_bounded(&bar_mma[b], ((gs >> 1) - 1) & 1, a.status);
             // 2. activation block of this stage (and, for Q2_K, the superblock's bsums tile)
@@ -427,7 +488,7 @@ __global__ void __launch_bounds__(256, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
                 uint32_t bytes = rows16 * 256u;
                 if (KIND == PF_Q2K && half == 0) bytes += rows16 * 32u;
                 mbar_expect_tx(&bar_full[b], bytes);
-                bulk_g2s(smem + PF_SMEM_B + b * PF_STAGE_A, btile + (size_t)s * rows16 * 256, rows16 * 256u, &bar_full[b]);
+                bulk_g2s(smem + PF_SMEM_B + b * PF_STAGE_A, btile + (size_t)(2 * kb + half) * rows16 * 256, rows16 * 256u, &bar_full[b]);
                 if (KIND == PF_Q2K && half == 0)
                     bulk_g2s(smem + PF_SMEM_B2 + (gsb & 1) * 4096, a.BS + ((size_t)kb * a.r_cap + boff) * 16, rows16 * 32u,
                              &bar_full[b]);
@@ -435,8 +496,9 @@ __global__ void __launch_bounds__(256, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
             // 3. decode this stage's weights; fetch the next stage's packed bytes meanwhile
             uint2 nx[2] = {pk[0], pk[1]};
             if (s + 1 < n_stages) {
-                nx[0] = pf_load_packed<KIND>(drow[0], a.layout, (s + 1) >> 1, (s + 1) & 1, dc);
-                nx[1] = pf_load_packed<KIND>(drow[1], a.layout, (s + 1) >> 1, (s + 1) & 1, dc);
+                const uint32_t nkb = pf_visit_block<KIND>(a.kblocks, (s + 1) >> 1);
+                nx[0] = pf_load_packed<KIND>(drow[0], a.layout, nkb, (s + 1) & 1, dc);
+                nx[1] = pf_load_packed<KIND>(drow[1], a.layout, nkb, (s + 1) & 1, dc);
             }
             uint8_t *sA = smem + PF_SMEM_A + b * PF_STAGE_A;
 #pragma unroll
@@ -483,7 +545,7 @@ __global__ void __launch_bounds__(256, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
             if (half == 1) {
                 if (s >= 3) {
                     tc05_fence_after_sync();
-                    drain(kb - 1, (gsb + 1) & 1);
+                    drain((s >> 1) - 1, (gsb + 1) & 1);
                 }
                 ++gsb;
             }
@@ -500,7 +562,7 @@ __global__ void __launch_bounds__(256, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
         // epilogue
         if (KIND == PF_IQ2) {
 #pragma unroll
-            for (int i = 0; i < 64; ++i) sX[arow * PF_XSTRIDE + acol0 + i] = acc[i];
+            for (int i = 0; i < 64; ++i) sX[arow * PF_XSTRIDE + acol0 + i] = p1[i];
             __syncthreads();
             for (uint32_t i = tid; i < 64u * rows; i += 256) {
                 const uint32_t col = i >> 6, r = i & 63;
@@ -568,7 +630,7 @@ bool prefill_eligible(uint32_t n_embd, uint32_t n_ff, const uint8_t *gate, const
                       int layout)
 {
     const uintptr_t al = layout == DSMOE_LAYOUT_ROWSOA ? 15 : 3;
-    return n_embd % QK_K == 0 && n_ff % QK_K == 0 && n_ff % 64 == 0 && n_embd % 128 == 0 && n_embd / QK_K <= 16 &&
+    return n_embd % QK_K == 0 && n_ff % QK_K == 0 && n_ff % 64 == 0 && n_embd % 128 == 0 && (n_embd / QK_K == 16 || n_embd / QK_K == 8) &&
            n_ff / QK_K <= 16 && (((uintptr_t)gate | (uintptr_t)up | (uintptr_t)down) & al) == 0 &&
            (layout == DSMOE_LAYOUT_NATIVE || ((n_embd / QK_K * IQ2XXS_BYTES) % 16 == 0 && (n_ff / QK_K * Q2K_BYTES) % 16 == 0));
 }
