@@ -31,6 +31,7 @@ SIGNATURES = {
     "dsmoe_destroy": (_int, [_vp]),
     "dsmoe_last_error": (C.c_char_p, [_vp]),
     "dsmoe_launch_count": (_u64, [_vp]),
+    "dsmoe_set_phase_events": (_int, [_vp, C.POINTER(_vp), _int]),
     "dsmoe_device_status": (_int, [_vp, _vp, C.POINTER(C.c_int)]),
     "dsmoe_q8k_quantize": (_int, [_vp, _vp, _vp, _vp, _u32, _u32]),
     "dsmoe_router_select": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _u32, _u32, _u32, _u32]),

@@ -35,6 +35,8 @@ struct dsmoe_handle {
     uint8_t *pf_scratch;
     PrefillScratch pf_lay;
     uint32_t prefill_min_tokens;
+    cudaEvent_t phase_events[6];
+    bool phase_events_set;
 };
 
 namespace {
@@ -175,6 +177,19 @@ int dsmoe_destroy(dsmoe_handle *h)
 }
 
 const char *dsmoe_last_error(const dsmoe_handle *h) { return h ? h->err : "null handle"; }
+
+int dsmoe_set_phase_events(dsmoe_handle *h, void **events, int n_events)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    if (!events || n_events == 0) {
+        h->phase_events_set = false;
+        return DSMOE_OK;
+    }
+    if (n_events != 6) return fail(h, DSMOE_ERR_ARG, "set_phase_events: expected 6 events, got %d", n_events);
+    for (int i = 0; i < 6; ++i) h->phase_events[i] = (cudaEvent_t)events[i];
+    h->phase_events_set = true;
+    return DSMOE_OK;
+}
 
 int dsmoe_device_status(dsmoe_handle *h, dsmoe_stream stream, int *code_out)
 {
@@ -383,7 +398,7 @@ int dsmoe_moe_forward(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, cons
     if (n_tokens >= h->prefill_min_tokens && prefill_eligible(c.n_embd, c.n_ff, ly.gate, ly.up, ly.down, ly.layout)) {
         PrefillArgs p = {ly.gate, ly.up, ly.down, h->xq, sel, wts, h->mid, h->midq, out, h->pf_scratch, h->pf_lay,
                          n_tokens, k, c.n_expert, c.n_embd, c.n_ff, c.swiglu_clamp, ly.layout, (int)c.f16_ieee,
-                         h->d_status};
+                         h->d_status, h->phase_events_set ? h->phase_events : nullptr};
         n += launch_prefill_experts(st, p);
         return check_launch(h, "moe_forward (batched)", n);
     }

@@ -78,6 +78,7 @@ struct PrefillArgs {
     float clamp;
     int layout, ieee;
     int *status;
+    cudaEvent_t *phase_events;         // optional, 6 events: start, grouped+gathered, gate/up, q8k+gather, down, sum
 };
 // Everything after the router and the Q8_K of x. Returns the number of kernels launched.
 int launch_prefill_experts(cudaStream_t st, const PrefillArgs &p);

@@ -661,6 +661,10 @@ int launch_prefill_experts(cudaStream_t st, const PrefillArgs &p)
     }
     const int sms = pf_sm_count();
     int n = 0;
+    auto mark = [&](int i) {
+        if (p.phase_events) cudaEventRecord(p.phase_events[i], st);
+    };
+    mark(0);
     // 1. group pairs by expert
     pf_count_kernel<<<p.n_expert, 256, 0, st>>>(p.selected, P, u32p(L.counts));
     pf_plan_kernel<<<1, 32, 0, st>>>(u32p(L.counts), (int)p.n_expert, u32p(L.offsets), u32p(L.tile_expert),
@@ -672,6 +676,7 @@ int launch_prefill_experts(cudaStream_t st, const PrefillArgs &p)
     pf_gather_kernel<<<ggrid, 256, 0, st>>>(p.xq, xb, p.k, u32p(L.sorted), u32p(L.tile_start), u32p(L.tile_rows),
                                             u32p(L.tile_boff), u32p(L.plan), w + L.bx,
                                             reinterpret_cast<float *>(w + L.sx), nullptr, L.r_cap);
+    mark(1);
     // 3. gate / up / SwiGLU
     PfGemmArgs g = {};
     g.w0 = p.gate, g.w1 = p.up, g.expert_bytes = (uint64_t)p.n_ff * xb * IQ2XXS_BYTES;
@@ -681,20 +686,24 @@ int launch_prefill_experts(cudaStream_t st, const PrefillArgs &p)
     g.weights = p.weights, g.out = p.mid, g.out_dim = p.n_ff, g.kblocks = xb, g.clamp = p.clamp, g.ieee = p.ieee;
     g.layout = p.layout, g.status = p.status;
     pf_grouped_gemm_kernel<PF_IQ2><<<sms, 256, PF_SMEM_TOTAL, st>>>(g);
+    mark(2);
     // 4. Q8_K of mid, tiles of it (with bsums)
     launch_q8k_quantize(st, p.mid, p.midq, p.n_ff, P);
     pf_gather_kernel<<<ggrid, 256, 0, st>>>(p.midq, mb, 1, u32p(L.sorted), u32p(L.tile_start), u32p(L.tile_rows),
                                             u32p(L.tile_boff), u32p(L.plan), w + L.bm,
                                             reinterpret_cast<float *>(w + L.sm), reinterpret_cast<__half *>(w + L.bs),
                                             L.r_cap);
+    mark(3);
     // 5. down
     PfGemmArgs d = g;
     d.w0 = p.down, d.w1 = nullptr, d.expert_bytes = (uint64_t)p.n_embd * mb * Q2K_BYTES;
     d.B = w + L.bm, d.S = reinterpret_cast<const float *>(w + L.sm), d.BS = reinterpret_cast<const __half *>(w + L.bs);
     d.weights = nullptr, d.out = reinterpret_cast<float *>(w + L.down_pair), d.out_dim = p.n_embd, d.kblocks = mb;
     pf_grouped_gemm_kernel<PF_Q2K><<<sms, 256, PF_SMEM_TOTAL, st>>>(d);
+    mark(4);
     // 6. slots summed in slot order
     launch_moe_sum(st, reinterpret_cast<const float *>(w + L.down_pair), p.out, p.n_embd, p.k, p.n_tokens);
+    mark(5);
     return n + 6;
 }
 

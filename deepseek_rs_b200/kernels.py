@@ -76,6 +76,15 @@ class MoeKernels:
         self._check(self.lib.dsmoe_device_status(self.h, _stream(), C.byref(code)))
         return code.value
 
+    def set_phase_events(self, events):
+        """Six torch.cuda.Event(enable_timing=True), already recorded once, or None to clear: the batched path records
+        them between its phases."""
+        if not events:
+            self._check(self.lib.dsmoe_set_phase_events(self.h, None, 0))
+            return
+        arr = (C.c_void_p * 6)(*[C.c_void_p(e.cuda_event) for e in events])
+        self._check(self.lib.dsmoe_set_phase_events(self.h, arr, 6))
+
     @property
     def launch_count(self) -> int:
         return int(self.lib.dsmoe_launch_count(self.h))

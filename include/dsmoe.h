@@ -87,6 +87,10 @@ DSMOE_API const char *dsmoe_last_error(const dsmoe_handle *h);
  * *code_out == 0, or DSMOE_ERR_TIMEOUT with the code. The reference has no device-side error reporting
  * (launch errors only, engine/src/session.rs `?` propagation). */
 DSMOE_API int dsmoe_device_status(dsmoe_handle *h, dsmoe_stream stream, int *code_out);
+/* Measurement aid with no counterpart in the reference: when six cudaEvent_t are set, the batched (grouped-GEMM) path
+ * of dsmoe_moe_forward records them on the stream at: start, pairs grouped + activations gathered, gate/up GEMM done,
+ * Q8_K(mid) + gather done, down GEMM done, slot sum done. Pass NULL / 0 to clear. */
+DSMOE_API int dsmoe_set_phase_events(dsmoe_handle *h, void **events, int n_events);
 /* Number of kernels this handle has launched since creation (bookkeeping for benchmarks). */
 DSMOE_API uint64_t dsmoe_launch_count(const dsmoe_handle *h);
 
