@@ -46,6 +46,7 @@ SIGNATURES = {
     "dsmoe_relayout_q2k": (_int, [_vp, _vp, _vp, _vp, _u64, _u32, _int]),
     "dsmoe_layer_register": (_int, [_vp, _u32, _vp, _vp, _vp, _int]),
     "dsmoe_moe_forward": (_int, [_vp, _vp, _u32, _vp, _vp, _u32, _vp, _vp, _vp]),
+    "dsmoe_expert_ffn": (_int, [_vp, _vp, _u32, _vp, _vp, _vp, _u32, _vp]),
     "dsmoe_moe_forward_host": (_int, [_vp, _u32, _vp, _vp, _u32, _vp, _vp, _vp]),
     "dsmoe_moe_forward_noalloc": (_int, [_vp, _vp, _vp, _vp, _int, _vp, _vp, _u32, _vp, _vp, _vp]),
 }

@@ -365,6 +365,32 @@ int dsmoe_layer_register(dsmoe_handle *h, uint32_t layer, const uint8_t *gate, c
     return DSMOE_OK;
 }
 
+// Everything after the router and the Q8_K of x: gate/up/SwiGLU -> Q8_K(mid) -> down -> slot sum, on the decode
+// kernels or, from prefill_min_tokens rows upwards, on the grouped GEMM.
+static int expert_ffn_impl(dsmoe_handle *h, cudaStream_t st, const dsmoe_layer_slot &ly, const uint8_t *xq,
+                           const int32_t *sel, const float *wts, uint32_t n_tokens, float *out, int n, const char *what)
+{
+    const dsmoe_config &c = h->cfg;
+    const uint32_t k = c.n_expert_used, xb = c.n_embd / QK_K, mb = c.n_ff / QK_K;
+    if (n_tokens >= h->prefill_min_tokens && prefill_eligible(c.n_embd, c.n_ff, ly.gate, ly.up, ly.down, ly.layout)) {
+        PrefillArgs p = {ly.gate, ly.up, ly.down, xq, sel, wts, h->mid, h->midq, out, h->pf_scratch, h->pf_lay,
+                         n_tokens, k, c.n_expert, c.n_embd, c.n_ff, c.swiglu_clamp, ly.layout, (int)c.f16_ieee,
+                         h->d_status, h->phase_events_set ? h->phase_events : nullptr};
+        n += launch_prefill_experts(st, p);
+        return check_launch(h, what, n);
+    }
+    if ((uint64_t)n_tokens * k > 65535u) return fail(h, DSMOE_ERR_BOUNDS, "%s: n_tokens*k exceeds 65535 on the decode kernels", what);
+    GateUpArgs g = {ly.gate, ly.up, xq, sel, wts, nullptr, nullptr, h->mid, (uint64_t)c.n_ff * xb * IQ2XXS_BYTES,
+                    (uint64_t)xb * IQ2XXS_BYTES, xb, c.n_ff, k, n_tokens, c.swiglu_clamp, ly.layout, (int)c.f16_ieee};
+    n += ((h->use_tma && gate_up_tma_eligible(g)) ? launch_gate_up_mid_tma(st, g, h->d_status)
+                                                  : launch_gate_up_mid(st, g));
+    launch_q8k_quantize(st, h->mid, h->midq, c.n_ff, n_tokens * k);
+    DownArgs d = {ly.down, h->midq, sel, out, (uint64_t)c.n_embd * mb * Q2K_BYTES, (uint64_t)mb * Q2K_BYTES, mb,
+                  c.n_embd, k, n_tokens, ly.layout, (int)c.f16_ieee, 1};
+    n += 1 + ((h->use_tma && down_tma_eligible(d)) ? launch_down_tma(st, d, h->d_status) : launch_down(st, d));
+    return check_launch(h, what, n);
+}
+
 int dsmoe_moe_forward(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, const float *x, const float *logits,
                       uint32_t n_tokens, float *out, int32_t *selected_out, float *weights_out)
 {
@@ -377,10 +403,9 @@ int dsmoe_moe_forward(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, cons
     if (n_tokens == 0) return DSMOE_OK;
     DSMOE_REQUIRE(h, x && logits && out, "moe_forward: null pointer");
     DSMOE_REQUIRE(h, aligned(x, 16), "moe_forward: x must be 16-byte aligned");
-    DSMOE_REQUIRE(h, (uint64_t)n_tokens * c.n_expert_used <= 65535u, "moe_forward: n_tokens*k exceeds 65535");
     const dsmoe_layer_slot &ly = h->layers[layer];
     cudaStream_t st = (cudaStream_t)stream;
-    const uint32_t k = c.n_expert_used, xb = c.n_embd / QK_K, mb = c.n_ff / QK_K;
+    const uint32_t k = c.n_expert_used;
     int32_t *sel = selected_out ? selected_out : h->selected;
     float *wts = weights_out ? weights_out : h->weights;
 
@@ -395,22 +420,22 @@ int dsmoe_moe_forward(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, cons
         launch_q8k_quantize(st, x, h->xq, c.n_embd, n_tokens);
         n = 2;
     }
-    if (n_tokens >= h->prefill_min_tokens && prefill_eligible(c.n_embd, c.n_ff, ly.gate, ly.up, ly.down, ly.layout)) {
-        PrefillArgs p = {ly.gate, ly.up, ly.down, h->xq, sel, wts, h->mid, h->midq, out, h->pf_scratch, h->pf_lay,
-                         n_tokens, k, c.n_expert, c.n_embd, c.n_ff, c.swiglu_clamp, ly.layout, (int)c.f16_ieee,
-                         h->d_status, h->phase_events_set ? h->phase_events : nullptr};
-        n += launch_prefill_experts(st, p);
-        return check_launch(h, "moe_forward (batched)", n);
-    }
-    GateUpArgs g = {ly.gate, ly.up, h->xq, sel, wts, nullptr, nullptr, h->mid, (uint64_t)c.n_ff * xb * IQ2XXS_BYTES,
-                    (uint64_t)xb * IQ2XXS_BYTES, xb, c.n_ff, k, n_tokens, c.swiglu_clamp, ly.layout, (int)c.f16_ieee};
-    n += ((h->use_tma && gate_up_tma_eligible(g)) ? launch_gate_up_mid_tma(st, g, h->d_status)
-                                                         : launch_gate_up_mid(st, g));
-    launch_q8k_quantize(st, h->mid, h->midq, c.n_ff, n_tokens * k);
-    DownArgs d = {ly.down, h->midq, sel, out, (uint64_t)c.n_embd * mb * Q2K_BYTES, (uint64_t)mb * Q2K_BYTES, mb,
-                  c.n_embd, k, n_tokens, ly.layout, (int)c.f16_ieee, 1};
-    n += 1 + ((h->use_tma && down_tma_eligible(d)) ? launch_down_tma(st, d, h->d_status) : launch_down(st, d));
-    return check_launch(h, "moe_forward", n);
+    return expert_ffn_impl(h, st, ly, h->xq, sel, wts, n_tokens, out, n, "moe_forward");
+}
+
+int dsmoe_expert_ffn(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, const uint8_t *xq, const int32_t *selected,
+                     const float *weights, uint32_t n_tokens, float *out)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    const dsmoe_config &c = h->cfg;
+    const uint32_t L = c.max_layers ? c.max_layers : 1;
+    if (layer >= L || !h->layers[layer].set) return fail(h, DSMOE_ERR_STATE, "expert_ffn: layer %u not registered", layer);
+    if (n_tokens > c.max_tokens)
+        return fail(h, DSMOE_ERR_BOUNDS, "expert_ffn: n_tokens %u exceeds max_tokens %u", n_tokens, c.max_tokens);
+    if (n_tokens == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, xq && selected && weights && out, "expert_ffn: null pointer");
+    DSMOE_REQUIRE(h, aligned(xq, 16), "expert_ffn: xq must be 16-byte aligned");
+    return expert_ffn_impl(h, (cudaStream_t)stream, h->layers[layer], xq, selected, weights, n_tokens, out, 0, "expert_ffn");
 }
 
 int dsmoe_moe_forward_host(dsmoe_handle *h, uint32_t layer, const float *x_host, const float *logits_host,

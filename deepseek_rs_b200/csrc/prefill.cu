@@ -28,6 +28,9 @@ constexpr int PF_TN = 128;       // token rows per tile (MMA N), padded to a mul
 constexpr int PF_KS = 128;       // K elements per pipeline stage (half a superblock)
 constexpr int PF_STAGE_A = 128 * PF_KS * 2;  // 32 KB: 128 weight rows
 constexpr int PF_SBO = (PF_KS / 8) * 128;    // 2048: byte distance between 8-row groups in a stage
+constexpr int PF_THREADS = 256;  // 8 warps: two per TMEM lane quadrant, each draining PF_COLS accumulator columns (512 threads measured slower)
+constexpr int PF_COLS = PF_TN / (PF_THREADS / 128);
+constexpr int PF_PASSES = 128 / (PF_THREADS / 32 * 8);  // decode passes: a warp decodes 8 rows per pass
 
 // ---------------------------------------------------------------------------------------------------------------
 // 1. grouping: deterministic and stable (pairs of an expert keep ascending pair order), unlike the reference's
@@ -314,7 +317,7 @@ __device__ __forceinline__ uint32_t pf_visit_block(uint32_t kblocks, uint32_t j)
 }
 
 template <int KIND>
-__global__ void __launch_bounds__(256, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
+__global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t *bar_full = reinterpret_cast<uint64_t *>(smem + PF_SMEM_BAR);       // [2] activation stage landed
@@ -331,7 +334,7 @@ __global__ void __launch_bounds__(256, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
     const bool ieee = a.ieee != 0;
 
     if (KIND == PF_IQ2) {
-        for (int i = tid; i < 256; i += 256) {
+        for (int i = tid; i < 256; i += PF_THREADS) {
             const uint64_t g = c_iq2xxs_grid[i];
             lut_grid[i] = pf_bytes_to_f16x8((uint32_t)g, (uint32_t)(g >> 32));
         }
@@ -362,7 +365,7 @@ __global__ void __launch_bounds__(256, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
     // this thread in the decode phase: lane = c * 8 + r8 -> quarter c of the stage, row 16 warp + 8 pass + r8
     const uint32_t dc = lane >> 3, dr8 = lane & 7;
     // this thread in the drain phase: accumulator row and column half
-    const uint32_t arow = 32 * (warp & 3) + lane, acol0 = 64 * (warp >> 2);
+    const uint32_t arow = 32 * (warp & 3) + lane, acol0 = PF_COLS * (warp >> 2);
     const uint32_t tlane = (32u * (warp & 3)) << 16;
 
     uint32_t gs = 0, gsb = 0;  // stages / superblocks issued so far by this CTA (mbarrier and TMEM phase tracking)
@@ -378,10 +381,10 @@ __global__ void __launch_bounds__(256, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
         const uint8_t *btile = a.B + (size_t)boff * a.kblocks * 512;
 
         // weight rows this thread decodes (two passes) and the row it drains
-        const uint8_t *drow[2];
+        const uint8_t *drow[PF_PASSES];
 #pragma unroll
-        for (int p = 0; p < 2; ++p) {
-            const uint32_t rl = 16 * warp + 8 * p + dr8;
+        for (int p = 0; p < PF_PASSES; ++p) {
+            const uint32_t rl = 8 * PF_PASSES * warp + 8 * p + dr8;
             if (KIND == PF_IQ2) drow[p] = (rl < 64 ? a.w0 : a.w1) + ebase + (uint64_t)(mt * 64 + (rl & 63)) * row_bytes;
             else drow[p] = a.w0 + ebase + (uint64_t)(mt * 128 + rl) * row_bytes;
         }
@@ -389,17 +392,19 @@ __global__ void __launch_bounds__(256, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
         if (KIND == PF_IQ2) srow = (arow < 64 ? a.w0 : a.w1) + ebase + (uint64_t)(mt * 64 + (arow & 63)) * row_bytes;
         else srow = a.w0 + ebase + (uint64_t)(mt * 128 + arow) * row_bytes;
 
-        for (uint32_t i = tid; i < a.kblocks * rows16; i += 256) {
+        for (uint32_t i = tid; i < a.kblocks * rows16; i += PF_THREADS) {
             const uint32_t kb = i / rows16, c = i - kb * rows16;
             sS[kb * PF_TN + c] = a.S[(size_t)kb * a.r_cap + boff + c];
         }
-        float acc[64];                          // Q2K: running sum. IQ2: the current leaf's partial a_l
-        float p1[64];                           // IQ2: pair level of the reduction tree, finally the row total
+        float acc[PF_COLS];                         // Q2K: running sum. IQ2: the current leaf's partial a_l
+        float p1[PF_COLS];                         // IQ2: pair level of the reduction tree, finally the row total
 #pragma unroll
-        for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+        for (int i = 0; i < PF_COLS; ++i) acc[i] = 0.0f;
 
         const uint32_t kb0 = pf_visit_block<KIND>(a.kblocks, 0);
-        uint2 pk[2] = {pf_load_packed<KIND>(drow[0], a.layout, kb0, 0, dc), pf_load_packed<KIND>(drow[1], a.layout, kb0, 0, dc)};
+        uint2 pk[PF_PASSES];
+#pragma unroll
+        for (int p = 0; p < PF_PASSES; ++p) pk[p] = pf_load_packed<KIND>(drow[p], a.layout, kb0, 0, dc);
 
         auto drain = [&](uint32_t j, uint32_t buf) {
             const uint32_t kb = pf_visit_block<KIND>(a.kblocks, j);
@@ -420,7 +425,7 @@ __global__ void __launch_bounds__(256, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
             }
             const float *sx = sS + kb * PF_TN + acol0;
 #pragma unroll
-            for (int c0 = 0; c0 < 64; c0 += 16) {
+            for (int c0 = 0; c0 < PF_COLS; c0 += 16) {
                 if (acol0 + c0 >= rows16) break;  // warp-uniform: columns beyond the padded tile hold nothing
                 float v[16], v2[16];
                 tc05_ld16(tmem + tlane + buf * PF_TN + acol0 + c0, v);
@@ -443,7 +448,7 @@ __global__ void __launch_bounds__(256, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
                 // fold the finished leaf a_l (in acc) into the tree: P1 = pair sums (registers), P2 = quad sums and
                 // P3 = the even half (TMEM columns 256.. and 384.., used as spill space)
 #pragma unroll
-                for (int c0 = 0; c0 < 64; c0 += 16) {
+                for (int c0 = 0; c0 < PF_COLS; c0 += 16) {
                     if (acol0 + c0 >= rows16) break;
                     const uint32_t t2 = tmem + tlane + 256u + acol0 + c0, t3 = tmem + tlane + 384u + acol0 + c0;
                     float w[16];
@@ -494,16 +499,18 @@ __global__ void __launch_bounds__(256, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
                              &bar_full[b]);
             }
             // 3. decode this stage's weights; fetch the next stage's packed bytes meanwhile
-            uint2 nx[2] = {pk[0], pk[1]};
+            uint2 nx[PF_PASSES];
+#pragma unroll
+            for (int p = 0; p < PF_PASSES; ++p) nx[p] = pk[p];
             if (s + 1 < n_stages) {
                 const uint32_t nkb = pf_visit_block<KIND>(a.kblocks, (s + 1) >> 1);
-                nx[0] = pf_load_packed<KIND>(drow[0], a.layout, nkb, (s + 1) & 1, dc);
-                nx[1] = pf_load_packed<KIND>(drow[1], a.layout, nkb, (s + 1) & 1, dc);
+#pragma unroll
+                for (int p = 0; p < PF_PASSES; ++p) nx[p] = pf_load_packed<KIND>(drow[p], a.layout, nkb, (s + 1) & 1, dc);
             }
             uint8_t *sA = smem + PF_SMEM_A + b * PF_STAGE_A;
 #pragma unroll
-            for (int p = 0; p < 2; ++p) {
-                const uint32_t rl = 16 * warp + 8 * p + dr8;
+            for (int p = 0; p < PF_PASSES; ++p) {
+                const uint32_t rl = 8 * PF_PASSES * warp + 8 * p + dr8;
                 uint8_t *dst = sA + (rl >> 3) * PF_SBO + (rl & 7) * 16;
                 if (KIND == PF_IQ2) {
                     pf_decode_iq2(pk[p], dst + dc * 512, lut_grid, lut_sign);
@@ -517,8 +524,8 @@ __global__ void __launch_bounds__(256, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
                     }
                 }
             }
-            pk[0] = nx[0];
-            pk[1] = nx[1];
+#pragma unroll
+            for (int p = 0; p < PF_PASSES; ++p) pk[p] = nx[p];
             // 4. generic-proxy writes -> visible to the tensor core (async proxy); everyone has finished draining
             fence_async_smem();
             tc05_fence_before_sync();
@@ -562,9 +569,9 @@ __global__ void __launch_bounds__(256, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
         // epilogue
         if (KIND == PF_IQ2) {
 #pragma unroll
-            for (int i = 0; i < 64; ++i) sX[arow * PF_XSTRIDE + acol0 + i] = p1[i];
+            for (int i = 0; i < PF_COLS; ++i) sX[arow * PF_XSTRIDE + acol0 + i] = p1[i];
             __syncthreads();
-            for (uint32_t i = tid; i < 64u * rows; i += 256) {
+            for (uint32_t i = tid; i < 64u * rows; i += PF_THREADS) {
                 const uint32_t col = i >> 6, r = i & 63;
                 float g = sX[r * PF_XSTRIDE + col], u = sX[(64 + r) * PF_XSTRIDE + col];
                 if (a.clamp > 1.0e-6f) {
@@ -577,7 +584,7 @@ __global__ void __launch_bounds__(256, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
+            for (int i = 0; i < PF_COLS; ++i) {
                 const uint32_t col = acol0 + i;
                 if (col < rows) a.out[(size_t)a.sorted[start + col] * a.out_dim + mt * 128 + arow] = acc[i];
             }
@@ -685,7 +692,7 @@ int launch_prefill_experts(cudaStream_t st, const PrefillArgs &p)
     g.tile_rows = u32p(L.tile_rows), g.tile_boff = u32p(L.tile_boff), g.plan = u32p(L.plan);
     g.weights = p.weights, g.out = p.mid, g.out_dim = p.n_ff, g.kblocks = xb, g.clamp = p.clamp, g.ieee = p.ieee;
     g.layout = p.layout, g.status = p.status;
-    pf_grouped_gemm_kernel<PF_IQ2><<<sms, 256, PF_SMEM_TOTAL, st>>>(g);
+    pf_grouped_gemm_kernel<PF_IQ2><<<sms, PF_THREADS, PF_SMEM_TOTAL, st>>>(g);
     mark(2);
     // 4. Q8_K of mid, tiles of it (with bsums)
     launch_q8k_quantize(st, p.mid, p.midq, p.n_ff, P);
@@ -699,7 +706,7 @@ int launch_prefill_experts(cudaStream_t st, const PrefillArgs &p)
     d.w0 = p.down, d.w1 = nullptr, d.expert_bytes = (uint64_t)p.n_embd * mb * Q2K_BYTES;
     d.B = w + L.bm, d.S = reinterpret_cast<const float *>(w + L.sm), d.BS = reinterpret_cast<const __half *>(w + L.bs);
     d.weights = nullptr, d.out = reinterpret_cast<float *>(w + L.down_pair), d.out_dim = p.n_embd, d.kblocks = mb;
-    pf_grouped_gemm_kernel<PF_Q2K><<<sms, 256, PF_SMEM_TOTAL, st>>>(d);
+    pf_grouped_gemm_kernel<PF_Q2K><<<sms, PF_THREADS, PF_SMEM_TOTAL, st>>>(d);
     mark(4);
     // 6. slots summed in slot order
     launch_moe_sum(st, reinterpret_cast<const float *>(w + L.down_pair), p.out, p.n_embd, p.k, p.n_tokens);

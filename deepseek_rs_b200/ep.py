@@ -1,0 +1,127 @@
+"""Expert-parallel execution of the routed-expert step across the GPUs of one box.
+
+The reference is single-GPU (one context, one stream, engine/src/engine.rs:73-74); sharding is new here and is defined
+by "same result as one GPU". Layout: rank r of G owns experts [r*E/G, (r+1)*E/G) (all three tensors) and routes its own
+tokens. One exchange each way:
+
+  dispatch  every routed (token, slot) pair goes to the rank that owns its expert, as the token's Q8_K row (4672 B
+            instead of 16 KB of f32) plus (local expert id, router weight);
+  combine   the owner returns the pair's down-projection row (f32 [n_embd]); the source sums a token's k rows in slot
+            order, so the result does not depend on arrival order.
+
+The exchanges are ``torch.distributed.all_to_all_single`` (NCCL over NVLink on GPUs, gloo in the CPU tests); the
+compute on each side goes through the C ABI (``MoeKernels``). Split sizes are exchanged first and read on the host,
+which costs one synchronisation per step. ``route_fn`` / ``expert_fn`` can be replaced, which is how the CPU tests run
+the same plan with the oracle standing in for the kernels.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from .formats import Q8K_BYTES, QK_K
+
+
+@dataclass
+class DispatchPlan:
+    """Where each local pair goes. ``order`` lists local pair ids grouped by destination rank, ascending pair id inside
+    a group (stable), ``send_counts[d]`` pairs go to rank d, ``recv_counts[s]`` pairs come from rank s."""
+    order: torch.Tensor
+    send_counts: list
+    recv_counts: list
+
+
+def make_plan(selected: torch.Tensor, n_expert: int, world: int, group=None) -> DispatchPlan:
+    """selected: int32 [T, k] global expert ids (negative ids go to expert 0, as the kernels clamp them)."""
+    per_rank = n_expert // world
+    dest = (selected.reshape(-1).clamp(min=0).to(torch.int64) // per_rank)
+    order = torch.sort(dest, stable=True).indices
+    send = torch.bincount(dest, minlength=world).to(torch.int64)
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    return DispatchPlan(order, [int(v) for v in send.cpu()], [int(v) for v in recv.cpu()])
+
+
+def _exchange(buf: torch.Tensor, send_counts, recv_counts, group=None) -> torch.Tensor:
+    """all_to_all_single over the first dimension with the given row counts."""
+    out = buf.new_empty((sum(recv_counts),) + tuple(buf.shape[1:]))
+    dist.all_to_all_single(out, buf.contiguous(), output_split_sizes=list(recv_counts),
+                           input_split_sizes=list(send_counts), group=group)
+    return out
+
+
+class ExpertParallelMoe:
+    """One layer's routed experts sharded over the ranks of ``group``.
+
+    route_fn(x, logits) -> (xq uint8 [T, n_embd/256, 292], selected int32 [T, k], weights f32 [T, k])
+    expert_fn(xq_rows, local_expert int32 [R, 1], weights f32 [R, 1]) -> f32 [R, n_embd]   (k = 1 on the owner)
+    """
+
+    def __init__(self, route_fn, expert_fn, n_expert: int, k: int, n_embd: int, group=None):
+        self.route_fn, self.expert_fn = route_fn, expert_fn
+        self.n_expert, self.k, self.n_embd = n_expert, k, n_embd
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        assert n_expert % self.world == 0, "experts must divide evenly over the ranks"
+        self.per_rank = n_expert // self.world
+        self.last_plan = None
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor):
+        """x f32 [T, n_embd], logits f32 [T, n_expert] (this rank's tokens). Returns (out f32 [T, n_embd], selected)."""
+        T = x.shape[0]
+        xq, selected, weights = self.route_fn(x, logits)
+        plan = make_plan(selected, self.n_expert, self.world, self.group)
+        self.last_plan = plan
+        pair_tok = plan.order // self.k
+        # dispatch: Q8_K row of the pair's token, local expert id, router weight
+        xq_rows = xq.reshape(T, (self.n_embd // QK_K) * Q8K_BYTES)[pair_tok]
+        sel_flat = selected.reshape(-1).clamp(min=0)[plan.order]
+        meta_e = (sel_flat % self.per_rank).to(torch.int32).reshape(-1, 1)
+        meta_w = weights.reshape(-1)[plan.order].reshape(-1, 1).contiguous()
+        r_xq = _exchange(xq_rows, plan.send_counts, plan.recv_counts, self.group)
+        r_e = _exchange(meta_e, plan.send_counts, plan.recv_counts, self.group)
+        r_w = _exchange(meta_w, plan.send_counts, plan.recv_counts, self.group)
+        # the owner's compute: every received row is one (token, slot) pair of one local expert
+        if r_xq.shape[0]:
+            rows = self.expert_fn(r_xq.reshape(r_xq.shape[0], self.n_embd // QK_K, Q8K_BYTES), r_e, r_w)
+        else:
+            rows = x.new_empty((0, self.n_embd))
+        # combine: rows travel back along the same splits, land in dispatch order, are put back in pair order and
+        # summed per token in slot order
+        back = _exchange(rows, plan.recv_counts, plan.send_counts, self.group)
+        pair_rows = torch.empty((T * self.k, self.n_embd), dtype=back.dtype, device=back.device)
+        pair_rows[plan.order] = back
+        pr = pair_rows.reshape(T, self.k, self.n_embd)
+        out = torch.zeros((T, self.n_embd), dtype=back.dtype, device=back.device)
+        for s in range(self.k):  # 0 + r0 + r1 + ..., the order of the reference's slot sum (moe.rs:937-968, 983-1005)
+            out = out + pr[:, s]
+        return out, selected
+
+
+def gpu_functions(kernels_route, kernels_owner, layer: int = 0):
+    """route_fn / expert_fn over the C ABI. ``kernels_route``: a MoeKernels with the model's k (router + Q8_K only);
+    ``kernels_owner``: a MoeKernels created with n_expert = experts per rank and n_expert_used = 1, holding this rank's
+    shard in ``layer``."""
+    cfg = kernels_route.cfg
+
+    def route_fn(x, logits):
+        T = x.shape[0]
+        dev = x.device
+        probs = torch.empty((T, cfg.n_expert), dtype=torch.float32, device=dev)
+        sel = torch.empty((T, cfg.n_expert_used), dtype=torch.int32, device=dev)
+        w = torch.empty((T, cfg.n_expert_used), dtype=torch.float32, device=dev)
+        xq = torch.empty((T, cfg.n_embd // QK_K, Q8K_BYTES), dtype=torch.uint8, device=dev)
+        kernels_route.router_select_parallel(logits, None, None, None, probs, sel, w, 0, 0, T, 0, 0)
+        kernels_route.q8k_quantize(x, xq, cfg.n_embd, T)
+        return xq, sel, w
+
+    def expert_fn(xq_rows, local_expert, weights):
+        R = xq_rows.shape[0]
+        out = torch.empty((R, cfg.n_embd), dtype=torch.float32, device=xq_rows.device)
+        kernels_owner.expert_ffn(layer, xq_rows.contiguous(), local_expert.contiguous(), weights.contiguous(), R, out)
+        return out
+
+    return route_fn, expert_fn

@@ -163,6 +163,11 @@ class MoeKernels:
         self._check(self.lib.dsmoe_moe_forward(self.h, _stream(), layer, _ptr(x), _ptr(logits), n_tokens, _ptr(out),
                                                _ptr(selected_out), _ptr(weights_out)))
 
+    def expert_ffn(self, layer: int, xq, selected, weights, n_tokens: int, out):
+        """Rows already routed and Q8_K-quantised -> slot-summed expert output (what an expert-parallel rank runs)."""
+        self._check(self.lib.dsmoe_expert_ffn(self.h, _stream(), layer, _ptr(xq), _ptr(selected), _ptr(weights),
+                                              n_tokens, _ptr(out)))
+
     def moe_forward_host(self, layer: int, x_host, logits_host, n_tokens: int, out_host, selected_host=None,
                          weights_host=None):
         """Host (ideally pinned) tensors in and out; copies and a stream wait happen inside the call."""

@@ -170,6 +170,13 @@ DSMOE_API int dsmoe_moe_forward(dsmoe_handle *h, dsmoe_stream stream, uint32_t l
                                 const float *logits, uint32_t n_tokens, float *out, int32_t *selected_out,
                                 float *weights_out);
 
+/* The part of dsmoe_moe_forward after the router and the Q8_K of x (engine/src/session.rs:2075-2155): gate/up/SwiGLU,
+ * Q8_K(mid), down, slot sum, for rows that are already routed and quantised. xq: Q8_K [n_tokens][n_embd/256];
+ * selected / weights: [n_tokens][k] with k from the handle's config. This is what an expert-parallel rank runs on the
+ * rows it received (with a handle created for n_expert_used = 1 and expert ids local to its shard). */
+DSMOE_API int dsmoe_expert_ffn(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, const uint8_t *xq,
+                               const int32_t *selected, const float *weights, uint32_t n_tokens, float *out);
+
 /* Same with host buffers: copies x and logits in, runs dsmoe_moe_forward on an internal stream, copies out (and the
  * optional routing) back and waits. Host buffers should be page-locked for full copy speed. */
 DSMOE_API int dsmoe_moe_forward_host(dsmoe_handle *h, uint32_t layer, const float *x_host, const float *logits_host,

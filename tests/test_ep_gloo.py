@@ -1,0 +1,90 @@
+"""Expert-parallel dispatch / combine on two CPU ranks (gloo): the plan, the all-to-all exchanges and the slot-order
+combine of deepseek_rs_b200/ep.py, with the oracle standing in for the kernels on each rank. The sharded result must
+equal the single-rank oracle layer bit for bit, and the routing must be identical."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+
+    import oracle
+    from deepseek_rs_b200 import formats as F
+    from deepseek_rs_b200.ep import ExpertParallelMoe
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    oracle.set_num_threads(2)
+    n_e, n_embd, n_ff, k, T = 8, 512, 256, 3, 5 + rank  # ragged: ranks hold different token counts
+    lw = F.ExpertLayer(seed=41, n_expert=n_e, n_embd=n_embd, n_ff=n_ff)
+    per = n_e // world
+    gsh = lw.gate.reshape(n_e, -1)[rank * per:(rank + 1) * per].reshape(-1)
+    ush = lw.up.reshape(n_e, -1)[rank * per:(rank + 1) * per].reshape(-1)
+    dsh = lw.down.reshape(n_e, -1)[rank * per:(rank + 1) * per].reshape(-1)
+    rng = np.random.default_rng(100)  # same stream on both ranks; each takes its slice
+    x_all = rng.standard_normal((11, n_embd)).astype(np.float32)
+    lg_all = rng.standard_normal((11, n_e)).astype(np.float32)
+    lg_all[0, :] = 0.5  # ties: lowest expert ids win on every rank alike
+    lo = 0 if rank == 0 else 5
+    x, lg = x_all[lo:lo + T], lg_all[lo:lo + T]
+
+    def route_fn(xt, lt):
+        _, sel, w = oracle.router_select(lt.numpy(), k=k)
+        return torch.from_numpy(oracle.q8k_quantize(xt.numpy())), torch.from_numpy(sel), torch.from_numpy(w)
+
+    def expert_fn(xq_rows, local_e, w):
+        _, _, mid = oracle.gate_up_mid(gsh, ush, xq_rows.numpy(), local_e.numpy(), w.numpy(), n_ff, n_embd // 256)
+        midq = oracle.q8k_quantize(mid)
+        return torch.from_numpy(oracle.down(dsh, midq, local_e.numpy(), n_embd, n_ff // 256))
+
+    ep = ExpertParallelMoe(route_fn, expert_fn, n_e, k, n_embd)
+    out, sel = ep.forward(torch.from_numpy(x), torch.from_numpy(lg))
+    ref_out, ref_sel, _ = oracle.moe_layer(x, lg, lw.gate, lw.up, lw.down, k=k, n_ff=n_ff)
+    ok = bool(np.array_equal(out.numpy(), ref_out) and np.array_equal(sel.numpy(), ref_sel))
+    sent = sum(ep.last_plan.send_counts)
+    # a second step with no tokens on rank 1: empty sends and receives must not hang or mis-size anything
+    T2 = 4 if rank == 0 else 0
+    out2, _ = ep.forward(torch.from_numpy(x_all[:T2]), torch.from_numpy(lg_all[:T2]))
+    if T2:
+        ref2, _, _ = oracle.moe_layer(x_all[:T2], lg_all[:T2], lw.gate, lw.up, lw.down, k=k, n_ff=n_ff)
+        ok = ok and bool(np.array_equal(out2.numpy(), ref2))
+    else:
+        ok = ok and out2.shape == (0, n_embd)
+    q.put((rank, ok, sent, T * k))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_expert_parallel_two_ranks_matches_single_rank():
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, ok, sent, pairs in results:
+        assert ok, f"rank {rank}: sharded result differs from the single-rank layer"
+        assert sent == pairs  # every pair was dispatched exactly once
