@@ -44,6 +44,8 @@ SIGNATURES = {
     "dsmoe_dequant_q2k": (_int, [_vp, _vp, _vp, _u64, _vp]),
     "dsmoe_relayout_iq2xxs": (_int, [_vp, _vp, _vp, _vp, _u64, _u32, _int]),
     "dsmoe_relayout_q2k": (_int, [_vp, _vp, _vp, _vp, _u64, _u32, _int]),
+    "dsmoe_fp8_quantize": (_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _int]),
+    "dsmoe_fp8_linear": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32]),
     "dsmoe_layer_register": (_int, [_vp, _u32, _vp, _vp, _vp, _int]),
     "dsmoe_moe_forward": (_int, [_vp, _vp, _u32, _vp, _vp, _u32, _vp, _vp, _vp]),
     "dsmoe_expert_ffn": (_int, [_vp, _vp, _u32, _vp, _vp, _vp, _u32, _vp]),

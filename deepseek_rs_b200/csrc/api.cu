@@ -347,6 +347,34 @@ int dsmoe_relayout_q2k(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *src,
 }
 
 // ---------------------------------------------------------------------------------------------------------------
+// FP8 block-scaled projection
+// ---------------------------------------------------------------------------------------------------------------
+
+int dsmoe_fp8_quantize(dsmoe_handle *h, dsmoe_stream stream, const float *x, uint8_t *codes, float *scales,
+                       uint32_t rows, uint32_t cols, int rows_per_block)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_REQUIRE(h, rows_per_block == 1 || rows_per_block == 128, "fp8_quantize: rows_per_block must be 1 or 128");
+    DSMOE_REQUIRE(h, cols % 128 == 0, "fp8_quantize: cols %u is not a multiple of 128", cols);
+    if (rows == 0 || cols == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, x && codes && scales && aligned(x, 16) && aligned(codes, 4), "fp8_quantize: null or misaligned pointer");
+    launch_fp8_quantize((cudaStream_t)stream, x, codes, scales, rows, cols, rows_per_block);
+    return check_launch(h, "fp8_quantize", 1);
+}
+
+int dsmoe_fp8_linear(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *a_fp8, const float *a_scale,
+                     const uint8_t *w_fp8, const float *w_scale, void *out_bf16, uint32_t M, uint32_t N, uint32_t K)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_REQUIRE(h, K % 128 == 0 && N % 128 == 0 && K > 0, "fp8_linear: N %u and K %u must be multiples of 128", N, K);
+    if (M == 0 || N == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, a_fp8 && a_scale && w_fp8 && w_scale && out_bf16, "fp8_linear: null pointer");
+    DSMOE_REQUIRE(h, aligned(a_fp8, 16) && aligned(w_fp8, 16) && aligned(out_bf16, 4), "fp8_linear: misaligned pointer");
+    int n = launch_fp8_linear((cudaStream_t)stream, a_fp8, a_scale, w_fp8, w_scale, out_bf16, M, N, K, h->d_status);
+    return check_launch(h, "fp8_linear", n);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
 // tier 2
 // ---------------------------------------------------------------------------------------------------------------
 

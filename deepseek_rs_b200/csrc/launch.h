@@ -83,4 +83,10 @@ struct PrefillArgs {
 // Everything after the router and the Q8_K of x. Returns the number of kernels launched.
 int launch_prefill_experts(cudaStream_t st, const PrefillArgs &p);
 
+// FP8 E4M3 block-scaled projection. rows_per_block = 1 (activations, 1 x 128 blocks) or 128 (weights, 128 x 128).
+void launch_fp8_quantize(cudaStream_t st, const float *x, uint8_t *codes, float *scales, uint32_t rows, uint32_t cols,
+                         int rows_per_block);
+int launch_fp8_linear(cudaStream_t st, const uint8_t *a, const float *a_scale, const uint8_t *w, const float *w_scale,
+                      void *out_bf16, uint32_t M, uint32_t N, uint32_t K, int *status);
+
 }  // namespace dsmoe

@@ -154,6 +154,16 @@ class MoeKernels:
         self._check(self.lib.dsmoe_relayout_q2k(self.h, _stream(), _ptr(src), _ptr(dst), n_rows, blocks_per_row,
                                                 int(inverse)))
 
+    # ---- FP8 block-scaled projection -------------------------------------------------------------------------
+
+    def fp8_quantize(self, x, codes, scales, rows: int, cols: int, rows_per_block: int):
+        self._check(self.lib.dsmoe_fp8_quantize(self.h, _stream(), _ptr(x), _ptr(codes), _ptr(scales), rows, cols,
+                                                rows_per_block))
+
+    def fp8_linear(self, a_codes, a_scale, w_codes, w_scale, out_bf16, M: int, N: int, K: int):
+        self._check(self.lib.dsmoe_fp8_linear(self.h, _stream(), _ptr(a_codes), _ptr(a_scale), _ptr(w_codes),
+                                              _ptr(w_scale), _ptr(out_bf16), M, N, K))
+
     # ---- tier 2 ---------------------------------------------------------------------------------------------------
 
     def layer_register(self, layer: int, gate, up, down, layout: int):

@@ -154,6 +154,25 @@ DSMOE_API int dsmoe_relayout_q2k(dsmoe_handle *h, dsmoe_stream stream, const uin
                                  uint64_t n_rows, uint32_t blocks_per_row, int inverse);
 
 /* ------------------------------------------------------------------------------------------------------------ */
+/* FP8 E4M3 block-scaled dense projection                                                                         */
+/* ------------------------------------------------------------------------------------------------------------ */
+
+/* No FP8 GEMM exists in the reference: its dense projections are Q8_0 x Q8_0 matvecs
+ * (engine/src/kernels/matmul.rs:357-603) and E4M3 is only used to round KV rows (engine/src/kernels/quantize.rs:10-134,
+ * whose rounding rule these codes follow: nearest, ties to the even code, saturating at 448). These two calls stand
+ * where quantize_q8_0 + matmul_q8_0_preq_warp8 stand for a projection (engine/src/session.rs:1329-1437).
+ *
+ * dsmoe_fp8_quantize: x f32 [rows][cols] -> codes u8 [rows][cols], scales f32 [ceil(rows/rpb)][cols/128] with
+ * scale = max(amax, 1e-4) / 448 per rpb x 128 block; rows_per_block = 1 for activations, 128 for weights.
+ * dsmoe_fp8_linear: out bf16 [M][N] = sum over 128-wide K blocks of a_scale[m][kb] * w_scale[n/128][kb] * (a . w),
+ * a: [M][K] codes, w: [N][K] codes; N and K multiples of 128. */
+DSMOE_API int dsmoe_fp8_quantize(dsmoe_handle *h, dsmoe_stream stream, const float *x, uint8_t *codes, float *scales,
+                                 uint32_t rows, uint32_t cols, int rows_per_block);
+DSMOE_API int dsmoe_fp8_linear(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *a_fp8, const float *a_scale,
+                               const uint8_t *w_fp8, const float *w_scale, void *out_bf16, uint32_t M, uint32_t N,
+                               uint32_t K);
+
+/* ------------------------------------------------------------------------------------------------------------ */
 /* Tier 2: the routed-expert step as one call                                                                     */
 /* ------------------------------------------------------------------------------------------------------------ */
 
