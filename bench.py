@@ -41,6 +41,8 @@ WORKLOADS = {
     "moe_decode_b64": dict(tokens=64, layers=2, zipf=False),
     # prefill chunk: router logits N(0,1) - 1.1 ln(rank) (Zipf s = 1.1 expert popularity), tcgen05 grouped GEMM
     "moe_prefill_4096": dict(tokens=4096, layers=2, zipf=True),
+    # FP8 E4M3 block-scaled dense projection (no counterpart in the reference), all six (M, N) shapes in one line
+    "fp8_linear": dict(tokens=4096, layers=0, zipf=False),
 }
 DEFAULT_WORKLOAD = "moe_prefill_4096"
 METRIC, UNIT = "moe_expert_layer_tokens_per_s", "tokens/s"
@@ -322,6 +324,96 @@ def run_prefill(args, torch, dist, K, layers, layout, device, rank, world, sampl
     print(json.dumps(line), flush=True)
 
 
+def run_fp8(args, torch, dist, K, device, rank, world, sampler):
+    """Activations f32 -> E4M3 codes + 1x128 scales -> GEMM with 128x128-block-scaled weights -> bf16. A step is one
+    projection of M rows; the headline shape is M = 4096, N = K = 4096."""
+    Kdim, R = 4096, 16  # R weight matrices rotate so that no step finds its weights in L2 (16 x 16.8 MB)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(11 + rank)
+    results, t_load0 = [], time.time()
+    for N in (4096, 1536):
+        ws = []
+        for r in range(R):
+            w = torch.randn((N, Kdim), device=device, generator=gen)
+            wc = torch.empty((N, Kdim), dtype=torch.uint8, device=device)
+            wsc = torch.empty((N // 128, Kdim // 128), device=device)
+            K.fp8_quantize(w, wc, wsc, N, Kdim, 128)
+            ws.append((wc, wsc))
+        for M in (1, 128, 4096):
+            x = torch.randn((M, Kdim), device=device, generator=gen)
+            ac = torch.empty((M, Kdim), dtype=torch.uint8, device=device)
+            asc = torch.empty((M, Kdim // 128), device=device)
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+            K.fp8_quantize(x, ac, asc, M, Kdim, 1)
+            steps = args.steps if M >= 128 else max(args.steps, 200)
+            for i in range(args.warmup):
+                K.fp8_linear(ac, asc, *ws[i % R], out, M, N, Kdim)
+            g = torch.cuda.CUDAGraph()
+            cs = torch.cuda.Stream()
+            cs.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(cs):
+                torch.cuda.synchronize()
+                with torch.cuda.graph(g, stream=cs):
+                    for i in range(R):
+                        K.fp8_linear(ac, asc, *ws[i], out, M, N, Kdim)
+            torch.cuda.current_stream().wait_stream(cs)
+            g.replay()
+            torch.cuda.synchronize()
+            reps = max(1, steps // R)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / (reps * R)
+            # end to end: pinned f32 rows in, quantise, project, bf16 rows back
+            xh, oh = x.cpu().pin_memory(), torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+            n_e2e = 20
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for i in range(n_e2e):
+                xd = xh.to(device, non_blocking=True)
+                K.fp8_quantize(xd, ac, asc, M, Kdim, 1)
+                K.fp8_linear(ac, asc, *ws[i % R], out, M, N, Kdim)
+                oh.copy_(out, non_blocking=True)
+                torch.cuda.synchronize()
+            e2e_ms = (time.perf_counter() - t0) * 1e3 / n_e2e
+            results.append(dict(M=M, N=N, K=Kdim, ms=ms, tflops=2.0 * M * N * Kdim / (ms * 1e-3) / 1e12,
+                                weight_gbs=N * Kdim / (ms * 1e-3) / 1e9, e2e_ms=e2e_ms, steps=reps * R))
+        del ws
+    assert K.device_status() == 0
+    while time.time() - t_load0 < 2.0:
+        g.replay()
+        torch.cuda.synchronize()
+    clocks = sampler.stop(window=(t_load0, time.time()))
+    if rank != 0:
+        return
+    head = next(r for r in results if r["M"] == 4096 and r["N"] == 4096)
+    mv = next(r for r in results if r["M"] == 1 and r["N"] == 4096)
+    peak_tf, kind = measured_tflops()
+    hbm, _ = measured_peaks()
+    line = {
+        "metric": METRIC, "value": head["M"] * world / (head["ms"] * 1e-3), "unit": UNIT, "n_gpus": world,
+        "steps": head["steps"], "warmup": args.warmup, "ms_per_step": head["ms"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp8 e4m3 x fp8 e4m3, f32 accumulate, bf16 out",
+        "data": "synthetic",
+        "config": {"workload": "fp8_linear", "M": 4096, "N": 4096, "K": 4096, "block_scales": "1x128 act, 128x128 weight",
+                   "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
+                   "l2": f"{R} weight matrices rotate (268 MB > 126 MB L2)"},
+        "roofline": {"bound": "tensor", "kernel": "fp8_gemm_kernel (tcgen05 kind::f8f6f4)", "achieved": head["tflops"],
+                     "peak": peak_tf, "peak_kind": f"of {kind} bf16 GEMM (dense fp8 is nominally twice that)",
+                     "unit": "TFLOP/s", "frac": head["tflops"] / peak_tf, "traffic": None, "avg_launch_ms": head["ms"]},
+        "roofline_matvec": {"bound": "hbm", "kernel": "fp8_matvec_kernel (M = 1)", "achieved": mv["weight_gbs"],
+                            "peak": hbm, "unit": "GB/s", "frac": mv["weight_gbs"] / hbm, "avg_launch_ms": mv["ms"]},
+        "shapes": results,
+        "e2e": {"value": head["M"] * world / (head["e2e_ms"] * 1e-3), "unit": UNIT,
+                "h2d_bytes_per_step": head["M"] * Kdim * 4, "d2h_bytes_per_step": head["M"] * head["N"] * 2},
+        "gpu_launches": head["steps"], "timed_with": f"CUDA graph of {R} launches replayed", "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, T_total):
     """Expert-parallel prefill: the 4096-token chunk is split evenly over the ranks (strong scaling), rank r owns
     experts [r*256/G, (r+1)*256/G); NCCL all-to-all dispatch (Q8_K rows) and combine (f32 rows)."""
@@ -464,6 +556,11 @@ def main():
     sampler = ClockSampler(local_rank)
     sampler.start()  # started early (nvidia-smi takes a while to come up); samples are filtered to the load window
     wl = WORKLOADS[args.workload]
+    if args.workload == "fp8_linear":
+        run_fp8(args, torch, dist, MoeKernels(device=local_rank, max_tokens=1), device, rank, world, sampler)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if wl["tokens"] >= 1024 and world > 1:
         run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, wl["tokens"])
         dist.destroy_process_group()

@@ -470,3 +470,51 @@ def test_moe_forward_batched_tcgen05(torch_cuda, oracle, layout, T, n_e, zipf):
     assert not bad.any(), f"{bad.sum()} of {bad.size} outside tolerance, max abs err {err.max()}, ref scale {np.abs(ref_out).max()}"
     assert err.max() <= 1e-5 * np.abs(ref_out).max()  # only summation-order noise is left
     Kb.close()
+
+
+def test_expert_parallel_world1_matches_forward(torch_cuda, oracle):
+    """The expert-parallel host path on one rank (NCCL group of one): dispatch, owner compute through dsmoe_expert_ffn
+    with an n_expert_used = 1 handle, combine. With both sides on the decode kernels it must equal the tier-2 call bit
+    for bit; when the owner's 54 rows go through the grouped GEMM instead, only the down projection's summation
+    order differs (last bits)."""
+    torch = torch_cuda
+    import os
+
+    import torch.distributed as dist
+
+    from deepseek_rs_b200.ep import ExpertParallelMoe, gpu_functions
+    from deepseek_rs_b200.kernels import LAYOUT_ROWSOA, MoeKernels, MoeLayer
+
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    created = not dist.is_initialized()
+    if created:
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+    try:
+        n_e, T = 32, 9
+        lw = F.ExpertLayer(seed=51, n_expert=n_e)
+        rng = np.random.default_rng(52)
+        x = dev(torch, F.bf16_round(rng.standard_normal((T, 4096)).astype(np.float32)))
+        logits = dev(torch, rng.standard_normal((T, n_e)).astype(np.float32))
+        K_full = MoeKernels(device=0, n_expert=n_e, max_tokens=T)
+        layer = MoeLayer(K_full, lw.gate, lw.up, lw.down, layout=LAYOUT_ROWSOA)
+        want = layer.forward(x, logits)
+        for min_tokens, exact in (("1000000", True), ("1", False)):
+            os.environ["DSMOE_PREFILL_MIN_TOKENS"] = min_tokens
+            try:
+                K_owner = MoeKernels(device=0, n_expert=n_e, n_expert_used=1, max_tokens=T * 6)
+            finally:
+                del os.environ["DSMOE_PREFILL_MIN_TOKENS"]
+            MoeLayer(K_owner, lw.gate, lw.up, lw.down, layout=LAYOUT_ROWSOA)
+            rf, ef = gpu_functions(K_full, K_owner)
+            out, sel = ExpertParallelMoe(rf, ef, n_e, 6, 4096).forward(x, logits)
+            assert K_owner.device_status() == 0
+            if exact:
+                assert torch.equal(out, want)
+            else:
+                assert float((out - want).abs().max()) <= 1e-5 * float(want.abs().max())
+            K_owner.close()
+        K_full.close()
+    finally:
+        if created:
+            dist.destroy_process_group()
