@@ -58,15 +58,14 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up decode kernel, from the ncu captures summarised
+# in profiles/decode_gate_up_and_down_ncu.md (batch 1: equal to the algorithmic bytes; batch 64: 1.79 x, pairs of one
+# expert are not yet grouped)
+NCU_TRAFFIC = {"moe_decode_b1": 25999616, "moe_decode_b64": 1552575072}
+
+
 def ncu_traffic(workload: str):
-    """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if one exists for this workload."""
-    p = os.path.join(ROOT, "profiles", "ncu_traffic.json")
-    if os.path.exists(p):
-        try:
-            return json.load(open(p)).get(workload, {}).get("gate_up_dram_bytes_per_launch")
-        except Exception:
-            return None
-    return None
+    return NCU_TRAFFIC.get(workload)
 
 
 class ClockSampler:
