@@ -215,8 +215,8 @@ struct PfGemmArgs {
 
 constexpr int PF_SMEM_A = 0;                          // 2 x 32 KB
 constexpr int PF_SMEM_B = 2 * PF_STAGE_A;             // 2 x 32 KB
-constexpr int PF_SMEM_LUT = PF_SMEM_B + 2 * PF_STAGE_A;        // 4 KB codebook (f16) + 2 KB signs (f16)
-constexpr int PF_SMEM_A2 = PF_SMEM_LUT + 6144;        // 2 x 4 KB: sc_hi tile (Q2K), one per TMEM buffer
+constexpr int PF_SMEM_LUT = PF_SMEM_B + 2 * PF_STAGE_A;        // codebook (f16, 32 KB) + signs (f16, 16 KB), 8 copies each
+constexpr int PF_SMEM_A2 = PF_SMEM_LUT + 49152;       // 2 x 4 KB: sc_hi tile (Q2K), one per TMEM buffer
 constexpr int PF_SMEM_B2 = PF_SMEM_A2 + 8192;         // 2 x 4 KB: bsums tile (Q2K)
 constexpr int PF_SMEM_S = PF_SMEM_B2 + 8192;          // 16 x 128 f32 scales
 constexpr int PF_SMEM_BAR = PF_SMEM_S + 16 * PF_TN * 4;
@@ -271,15 +271,18 @@ __device__ __forceinline__ uint2 pf_load_q2k_scales(const uint8_t *row, int layo
 }
 
 // IQ2_XXS: decode one 32-weight group into four core-matrix rows (8 f16 each) at dst + u * 128, u = 0..3
-__device__ __forceinline__ void pf_decode_iq2(uint2 pk, uint8_t *dst, const uint4 *lut_grid, const uint4 *lut_sign)
+// The tables hold 8 copies of every entry (entry stride 128 bytes); lane7 = lane & 7 picks this lane's copy, so the
+// eight lanes of a shared-memory wavefront never share a bank group.
+__device__ __forceinline__ void pf_decode_iq2(uint2 pk, uint8_t *dst, const uint4 *lut_grid, const uint4 *lut_sign,
+                                              uint32_t lane7)
 {
     const uint32_t aux0 = pk.x, aux1 = pk.y;
     const __half2 ls = __float2half2_rn((float)(2u * (aux1 >> 28) + 1u));
     const uint32_t ls2 = *reinterpret_cast<const uint32_t *>(&ls);
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-        const uint4 g = lut_grid[(aux0 >> (8 * u)) & 255u];   // magnitudes as f16
-        const uint4 s = lut_sign[(aux1 >> (7 * u)) & 127u];   // +1 / -1 as f16
+        const uint4 g = lut_grid[((aux0 >> (8 * u)) & 255u) * 8 + lane7];   // magnitudes as f16
+        const uint4 s = lut_sign[((aux1 >> (7 * u)) & 127u) * 8 + lane7];   // +1 / -1 as f16
         uint4 w;
         w.x = pf_hmul2(g.x, pf_hmul2(s.x, ls2));
         w.y = pf_hmul2(g.y, pf_hmul2(s.y, ls2));
@@ -324,7 +327,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
     uint64_t *bar_mma = bar_full + 2;                                             // [2] stage's MMAs retired
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_mma + 2);
     uint4 *lut_grid = reinterpret_cast<uint4 *>(smem + PF_SMEM_LUT);
-    uint4 *lut_sign = lut_grid + 256;
+    uint4 *lut_sign = lut_grid + 256 * 8;
     float *sS = reinterpret_cast<float *>(smem + PF_SMEM_S);
     float *sX = reinterpret_cast<float *>(smem);  // epilogue exchange buffer, aliases the A and B stages
 
@@ -334,17 +337,17 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
     const bool ieee = a.ieee != 0;
 
     if (KIND == PF_IQ2) {
-        for (int i = tid; i < 256; i += PF_THREADS) {
-            const uint64_t g = c_iq2xxs_grid[i];
+        for (int i = tid; i < 256 * 8; i += PF_THREADS) {
+            const uint64_t g = c_iq2xxs_grid[i >> 3];
             lut_grid[i] = pf_bytes_to_f16x8((uint32_t)g, (uint32_t)(g >> 32));
         }
-        if (tid < 128) {
-            const uint32_t sb = dsmoe_iq2_sign_byte((uint32_t)tid);
+        for (int e = tid; e < 128 * 8; e += PF_THREADS) {
+            const uint32_t sb = dsmoe_iq2_sign_byte((uint32_t)(e >> 3));
             uint32_t h[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i)
                 h[i] = (((sb >> (2 * i)) & 1u) ? 0xBC00u : 0x3C00u) | ((((sb >> (2 * i + 1)) & 1u) ? 0xBC00u : 0x3C00u) << 16);
-            lut_sign[tid] = make_uint4(h[0], h[1], h[2], h[3]);
+            lut_sign[e] = make_uint4(h[0], h[1], h[2], h[3]);
         }
     }
     if (warp == 0) tc05_alloc(tmem_slot, TMEM_COLS);
@@ -423,7 +426,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
                 dw = f16_bits_to_f32(dd & 0xFFFFu, ieee);
                 dmin = f16_bits_to_f32(dd >> 16, ieee);
             }
-            const float *sx = sS + kb * PF_TN + acol0;
+            const float4 *sx4 = reinterpret_cast<const float4 *>(sS + kb * PF_TN + acol0);
 #pragma unroll
             for (int c0 = 0; c0 < PF_COLS; c0 += 16) {
                 if (acol0 + c0 >= rows16) break;  // warp-uniform: columns beyond the padded tile hold nothing
@@ -431,9 +434,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
                 tc05_ld16(tmem + tlane + buf * PF_TN + acol0 + c0, v);
                 if (KIND == PF_Q2K) tc05_ld16(tmem + tlane + 256u + buf * PF_TN + acol0 + c0, v2);
                 tc05_wait_ld();
+                float dxs[16];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float4 t = sx4[(c0 >> 2) + i];
+                    dxs[4 * i] = t.x, dxs[4 * i + 1] = t.y, dxs[4 * i + 2] = t.z, dxs[4 * i + 3] = t.w;
+                }
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const float dx = sx[c0 + i];
+                    const float dx = dxs[i];
                     if (KIND == PF_IQ2) {
                         // ((0.125 d_w) d_x) bsum, added to 0 or to the leaf's first block
                         const float t = __fmul_rn(__fmul_rn(dw, dx), v[i]);
@@ -513,7 +522,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
                 const uint32_t rl = 8 * PF_PASSES * warp + 8 * p + dr8;
                 uint8_t *dst = sA + (rl >> 3) * PF_SBO + (rl & 7) * 16;
                 if (KIND == PF_IQ2) {
-                    pf_decode_iq2(pk[p], dst + dc * 512, lut_grid, lut_sign);
+                    pf_decode_iq2(pk[p], dst + dc * 512, lut_grid, lut_sign, dr8);
                 } else {
                     const uint2 sc8 = pf_load_q2k_scales(drow[p], a.layout, kb, half);
                     pf_decode_q2k(pk[p], sc8, dc, dst + dc * 128);
