@@ -33,6 +33,30 @@ __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, u
                  : "memory");
 }
 
+// One arrival on the mbarrier (release semantics at CTA scope).
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Named barrier `id` over the first `nthreads` arrivals (a multiple of 32), returning the AND of every participant's
+// predicate. All participating warps must call it the same number of times.
+__device__ __forceinline__ bool named_barrier_and(uint32_t id, uint32_t nthreads, bool pred)
+{
+    uint32_t r;
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        "setp.ne.b32 q, %3, 0;\n"
+        "bar.red.and.pred p, %1, %2, q;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(r)
+        : "r"(id), "r"(nthreads), "r"((uint32_t)pred)
+        : "memory");
+    return r != 0;
+}
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 {
     uint32_t ok;

@@ -17,6 +17,7 @@
 //   5 grouped_gemm<Q2K>                     down, min-term as a second K=16 MMA -> per-pair rows
 //   6 moe_sum                               slots summed in slot order
 #include <cuda_fp16.h>
+#include <stdio.h>
 
 #include "common.cuh"
 #include "launch.h"
@@ -28,9 +29,25 @@ constexpr int PF_TN = 128;       // token rows per tile (MMA N), padded to a mul
 constexpr int PF_KS = 128;       // K elements per pipeline stage (half a superblock)
 constexpr int PF_STAGE_A = 128 * PF_KS * 2;  // 32 KB: 128 weight rows
 constexpr int PF_SBO = (PF_KS / 8) * 128;    // 2048: byte distance between 8-row groups in a stage
-constexpr int PF_THREADS = 256;  // 8 warps: two per TMEM lane quadrant, each draining PF_COLS accumulator columns (512 threads measured slower)
-constexpr int PF_COLS = PF_TN / (PF_THREADS / 128);
-constexpr int PF_PASSES = 128 / (PF_THREADS / 32 * 8);  // decode passes: a warp decodes 8 rows per pass
+constexpr int PF_DRAIN_WARPS = 8;    // consumers: two per TMEM lane quadrant, each draining PF_COLS accumulator columns
+constexpr int PF_DECODE_WARPS = 16;  // producers: 8 weight rows each
+constexpr int PF_AUX_WARPS = 4;      // MMA issuer, activation loader, two idle (register reallocation works on 4 warps)
+constexpr int PF_THREADS = 32 * (PF_DRAIN_WARPS + PF_DECODE_WARPS + PF_AUX_WARPS);
+constexpr int PF_COLS = PF_TN / (PF_DRAIN_WARPS / 4);
+// Registers per thread. The kernel is compiled for PF_REG_LAUNCH (the most 896 threads can have); after the role
+// split the producers and the auxiliary warps release registers and the consumers take them (setmaxnreg). An
+// increase blocks until the CTA's warps have RELEASED as many registers as it asks for (registers the CTA never
+// allocated do not count), so the released total must cover the request or the consumers would wait for ever.
+constexpr int PF_REG_LAUNCH = 72;
+#ifndef PF_REG_CONSUMER
+#define PF_REG_CONSUMER 120
+#define PF_REG_PRODUCER 56
+#define PF_REG_AUX 32
+#endif
+static_assert(32 * PF_DRAIN_WARPS * (PF_REG_CONSUMER - PF_REG_LAUNCH) <=
+                  32 * PF_DECODE_WARPS * (PF_REG_LAUNCH - PF_REG_PRODUCER) + 32 * PF_AUX_WARPS * (PF_REG_LAUNCH - PF_REG_AUX),
+              "setmaxnreg: the consumers ask for more registers than the other roles release");
+static_assert(PF_THREADS * PF_REG_LAUNCH <= 65536, "register file");
 
 // ---------------------------------------------------------------------------------------------------------------
 // 1. grouping: deterministic and stable (pairs of an expert keep ascending pair order), unlike the reference's
@@ -183,19 +200,30 @@ __global__ void __launch_bounds__(256) pf_gather_kernel(const uint8_t *__restric
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// 3 / 5. grouped GEMM on tcgen05
+// 3 / 5. grouped GEMM on tcgen05, warp-specialised
 //
-// One persistent CTA per SM (256 threads) walks items = (token tile, M tile). D (128 x N f32, N = padded token rows)
-// lives in TMEM, two buffers so that the accumulator of superblock j is drained (tcgen05.ld -> scale by d_w * d_x ->
-// add to 64 f32 registers per thread) while the MMAs of superblock j+1 run. A stage is half a superblock (K = 128):
-//   all threads  decode 128 weight rows x 128 K into shared memory as exact f16 integers (the producer side),
-//   thread 0     bulk-copies the matching activation block (already f16, already in operand layout) onto an mbarrier,
-//                then issues eight K=16 MMAs and commits them to the stage's second mbarrier,
-//   all threads  drain the previous superblock.
-// IQ2_XXS tile rows: 0-63 gate rows, 64-127 the same rows of up, so that SwiGLU meets both halves in one tile.
+// One persistent CTA per SM (896 threads) walks items = (token tile, M tile). Four roles run asynchronously and meet
+// only on mbarriers:
+//   warps 8-23  producers  decode 128 weight rows x 128 K per stage (half a superblock) into a two-stage ring in
+//                          shared memory as exact f16 integers, 8 rows per warp;
+//   warp 25     loader     bulk-copies the matching activation blocks (already f16, already in operand layout) into a
+//                          three-stage ring, running ahead of the decode;
+//   warp 24     issuer     one elected lane issues the stage's eight K=16 MMAs once both operands are there, and
+//                          commits them to the rings' "free" mbarriers and, at the end of a superblock, to the
+//                          accumulator's "full" mbarrier;
+//   warps 0-7   consumers  drain the accumulator of a superblock (tcgen05.ld -> scale by d_w * d_x -> add to 64 f32
+//                          registers per thread), hand the TMEM buffer back ("accumulator free") and write the item's
+//                          result while the other roles already work on the next item.
+// Registers move between the roles with setmaxnreg.
+// TMEM (512 columns). Q2_K: two accumulator buffers (D at 0/128, min-term D2 at 256/384), so superblock j is drained
+// while j+1 is contracted. IQ2_XXS: one accumulator (columns 0-127) and three spill sets P1/P2/P3 (128.., 256.., 384..)
+// that hold the upper levels of the reference's reduction tree, private to the draining thread.
+// IQ2_XXS tile rows: row 2r is gate row r and row 2r+1 the same row of up, so the two inputs of SwiGLU sit in
+// neighbouring lanes of one warp and are exchanged with shuffles.
 // Q2_K: the min term -dmin * d_x * sum_j bsums[j] * sc_hi[j] is a second accumulator fed by one K=16 MMA per
 // superblock (A = sc_hi, B = bsums, both exact in f16).
-// Every wait is bounded; on expiry all threads leave through the common exit that frees TMEM.
+// Every wait is bounded; on expiry the error is recorded and all threads leave through the common exit that frees
+// TMEM. Consumers agree on the error at the item barrier, so nobody is left waiting on it.
 // ---------------------------------------------------------------------------------------------------------------
 struct PfGemmArgs {
     const uint8_t *w0, *w1;  // IQ2: gate, up tensors; Q2K: down tensor (w1 unused)
@@ -213,18 +241,34 @@ struct PfGemmArgs {
     int *status;
 };
 
-constexpr int PF_SMEM_A = 0;                          // 2 x 32 KB
-constexpr int PF_SMEM_B = 2 * PF_STAGE_A;             // 2 x 32 KB
-constexpr int PF_SMEM_LUT = PF_SMEM_B + 2 * PF_STAGE_A;        // codebook (f16, 32 KB) + signs (f16, 16 KB), 8 copies each
-constexpr int PF_SMEM_A2 = PF_SMEM_LUT + 49152;       // 2 x 4 KB: sc_hi tile (Q2K), one per TMEM buffer
-constexpr int PF_SMEM_B2 = PF_SMEM_A2 + 8192;         // 2 x 4 KB: bsums tile (Q2K)
-constexpr int PF_SMEM_S = PF_SMEM_B2 + 8192;          // 16 x 128 f32 scales
-constexpr int PF_SMEM_BAR = PF_SMEM_S + 16 * PF_TN * 4;
-constexpr int PF_SMEM_TOTAL = PF_SMEM_BAR + 64;
-constexpr int PF_XSTRIDE = 129;                       // f32 stride of the epilogue exchange buffer (aliases A and B)
-static_assert(128 * PF_XSTRIDE * 4 <= PF_SMEM_LUT, "exchange buffer must fit in the A and B stages");
+constexpr int PF_A_STAGES = 2, PF_B_STAGES = 3;
+constexpr int PF_SMEM_A = 0;                                          // 2 x 32 KB decoded weights
+constexpr int PF_SMEM_B = PF_A_STAGES * PF_STAGE_A;                   // 3 x 32 KB activations
+constexpr int PF_SMEM_LUT = PF_SMEM_B + PF_B_STAGES * PF_STAGE_A;     // IQ2: codebook (f16, 32 KB) + signs (16 KB), 8 copies each
+constexpr int PF_SMEM_A2 = PF_SMEM_LUT;                               // Q2K (no tables): 2 x 4 KB sc_hi tile, one per TMEM buffer
+constexpr int PF_SMEM_B2 = PF_SMEM_A2 + 8192;                         // Q2K: 2 x 4 KB bsums tile
+constexpr int PF_SMEM_S = PF_SMEM_LUT + 49152;                        // 2 x (16 x 128 f32 scales), one per item parity
+constexpr int PF_SMEM_P = PF_SMEM_S + 2 * 16 * PF_TN * 4;             // 2 x 128 pair ids
+constexpr int PF_SMEM_W = PF_SMEM_P + 2 * PF_TN * 4;                  // 2 x 128 router weights
+constexpr int PF_SMEM_BAR = PF_SMEM_W + 2 * PF_TN * 4;
+constexpr int PF_SMEM_TOTAL = PF_SMEM_BAR + 128;
+static_assert(PF_SMEM_TOTAL <= 232448, "shared memory per CTA");
 
 enum { PF_IQ2 = 0, PF_Q2K = 1 };
+
+// Optional in-kernel phase timing (diagnostic builds only, -DPF_PROFILE): cycles per role and phase, one record per CTA.
+#ifdef PF_PROFILE
+__device__ long long g_pf_prof[2][160][32];
+#define PF_T0() long long pf_t_ = clock64()
+#define PF_ACC(i) do { const long long pf_n_ = clock64(); pf_c_[i] += pf_n_ - pf_t_; pf_t_ = pf_n_; } while (0)
+#define PF_DECL() long long pf_c_[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define PF_DUMP(cond, base) do { if (cond) for (int q_ = 0; q_ < 8; ++q_) g_pf_prof[KIND][blockIdx.x][(base) + q_] = pf_c_[q_]; } while (0)
+#else
+#define PF_T0() do { } while (0)
+#define PF_ACC(i) do { } while (0)
+#define PF_DECL() do { } while (0)
+#define PF_DUMP(cond, base) do { } while (0)
+#endif
 
 // 8 unsigned bytes (two words) -> 8 exact f16 integers; 0x6400 | b is 1024 + b
 __device__ __forceinline__ uint4 pf_bytes_to_f16x8(uint32_t lo, uint32_t hi)
@@ -319,20 +363,49 @@ __device__ __forceinline__ uint32_t pf_visit_block(uint32_t kblocks, uint32_t j)
     return kblocks == 16 ? l + 8 * (j & 1) : l;
 }
 
+// Weight row behind row `rl` of an item's 128-row operand tile.
+template <int KIND>
+__device__ __forceinline__ const uint8_t *pf_tile_row(const PfGemmArgs &a, uint64_t ebase, uint32_t mt, uint32_t rl,
+                                                      uint32_t row_bytes)
+{
+    if (KIND == PF_IQ2) return ((rl & 1u) ? a.w1 : a.w0) + ebase + (uint64_t)(mt * 64 + (rl >> 1)) * row_bytes;
+    return a.w0 + ebase + (uint64_t)(mt * 128 + rl) * row_bytes;
+}
+
+// Asks L2 for the weight rows of an item (contiguous per tensor) so that the decode loads and the scale loads of the
+// item find them there. `t` of `nt` threads share the lines.
+template <int KIND>
+__device__ __forceinline__ void pf_prefetch_item(const PfGemmArgs &a, uint32_t item, uint32_t n_mtiles, uint32_t row_bytes,
+                                                 uint32_t t, uint32_t nt)
+{
+    const uint32_t tile = item / n_mtiles, mt = item - tile * n_mtiles;
+    const uint64_t ebase = (uint64_t)a.tile_expert[tile] * a.expert_bytes;
+    const uint32_t m_out = KIND == PF_IQ2 ? 64u : 128u, bytes = m_out * row_bytes;
+    const uint8_t *p0 = a.w0 + ebase + (uint64_t)mt * bytes;
+    for (uint32_t o = t * 128u; o < bytes; o += nt * 128u) asm volatile("prefetch.global.L2 [%0];" ::"l"(p0 + o));
+    if (KIND == PF_IQ2) {
+        const uint8_t *p1 = a.w1 + ebase + (uint64_t)mt * bytes;
+        for (uint32_t o = t * 128u; o < bytes; o += nt * 128u) asm volatile("prefetch.global.L2 [%0];" ::"l"(p1 + o));
+    }
+}
+
 template <int KIND>
 __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmArgs a)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint64_t *bar_full = reinterpret_cast<uint64_t *>(smem + PF_SMEM_BAR);       // [2] activation stage landed
-    uint64_t *bar_mma = bar_full + 2;                                             // [2] stage's MMAs retired
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_mma + 2);
+    uint64_t *bar_a_full = reinterpret_cast<uint64_t *>(smem + PF_SMEM_BAR);  // [2] weight stage decoded (16 warps)
+    uint64_t *bar_a_free = bar_a_full + 2;                                     // [2] its MMAs retired
+    uint64_t *bar_b_full = bar_a_full + 4;                                     // [3] activation stage landed
+    uint64_t *bar_b_free = bar_a_full + 7;                                     // [3] its MMAs retired
+    uint64_t *bar_acc_full = bar_a_full + 10;                                  // [2] superblock contracted
+    uint64_t *bar_acc_free = bar_a_full + 12;                                  // [2] accumulator drained (8 warps)
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_a_full + 14);
     uint4 *lut_grid = reinterpret_cast<uint4 *>(smem + PF_SMEM_LUT);
     uint4 *lut_sign = lut_grid + 256 * 8;
-    float *sS = reinterpret_cast<float *>(smem + PF_SMEM_S);
-    float *sX = reinterpret_cast<float *>(smem);  // epilogue exchange buffer, aliases the A and B stages
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    constexpr uint32_t TMEM_COLS = 512u;  // D x2 at 0/128; Q2K: D2 x2 at 256/384; IQ2: spill sets P2 at 256, P3 at 384
+    constexpr uint32_t TMEM_COLS = 512u;
+    constexpr uint32_t NBUF = KIND == PF_IQ2 ? 1u : 2u;      // accumulator buffers in TMEM
     constexpr uint32_t M_OUT = KIND == PF_IQ2 ? 64u : 128u;  // output rows per tile
     const bool ieee = a.ieee != 0;
 
@@ -352,10 +425,18 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
     }
     if (warp == 0) tc05_alloc(tmem_slot, TMEM_COLS);
     if (tid == 0) {
-        mbar_init(&bar_full[0], 1);
-        mbar_init(&bar_full[1], 1);
-        mbar_init(&bar_mma[0], 1);
-        mbar_init(&bar_mma[1], 1);
+        for (int i = 0; i < PF_A_STAGES; ++i) {
+            mbar_init(&bar_a_full[i], PF_DECODE_WARPS);
+            mbar_init(&bar_a_free[i], 1);
+        }
+        for (int i = 0; i < PF_B_STAGES; ++i) {
+            mbar_init(&bar_b_full[i], 1);
+            mbar_init(&bar_b_free[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bar_acc_full[i], 1);
+            mbar_init(&bar_acc_free[i], PF_DRAIN_WARPS);
+        }
         fence_async_smem();
     }
     tc05_fence_before_sync();
@@ -365,242 +446,325 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
 
     const uint32_t n_tiles = a.plan[0], n_mtiles = a.out_dim / M_OUT, n_items = n_tiles * n_mtiles;
     const uint32_t n_stages = 2 * a.kblocks;
-    // this thread in the decode phase: lane = c * 8 + r8 -> quarter c of the stage, row 16 warp + 8 pass + r8
-    const uint32_t dc = lane >> 3, dr8 = lane & 7;
-    // this thread in the drain phase: accumulator row and column half
-    const uint32_t arow = 32 * (warp & 3) + lane, acol0 = PF_COLS * (warp >> 2);
-    const uint32_t tlane = (32u * (warp & 3)) << 16;
+    const uint32_t row_bytes = (KIND == PF_IQ2 ? IQ2XXS_BYTES : Q2K_BYTES) * a.kblocks;
 
-    uint32_t gs = 0, gsb = 0;  // stages / superblocks issued so far by this CTA (mbarrier and TMEM phase tracking)
-    bool ok = true;
+    if (warp < PF_DRAIN_WARPS) {
+        // ------------------------------------------------------------------------------------------- consumers
+        reg_alloc<PF_REG_CONSUMER>();
+        // accumulator row (TMEM lane) and column half of this thread
+        const uint32_t arow = 32 * (warp & 3) + lane, acol0 = PF_COLS * (warp >> 2);
+        const uint32_t tlane = (32u * (warp & 3)) << 16;
+        uint32_t gsb = 0, it = 0;  // superblocks drained so far (TMEM buffer and mbarrier phase), items started
+        bool ok = true;
+        PF_DECL();
+        PF_T0();
 
-    for (uint32_t item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
-        const uint32_t tile = item / n_mtiles, mt = item - tile * n_mtiles;
-        const uint32_t rows = a.tile_rows[tile], rows16 = (rows + 15u) & ~15u, boff = a.tile_boff[tile];
-        const uint32_t start = a.tile_start[tile];
-        const uint64_t ebase = (uint64_t)a.tile_expert[tile] * a.expert_bytes;
-        const uint32_t row_bytes = (KIND == PF_IQ2 ? IQ2XXS_BYTES : Q2K_BYTES) * a.kblocks;
-        const uint32_t idesc = tc05_idesc_f16(128, rows16);
-        const uint8_t *btile = a.B + (size_t)boff * a.kblocks * 512;
+        for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x, ++it) {
+            const uint32_t tile = item / n_mtiles, mt = item - tile * n_mtiles;
+            const uint32_t rows = a.tile_rows[tile], rows16 = (rows + 15u) & ~15u, boff = a.tile_boff[tile];
+            const uint32_t start = a.tile_start[tile];
+            const uint64_t ebase = (uint64_t)a.tile_expert[tile] * a.expert_bytes;
+            const uint8_t *srow = pf_tile_row<KIND>(a, ebase, mt, arow, row_bytes);  // the row whose scales apply here
 
-        // weight rows this thread decodes (two passes) and the row it drains
-        const uint8_t *drow[PF_PASSES];
-#pragma unroll
-        for (int p = 0; p < PF_PASSES; ++p) {
-            const uint32_t rl = 8 * PF_PASSES * warp + 8 * p + dr8;
-            if (KIND == PF_IQ2) drow[p] = (rl < 64 ? a.w0 : a.w1) + ebase + (uint64_t)(mt * 64 + (rl & 63)) * row_bytes;
-            else drow[p] = a.w0 + ebase + (uint64_t)(mt * 128 + rl) * row_bytes;
-        }
-        const uint8_t *srow;  // the row whose scales this thread applies when draining
-        if (KIND == PF_IQ2) srow = (arow < 64 ? a.w0 : a.w1) + ebase + (uint64_t)(mt * 64 + (arow & 63)) * row_bytes;
-        else srow = a.w0 + ebase + (uint64_t)(mt * 128 + arow) * row_bytes;
-
-        for (uint32_t i = tid; i < a.kblocks * rows16; i += PF_THREADS) {
-            const uint32_t kb = i / rows16, c = i - kb * rows16;
-            sS[kb * PF_TN + c] = a.S[(size_t)kb * a.r_cap + boff + c];
-        }
-        float acc[PF_COLS];                         // Q2K: running sum. IQ2: the current leaf's partial a_l
-        float p1[PF_COLS];                         // IQ2: pair level of the reduction tree, finally the row total
-#pragma unroll
-        for (int i = 0; i < PF_COLS; ++i) acc[i] = 0.0f;
-
-        const uint32_t kb0 = pf_visit_block<KIND>(a.kblocks, 0);
-        uint2 pk[PF_PASSES];
-#pragma unroll
-        for (int p = 0; p < PF_PASSES; ++p) pk[p] = pf_load_packed<KIND>(drow[p], a.layout, kb0, 0, dc);
-
-        auto drain = [&](uint32_t j, uint32_t buf) {
-            const uint32_t kb = pf_visit_block<KIND>(a.kblocks, j);
-            // IQ2: position of this block in the reference's reduction tree
-            const uint32_t leaf = a.kblocks == 16 ? (j >> 1) : j;
-            const bool first_of_leaf = a.kblocks == 16 ? (j & 1) == 0 : true;
-            const bool last_of_leaf = a.kblocks == 16 ? (j & 1) == 1 : true;
-            // scales of this row for superblock kb
-            float dw, dmin = 0.0f;
-            if (KIND == PF_IQ2) {
-                const uint32_t bits = a.layout == DSMOE_LAYOUT_ROWSOA ? ld_u16(srow + 2 * kb) : ld_u16(srow + IQ2XXS_BYTES * kb);
-                dw = __fmul_rn(0.125f, f16_bits_to_f32(bits, ieee));
-            } else {
-                const uint32_t dd = a.layout == DSMOE_LAYOUT_ROWSOA ? ld_u32(srow + 80 * a.kblocks + 4 * kb)
-                                                                    : ld_u32(srow + Q2K_BYTES * kb + 80);
-                dw = f16_bits_to_f32(dd & 0xFFFFu, ieee);
-                dmin = f16_bits_to_f32(dd >> 16, ieee);
+            // per-item tables (double-buffered by item parity): activation scales, pair ids, router weights
+            float *sS = reinterpret_cast<float *>(smem + PF_SMEM_S) + (it & 1u) * 16 * PF_TN;
+            uint32_t *sP = reinterpret_cast<uint32_t *>(smem + PF_SMEM_P) + (it & 1u) * PF_TN;
+            float *sW = reinterpret_cast<float *>(smem + PF_SMEM_W) + (it & 1u) * PF_TN;
+            for (uint32_t i = tid; i < a.kblocks * rows16; i += 32 * PF_DRAIN_WARPS) {
+                const uint32_t kb = i / rows16, c = i - kb * rows16;
+                sS[kb * PF_TN + c] = a.S[(size_t)kb * a.r_cap + boff + c];
             }
-            const float4 *sx4 = reinterpret_cast<const float4 *>(sS + kb * PF_TN + acol0);
-#pragma unroll
-            for (int c0 = 0; c0 < PF_COLS; c0 += 16) {
-                if (acol0 + c0 >= rows16) break;  // warp-uniform: columns beyond the padded tile hold nothing
-                float v[16], v2[16];
-                tc05_ld16(tmem + tlane + buf * PF_TN + acol0 + c0, v);
-                if (KIND == PF_Q2K) tc05_ld16(tmem + tlane + 256u + buf * PF_TN + acol0 + c0, v2);
-                tc05_wait_ld();
-                float dxs[16];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float4 t = sx4[(c0 >> 2) + i];
-                    dxs[4 * i] = t.x, dxs[4 * i + 1] = t.y, dxs[4 * i + 2] = t.z, dxs[4 * i + 3] = t.w;
-                }
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float dx = dxs[i];
-                    if (KIND == PF_IQ2) {
-                        // ((0.125 d_w) d_x) bsum, added to 0 or to the leaf's first block
-                        const float t = __fmul_rn(__fmul_rn(dw, dx), v[i]);
-                        acc[c0 + i] = __fadd_rn(first_of_leaf ? 0.0f : acc[c0 + i], t);
-                    } else {
-                        const float t = __fsub_rn(__fmul_rn(__fmul_rn(dx, dw), v[i]), __fmul_rn(__fmul_rn(dx, dmin), v2[i]));
-                        acc[c0 + i] = __fadd_rn(acc[c0 + i], t);
-                    }
-                }
+            if ((uint32_t)tid < rows) {
+                const uint32_t pair = a.sorted[start + tid];
+                sP[tid] = pair;
+                if (KIND == PF_IQ2) sW[tid] = a.weights[pair];
             }
-            if (KIND == PF_IQ2 && last_of_leaf) {
-                // fold the finished leaf a_l (in acc) into the tree: P1 = pair sums (registers), P2 = quad sums and
-                // P3 = the even half (TMEM columns 256.. and 384.., used as spill space)
+            ok = named_barrier_and(1, 32 * PF_DRAIN_WARPS, ok);
+            if (!ok) break;  // the same decision in all consumer warps
+            PF_ACC(0);
+
+            // Q2K: running sum. IQ2: the current leaf's partial a_l, after the last leaf the row total
+            float acc[PF_COLS];
+#pragma unroll
+            for (int i = 0; i < PF_COLS; ++i) acc[i] = 0.0f;
+
+            for (uint32_t j = 0; j < a.kblocks; ++j) {
+                if (!ok) break;  // keeps walking the items, so that every warp reaches the item barrier
+                const uint32_t buf = gsb % NBUF, use = gsb / NBUF, kb = pf_visit_block<KIND>(a.kblocks, j);
+                // IQ2: position of this block in the reference's reduction tree
+                const uint32_t leaf = a.kblocks == 16 ? (j >> 1) : j;
+                const bool first_of_leaf = a.kblocks == 16 ? (j & 1) == 0 : true;
+                const bool last_of_leaf = a.kblocks == 16 ? (j & 1) == 1 : true;
+                // scales of this row for superblock kb (requested before the wait)
+                float dw, dmin = 0.0f;
+                if (KIND == PF_IQ2) {
+                    const uint32_t bits = a.layout == DSMOE_LAYOUT_ROWSOA ? ld_u16(srow + 2 * kb) : ld_u16(srow + IQ2XXS_BYTES * kb);
+                    dw = __fmul_rn(0.125f, f16_bits_to_f32(bits, ieee));
+                } else {
+                    const uint32_t dd = a.layout == DSMOE_LAYOUT_ROWSOA ? ld_u32(srow + 80 * a.kblocks + 4 * kb)
+                                                                        : ld_u32(srow + Q2K_BYTES * kb + 80);
+                    dw = f16_bits_to_f32(dd & 0xFFFFu, ieee);
+                    dmin = f16_bits_to_f32(dd >> 16, ieee);
+                }
+                PF_ACC(1);
+                ok = mbar_wait_bounded(&bar_acc_full[buf], use & 1u, a.status);
+                ok = __all_sync(FULL, ok);
+                if (!ok) break;
+                tc05_fence_after_sync();
+                PF_ACC(2);
+                const float4 *sx4 = reinterpret_cast<const float4 *>(sS + kb * PF_TN + acol0);
 #pragma unroll
                 for (int c0 = 0; c0 < PF_COLS; c0 += 16) {
-                    if (acol0 + c0 >= rows16) break;
-                    const uint32_t t2 = tmem + tlane + 256u + acol0 + c0, t3 = tmem + tlane + 384u + acol0 + c0;
-                    float w[16];
-                    if ((leaf & 1) == 0) {
+                    if (acol0 + c0 >= rows16) break;  // warp-uniform: columns beyond the padded tile hold nothing
+                    float v[16], v2[16];
+                    tc05_ld16(tmem + tlane + buf * PF_TN + acol0 + c0, v);
+                    if (KIND == PF_Q2K) tc05_ld16(tmem + tlane + 256u + buf * PF_TN + acol0 + c0, v2);
+                    tc05_wait_ld();
+                    float dxs[16];
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) p1[c0 + i] = acc[c0 + i];
+                    for (int i = 0; i < 4; ++i) {
+                        const float4 t = sx4[(c0 >> 2) + i];
+                        dxs[4 * i] = t.x, dxs[4 * i + 1] = t.y, dxs[4 * i + 2] = t.z, dxs[4 * i + 3] = t.w;
+                    }
+                    if (KIND == PF_IQ2) {
+                        // ((0.125 d_w) d_x) bsum, added to 0 or to the leaf's first block
+                        if (first_of_leaf) {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                acc[c0 + i] = __fadd_rn(0.0f, __fmul_rn(__fmul_rn(dw, dxs[i]), v[i]));
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                acc[c0 + i] = __fadd_rn(acc[c0 + i], __fmul_rn(__fmul_rn(dw, dxs[i]), v[i]));
+                        }
                     } else {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) p1[c0 + i] = __fadd_rn(p1[c0 + i], acc[c0 + i]);
-                        if (leaf == 1 || leaf == 5) {          // P2 = first pair sum of this half
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) w[i] = p1[c0 + i];
-                            tc05_st16(t2, w);
-                            tc05_wait_st();
-                        } else {                               // leaf 3 or 7: quad sum = P2 + P1
-                            tc05_ld16(t2, w);
-                            tc05_wait_ld();
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) w[i] = __fadd_rn(w[i], p1[c0 + i]);
-                            if (leaf == 3) {                   // even half done: park it in P3
-                                tc05_st16(t3, w);
-                                tc05_wait_st();
-                            } else {                           // total = even half + odd half
-                                float e[16];
-                                tc05_ld16(t3, e);
-                                tc05_wait_ld();
-#pragma unroll
-                                for (int i = 0; i < 16; ++i) p1[c0 + i] = __fadd_rn(e[i], w[i]);
-                            }
+                        for (int i = 0; i < 16; ++i) {
+                            const float t = __fsub_rn(__fmul_rn(__fmul_rn(dxs[i], dw), v[i]),
+                                                      __fmul_rn(__fmul_rn(dxs[i], dmin), v2[i]));
+                            acc[c0 + i] = __fadd_rn(acc[c0 + i], t);
                         }
                     }
                 }
-            }
-        };
+                // the accumulator buffer has been read: hand it back to the issuer
+                tc05_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_acc_free[buf]);
+                ++gsb;
+                PF_ACC(3);
 
-        for (uint32_t s = 0; s < n_stages; ++s, ++gs) {
-            const uint32_t b = gs & 1, kb = pf_visit_block<KIND>(a.kblocks, s >> 1), half = s & 1;
-            // 1. the stage buffer is free once the MMAs of the stage issued two stages ago have retired
-            if (gs >= 2) ok = ok && mbar_wait_bounded(&bar_mma[b], ((gs >> 1) - 1) & 1, a.status);
-            // 2. activation block of this stage (and, for Q2_K, the superblock's bsums tile)
-            if (tid == 0) {
-                uint32_t bytes = rows16 * 256u;
-                if (KIND == PF_Q2K && half == 0) bytes += rows16 * 32u;
-                mbar_expect_tx(&bar_full[b], bytes);
-                bulk_g2s(smem + PF_SMEM_B + b * PF_STAGE_A, btile + (size_t)(2 * kb + half) * rows16 * 256, rows16 * 256u, &bar_full[b]);
-                if (KIND == PF_Q2K && half == 0)
-                    bulk_g2s(smem + PF_SMEM_B2 + (gsb & 1) * 4096, a.BS + ((size_t)kb * a.r_cap + boff) * 16, rows16 * 32u,
-                             &bar_full[b]);
+                if (KIND == PF_IQ2 && last_of_leaf) {
+                    // fold the finished leaf a_l (in acc) into the tree. P1 = pair sums, P2 = quad sums, P3 = the even
+                    // half: TMEM columns 128.., 256.., 384.. of this thread's lane, used as spill space
+#pragma unroll
+                    for (int c0 = 0; c0 < PF_COLS; c0 += 16) {
+                        if (acol0 + c0 >= rows16) break;
+                        const uint32_t t1 = tmem + tlane + 128u + acol0 + c0, t2 = t1 + 128u, t3 = t1 + 256u;
+                        float w[16], e[16];
+                        if ((leaf & 1) == 0) {                     // first leaf of a pair
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) w[i] = acc[c0 + i];
+                            tc05_st16(t1, w);
+                        } else if (leaf == 1 || leaf == 5) {       // pair sum, the first of its half: P2
+                            tc05_ld16(t1, w);
+                            tc05_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) w[i] = __fadd_rn(w[i], acc[c0 + i]);
+                            tc05_st16(t2, w);
+                        } else {                                   // leaf 3 or 7: quad sum = P2 + (P1 + a_l)
+                            tc05_ld16(t1, w);
+                            tc05_ld16(t2, e);
+                            tc05_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) w[i] = __fadd_rn(e[i], __fadd_rn(w[i], acc[c0 + i]));
+                            if (leaf == 3) {                       // even half done: park it in P3
+                                tc05_st16(t3, w);
+                            } else {                               // row total = even half + odd half
+                                tc05_ld16(t3, e);
+                                tc05_wait_ld();
+#pragma unroll
+                                for (int i = 0; i < 16; ++i) acc[c0 + i] = __fadd_rn(e[i], w[i]);
+                            }
+                        }
+                    }
+                    tc05_wait_st();
+                }
+                PF_ACC(4);
             }
-            // 3. decode this stage's weights; fetch the next stage's packed bytes meanwhile
-            uint2 nx[PF_PASSES];
+            if (!ok) continue;
+
+            // the item's result
+            if (KIND == PF_IQ2) {
+                // lanes 2r / 2r+1 hold gate / up of output row r; the even lane finishes columns 0-31 of this warp's
+                // column half, the odd lane columns 32-63, each receiving the other input from its neighbour
+                const bool odd = (lane & 1) != 0;
+                const uint32_t orow = mt * 64 + (arow >> 1);
 #pragma unroll
-            for (int p = 0; p < PF_PASSES; ++p) nx[p] = pk[p];
-            if (s + 1 < n_stages) {
-                const uint32_t nkb = pf_visit_block<KIND>(a.kblocks, (s + 1) >> 1);
+                for (int i = 0; i < PF_COLS / 2; ++i) {
+                    const float send = odd ? acc[i] : acc[PF_COLS / 2 + i];
+                    const float recv = __shfl_xor_sync(FULL, send, 1);
+                    float g = odd ? recv : acc[i], u = odd ? acc[PF_COLS / 2 + i] : recv;
+                    const uint32_t col = acol0 + (odd ? PF_COLS / 2 + i : i);
+                    if (col < rows) {
+                        if (a.clamp > 1.0e-6f) {
+                            if (g > a.clamp) g = a.clamp;
+                            if (u > a.clamp) u = a.clamp;
+                            if (u < -a.clamp) u = -a.clamp;
+                        }
+                        a.out[(size_t)sP[col] * a.out_dim + orow] = swiglu_weighted(g, u, sW[col]);
+                    }
+                }
+            } else {
 #pragma unroll
-                for (int p = 0; p < PF_PASSES; ++p) nx[p] = pf_load_packed<KIND>(drow[p], a.layout, nkb, (s + 1) & 1, dc);
+                for (int i = 0; i < PF_COLS; ++i) {
+                    const uint32_t col = acol0 + i;
+                    if (col < rows) a.out[(size_t)sP[col] * a.out_dim + mt * 128 + arow] = acc[i];
+                }
             }
-            uint8_t *sA = smem + PF_SMEM_A + b * PF_STAGE_A;
-#pragma unroll
-            for (int p = 0; p < PF_PASSES; ++p) {
-                const uint32_t rl = 8 * PF_PASSES * warp + 8 * p + dr8;
-                uint8_t *dst = sA + (rl >> 3) * PF_SBO + (rl & 7) * 16;
+            PF_ACC(5);
+        }
+        PF_DUMP(tid == 0, 0);
+    } else if (warp < PF_DRAIN_WARPS + PF_DECODE_WARPS) {
+        // ------------------------------------------------------------------------------------------- producers
+        reg_dealloc<PF_REG_PRODUCER>();
+        const uint32_t dwarp = warp - PF_DRAIN_WARPS, dtid = tid - 32 * PF_DRAIN_WARPS;
+        // this thread in the decode: lane = c * 8 + r8 -> quarter c of the stage, tile row 8 dwarp + r8
+        const uint32_t dc = lane >> 3, dr8 = lane & 7, rl = 8 * dwarp + dr8;
+        uint32_t gs = 0, gsb = 0;  // stages / superblocks started so far by this CTA (ring slot and mbarrier phase)
+        bool ok = true;
+        PF_DECL();
+        PF_T0();
+
+        if (blockIdx.x < n_items) pf_prefetch_item<KIND>(a, blockIdx.x, n_mtiles, row_bytes, dtid, 32 * PF_DECODE_WARPS);
+        for (uint32_t item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+            if (item + gridDim.x < n_items)
+                pf_prefetch_item<KIND>(a, item + gridDim.x, n_mtiles, row_bytes, dtid, 32 * PF_DECODE_WARPS);
+            const uint32_t tile = item / n_mtiles, mt = item - tile * n_mtiles;
+            const uint64_t ebase = (uint64_t)a.tile_expert[tile] * a.expert_bytes;
+            const uint8_t *drow = pf_tile_row<KIND>(a, ebase, mt, rl, row_bytes);
+            uint2 pk = pf_load_packed<KIND>(drow, a.layout, pf_visit_block<KIND>(a.kblocks, 0), 0, dc);
+
+            for (uint32_t s = 0; s < n_stages; ++s, ++gs) {
+                const uint32_t b = gs & 1u, kb = pf_visit_block<KIND>(a.kblocks, s >> 1), half = s & 1u;
+                // the ring slot is free once the MMAs of the stage issued two stages ago have retired
+                PF_ACC(0);
+                if (gs >= 2) ok = mbar_wait_bounded(&bar_a_free[b], ((gs >> 1) - 1) & 1u, a.status);
+                ok = __all_sync(FULL, ok);
+                if (!ok) break;
+                PF_ACC(1);
+                // decode this stage's weights; fetch the next stage's packed bytes meanwhile
+                uint2 nx = pk;
+                if (s + 1 < n_stages)
+                    nx = pf_load_packed<KIND>(drow, a.layout, pf_visit_block<KIND>(a.kblocks, (s + 1) >> 1), (s + 1) & 1, dc);
+                uint8_t *dst = smem + PF_SMEM_A + b * PF_STAGE_A + (rl >> 3) * PF_SBO + (rl & 7) * 16;
                 if (KIND == PF_IQ2) {
-                    pf_decode_iq2(pk[p], dst + dc * 512, lut_grid, lut_sign, dr8);
+                    pf_decode_iq2(pk, dst + dc * 512, lut_grid, lut_sign, dr8);
                 } else {
-                    const uint2 sc8 = pf_load_q2k_scales(drow[p], a.layout, kb, half);
-                    pf_decode_q2k(pk[p], sc8, dc, dst + dc * 128);
+                    const uint2 sc8 = pf_load_q2k_scales(drow, a.layout, kb, half);
+                    pf_decode_q2k(pk, sc8, dc, dst + dc * 128);
                     if (half == 0 && dc < 2) {  // sc_hi of sub-blocks 8 dc .. 8 dc + 7 -> min-term operand, core dc
-                        const uint2 sh = pf_load_q2k_scales(drow[p], a.layout, kb, dc);
-                        *reinterpret_cast<uint4 *>(smem + PF_SMEM_A2 + (gsb & 1) * 4096 + (rl >> 3) * 256 + dc * 128 + (rl & 7) * 16) =
+                        const uint2 sh = pf_load_q2k_scales(drow, a.layout, kb, dc);
+                        *reinterpret_cast<uint4 *>(smem + PF_SMEM_A2 + (gsb & 1u) * 4096 + (rl >> 3) * 256 + dc * 128 +
+                                                   (rl & 7) * 16) =
                             pf_bytes_to_f16x8((sh.x >> 4) & 0x0F0F0F0Fu, (sh.y >> 4) & 0x0F0F0F0Fu);
                     }
                 }
-            }
-#pragma unroll
-            for (int p = 0; p < PF_PASSES; ++p) pk[p] = nx[p];
-            // 4. generic-proxy writes -> visible to the tensor core (async proxy); everyone has finished draining
-            fence_async_smem();
-            tc05_fence_before_sync();
-            ok = __syncthreads_and(ok);
-            if (!ok) break;
-            // 5. issue
-            if (tid == 0) {
-                if (mbar_wait_bounded(&bar_full[b], (gs >> 1) & 1, a.status)) {
-                    tc05_fence_after_sync();
-                    const uint32_t d_tmem = tmem + (gsb & 1) * PF_TN;
-                    const uint32_t sa = smem_u32(sA), sb = smem_u32(smem + PF_SMEM_B + b * PF_STAGE_A);
-#pragma unroll
-                    for (int ks = 0; ks < PF_KS / 16; ++ks)
-                        tc05_mma_f16(d_tmem, tc05_smem_desc(sa + ks * 256, 128, PF_SBO),
-                                     tc05_smem_desc(sb + ks * 256, 128, PF_SBO), idesc, (half | ks) != 0);
-                    if (KIND == PF_Q2K && half == 1)
-                        tc05_mma_f16(tmem + 256u + (gsb & 1) * PF_TN,
-                                     tc05_smem_desc(smem_u32(smem + PF_SMEM_A2 + (gsb & 1) * 4096), 128, 256),
-                                     tc05_smem_desc(smem_u32(smem + PF_SMEM_B2 + (gsb & 1) * 4096), 128, 256), idesc, 0);
-                }
-                tc05_commit(&bar_mma[b]);  // also arrives when the wait above gave up, so nobody waits on it for ever
-            }
-            // 6. drain the previous superblock while this stage's MMAs run (its last stage retired at step 1)
-            if (half == 1) {
-                if (s >= 3) {
-                    tc05_fence_after_sync();
-                    drain((s >> 1) - 1, (gsb + 1) & 1);
-                }
-                ++gsb;
+                pk = nx;
+                // generic-proxy writes -> visible to the tensor core (async proxy); this warp's share is done
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_a_full[b]);
+                if (half == 1) ++gsb;
+                PF_ACC(2);
             }
         }
-        if (!ok) break;
-        // last superblock: wait for the final stage (commits retire in order, so the one before is done too)
-        ok = mbar_wait_bounded(&bar_mma[(gs - 1) & 1], ((gs - 1) >> 1) & 1, a.status);
-        tc05_fence_after_sync();
-        if (ok) drain(a.kblocks - 1, (gsb + 1) & 1);
-        tc05_fence_before_sync();
-        ok = __syncthreads_and(ok);
-        if (!ok) break;
-
-        // epilogue
-        if (KIND == PF_IQ2) {
+        PF_DUMP(dtid == 0, 16);
+    } else {
+        // ------------------------------------------------------------------------------------ issuer and loader
+        reg_dealloc<PF_REG_AUX>();
+        const uint32_t awarp = warp - PF_DRAIN_WARPS - PF_DECODE_WARPS;
+        if (awarp == 0) {
+            // issuer: the whole warp walks the stages, one elected lane issues
+            uint32_t gs = 0, gsb = 0, bslot = 0, bpar = 0;
+            bool ok = true;
+            PF_DECL();
+            PF_T0();
+            for (uint32_t item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+                const uint32_t tile = item / n_mtiles;
+                const uint32_t rows16 = (a.tile_rows[tile] + 15u) & ~15u;
+                const uint32_t idesc = tc05_idesc_f16(128, rows16);
+                for (uint32_t s = 0; s < n_stages; ++s, ++gs) {
+                    const uint32_t b = gs & 1u, half = s & 1u, buf = gsb % NBUF, use = gsb / NBUF;
+                    PF_ACC(0);
+                    ok = mbar_wait_bounded(&bar_a_full[b], (gs >> 1) & 1u, a.status);
+                    PF_ACC(1);
+                    ok = ok && mbar_wait_bounded(&bar_b_full[bslot], bpar, a.status);
+                    PF_ACC(2);
+                    // at the start of a superblock the consumers must have handed the accumulator buffer back
+                    if (half == 0 && gsb >= NBUF) ok = ok && mbar_wait_bounded(&bar_acc_free[buf], (use - 1u) & 1u, a.status);
+                    PF_ACC(3);
+                    ok = __all_sync(FULL, ok);
+                    tc05_fence_after_sync();
+                    if (elect_one()) {
+                        if (ok) {
+                            const uint32_t d_tmem = tmem + buf * PF_TN;
+                            const uint64_t da = tc05_smem_desc(smem_u32(smem + PF_SMEM_A + b * PF_STAGE_A), 128, PF_SBO);
+                            const uint64_t db = tc05_smem_desc(smem_u32(smem + PF_SMEM_B + bslot * PF_STAGE_A), 128, PF_SBO);
 #pragma unroll
-            for (int i = 0; i < PF_COLS; ++i) sX[arow * PF_XSTRIDE + acol0 + i] = p1[i];
-            __syncthreads();
-            for (uint32_t i = tid; i < 64u * rows; i += PF_THREADS) {
-                const uint32_t col = i >> 6, r = i & 63;
-                float g = sX[r * PF_XSTRIDE + col], u = sX[(64 + r) * PF_XSTRIDE + col];
-                if (a.clamp > 1.0e-6f) {
-                    if (g > a.clamp) g = a.clamp;
-                    if (u > a.clamp) u = a.clamp;
-                    if (u < -a.clamp) u = -a.clamp;
+                            for (int ks = 0; ks < PF_KS / 16; ++ks)  // K advances 256 bytes = 16 descriptor units
+                                tc05_mma_f16(d_tmem, da + 16u * ks, db + 16u * ks, idesc, (half | ks) != 0);
+                            if (KIND == PF_Q2K && half == 1)
+                                tc05_mma_f16(tmem + 256u + buf * PF_TN,
+                                             tc05_smem_desc(smem_u32(smem + PF_SMEM_A2 + (gsb & 1u) * 4096), 128, 256),
+                                             tc05_smem_desc(smem_u32(smem + PF_SMEM_B2 + (gsb & 1u) * 4096), 128, 256), idesc, 0);
+                        }
+                        // the commits also arrive when a wait above gave up, so nobody waits on them for ever
+                        tc05_commit(&bar_a_free[b]);
+                        tc05_commit(&bar_b_free[bslot]);
+                        if (half == 1) tc05_commit(&bar_acc_full[buf]);
+                    }
+                    __syncwarp();
+                    if (half == 1) ++gsb;
+                    if (++bslot == PF_B_STAGES) bslot = 0, bpar ^= 1u;
+                    PF_ACC(4);
+                    if (!ok) break;
                 }
-                const uint32_t pair = a.sorted[start + col];
-                a.out[(size_t)pair * a.out_dim + mt * 64 + r] = swiglu_weighted(g, u, a.weights[pair]);
             }
-        } else {
-#pragma unroll
-            for (int i = 0; i < PF_COLS; ++i) {
-                const uint32_t col = acol0 + i;
-                if (col < rows) a.out[(size_t)a.sorted[start + col] * a.out_dim + mt * 128 + arow] = acc[i];
+            PF_DUMP(lane == 0, 8);
+        } else if (awarp == 1) {
+            // loader: activation blocks (and, for Q2_K, the superblock's bsums tile) into the three-stage ring
+            uint32_t gs = 0, gsb = 0, bslot = 0, bpar = 0;
+            bool ok = true;
+            for (uint32_t item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+                const uint32_t tile = item / n_mtiles;
+                const uint32_t rows16 = (a.tile_rows[tile] + 15u) & ~15u, boff = a.tile_boff[tile];
+                const uint8_t *btile = a.B + (size_t)boff * a.kblocks * 512;
+                for (uint32_t s = 0; s < n_stages; ++s, ++gs) {
+                    const uint32_t kb = pf_visit_block<KIND>(a.kblocks, s >> 1), half = s & 1u;
+                    // the slot (and the bsums slot of two superblocks ago) is free once the stage that used it last
+                    // has retired
+                    if (gs >= PF_B_STAGES) ok = mbar_wait_bounded(&bar_b_free[bslot], bpar ^ 1u, a.status);
+                    ok = __all_sync(FULL, ok);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        uint32_t bytes = rows16 * 256u;
+                        if (KIND == PF_Q2K && half == 0) bytes += rows16 * 32u;
+                        mbar_expect_tx(&bar_b_full[bslot], bytes);
+                        bulk_g2s(smem + PF_SMEM_B + bslot * PF_STAGE_A, btile + (size_t)(2 * kb + half) * rows16 * 256,
+                                 rows16 * 256u, &bar_b_full[bslot]);
+                        if (KIND == PF_Q2K && half == 0)
+                            bulk_g2s(smem + PF_SMEM_B2 + (gsb & 1u) * 4096, a.BS + ((size_t)kb * a.r_cap + boff) * 16,
+                                     rows16 * 32u, &bar_b_full[bslot]);
+                    }
+                    __syncwarp();
+                    if (half == 1) ++gsb;
+                    if (++bslot == PF_B_STAGES) bslot = 0, bpar ^= 1u;
+                }
             }
         }
-        __syncthreads();  // the exchange buffer and the scale table are reused by the next item
     }
 
+    // common exit: every MMA has retired (the consumers waited for the last accumulator) or an error is recorded
     tc05_fence_before_sync();
     __syncthreads();
     if (warp == 0) tc05_dealloc(tmem, TMEM_COLS);
@@ -642,9 +806,24 @@ size_t prefill_scratch_bytes(uint32_t max_tokens, uint32_t k, uint32_t n_expert,
     return off;
 }
 
+// The register reallocation inside the grouped GEMM is only safe if the kernels were compiled with exactly the
+// register count the split was computed for.
+static bool pf_kernels_as_planned()
+{
+    static int state = -1;
+    if (state < 0) {
+        cudaFuncAttributes f0, f1;
+        const bool got = cudaFuncGetAttributes(&f0, pf_grouped_gemm_kernel<PF_IQ2>) == cudaSuccess &&
+                         cudaFuncGetAttributes(&f1, pf_grouped_gemm_kernel<PF_Q2K>) == cudaSuccess;
+        state = got && f0.numRegs == PF_REG_LAUNCH && f1.numRegs == PF_REG_LAUNCH ? 1 : 0;
+    }
+    return state == 1;
+}
+
 bool prefill_eligible(uint32_t n_embd, uint32_t n_ff, const uint8_t *gate, const uint8_t *up, const uint8_t *down,
                       int layout)
 {
+    if (!pf_kernels_as_planned()) return false;
     const uintptr_t al = layout == DSMOE_LAYOUT_ROWSOA ? 15 : 3;
     return n_embd % QK_K == 0 && n_ff % QK_K == 0 && n_ff % 64 == 0 && n_embd % 128 == 0 && (n_embd / QK_K == 16 || n_embd / QK_K == 8) &&
            n_ff / QK_K <= 16 && (((uintptr_t)gate | (uintptr_t)up | (uintptr_t)down) & al) == 0 &&
@@ -720,6 +899,20 @@ int launch_prefill_experts(cudaStream_t st, const PrefillArgs &p)
     // 6. slots summed in slot order
     launch_moe_sum(st, reinterpret_cast<const float *>(w + L.down_pair), p.out, p.n_embd, p.k, p.n_tokens);
     mark(5);
+#ifdef PF_PROFILE
+    {
+        static long long h[2][160][32];
+        cudaStreamSynchronize(st);
+        cudaMemcpyFromSymbol(h, g_pf_prof, sizeof(h));
+        for (int k = 0; k < 2; ++k) {
+            double sum[32] = {0};
+            for (int c = 0; c < sms; ++c)
+                for (int q = 0; q < 32; ++q) sum[q] += (double)h[k][c][q] / sms / 1e3;
+            fprintf(stderr, "pf_prof kind %d (kcycles/CTA): consumer tab %.0f scale %.0f wait_full %.0f drain %.0f fold %.0f epi %.0f | issuer loop %.0f wait_a %.0f wait_b %.0f wait_acc %.0f issue %.0f | producer loop %.0f wait_free %.0f decode %.0f\n",
+                    k, sum[0], sum[1], sum[2], sum[3], sum[4], sum[5], sum[8], sum[9], sum[10], sum[11], sum[12], sum[16], sum[17], sum[18]);
+        }
+    }
+#endif
     return n + 6;
 }
 

@@ -122,4 +122,31 @@ __device__ __forceinline__ void tc05_wait_st() { asm volatile("tcgen05.wait::st.
 
 __device__ __forceinline__ void tc05_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// True in exactly one lane of a converged warp; lets the compiler treat the guarded code as executed once per warp.
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t r;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "elect.sync _|p, 0xffffffff;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(r));
+    return r != 0;
+}
+
+// Register reallocation between the warpgroups of a warp-specialised kernel. Every warp of a warpgroup (four
+// consecutive warps) must execute the same one; the count is a multiple of 8.
+template <uint32_t N>
+__device__ __forceinline__ void reg_alloc()
+{
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <uint32_t N>
+__device__ __forceinline__ void reg_dealloc()
+{
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 }  // namespace dsmoe
