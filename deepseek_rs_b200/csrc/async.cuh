@@ -57,6 +57,12 @@ __device__ __forceinline__ bool named_barrier_and(uint32_t id, uint32_t nthreads
     return r != 0;
 }
 
+// Named barrier `id` over `nthreads` threads (a multiple of 32), no reduction.
+__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t nthreads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 {
     uint32_t ok;

@@ -34,14 +34,18 @@ constexpr int PF_DECODE_WARPS = 16;  // producers: 8 weight rows each
 constexpr int PF_AUX_WARPS = 4;      // MMA issuer, activation loader, two idle (register reallocation works on 4 warps)
 constexpr int PF_THREADS = 32 * (PF_DRAIN_WARPS + PF_DECODE_WARPS + PF_AUX_WARPS);
 constexpr int PF_COLS = PF_TN / (PF_DRAIN_WARPS / 4);
+static_assert(PF_COLS == 64, "the drain reads its 64 TMEM columns per thread with two 32-column loads");
 // Registers per thread. The kernel is compiled for PF_REG_LAUNCH (the most 896 threads can have); after the role
 // split the producers and the auxiliary warps release registers and the consumers take them (setmaxnreg). An
 // increase blocks until the CTA's warps have RELEASED as many registers as it asks for (registers the CTA never
 // allocated do not count), so the released total must cover the request or the consumers would wait for ever.
 constexpr int PF_REG_LAUNCH = 72;
+#ifndef PF_DRAIN_WIDE
+#define PF_DRAIN_WIDE 1
+#endif
 #ifndef PF_REG_CONSUMER
-#define PF_REG_CONSUMER 120
-#define PF_REG_PRODUCER 56
+#define PF_REG_CONSUMER 152
+#define PF_REG_PRODUCER 40
 #define PF_REG_AUX 32
 #endif
 static_assert(32 * PF_DRAIN_WARPS * (PF_REG_CONSUMER - PF_REG_LAUNCH) <=
@@ -247,10 +251,11 @@ constexpr int PF_SMEM_B = PF_A_STAGES * PF_STAGE_A;                   // 3 x 32 
 constexpr int PF_SMEM_LUT = PF_SMEM_B + PF_B_STAGES * PF_STAGE_A;     // IQ2: codebook (f16, 32 KB) + signs (16 KB), 8 copies each
 constexpr int PF_SMEM_A2 = PF_SMEM_LUT;                               // Q2K (no tables): 2 x 4 KB sc_hi tile, one per TMEM buffer
 constexpr int PF_SMEM_B2 = PF_SMEM_A2 + 8192;                         // Q2K: 2 x 4 KB bsums tile
-constexpr int PF_SMEM_S = PF_SMEM_LUT + 49152;                        // 2 x (16 x 128 f32 scales), one per item parity
-constexpr int PF_SMEM_P = PF_SMEM_S + 2 * 16 * PF_TN * 4;             // 2 x 128 pair ids
-constexpr int PF_SMEM_W = PF_SMEM_P + 2 * PF_TN * 4;                  // 2 x 128 router weights
-constexpr int PF_SMEM_BAR = PF_SMEM_W + 2 * PF_TN * 4;
+constexpr int PF_SMEM_S = PF_SMEM_LUT + 49152;                        // per-item tables: 16 x 128 f32 activation scales,
+constexpr int PF_SMEM_D = PF_SMEM_S + 16 * PF_TN * 4;                 //   16 x 128 raw weight-scale words,
+constexpr int PF_SMEM_P = PF_SMEM_D + 16 * PF_TN * 4;                 //   128 pair ids,
+constexpr int PF_SMEM_W = PF_SMEM_P + PF_TN * 4;                      //   128 router weights
+constexpr int PF_SMEM_BAR = PF_SMEM_W + PF_TN * 4;
 constexpr int PF_SMEM_TOTAL = PF_SMEM_BAR + 128;
 static_assert(PF_SMEM_TOTAL <= 232448, "shared memory per CTA");
 
@@ -312,6 +317,14 @@ __device__ __forceinline__ uint2 pf_load_q2k_scales(const uint8_t *row, int layo
     const uint8_t *p = layout == DSMOE_LAYOUT_ROWSOA ? row + 16 * kb + 8 * half : row + Q2K_BYTES * kb + 8 * half;
     const uint32_t *q = reinterpret_cast<const uint32_t *>(p);
     return make_uint2(q[0], q[1]);
+}
+
+// the 16 scale bytes of Q2_K block kb
+__device__ __forceinline__ uint4 pf_load_q2k_scales16(const uint8_t *row, int layout, uint32_t kb)
+{
+    if (layout == DSMOE_LAYOUT_ROWSOA) return *reinterpret_cast<const uint4 *>(row + 16 * kb);
+    const uint32_t *q = reinterpret_cast<const uint32_t *>(row + Q2K_BYTES * kb);
+    return make_uint4(q[0], q[1], q[2], q[3]);
 }
 
 // IQ2_XXS: decode one 32-weight group into four core-matrix rows (8 f16 each) at dst + u * 128, u = 0..3
@@ -454,33 +467,41 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
         // accumulator row (TMEM lane) and column half of this thread
         const uint32_t arow = 32 * (warp & 3) + lane, acol0 = PF_COLS * (warp >> 2);
         const uint32_t tlane = (32u * (warp & 3)) << 16;
-        uint32_t gsb = 0, it = 0;  // superblocks drained so far (TMEM buffer and mbarrier phase), items started
+        uint32_t gsb = 0;  // superblocks drained so far (TMEM buffer and mbarrier phase)
         bool ok = true;
         PF_DECL();
         PF_T0();
 
-        for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x, ++it) {
+        for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x) {
             const uint32_t tile = item / n_mtiles, mt = item - tile * n_mtiles;
             const uint32_t rows = a.tile_rows[tile], rows16 = (rows + 15u) & ~15u, boff = a.tile_boff[tile];
             const uint32_t start = a.tile_start[tile];
             const uint64_t ebase = (uint64_t)a.tile_expert[tile] * a.expert_bytes;
             const uint8_t *srow = pf_tile_row<KIND>(a, ebase, mt, arow, row_bytes);  // the row whose scales apply here
 
-            // per-item tables (double-buffered by item parity): activation scales, pair ids, router weights
-            float *sS = reinterpret_cast<float *>(smem + PF_SMEM_S) + (it & 1u) * 16 * PF_TN;
-            uint32_t *sP = reinterpret_cast<uint32_t *>(smem + PF_SMEM_P) + (it & 1u) * PF_TN;
-            float *sW = reinterpret_cast<float *>(smem + PF_SMEM_W) + (it & 1u) * PF_TN;
-            for (uint32_t i = tid; i < a.kblocks * rows16; i += 32 * PF_DRAIN_WARPS) {
-                const uint32_t kb = i / rows16, c = i - kb * rows16;
-                sS[kb * PF_TN + c] = a.S[(size_t)kb * a.r_cap + boff + c];
+            // per-item tables: activation scales, this tile's weight scales (raw bits: IQ2 d as f16, Q2K d | dmin << 16),
+            // pair ids, router weights. They are rewritten once every warp is done with the previous item's.
+            float *sS = reinterpret_cast<float *>(smem + PF_SMEM_S);
+            uint32_t *sD = reinterpret_cast<uint32_t *>(smem + PF_SMEM_D);
+            uint32_t *sP = reinterpret_cast<uint32_t *>(smem + PF_SMEM_P);
+            float *sW = reinterpret_cast<float *>(smem + PF_SMEM_W);
+            ok = named_barrier_and(1, 32 * PF_DRAIN_WARPS, ok);
+            if (!ok) break;  // the same decision in all consumer warps
+            if ((uint32_t)(tid & (PF_TN - 1)) < rows16)
+                for (uint32_t kb = tid / PF_TN; kb < a.kblocks; kb += 32 * PF_DRAIN_WARPS / PF_TN)
+                    sS[kb * PF_TN + (tid & (PF_TN - 1))] = a.S[(size_t)kb * a.r_cap + boff + (tid & (PF_TN - 1))];
+            for (uint32_t kb = tid / PF_TN; kb < a.kblocks; kb += 32 * PF_DRAIN_WARPS / PF_TN) {  // row arow = tid % 128
+                uint32_t bits;
+                if (KIND == PF_IQ2) bits = a.layout == DSMOE_LAYOUT_ROWSOA ? ld_u16(srow + 2 * kb) : ld_u16(srow + IQ2XXS_BYTES * kb);
+                else bits = a.layout == DSMOE_LAYOUT_ROWSOA ? ld_u32(srow + 80 * a.kblocks + 4 * kb) : ld_u32(srow + Q2K_BYTES * kb + 80);
+                sD[kb * PF_TN + arow] = bits;
             }
             if ((uint32_t)tid < rows) {
                 const uint32_t pair = a.sorted[start + tid];
                 sP[tid] = pair;
                 if (KIND == PF_IQ2) sW[tid] = a.weights[pair];
             }
-            ok = named_barrier_and(1, 32 * PF_DRAIN_WARPS, ok);
-            if (!ok) break;  // the same decision in all consumer warps
+            named_barrier_sync(1, 32 * PF_DRAIN_WARPS);
             PF_ACC(0);
 
             // Q2K: running sum. IQ2: the current leaf's partial a_l, after the last leaf the row total
@@ -489,55 +510,100 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
             for (int i = 0; i < PF_COLS; ++i) acc[i] = 0.0f;
 
             for (uint32_t j = 0; j < a.kblocks; ++j) {
-                if (!ok) break;  // keeps walking the items, so that every warp reaches the item barrier
+                if (!ok) break;  // keeps walking the items, so that every warp reaches the item barriers
                 const uint32_t buf = gsb % NBUF, use = gsb / NBUF, kb = pf_visit_block<KIND>(a.kblocks, j);
                 // IQ2: position of this block in the reference's reduction tree
                 const uint32_t leaf = a.kblocks == 16 ? (j >> 1) : j;
                 const bool first_of_leaf = a.kblocks == 16 ? (j & 1) == 0 : true;
                 const bool last_of_leaf = a.kblocks == 16 ? (j & 1) == 1 : true;
-                // scales of this row for superblock kb (requested before the wait)
-                float dw, dmin = 0.0f;
-                if (KIND == PF_IQ2) {
-                    const uint32_t bits = a.layout == DSMOE_LAYOUT_ROWSOA ? ld_u16(srow + 2 * kb) : ld_u16(srow + IQ2XXS_BYTES * kb);
-                    dw = __fmul_rn(0.125f, f16_bits_to_f32(bits, ieee));
-                } else {
-                    const uint32_t dd = a.layout == DSMOE_LAYOUT_ROWSOA ? ld_u32(srow + 80 * a.kblocks + 4 * kb)
-                                                                        : ld_u32(srow + Q2K_BYTES * kb + 80);
-                    dw = f16_bits_to_f32(dd & 0xFFFFu, ieee);
-                    dmin = f16_bits_to_f32(dd >> 16, ieee);
-                }
+                const uint32_t sc_bits = sD[kb * PF_TN + arow];
                 PF_ACC(1);
                 ok = mbar_wait_bounded(&bar_acc_full[buf], use & 1u, a.status);
                 ok = __all_sync(FULL, ok);
                 if (!ok) break;
                 tc05_fence_after_sync();
                 PF_ACC(2);
+                float dw, dmin = 0.0f;
+                if (KIND == PF_IQ2) {
+                    dw = __fmul_rn(0.125f, f16_bits_to_f32(sc_bits, ieee));
+                } else {
+                    dw = f16_bits_to_f32(sc_bits & 0xFFFFu, ieee);
+                    dmin = f16_bits_to_f32(sc_bits >> 16, ieee);
+                }
                 const float4 *sx4 = reinterpret_cast<const float4 *>(sS + kb * PF_TN + acol0);
+                if (KIND == PF_IQ2) {
+                    // One accumulator buffer: it goes back to the issuer as soon as this thread's columns are in
+                    // registers, so that the next superblock's MMAs overlap the arithmetic.
+                    // ((0.125 d_w) d_x) bsum is added to 0 (first block of a leaf) or to the leaf's first block.
+                    auto release = [&]() {
+                        tc05_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&bar_acc_free[buf]);
+                    };
+                    auto scaled = [&](int c0, const float *v, bool first) {  // 16 columns from c0; v = their bsums
+                        float dxs[16];
 #pragma unroll
-                for (int c0 = 0; c0 < PF_COLS; c0 += 16) {
-                    if (acol0 + c0 >= rows16) break;  // warp-uniform: columns beyond the padded tile hold nothing
-                    float v[16], v2[16];
-                    tc05_ld16(tmem + tlane + buf * PF_TN + acol0 + c0, v);
-                    if (KIND == PF_Q2K) tc05_ld16(tmem + tlane + 256u + buf * PF_TN + acol0 + c0, v2);
-                    tc05_wait_ld();
-                    float dxs[16];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float4 t = sx4[(c0 >> 2) + i];
-                        dxs[4 * i] = t.x, dxs[4 * i + 1] = t.y, dxs[4 * i + 2] = t.z, dxs[4 * i + 3] = t.w;
-                    }
-                    if (KIND == PF_IQ2) {
-                        // ((0.125 d_w) d_x) bsum, added to 0 or to the leaf's first block
-                        if (first_of_leaf) {
-#pragma unroll
-                            for (int i = 0; i < 16; ++i)
-                                acc[c0 + i] = __fadd_rn(0.0f, __fmul_rn(__fmul_rn(dw, dxs[i]), v[i]));
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 16; ++i)
-                                acc[c0 + i] = __fadd_rn(acc[c0 + i], __fmul_rn(__fmul_rn(dw, dxs[i]), v[i]));
+                        for (int i = 0; i < 4; ++i) {
+                            const float4 t = sx4[(c0 >> 2) + i];
+                            dxs[4 * i] = t.x, dxs[4 * i + 1] = t.y, dxs[4 * i + 2] = t.z, dxs[4 * i + 3] = t.w;
                         }
-                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            acc[c0 + i] = __fadd_rn(first ? 0.0f : acc[c0 + i], __fmul_rn(__fmul_rn(dw, dxs[i]), v[i]));
+                    };
+                    if (!PF_DRAIN_WIDE) {  // 16 columns at a time, release at the end
+                        float v[16];
+#pragma unroll
+                        for (int c0 = 0; c0 < PF_COLS; c0 += 16) {
+                            if (acol0 + c0 >= rows16) break;
+                            tc05_ld16(tmem + tlane + acol0 + c0, v);
+                            tc05_wait_ld();
+                            if (first_of_leaf) scaled(c0, v, true);
+                            else scaled(c0, v, false);
+                        }
+                        release();
+                    } else if (first_of_leaf) {  // acc is dead: load all 64 columns into it, release, scale in place
+                        if (acol0 < rows16) {  // warp-uniform: columns beyond the padded tile hold nothing
+                            tc05_ld32(tmem + tlane + acol0, acc);
+                            if (acol0 + 32 < rows16) tc05_ld32(tmem + tlane + acol0 + 32, acc + 32);
+                            tc05_wait_ld();
+                        }
+                        release();
+#pragma unroll
+                        for (int c0 = 0; c0 < PF_COLS; c0 += 16) {
+                            if (acol0 + c0 >= rows16) break;
+                            scaled(c0, acc + c0, true);
+                        }
+                    } else {              // acc is live: two halves through 32 registers
+                        float v[32];
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            if (acol0 + 32 * h < rows16) {
+                                tc05_ld32(tmem + tlane + acol0 + 32 * h, v);
+                                tc05_wait_ld();
+                            }
+                            if (h == 1) release();
+#pragma unroll
+                            for (int c0 = 32 * h; c0 < 32 * h + 32; c0 += 16) {
+                                if (acol0 + c0 >= rows16) break;
+                                scaled(c0, v + (c0 - 32 * h), false);
+                            }
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int c0 = 0; c0 < PF_COLS; c0 += 16) {
+                        if (acol0 + c0 >= rows16) break;
+                        float v[16], v2[16];
+                        tc05_ld16(tmem + tlane + buf * PF_TN + acol0 + c0, v);
+                        tc05_ld16(tmem + tlane + 256u + buf * PF_TN + acol0 + c0, v2);
+                        tc05_wait_ld();
+                        float dxs[16];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float4 t = sx4[(c0 >> 2) + i];
+                            dxs[4 * i] = t.x, dxs[4 * i + 1] = t.y, dxs[4 * i + 2] = t.z, dxs[4 * i + 3] = t.w;
+                        }
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
                             const float t = __fsub_rn(__fmul_rn(__fmul_rn(dxs[i], dw), v[i]),
@@ -545,11 +611,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
                             acc[c0 + i] = __fadd_rn(acc[c0 + i], t);
                         }
                     }
+                    // both accumulators have been read: hand the buffer back to the issuer
+                    tc05_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bar_acc_free[buf]);
                 }
-                // the accumulator buffer has been read: hand it back to the issuer
-                tc05_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bar_acc_free[buf]);
                 ++gsb;
                 PF_ACC(3);
 
@@ -599,26 +665,52 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
                 // column half, the odd lane columns 32-63, each receiving the other input from its neighbour
                 const bool odd = (lane & 1) != 0;
                 const uint32_t orow = mt * 64 + (arow >> 1);
+                // eight columns at a time; pair ids and router weights are fetched first and everything but the store
+                // is unconditional, so that the eight dependency chains interleave
+                const uint32_t ecol0 = acol0 + (odd ? PF_COLS / 2 : 0);
 #pragma unroll
-                for (int i = 0; i < PF_COLS / 2; ++i) {
-                    const float send = odd ? acc[i] : acc[PF_COLS / 2 + i];
-                    const float recv = __shfl_xor_sync(FULL, send, 1);
-                    float g = odd ? recv : acc[i], u = odd ? acc[PF_COLS / 2 + i] : recv;
-                    const uint32_t col = acol0 + (odd ? PF_COLS / 2 + i : i);
-                    if (col < rows) {
+                for (int i0 = 0; i0 < PF_COLS / 2; i0 += 8) {
+                    if (acol0 + i0 >= rows) break;  // warp-uniform: the odd lanes' columns lie 32 further on
+                    uint32_t pr[8];
+                    float wr[8], r[8];
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        const uint4 t = *reinterpret_cast<const uint4 *>(sP + ecol0 + i0 + 4 * q);
+                        const float4 w4 = *reinterpret_cast<const float4 *>(sW + ecol0 + i0 + 4 * q);
+                        pr[4 * q] = t.x, pr[4 * q + 1] = t.y, pr[4 * q + 2] = t.z, pr[4 * q + 3] = t.w;
+                        wr[4 * q] = w4.x, wr[4 * q + 1] = w4.y, wr[4 * q + 2] = w4.z, wr[4 * q + 3] = w4.w;
+                    }
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const int i = i0 + k;
+                        const float send = odd ? acc[i] : acc[PF_COLS / 2 + i];
+                        const float recv = __shfl_xor_sync(FULL, send, 1);
+                        float g = odd ? recv : acc[i], u = odd ? acc[PF_COLS / 2 + i] : recv;
                         if (a.clamp > 1.0e-6f) {
                             if (g > a.clamp) g = a.clamp;
                             if (u > a.clamp) u = a.clamp;
                             if (u < -a.clamp) u = -a.clamp;
                         }
-                        a.out[(size_t)sP[col] * a.out_dim + orow] = swiglu_weighted(g, u, sW[col]);
+                        r[k] = swiglu_weighted(g, u, wr[k]);
                     }
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+                        if (ecol0 + i0 + k < rows) a.out[(size_t)pr[k] * a.out_dim + orow] = r[k];
                 }
             } else {
+                float *orow = a.out + mt * 128 + arow;
 #pragma unroll
-                for (int i = 0; i < PF_COLS; ++i) {
-                    const uint32_t col = acol0 + i;
-                    if (col < rows) a.out[(size_t)sP[col] * a.out_dim + mt * 128 + arow] = acc[i];
+                for (int i0 = 0; i0 < PF_COLS; i0 += 8) {
+                    if (acol0 + i0 >= rows) break;
+                    uint32_t pr[8];
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        const uint4 t = *reinterpret_cast<const uint4 *>(sP + acol0 + i0 + 4 * q);
+                        pr[4 * q] = t.x, pr[4 * q + 1] = t.y, pr[4 * q + 2] = t.z, pr[4 * q + 3] = t.w;
+                    }
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+                        if (acol0 + i0 + k < rows) orow[(size_t)pr[k] * a.out_dim] = acc[i0 + k];
                 }
             }
             PF_ACC(5);
@@ -642,40 +734,52 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
             const uint32_t tile = item / n_mtiles, mt = item - tile * n_mtiles;
             const uint64_t ebase = (uint64_t)a.tile_expert[tile] * a.expert_bytes;
             const uint8_t *drow = pf_tile_row<KIND>(a, ebase, mt, rl, row_bytes);
-            uint2 pk = pf_load_packed<KIND>(drow, a.layout, pf_visit_block<KIND>(a.kblocks, 0), 0, dc);
+            // Packed bytes are fetched one stage ahead and Q2_K scale bytes one superblock ahead. The loop is written
+            // two superblocks at a time over two register sets, so that a fetched value is first touched by the
+            // decode that needs it (a register copy at the end of a stage would wait for the load there).
+            uint2 pkA = pf_load_packed<KIND>(drow, a.layout, pf_visit_block<KIND>(a.kblocks, 0), 0, dc), pkB = pkA;
+            uint4 scA = make_uint4(0, 0, 0, 0), scB = scA;
+            if (KIND == PF_Q2K) scA = pf_load_q2k_scales16(drow, a.layout, pf_visit_block<KIND>(a.kblocks, 0));
 
-            for (uint32_t s = 0; s < n_stages; ++s, ++gs) {
-                const uint32_t b = gs & 1u, kb = pf_visit_block<KIND>(a.kblocks, s >> 1), half = s & 1u;
+            auto stage = [&](uint32_t s, const uint2 &cur, uint2 &nxt, const uint4 &sc) -> bool {
+                const uint32_t b = gs & 1u, half = s & 1u;
                 // the ring slot is free once the MMAs of the stage issued two stages ago have retired
                 PF_ACC(0);
                 if (gs >= 2) ok = mbar_wait_bounded(&bar_a_free[b], ((gs >> 1) - 1) & 1u, a.status);
                 ok = __all_sync(FULL, ok);
-                if (!ok) break;
+                if (!ok) return false;
                 PF_ACC(1);
-                // decode this stage's weights; fetch the next stage's packed bytes meanwhile
-                uint2 nx = pk;
                 if (s + 1 < n_stages)
-                    nx = pf_load_packed<KIND>(drow, a.layout, pf_visit_block<KIND>(a.kblocks, (s + 1) >> 1), (s + 1) & 1, dc);
+                    nxt = pf_load_packed<KIND>(drow, a.layout, pf_visit_block<KIND>(a.kblocks, (s + 1) >> 1), (s + 1) & 1, dc);
                 uint8_t *dst = smem + PF_SMEM_A + b * PF_STAGE_A + (rl >> 3) * PF_SBO + (rl & 7) * 16;
                 if (KIND == PF_IQ2) {
-                    pf_decode_iq2(pk, dst + dc * 512, lut_grid, lut_sign, dr8);
+                    pf_decode_iq2(cur, dst + dc * 512, lut_grid, lut_sign, dr8);
                 } else {
-                    const uint2 sc8 = pf_load_q2k_scales(drow, a.layout, kb, half);
-                    pf_decode_q2k(pk, sc8, dc, dst + dc * 128);
+                    pf_decode_q2k(cur, half ? make_uint2(sc.z, sc.w) : make_uint2(sc.x, sc.y), dc, dst + dc * 128);
                     if (half == 0 && dc < 2) {  // sc_hi of sub-blocks 8 dc .. 8 dc + 7 -> min-term operand, core dc
-                        const uint2 sh = pf_load_q2k_scales(drow, a.layout, kb, dc);
+                        const uint2 sh = dc ? make_uint2(sc.z, sc.w) : make_uint2(sc.x, sc.y);
                         *reinterpret_cast<uint4 *>(smem + PF_SMEM_A2 + (gsb & 1u) * 4096 + (rl >> 3) * 256 + dc * 128 +
                                                    (rl & 7) * 16) =
                             pf_bytes_to_f16x8((sh.x >> 4) & 0x0F0F0F0Fu, (sh.y >> 4) & 0x0F0F0F0Fu);
                     }
                 }
-                pk = nx;
                 // generic-proxy writes -> visible to the tensor core (async proxy); this warp's share is done
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bar_a_full[b]);
                 if (half == 1) ++gsb;
+                ++gs;
                 PF_ACC(2);
+                return true;
+            };
+            auto superblock = [&](uint32_t j, const uint4 &sc_cur, uint4 &sc_nxt) -> bool {
+                if (KIND == PF_Q2K && j + 1 < a.kblocks)
+                    sc_nxt = pf_load_q2k_scales16(drow, a.layout, pf_visit_block<KIND>(a.kblocks, j + 1));
+                return stage(2 * j, pkA, pkB, sc_cur) && stage(2 * j + 1, pkB, pkA, sc_cur);
+            };
+            for (uint32_t j = 0; j < a.kblocks; j += 2) {
+                if (!superblock(j, scA, scB)) break;
+                if (j + 1 < a.kblocks && !superblock(j + 1, scB, scA)) break;
             }
         }
         PF_DUMP(dtid == 0, 16);
