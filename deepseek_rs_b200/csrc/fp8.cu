@@ -201,7 +201,7 @@ __global__ void __launch_bounds__(256, 1) fp8_gemm_kernel(const uint8_t *__restr
         for (int c0 = 0; c0 < 64; c0 += 16) {
             float v[16];
             tc05_ld16(tmem + tlane + (kb & 1) * 128 + acol0 + c0, v);
-            tc05_wait_ld();
+            tc05_wait_ld16(v);
 #pragma unroll
             for (int i = 0; i < 16; ++i) acc[c0 + i] = fmaf(scale, v[i], acc[c0 + i]);
         }

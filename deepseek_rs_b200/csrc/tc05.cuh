@@ -132,7 +132,17 @@ __device__ __forceinline__ void tc05_st16(uint32_t taddr, const float (&v)[16])
 
 __device__ __forceinline__ void tc05_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-__device__ __forceinline__ void tc05_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Waits for this thread's TMEM loads. The registers a tcgen05.ld names are written asynchronously and may only be
+// read after this wait; the compiler sees an inline-asm load as complete, so the wait takes the loaded registers as
+// read-write operands, which keeps every use of them behind it.
+__device__ __forceinline__ void tc05_wait_ld16(float (&v)[16])
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : "+f"(v[0]), "+f"(v[1]), "+f"(v[2]), "+f"(v[3]), "+f"(v[4]), "+f"(v[5]), "+f"(v[6]), "+f"(v[7]), "+f"(v[8]), "+f"(v[9]), "+f"(v[10]), "+f"(v[11]), "+f"(v[12]), "+f"(v[13]), "+f"(v[14]), "+f"(v[15]) : : "memory");
+}
+__device__ __forceinline__ void tc05_wait_ld32(float *v)
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : "+f"(v[0]), "+f"(v[1]), "+f"(v[2]), "+f"(v[3]), "+f"(v[4]), "+f"(v[5]), "+f"(v[6]), "+f"(v[7]), "+f"(v[8]), "+f"(v[9]), "+f"(v[10]), "+f"(v[11]), "+f"(v[12]), "+f"(v[13]), "+f"(v[14]), "+f"(v[15]), "+f"(v[16]), "+f"(v[17]), "+f"(v[18]), "+f"(v[19]), "+f"(v[20]), "+f"(v[21]), "+f"(v[22]), "+f"(v[23]), "+f"(v[24]), "+f"(v[25]), "+f"(v[26]), "+f"(v[27]), "+f"(v[28]), "+f"(v[29]), "+f"(v[30]), "+f"(v[31]) : : "memory");
+}
 
 // True in exactly one lane of a converged warp; lets the compiler treat the guarded code as executed once per warp.
 __device__ __forceinline__ bool elect_one()

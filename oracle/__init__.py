@@ -84,6 +84,8 @@ def _declare(L: C.CDLL) -> None:
                                 C.c_uint32, C.c_int, C.c_int, C.c_float, C.c_int]
     L.orc_quantize_q8_0.argtypes = [_f32p, _i8p, _f32p, C.c_int64, C.c_int64]
     L.orc_matmul_q8_0.argtypes = [_u8p, _i8p, _f32p, _f32p, C.c_int64, C.c_int64, C.c_int64]
+    L.orc_check_div_rn.argtypes = [C.c_int64, C.c_uint64, C.POINTER(C.c_int64)]
+    L.orc_check_div_rn.restype = C.c_int64
     L.orc_e4m3_value.restype = C.c_float
     L.orc_e4m3_value.argtypes = [C.c_int]
     L.orc_e4m3_encode.restype = C.c_uint8
@@ -325,3 +327,10 @@ def fp8_gemm(a: np.ndarray, a_scale: np.ndarray, w: np.ndarray, w_scale: np.ndar
     out = np.empty((M, N), np.float32)
     lib().orc_fp8_gemm(_p(a, _u8p), _p(a_scale, _f32p), _p(w, _u8p), _p(w_scale, _f32p), _p(out, _f32p), M, N, K)
     return out
+
+
+def check_div_rn(n: int, seed: int = 1):
+    """(mismatches, skipped) of the SwiGLU division sequence against IEEE division over n pseudo-random pairs."""
+    skipped = C.c_int64(0)
+    bad = lib().orc_check_div_rn(int(n), int(seed), C.byref(skipped))
+    return int(bad), int(skipped.value)

@@ -787,3 +787,50 @@ void orc_set_num_threads(int n)
     (void)n;
 #endif
 }
+
+/* ------------------------------------------------------------------------------------------------------------ */
+/*
+ * Check of the division the CUDA SwiGLU uses in place of the library's (common.cuh, fdiv_rn_swiglu): for b in
+ * [1, 2^60) and |a| in [2^-60, 2^60), reciprocal by two Newton steps from an approximation that is off by up to
+ * three units in the last place (the hardware's is within one), then q + (a - b q) * y with an exact residual.
+ * The engine divides with the host's IEEE division (engine/src/kernels/moe.rs:703-710). Returns the number of
+ * operand pairs, out of n pseudo-random ones (one in four with a significand of b next to all ones or all zeros),
+ * for which the two differ; pairs whose b has an all-ones significand are counted in *skipped instead, because
+ * the CUDA code sends those to the library division.
+ */
+static inline float orc_u2f(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+static inline uint32_t orc_f2u(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+
+int64_t orc_check_div_rn(int64_t n, uint64_t seed, int64_t *skipped)
+{
+    int64_t bad = 0, skip = 0;
+#if defined(_OPENMP)
+#pragma omp parallel for reduction(+ : bad, skip) schedule(static)
+#endif
+    for (int64_t i = 0; i < n; ++i) {
+        uint64_t x = seed + 0x9E3779B97F4A7C15ull * (uint64_t)(2 * i + 1), y;
+        x ^= x >> 30, x *= 0xBF58476D1CE4E5B9ull, x ^= x >> 27, x *= 0x94D049BB133111EBull, x ^= x >> 31;
+        y = x + 0x9E3779B97F4A7C15ull;
+        y ^= y >> 30, y *= 0xBF58476D1CE4E5B9ull, y ^= y >> 27, y *= 0x94D049BB133111EBull, y ^= y >> 31;
+        uint32_t mb = (uint32_t)(x & 0x7FFFFF);
+        if ((i & 7) == 0) mb = 0x7FFFFF - (uint32_t)((x >> 40) & 3);
+        if ((i & 7) == 1) mb = (uint32_t)((x >> 40) & 3);
+        float b = orc_u2f(((127u + (uint32_t)((x >> 23) % 60)) << 23) | mb);
+        uint32_t ma = (uint32_t)(y & 0x7FFFFF);
+        if ((i & 15) == 2) ma = 0x7FFFFF - (uint32_t)((y >> 40) & 3);
+        float a = orc_u2f(((uint32_t)((y >> 63) & 1) << 31) | ((67u + (uint32_t)((y >> 23) % 120)) << 23) | ma);
+        float r = orc_u2f(orc_f2u(1.0f / b) + (uint32_t)((int)((y >> 50) % 7) - 3));
+        float e = fmaf(-b, r, 1.0f);
+        r = fmaf(r, e, r);
+        e = fmaf(-b, r, 1.0f);
+        r = fmaf(r, e, r);
+        float q = a * r;
+        float got = fmaf(fmaf(-b, q, a), r, q);
+        if (orc_f2u(got) != orc_f2u(a / b)) {
+            if (mb == 0x7FFFFF) ++skip;
+            else ++bad;
+        }
+    }
+    if (skipped) *skipped = skip;
+    return bad;
+}
