@@ -413,43 +413,50 @@ def run_fp8(args, torch, dist, K, device, rank, world, sampler):
     print(json.dumps(line), flush=True)
 
 
-def run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, T_total):
-    """Expert-parallel prefill: the 4096-token chunk is split evenly over the ranks (strong scaling), rank r owns
-    experts [r*256/G, (r+1)*256/G); NCCL all-to-all dispatch (Q8_K rows) and combine (f32 rows)."""
-    from deepseek_rs_b200.ep import ExpertParallelMoe, gpu_functions
+def run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, T_chunk):
+    """Expert-parallel prefill: rank r owns experts [r*256/G, (r+1)*256/G) and routes its own tokens; NCCL all-to-all
+    dispatch (Q8_K rows) and combine (f32 rows). Weak scaling (default): every rank brings its own 4096-token chunk.
+    --ep-scaling strong: one 4096-token chunk split evenly over the ranks."""
+    from deepseek_rs_b200.ep import ExpertParallelMoe, gpu_functions, gpu_sum_function
     from deepseek_rs_b200.kernels import LAYOUT_ROWSOA, MoeKernels, MoeLayer
 
+    weak = args.ep_scaling == "weak"
+    T_total = T_chunk * world if weak else T_chunk
     T = T_total // world
     per = N_EXPERT // world
     L, V = 2, 4
-    K_route = MoeKernels(device=local_rank, max_tokens=T_total, max_layers=1)
+    K_route = MoeKernels(device=local_rank, max_tokens=T, max_layers=1)
     K_owner = MoeKernels(device=local_rank, n_expert=per, n_expert_used=1, max_tokens=T_total * TOP_K, max_layers=L)
     for il in range(L):
         gate, up, down = gen_layer_gpu(torch, device, seed=1000 * rank + il, n_expert=per)
         MoeLayer(K_owner, gate, up, down, layout=LAYOUT_ROWSOA, layer=il)
         del gate, up, down
+    # expert popularity: the same on every rank. Tokens: weak = every rank its own chunk; strong = slices of one chunk
     gen = torch.Generator(device=device)
-    gen.manual_seed(7)  # the same global chunk on every rank; each takes its slice
-    xs = torch.randn((V, T_total, N_EMBD), device=device, generator=gen).to(torch.bfloat16).to(torch.float32)
+    gen.manual_seed(7)
     rank_e = (torch.randperm(N_EXPERT, device=device, generator=gen) + 1).float()
-    lgs = torch.randn((V, T_total, N_EXPERT), device=device, generator=gen) - 1.1 * torch.log(rank_e)[None, None, :]
-    lo = rank * T
+    xl, ll = [], []
+    for v in range(V):
+        gen.manual_seed(100 + v if not weak else 100 + v + 1000 * rank)
+        n_gen, lo = (T, 0) if weak else (T_total, rank * T)
+        x = torch.randn((n_gen, N_EMBD), device=device, generator=gen).to(torch.bfloat16).to(torch.float32)
+        lg = torch.randn((n_gen, N_EXPERT), device=device, generator=gen) - 1.1 * torch.log(rank_e)[None, :]
+        xl.append(x[lo:lo + T].contiguous())
+        ll.append(lg[lo:lo + T].contiguous())
+        del x, lg
     eps = []
     for il in range(L):
         rf, ef = gpu_functions(K_route, K_owner, layer=il)
-        eps.append(ExpertParallelMoe(rf, ef, N_EXPERT, TOP_K, N_EMBD))
-    # routing of the slice must equal the slice of the single-GPU routing (same kernel on the full chunk)
-    full_route = gpu_functions(K_route, K_owner)[0]
+        eps.append(ExpertParallelMoe(rf, ef, N_EXPERT, TOP_K, N_EMBD, sum_fn=gpu_sum_function(K_route)))
+    # the routing that comes out of the expert-parallel step must equal the single-GPU router's on the same tokens
+    solo_route = gpu_functions(K_route, K_owner)[0]
     same = True
     for v in range(V):
-        _, sel_full, _ = full_route(xs[v], lgs[v].contiguous())
-        _, sel = eps[0].forward(xs[v, lo:lo + T].contiguous(), lgs[v, lo:lo + T].contiguous())
-        same = same and bool(torch.equal(sel, sel_full[lo:lo + T]))
+        _, sel_solo, _ = solo_route(xl[v], ll[v])
+        _, sel = eps[0].forward(xl[v], ll[v])
+        same = same and bool(torch.equal(sel, sel_solo))
     flag = torch.tensor([1 if same else 0], device=device)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-    xl = [xs[v, lo:lo + T].contiguous() for v in range(V)]
-    ll = [lgs[v, lo:lo + T].contiguous() for v in range(V)]
-    del xs, lgs
 
     def step(i):
         return eps[i % L].forward(xl[i % V], ll[i % V])[0]
@@ -471,6 +478,24 @@ def run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, 
     launches = K_route.launch_count + K_owner.launch_count - l0
     recv_pairs = sum(eps[0].last_plan.recv_counts)
     assert K_owner.device_status() == 0
+
+    # phase times on this rank (events at the phase boundaries of the step)
+    names = ["route", "plan", "dispatch", "experts", "combine", "sum"]
+    phase = {n: 0.0 for n in names}
+    reps = min(args.steps, 5)
+    for i in range(reps):
+        evs = {}
+
+        def mark(name):
+            evs[name] = torch.cuda.Event(enable_timing=True)
+            evs[name].record()
+
+        eps[i % L].forward(xl[i % V], ll[i % V], mark=mark)
+        torch.cuda.synchronize()
+        prev = "start"
+        for n in names:
+            phase[n] += evs[prev].elapsed_time(evs[n]) / reps
+            prev = n
 
     # end to end: pinned host slices in, result back on the host, every step
     xh = [t.cpu().pin_memory() for t in xl]
@@ -496,7 +521,7 @@ def run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, 
     ms_step = ms_total / args.steps
     line = {
         "metric": METRIC, "value": T_total / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.ep_scaling,
         "vs_baseline": None, "dtype": "f16 integer codes x int8 (exact), f32 accumulate in TMEM", "data": "synthetic",
         "config": {"workload": args.workload, "tokens_per_step_all_gpus": T_total, "tokens_per_step_per_gpu": T,
                    "top_k": TOP_K, "n_expert": N_EXPERT, "experts_per_gpu": per, "n_embd": N_EMBD, "n_ff": N_FF,
@@ -510,6 +535,7 @@ def run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, 
                      "note": "kernel-level figures are reported by the 1-GPU run; this line is the whole EP step"},
         "e2e": {"value": T_total / (e2e_ms_step * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": T * (N_EMBD + N_EXPERT) * 4 * world, "d2h_bytes_per_step": T * N_EMBD * 4 * world},
+        "phases_ms_rank0": phase,
         "gpu_launches": launches, "timed_with": "CUDA events around K back-to-back steps, max over ranks",
         "clocks": clocks,
     }
@@ -525,6 +551,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layout", default="rowsoa", choices=["rowsoa", "native"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep-scaling", default="weak", choices=["weak", "strong"],
+                    help="N > 1: every rank its own chunk (weak) or one chunk split over the ranks (strong)")
     ap.add_argument("--layers", type=int, default=0, help="layers to rotate over (0 = the workload's default; 1 keeps "
                     "device memory small for profiler captures)")
     args = ap.parse_args()

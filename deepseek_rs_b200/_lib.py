@@ -40,6 +40,7 @@ SIGNATURES = {
     "dsmoe_down": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _u64, _u64, _u32, _u32, _u32, _u32, _int]),
     "dsmoe_down_sum": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _u64, _u64, _u32, _u32, _u32, _u32, _int]),
     "dsmoe_moe_sum": (_int, [_vp, _vp, _vp, _vp, _u32, _u32, _u32]),
+    "dsmoe_moe_sum_indexed": (_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32]),
     "dsmoe_dequant_iq2xxs": (_int, [_vp, _vp, _vp, _u64, _vp]),
     "dsmoe_dequant_q2k": (_int, [_vp, _vp, _vp, _u64, _vp]),
     "dsmoe_relayout_iq2xxs": (_int, [_vp, _vp, _vp, _vp, _u64, _u32, _int]),

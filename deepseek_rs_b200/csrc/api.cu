@@ -31,7 +31,8 @@ struct dsmoe_handle {
     float *d_x, *d_logits, *d_out;
     int *d_status;  // device status word: 0, or the first device-side error code (a bounded wait that expired)
     bool use_tma;   // stage packed rows with bulk asynchronous copies where the shapes allow (default on)
-    // batched (tcgen05 grouped GEMM) path: used by the tier-2 call from prefill_min_tokens tokens upwards
+    // batched (tcgen05 grouped GEMM) path: used by the tier-2 call from prefill_min_tokens tokens upwards (default:
+    // 4.5 pairs per expert; DSMOE_PREFILL_MIN_TOKENS overrides)
     uint8_t *pf_scratch;
     PrefillScratch pf_lay;
     uint32_t prefill_min_tokens;
@@ -142,7 +143,11 @@ int dsmoe_create(const dsmoe_config *cfg, int device, dsmoe_handle **out)
                                                       cfg->n_ff, &h->pf_lay);
         ok = ok && dev_alloc(&h->pf_scratch, pf_bytes) == cudaSuccess;
         const char *pm = getenv("DSMOE_PREFILL_MIN_TOKENS");
-        h->prefill_min_tokens = pm ? (uint32_t)strtoul(pm, nullptr, 10) : 48u;
+        // The grouped GEMM costs about 9.4 us per token tile (every tile decodes its expert's weights once, however
+        // few rows it holds), the decode kernels about 1.9 us per (token, slot) pair, both measured on a B200. With
+        // every expert hit, the batched path wins from about 4.5 pairs per expert upwards.
+        const uint32_t by_occupancy = (9u * cfg->n_expert + 2u * cfg->n_expert_used - 1u) / (2u * cfg->n_expert_used);
+        h->prefill_min_tokens = pm ? (uint32_t)strtoul(pm, nullptr, 10) : by_occupancy;
     }
     const char *no_tma = getenv("DSMOE_DISABLE_TMA");
     h->use_tma = !(no_tma && no_tma[0] == '1');
@@ -302,8 +307,18 @@ int dsmoe_moe_sum(dsmoe_handle *h, dsmoe_stream stream, const float *down, float
     if (!h) return DSMOE_ERR_ARG;
     if (n_tokens == 0 || out_dim == 0) return DSMOE_OK;
     DSMOE_REQUIRE(h, down && out, "moe_sum: null pointer");
-    launch_moe_sum((cudaStream_t)stream, down, out, out_dim, n_expert_used, n_tokens);
+    launch_moe_sum((cudaStream_t)stream, down, nullptr, out, out_dim, n_expert_used, n_tokens);
     return check_launch(h, "moe_sum", 1);
+}
+
+int dsmoe_moe_sum_indexed(dsmoe_handle *h, dsmoe_stream stream, const float *rows, const int32_t *pos, float *out,
+                          uint32_t out_dim, uint32_t n_expert_used, uint32_t n_tokens)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    if (n_tokens == 0 || out_dim == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, rows && pos && out, "moe_sum_indexed: null pointer");
+    launch_moe_sum((cudaStream_t)stream, rows, pos, out, out_dim, n_expert_used, n_tokens);
+    return check_launch(h, "moe_sum_indexed", 1);
 }
 
 int dsmoe_dequant_iq2xxs(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *blocks, uint64_t n_blocks, float *out)

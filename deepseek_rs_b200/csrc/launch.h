@@ -23,7 +23,8 @@ void launch_dequant_iq2xxs(cudaStream_t st, const uint8_t *blocks, uint64_t n_bl
 void launch_dequant_q2k(cudaStream_t st, const uint8_t *blocks, uint64_t n_blocks, float *out, int ieee);
 void launch_relayout_iq2xxs(cudaStream_t st, const uint8_t *src, uint8_t *dst, uint64_t n_rows, uint32_t xb, int inverse);
 void launch_relayout_q2k(cudaStream_t st, const uint8_t *src, uint8_t *dst, uint64_t n_rows, uint32_t mb, int inverse);
-void launch_moe_sum(cudaStream_t st, const float *down, float *out, uint32_t out_dim, uint32_t k, uint32_t n_tokens);
+void launch_moe_sum(cudaStream_t st, const float *down, const int32_t *pos, float *out, uint32_t out_dim, uint32_t k,
+                    uint32_t n_tokens);
 
 struct GateUpArgs {
     const uint8_t *gate_base, *up_base, *xq;

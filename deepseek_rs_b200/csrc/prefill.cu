@@ -1013,7 +1013,7 @@ int launch_prefill_experts(cudaStream_t st, const PrefillArgs &p)
     pf_grouped_gemm_kernel<PF_Q2K><<<sms, PF_THREADS, PF_SMEM_TOTAL, st>>>(d);
     mark(4);
     // 6. slots summed in slot order
-    launch_moe_sum(st, reinterpret_cast<const float *>(w + L.down_pair), p.out, p.n_embd, p.k, p.n_tokens);
+    launch_moe_sum(st, reinterpret_cast<const float *>(w + L.down_pair), nullptr, p.out, p.n_embd, p.k, p.n_tokens);
     mark(5);
 #ifdef PF_PROFILE
     {

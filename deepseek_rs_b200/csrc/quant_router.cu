@@ -390,22 +390,42 @@ void launch_relayout_q2k(cudaStream_t st, const uint8_t *src, uint8_t *dst, uint
 // ---------------------------------------------------------------------------------------------------------------
 // Slot sum (engine/src/kernels/moe.rs:983-1005): out[t][row] = sum over slots, in slot order, starting from 0.
 // ---------------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) moe_sum_kernel(const float *__restrict__ down, float *__restrict__ out,
-                                                       uint32_t out_dim, uint32_t k, uint64_t n)
+// out[tok] = ((0 + r_0) + r_1) + ... over the token's k slot rows, r_e = down[pos ? pos[tok*k+e] : tok*k+e].
+// VEC = 4: one float4 per thread (out_dim a multiple of 4, pointers 16-byte aligned); VEC = 1 otherwise.
+template <int VEC>
+__global__ void __launch_bounds__(256) moe_sum_kernel(const float *__restrict__ down, const int32_t *__restrict__ pos,
+                                                       float *__restrict__ out, uint32_t out_dim, uint32_t k, uint64_t n)
 {
-    uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (gid >= n) return;
-    uint64_t tok = gid / out_dim, row = gid - tok * out_dim;
-    float acc = 0.0f;
-    for (uint32_t e = 0; e < k; ++e) acc = __fadd_rn(acc, down[(tok * k + e) * out_dim + row]);
-    out[gid] = acc;
+    const uint32_t per_row = out_dim / VEC;
+    const uint64_t tok = gid / per_row, col = (gid - tok * per_row) * VEC;
+    float acc[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = 0.0f;
+    for (uint32_t e = 0; e < k; ++e) {
+        const uint64_t row = pos ? (uint64_t)(uint32_t)pos[tok * k + e] : tok * k + e;
+        const float *src = down + row * out_dim + col;
+        if (VEC == 4) {
+            const float4 v = *reinterpret_cast<const float4 *>(src);
+            acc[0] = __fadd_rn(acc[0], v.x), acc[1] = __fadd_rn(acc[1], v.y);
+            acc[2] = __fadd_rn(acc[2], v.z), acc[3] = __fadd_rn(acc[3], v.w);
+        } else {
+            acc[0] = __fadd_rn(acc[0], src[0]);
+        }
+    }
+    if (VEC == 4) *reinterpret_cast<float4 *>(out + tok * out_dim + col) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    else out[tok * out_dim + col] = acc[0];
 }
 
-void launch_moe_sum(cudaStream_t st, const float *down, float *out, uint32_t out_dim, uint32_t k, uint32_t n_tokens)
+void launch_moe_sum(cudaStream_t st, const float *down, const int32_t *pos, float *out, uint32_t out_dim, uint32_t k,
+                    uint32_t n_tokens)
 {
-    uint64_t n = (uint64_t)n_tokens * out_dim;
-    if (n == 0) return;
-    moe_sum_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(down, out, out_dim, k, n);
+    if (n_tokens == 0 || out_dim == 0) return;
+    const bool vec = out_dim % 4 == 0 && (((uintptr_t)down | (uintptr_t)out) & 15) == 0;
+    const uint64_t n = (uint64_t)n_tokens * (vec ? out_dim / 4 : out_dim);
+    if (vec) moe_sum_kernel<4><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(down, pos, out, out_dim, k, n);
+    else moe_sum_kernel<1><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(down, pos, out, out_dim, k, n);
 }
 
 }  // namespace dsmoe

@@ -57,10 +57,12 @@ class ExpertParallelMoe:
 
     route_fn(x, logits) -> (xq uint8 [T, n_embd/256, 292], selected int32 [T, k], weights f32 [T, k])
     expert_fn(xq_rows, local_expert int32 [R, 1], weights f32 [R, 1]) -> f32 [R, n_embd]   (k = 1 on the owner)
+    sum_fn(rows f32 [T*k, n_embd], pos int32 [T*k], T) -> f32 [T, n_embd]: slot e of token t is rows[pos[t*k+e]],
+        slots added in slot order (default: un-permute, then k torch additions)
     """
 
-    def __init__(self, route_fn, expert_fn, n_expert: int, k: int, n_embd: int, group=None):
-        self.route_fn, self.expert_fn = route_fn, expert_fn
+    def __init__(self, route_fn, expert_fn, n_expert: int, k: int, n_embd: int, group=None, sum_fn=None):
+        self.route_fn, self.expert_fn, self.sum_fn = route_fn, expert_fn, sum_fn
         self.n_expert, self.k, self.n_embd = n_expert, k, n_embd
         self.group = group
         self.world = dist.get_world_size(group)
@@ -69,29 +71,46 @@ class ExpertParallelMoe:
         self.per_rank = n_expert // self.world
         self.last_plan = None
 
-    def forward(self, x: torch.Tensor, logits: torch.Tensor):
-        """x f32 [T, n_embd], logits f32 [T, n_expert] (this rank's tokens). Returns (out f32 [T, n_embd], selected)."""
+    def forward(self, x: torch.Tensor, logits: torch.Tensor, mark=None):
+        """x f32 [T, n_embd], logits f32 [T, n_expert] (this rank's tokens). Returns (out f32 [T, n_embd], selected).
+        ``mark(name)``, if given, is called at the phase boundaries (the bench records CUDA events there)."""
+        mark = mark or (lambda name: None)
         T = x.shape[0]
+        mark("start")
         xq, selected, weights = self.route_fn(x, logits)
+        mark("route")
         plan = make_plan(selected, self.n_expert, self.world, self.group)
         self.last_plan = plan
+        mark("plan")
         pair_tok = plan.order // self.k
-        # dispatch: Q8_K row of the pair's token, local expert id, router weight
+        # dispatch: Q8_K row of the pair's token; local expert id and router weight (as its bit pattern) in one
+        # int32 [pairs, 2] message
         xq_rows = xq.reshape(T, (self.n_embd // QK_K) * Q8K_BYTES)[pair_tok]
         sel_flat = selected.reshape(-1).clamp(min=0)[plan.order]
-        meta_e = (sel_flat % self.per_rank).to(torch.int32).reshape(-1, 1)
-        meta_w = weights.reshape(-1)[plan.order].reshape(-1, 1).contiguous()
+        meta = torch.stack(((sel_flat % self.per_rank).to(torch.int32),
+                            weights.reshape(-1)[plan.order].contiguous().view(torch.int32)), dim=1)
         r_xq = _exchange(xq_rows, plan.send_counts, plan.recv_counts, self.group)
-        r_e = _exchange(meta_e, plan.send_counts, plan.recv_counts, self.group)
-        r_w = _exchange(meta_w, plan.send_counts, plan.recv_counts, self.group)
+        r_meta = _exchange(meta, plan.send_counts, plan.recv_counts, self.group)
+        r_e = r_meta[:, 0:1].contiguous()
+        r_w = r_meta[:, 1:2].contiguous().view(torch.float32)
+        mark("dispatch")
         # the owner's compute: every received row is one (token, slot) pair of one local expert
         if r_xq.shape[0]:
             rows = self.expert_fn(r_xq.reshape(r_xq.shape[0], self.n_embd // QK_K, Q8K_BYTES), r_e, r_w)
         else:
             rows = x.new_empty((0, self.n_embd))
+        mark("experts")
         # combine: rows travel back along the same splits, land in dispatch order, are put back in pair order and
         # summed per token in slot order
         back = _exchange(rows, plan.recv_counts, plan.send_counts, self.group)
+        mark("combine")
+        if self.sum_fn is not None:
+            # position of every pair's row in ``back``: the inverse of the dispatch order
+            pos = torch.empty_like(plan.order)
+            pos[plan.order] = torch.arange(plan.order.numel(), device=plan.order.device)
+            out = self.sum_fn(back, pos.to(torch.int32), T)
+            mark("sum")
+            return out, selected
         pair_rows = torch.empty((T * self.k, self.n_embd), dtype=back.dtype, device=back.device)
         pair_rows[plan.order] = back
         pr = pair_rows.reshape(T, self.k, self.n_embd)
@@ -102,7 +121,7 @@ class ExpertParallelMoe:
 
 
 def gpu_functions(kernels_route, kernels_owner, layer: int = 0):
-    """route_fn / expert_fn over the C ABI. ``kernels_route``: a MoeKernels with the model's k (router + Q8_K only);
+    """route_fn / expert_fn over the C ABI (``gpu_sum_function`` gives the matching sum_fn). ``kernels_route``: a MoeKernels with the model's k (router + Q8_K only);
     ``kernels_owner``: a MoeKernels created with n_expert = experts per rank and n_expert_used = 1, holding this rank's
     shard in ``layer``."""
     cfg = kernels_route.cfg
@@ -125,3 +144,15 @@ def gpu_functions(kernels_route, kernels_owner, layer: int = 0):
         return out
 
     return route_fn, expert_fn
+
+
+def gpu_sum_function(kernels_route):
+    """sum_fn over the C ABI: the slot-order sum kernel (engine/src/kernels/moe.rs:983)."""
+    cfg = kernels_route.cfg
+
+    def sum_fn(rows, pos, T):
+        out = torch.empty((T, cfg.n_embd), dtype=torch.float32, device=rows.device)
+        kernels_route.moe_sum_indexed(rows.contiguous(), pos.contiguous(), out, cfg.n_embd, cfg.n_expert_used, T)
+        return out
+
+    return sum_fn

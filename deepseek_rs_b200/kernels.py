@@ -140,6 +140,11 @@ class MoeKernels:
 
     # ---- helpers with no reference kernel ------------------------------------------------------------------------
 
+    def moe_sum_indexed(self, rows, pos, out, out_dim: int, n_expert: int, n_tokens: int):
+        """The slot-order sum of engine/src/kernels/moe.rs:983 over rows addressed through ``pos`` (int32)."""
+        self._check(self.lib.dsmoe_moe_sum_indexed(self.h, _stream(), _ptr(rows), _ptr(pos), _ptr(out), out_dim, n_expert,
+                                                   n_tokens))
+
     def dequant_iq2xxs(self, blocks, n_blocks: int, out):
         self._check(self.lib.dsmoe_dequant_iq2xxs(self.h, _stream(), _ptr(blocks), n_blocks, _ptr(out)))
 

@@ -138,6 +138,13 @@ DSMOE_API int dsmoe_down_sum(dsmoe_handle *h, dsmoe_stream stream, const uint8_t
 DSMOE_API int dsmoe_moe_sum(dsmoe_handle *h, dsmoe_stream stream, const float *down, float *out, uint32_t out_dim,
                             uint32_t n_expert_used, uint32_t n_tokens);
 
+/* The same sum (engine/src/kernels/moe.rs:983-1005: 0 + r_0 + r_1 + ... in slot order) over rows that are not stored
+ * in pair order: slot e of token t is rows[pos[t*n_expert_used + e]]. No counterpart in the reference, which is
+ * single-GPU; the expert-parallel combine uses it to sum the rows in the order they came back from their owners.
+ * pos entries must lie in [0, number of rows). */
+DSMOE_API int dsmoe_moe_sum_indexed(dsmoe_handle *h, dsmoe_stream stream, const float *rows, const int32_t *pos,
+                                    float *out, uint32_t out_dim, uint32_t n_expert_used, uint32_t n_tokens);
+
 /* Dequantised weights. The reference has no such kernel; the values are defined by its block dots
  * (engine/src/kernels/quantize.rs:811, :900): IQ2_XXS w = (0.125*d) * (ls * +/-g); Q2_K w = d*(sc*q) - dmin*m.
  * blocks are in NATIVE order; out: f32 [n_blocks][256]. Bit-exact against the CPU oracle. */

@@ -482,7 +482,7 @@ def test_expert_parallel_world1_matches_forward(torch_cuda, oracle):
 
     import torch.distributed as dist
 
-    from deepseek_rs_b200.ep import ExpertParallelMoe, gpu_functions
+    from deepseek_rs_b200.ep import ExpertParallelMoe, gpu_functions, gpu_sum_function
     from deepseek_rs_b200.kernels import LAYOUT_ROWSOA, MoeKernels, MoeLayer
 
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -507,7 +507,7 @@ def test_expert_parallel_world1_matches_forward(torch_cuda, oracle):
                 del os.environ["DSMOE_PREFILL_MIN_TOKENS"]
             MoeLayer(K_owner, lw.gate, lw.up, lw.down, layout=LAYOUT_ROWSOA)
             rf, ef = gpu_functions(K_full, K_owner)
-            out, sel = ExpertParallelMoe(rf, ef, n_e, 6, 4096).forward(x, logits)
+            out, sel = ExpertParallelMoe(rf, ef, n_e, 6, 4096, sum_fn=gpu_sum_function(K_full)).forward(x, logits)
             assert K_owner.device_status() == 0
             if exact:
                 assert torch.equal(out, want)
