@@ -60,8 +60,9 @@ def measured_peaks():
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up decode kernel, from the ncu captures summarised
 # in profiles/decode_gate_up_and_down_ncu.md (batch 1: equal to the algorithmic bytes; batch 64: 1.79 x, pairs of one
-# expert are not yet grouped)
-NCU_TRAFFIC = {"moe_decode_b1": 25999616, "moe_decode_b64": 1552575072}
+# expert are not yet grouped) and, for the prefill workload, of the gate/up grouped GEMM
+# (profiles/prefill_grouped_gemm_ncu.md: the packed weights once per token tile plus activations and mid)
+NCU_TRAFFIC = {"moe_decode_b1": 25999616, "moe_decode_b64": 1552575072, "moe_prefill_4096": 989383936}
 
 
 def ncu_traffic(workload: str):
@@ -307,7 +308,8 @@ def run_prefill(args, torch, dist, K, layers, layout, device, rank, world, sampl
         "packed_weight_gbs": u_mean * EXPERT_BYTES * world / (ms_step * 1e-3) / 1e9,
         "roofline": {"bound": "tensor", "kernel": "pf_grouped_gemm_kernel<IQ2> (gate+up+SwiGLU, tcgen05 kind::f16)",
                      "achieved": gu_flops / (phase[1] * 1e-3) / 1e12, "peak": peak_tf, "peak_kind": f"of {peak_kind}",
-                     "unit": "TFLOP/s", "frac": gu_flops / (phase[1] * 1e-3) / 1e12 / peak_tf, "traffic": None,
+                     "unit": "TFLOP/s", "frac": gu_flops / (phase[1] * 1e-3) / 1e12 / peak_tf,
+                     "traffic": ncu_traffic(args.workload) if L >= 1 else None,
                      "algorithmic_flops_per_launch": gu_flops, "avg_launch_ms": phase[1]},
         "roofline_down": {"bound": "tensor", "kernel": "pf_grouped_gemm_kernel<Q2K> (down, tcgen05 kind::f16)",
                           "achieved": dn_flops / (phase[3] * 1e-3) / 1e12, "peak": peak_tf, "unit": "TFLOP/s",
