@@ -212,6 +212,45 @@ def measured_tflops():
     return 1590.0, "fallback"
 
 
+def ref_mapping_gpu(torch, device, K, workload_tokens: int, ours_ms_per_step: float):
+    """GPU baseline beside the product: the reference kernels' thread mapping restated in CUDA (baseline/ref_mapping.cu),
+    run the way the reference runs the path — one token at a time, four launches per token. Timed on a bounded sample
+    of tokens on one layer in the reference's own (NATIVE) byte order; routing comes from the product's router."""
+    from baseline import RefMapping
+
+    R = RefMapping()
+    T = min(256, max(workload_tokens, 32))
+    gate, up, down = gen_layer_gpu(torch, device, seed=0)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(99)
+    x = torch.randn((T, N_EMBD), device=device, generator=gen).to(torch.bfloat16).to(torch.float32).contiguous()
+    rank_e = (torch.randperm(N_EXPERT, device=device, generator=gen) + 1).float()
+    lg = (torch.randn((T, N_EXPERT), device=device, generator=gen) - 1.1 * torch.log(rank_e)[None, :]).contiguous()
+    probs = torch.empty((T, N_EXPERT), device=device)
+    sel = torch.empty((T, TOP_K), dtype=torch.int32, device=device)
+    w = torch.empty((T, TOP_K), device=device)
+    K.router_select_parallel(lg, None, None, None, probs, sel, w, 0, 0, T, 0, 0)
+    xq = torch.empty((N_EMBD // 256) * 292, dtype=torch.uint8, device=device)
+    mid = torch.empty((TOP_K, N_FF), device=device)
+    midq = torch.empty(TOP_K * (N_FF // 256) * 292, dtype=torch.uint8, device=device)
+    out = torch.empty((T, N_EMBD), device=device)
+    R.tokens(gate, up, down, x, sel, w, xq, mid, midq, out, N_EMBD, N_FF, 8, 10.0)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    R.tokens(gate, up, down, x, sel, w, xq, mid, midq, out, N_EMBD, N_FF, T, 10.0)
+    e1.record()
+    torch.cuda.synchronize()
+    ms_tok = e0.elapsed_time(e1) / T
+    del gate, up, down
+    ref_ms_step = ms_tok * workload_tokens
+    return {"kind": "restatement of the reference kernels' thread mapping and scalar loads, not the cuda-oxide binary",
+            "launches_per_token": 4, "tokens_timed": T, "ms_per_token": ms_tok, "value": 1e3 / ms_tok, "unit": UNIT,
+            "ms_for_this_workload_step": ref_ms_step, "extrapolated": workload_tokens > T,
+            "product_speedup": ref_ms_step / ours_ms_per_step,
+            "note": "router excluded on the baseline side (it is the product's kernel); Q8_K, gate/up, Q8_K, down+sum timed"}
+
+
 def run_prefill(args, torch, dist, K, layers, layout, device, rank, world, sampler, T, L):
     """The batched (grouped-GEMM) workload: one step = one 4096-token chunk through one layer's routed experts."""
     V = 4
@@ -322,6 +361,8 @@ def run_prefill(args, torch, dist, K, layers, layout, device, rank, world, sampl
     }
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(args.workload)
+    if world == 1 and not args.no_ref_mapping:
+        line["ref_mapping_gpu"] = ref_mapping_gpu(torch, device, K, T, ms_step)
     print(json.dumps(line), flush=True)
 
 
@@ -553,6 +594,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layout", default="rowsoa", choices=["rowsoa", "native"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-ref-mapping", action="store_true", help="skip the GPU baseline (restated reference mapping)")
     ap.add_argument("--ep-scaling", default="weak", choices=["weak", "strong"],
                     help="N > 1: every rank its own chunk (weak) or one chunk split over the ranks (strong)")
     ap.add_argument("--layers", type=int, default=0, help="layers to rotate over (0 = the workload's default; 1 keeps "
@@ -790,6 +832,8 @@ def main():
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(args.workload)
+        if world == 1 and not args.no_ref_mapping:
+            line["ref_mapping_gpu"] = ref_mapping_gpu(torch, device, K, T, ms_total / args.steps)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
