@@ -43,6 +43,8 @@ WORKLOADS = {
     "moe_prefill_4096": dict(tokens=4096, layers=2, zipf=True),
     # FP8 E4M3 block-scaled dense projection (no counterpart in the reference), all six (M, N) shapes in one line
     "fp8_linear": dict(tokens=4096, layers=0, zipf=False),
+    # router logits (f16) + shared expert (Q8_0), the steps beside the routed experts; batch 1, 8 and 64 in one line
+    "shared_expert": dict(tokens=1, layers=0, zipf=False),
 }
 DEFAULT_WORKLOAD = "moe_prefill_4096"
 METRIC, UNIT = "moe_expert_layer_tokens_per_s", "tokens/s"
@@ -456,6 +458,96 @@ def run_fp8(args, torch, dist, K, device, rank, world, sampler):
     print(json.dumps(line), flush=True)
 
 
+def run_shared(args, torch, dist, K, device, rank, world, sampler):
+    """Router logits (matmul_f16, 2 MB of f16 weights) and the shared expert (three Q8_0 matrices, 26.7 MB) for
+    batches of 1, 8 and 64 tokens. R layers' weights rotate so that a step never finds its weights in L2."""
+    R = 8  # 8 x 28.8 MB = 231 MB > 126 MB L2
+    gen = torch.Generator(device=device)
+    gen.manual_seed(21 + rank)
+
+    def q8_0(rows, cols):
+        t = torch.randint(0, 256, (rows * (cols // 32), 34), dtype=torch.uint8, device=device, generator=gen)
+        sc = (torch.randn(rows * (cols // 32), device=device, generator=gen).abs() * 1e-3).to(torch.float16)
+        t[:, 0:2] = sc.view(torch.uint8).view(-1, 2)
+        return t.view(-1)
+
+    layers = [(q8_0(N_FF, N_EMBD), q8_0(N_FF, N_EMBD), q8_0(N_EMBD, N_FF),
+               (torch.randn((N_EXPERT, N_EMBD), device=device, generator=gen) * 0.05).to(torch.float16)) for _ in range(R)]
+    sh_bytes = (2 * N_FF * (N_EMBD // 32) + N_EMBD * (N_FF // 32)) * 34
+    results, t_load0, g = [], time.time(), None
+    for T in (1, 8, 64):
+        x = torch.randn((T, N_EMBD), device=device, generator=gen).to(torch.bfloat16).to(torch.float32)
+        out = torch.empty((T, N_EMBD), device=device)
+        logits = torch.empty((T, N_EXPERT), device=device)
+
+        def step(i):
+            gw, uw, dw, rw = layers[i % R]
+            K.matmul_f16(rw, x, logits, N_EMBD, N_EXPERT, T)
+            K.shared_expert(gw, uw, dw, x, T, out)
+
+        for i in range(args.warmup):
+            step(i)
+        g = torch.cuda.CUDAGraph()
+        cs = torch.cuda.Stream()
+        cs.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(cs):
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g, stream=cs):
+                for i in range(R):
+                    step(i)
+        torch.cuda.current_stream().wait_stream(cs)
+        g.replay()
+        torch.cuda.synchronize()
+        reps = max(1, max(args.steps, 200) // R)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / (reps * R)
+        xh, oh = x.cpu().pin_memory(), torch.empty((T, N_EMBD)).pin_memory()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for i in range(20):
+            xd = xh.to(device, non_blocking=True)
+            gw, uw, dw, rw = layers[i % R]
+            K.matmul_f16(rw, xd, logits, N_EMBD, N_EXPERT, T)
+            K.shared_expert(gw, uw, dw, xd, T, out)
+            oh.copy_(out, non_blocking=True)
+            torch.cuda.synchronize()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / 20
+        results.append(dict(tokens=T, ms=ms, weight_gbs=(sh_bytes + N_EXPERT * N_EMBD * 2) / (ms * 1e-3) / 1e9,
+                            e2e_ms=e2e_ms, steps=reps * R))
+    assert K.device_status() == 0
+    while time.time() - t_load0 < 2.0:
+        g.replay()
+        torch.cuda.synchronize()
+    clocks = sampler.stop(window=(t_load0, time.time()))
+    if rank != 0:
+        return
+    hbm, kind = measured_peaks()
+    head = results[0]
+    line = {
+        "metric": "shared_expert_and_router_logits_tokens_per_s", "value": head["tokens"] * world / (head["ms"] * 1e-3),
+        "unit": UNIT, "n_gpus": world, "steps": head["steps"], "warmup": args.warmup, "ms_per_step": head["ms"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 x int8 (dp4a) with f32 block scales; f16 x f32 for the router", "data": "synthetic",
+        "config": {"workload": "shared_expert", "tokens_per_step_per_gpu": 1, "n_embd": N_EMBD, "n_ff": N_FF,
+                   "n_expert": N_EXPERT, "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
+                   "l2": f"{R} layers' weights rotate ({R} x 28.8 MB > 126 MB L2)"},
+        "roofline": {"bound": "hbm", "kernel": "matmul_q8_0_kernel x3 + matmul_f16_kernel + quantise / SwiGLU (whole step)",
+                     "achieved": head["weight_gbs"], "peak": hbm, "peak_kind": f"of {kind}", "unit": "GB/s",
+                     "frac": head["weight_gbs"] / hbm, "traffic": None,
+                     "algorithmic_bytes_per_step": sh_bytes + N_EXPERT * N_EMBD * 2, "avg_launch_ms": head["ms"]},
+        "batches": results,
+        "e2e": {"value": head["tokens"] * world / (head["e2e_ms"] * 1e-3), "unit": UNIT,
+                "h2d_bytes_per_step": N_EMBD * 4, "d2h_bytes_per_step": N_EMBD * 4},
+        "gpu_launches": head["steps"] * 7, "timed_with": f"CUDA graph of {R} steps (7 kernels each) replayed", "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, T_chunk):
     """Expert-parallel prefill: rank r owns experts [r*256/G, (r+1)*256/G) and routes its own tokens; NCCL all-to-all
     dispatch (Q8_K rows) and combine (f32 rows). Weak scaling (default): every rank brings its own 4096-token chunk.
@@ -627,6 +719,11 @@ def main():
     sampler = ClockSampler(local_rank)
     sampler.start()  # started early (nvidia-smi takes a while to come up); samples are filtered to the load window
     wl = WORKLOADS[args.workload]
+    if args.workload == "shared_expert":
+        run_shared(args, torch, dist, MoeKernels(device=local_rank, max_tokens=64), device, rank, world, sampler)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if args.workload == "fp8_linear":
         run_fp8(args, torch, dist, MoeKernels(device=local_rank, max_tokens=1), device, rank, world, sampler)
         if world > 1:

@@ -41,6 +41,11 @@ SIGNATURES = {
     "dsmoe_down_sum": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _u64, _u64, _u32, _u32, _u32, _u32, _int]),
     "dsmoe_moe_sum": (_int, [_vp, _vp, _vp, _vp, _u32, _u32, _u32]),
     "dsmoe_moe_sum_indexed": (_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32]),
+    "dsmoe_quantize_q8_0": (_int, [_vp, _vp, _vp, _vp, _vp, _u64, _u64]),
+    "dsmoe_matmul_q8_0": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _u64, _u64, _u64]),
+    "dsmoe_swiglu": (_int, [_vp, _vp, _vp, _vp, _vp, _u64, _f32, _f32]),
+    "dsmoe_matmul_f16": (_int, [_vp, _vp, _vp, _vp, _vp, _u64, _u64, _u64]),
+    "dsmoe_shared_expert": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _vp]),
     "dsmoe_dequant_iq2xxs": (_int, [_vp, _vp, _vp, _u64, _vp]),
     "dsmoe_dequant_q2k": (_int, [_vp, _vp, _vp, _u64, _vp]),
     "dsmoe_relayout_iq2xxs": (_int, [_vp, _vp, _vp, _vp, _u64, _u32, _int]),

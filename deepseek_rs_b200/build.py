@@ -11,7 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libdsmoe.so")
-SOURCES = ["api.cu", "quant_router.cu", "experts.cu", "experts_tma.cu", "noalloc.cu", "prefill.cu", "fp8.cu"]
+SOURCES = ["api.cu", "quant_router.cu", "experts.cu", "experts_tma.cu", "noalloc.cu", "prefill.cu", "fp8.cu", "shared.cu"]
 HEADERS = ["common.cuh", "launch.h", "async.cuh", "tc05.cuh", os.path.join("..", "..", "include", "dsmoe.h"),
            os.path.join("..", "..", "include", "dsmoe_iq2_tables.h")]
 

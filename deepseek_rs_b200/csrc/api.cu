@@ -38,6 +38,10 @@ struct dsmoe_handle {
     uint32_t prefill_min_tokens;
     cudaEvent_t phase_events[6];
     bool phase_events_set;
+    // scratch of the shared-expert call, for sh_chunk tokens at a time
+    uint32_t sh_chunk;
+    int8_t *sh_xq;
+    float *sh_xscale, *sh_gate, *sh_up, *sh_mid;
 };
 
 namespace {
@@ -136,6 +140,15 @@ int dsmoe_create(const dsmoe_config *cfg, int device, dsmoe_handle **out)
     ok = ok && dev_alloc(&h->d_x, T * cfg->n_embd) == cudaSuccess;
     ok = ok && dev_alloc(&h->d_logits, T * cfg->n_expert) == cudaSuccess;
     ok = ok && dev_alloc(&h->d_out, T * cfg->n_embd) == cudaSuccess;
+    {
+        h->sh_chunk = cfg->max_tokens < 1024u ? cfg->max_tokens : 1024u;
+        const size_t C = h->sh_chunk, wide = cfg->n_embd > cfg->n_ff ? cfg->n_embd : cfg->n_ff;
+        ok = ok && dev_alloc(&h->sh_xq, C * wide) == cudaSuccess;
+        ok = ok && dev_alloc(&h->sh_xscale, C * ((wide + 31) / 32)) == cudaSuccess;
+        ok = ok && dev_alloc(&h->sh_gate, C * cfg->n_ff) == cudaSuccess;
+        ok = ok && dev_alloc(&h->sh_up, C * cfg->n_ff) == cudaSuccess;
+        ok = ok && dev_alloc(&h->sh_mid, C * cfg->n_ff) == cudaSuccess;
+    }
     ok = ok && cudaStreamCreateWithFlags(&h->hstream, cudaStreamNonBlocking) == cudaSuccess;
     ok = ok && dev_alloc(&h->d_status, 1) == cudaSuccess && cudaMemset(h->d_status, 0, sizeof(int)) == cudaSuccess;
     {
@@ -176,6 +189,11 @@ int dsmoe_destroy(dsmoe_handle *h)
     cudaFree(h->d_out);
     cudaFree(h->d_status);
     cudaFree(h->pf_scratch);
+    cudaFree(h->sh_xq);
+    cudaFree(h->sh_xscale);
+    cudaFree(h->sh_gate);
+    cudaFree(h->sh_up);
+    cudaFree(h->sh_mid);
     delete[] h->layers;
     delete h;
     return DSMOE_OK;
@@ -319,6 +337,72 @@ int dsmoe_moe_sum_indexed(dsmoe_handle *h, dsmoe_stream stream, const float *row
     DSMOE_REQUIRE(h, rows && pos && out, "moe_sum_indexed: null pointer");
     launch_moe_sum((cudaStream_t)stream, rows, pos, out, out_dim, n_expert_used, n_tokens);
     return check_launch(h, "moe_sum_indexed", 1);
+}
+
+int dsmoe_quantize_q8_0(dsmoe_handle *h, dsmoe_stream stream, const float *x, int8_t *xq, float *xscale, uint64_t in_dim,
+                        uint64_t n_tokens)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    if (n_tokens == 0 || in_dim == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, x && xq && xscale, "quantize_q8_0: null pointer");
+    launch_quantize_q8_0((cudaStream_t)stream, x, xq, xscale, in_dim, n_tokens);
+    return check_launch(h, "quantize_q8_0", 1);
+}
+
+int dsmoe_matmul_q8_0(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *w, const int8_t *xq, const float *xscale,
+                      float *out, uint64_t in_dim, uint64_t out_dim, uint64_t n_tokens)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    if (n_tokens == 0 || out_dim == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, w && xq && xscale && out, "matmul_q8_0: null pointer");
+    DSMOE_REQUIRE(h, ((uintptr_t)w & 3) == 0 && ((uintptr_t)xq & 15) == 0, "matmul_q8_0: w needs 4-byte, xq 16-byte alignment");
+    launch_matmul_q8_0((cudaStream_t)stream, w, xq, xscale, out, in_dim, out_dim, n_tokens);
+    return check_launch(h, "matmul_q8_0", 1);
+}
+
+int dsmoe_swiglu(dsmoe_handle *h, dsmoe_stream stream, const float *gate, const float *up, float *out, uint64_t n,
+                 float clamp, float weight)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    if (n == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, gate && up && out, "swiglu: null pointer");
+    launch_swiglu((cudaStream_t)stream, gate, up, out, n, clamp, weight);
+    return check_launch(h, "swiglu", 1);
+}
+
+int dsmoe_matmul_f16(dsmoe_handle *h, dsmoe_stream stream, const uint16_t *w, const float *x, float *out, uint64_t in_dim,
+                     uint64_t out_dim, uint64_t n_tokens)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    if (n_tokens == 0 || out_dim == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, w && x && out, "matmul_f16: null pointer");
+    DSMOE_REQUIRE(h, n_tokens <= 65535, "matmul_f16: at most 65535 tokens per call");
+    launch_matmul_f16((cudaStream_t)stream, w, x, out, in_dim, out_dim, n_tokens);
+    return check_launch(h, "matmul_f16", 1);
+}
+
+int dsmoe_shared_expert(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *gate_w, const uint8_t *up_w,
+                        const uint8_t *down_w, const float *x, uint32_t n_tokens, float *out)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    if (n_tokens == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, gate_w && up_w && down_w && x && out, "shared_expert: null pointer");
+    DSMOE_REQUIRE(h, (((uintptr_t)gate_w | (uintptr_t)up_w | (uintptr_t)down_w) & 3) == 0, "shared_expert: weights need 4-byte alignment");
+    const dsmoe_config &c = h->cfg;
+    cudaStream_t st = (cudaStream_t)stream;
+    int n = 0;
+    for (uint32_t t0 = 0; t0 < n_tokens; t0 += h->sh_chunk) {
+        const uint32_t T = n_tokens - t0 < h->sh_chunk ? n_tokens - t0 : h->sh_chunk;
+        const float *xc = x + (size_t)t0 * c.n_embd;
+        launch_quantize_q8_0(st, xc, h->sh_xq, h->sh_xscale, c.n_embd, T);
+        launch_matmul_q8_0(st, gate_w, h->sh_xq, h->sh_xscale, h->sh_gate, c.n_embd, c.n_ff, T);
+        launch_matmul_q8_0(st, up_w, h->sh_xq, h->sh_xscale, h->sh_up, c.n_embd, c.n_ff, T);
+        launch_swiglu(st, h->sh_gate, h->sh_up, h->sh_mid, (uint64_t)T * c.n_ff, c.swiglu_clamp, 1.0f);
+        launch_quantize_q8_0(st, h->sh_mid, h->sh_xq, h->sh_xscale, c.n_ff, T);
+        launch_matmul_q8_0(st, down_w, h->sh_xq, h->sh_xscale, out + (size_t)t0 * c.n_embd, c.n_ff, c.n_embd, T);
+        n += 6;
+    }
+    return check_launch(h, "shared_expert", n);
 }
 
 int dsmoe_dequant_iq2xxs(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *blocks, uint64_t n_blocks, float *out)

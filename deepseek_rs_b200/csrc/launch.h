@@ -26,6 +26,14 @@ void launch_relayout_q2k(cudaStream_t st, const uint8_t *src, uint8_t *dst, uint
 void launch_moe_sum(cudaStream_t st, const float *down, const int32_t *pos, float *out, uint32_t out_dim, uint32_t k,
                     uint32_t n_tokens);
 
+// Router logits and shared expert (shared.cu)
+void launch_quantize_q8_0(cudaStream_t st, const float *x, int8_t *xq, float *xscale, uint64_t in_dim, uint64_t n_tok);
+void launch_matmul_q8_0(cudaStream_t st, const uint8_t *w, const int8_t *xq, const float *xscale, float *out,
+                        uint64_t in_dim, uint64_t out_dim, uint64_t n_tok);
+void launch_swiglu(cudaStream_t st, const float *gate, const float *up, float *out, uint64_t n, float clamp, float weight);
+void launch_matmul_f16(cudaStream_t st, const uint16_t *w, const float *x, float *out, uint64_t in_dim, uint64_t out_dim,
+                       uint64_t n_tok);
+
 struct GateUpArgs {
     const uint8_t *gate_base, *up_base, *xq;
     const int32_t *selected;

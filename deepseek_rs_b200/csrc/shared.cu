@@ -1,0 +1,191 @@
+// The steps that run on the same normalised activations right beside the routed experts: router logits (f16 weights),
+// and the shared expert (Q8_0 weights x Q8_0 activations, SwiGLU between). Kernel for kernel these stand where
+//   quantize_q8_0            engine/src/kernels/quantize.rs:147-225
+//   matmul_q8_0_preq_warp8   engine/src/kernels/matmul.rs:357-405 (and its batched twin)
+//   swiglu                   engine/src/kernels/utils.rs:141-163
+//   matmul_f16               engine/src/kernels/matmul.rs:57-105
+// stand in engine/src/session.rs:1894-2008. The arithmetic order of each (which partial sums exist and in which order
+// they are added) is kept, so the results equal the CPU oracle bit for bit; the thread mapping is new.
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "launch.h"
+
+namespace dsmoe {
+
+constexpr int Q8_0_BYTES = 34;  // f16 scale + 32 int8
+
+// ---------------------------------------------------------------------------------------------------------------
+// quantize_q8_0: one warp per 32-element block, one element per lane. d = amax / 127, id = 1 / d (0 when d is 0),
+// q = trunc(x * id +/- 0.5) clamped to int8; lanes past the end of the row write 0.
+// ---------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float *__restrict__ x, int8_t *__restrict__ xq,
+                                                             float *__restrict__ xscale, uint64_t in_dim, uint64_t blocks,
+                                                             uint64_t n_units)
+{
+    const uint64_t unit = (uint64_t)blockIdx.x * 8 + (threadIdx.x >> 5);  // (token, block)
+    if (unit >= n_units) return;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint64_t tok = unit / blocks, b = unit - tok * blocks, i = b * 32 + lane;
+    const float v = i < in_dim ? x[tok * in_dim + i] : 0.0f;
+    float amax = v < 0.0f ? -v : v;
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+        const float o = __shfl_xor_sync(FULL, amax, m);
+        amax = o > amax ? o : amax;
+    }
+    const float d = __fdiv_rn(amax, 127.0f), id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    if (lane == 0) xscale[unit] = d;
+    int q = 0;
+    if (i < in_dim) {
+        const float raw = __fmul_rn(v, id);
+        q = raw >= 0.0f ? (int)__fadd_rn(raw, 0.5f) : (int)__fsub_rn(raw, 0.5f);
+        q = q > 127 ? 127 : (q < -128 ? -128 : q);
+    }
+    xq[unit * 32 + lane] = (int8_t)q;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// matmul_q8_0: out[tok][row] = sum over blocks of (scale_w * xscale[b]) * dot_int8. One warp per (row, tile of TOK
+// tokens); lane l takes blocks l, l+32, ... in ascending order (the reference's lane partials), then the xor
+// butterfly 16, 8, 4, 2, 1. A 34-byte block starts on a 2-byte boundary: it is fetched as nine aligned words and, for
+// odd blocks, realigned with funnel shifts. The weight words of a block are reused for all TOK tokens of the tile.
+// ---------------------------------------------------------------------------------------------------------------
+template <int TOK>
+__global__ void __launch_bounds__(256) matmul_q8_0_kernel(const uint8_t *__restrict__ w, const int8_t *__restrict__ xq,
+                                                           const float *__restrict__ xscale, float *__restrict__ out,
+                                                           uint64_t out_dim, uint64_t blocks, uint64_t n_tok)
+{
+    const uint64_t row = (uint64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= out_dim) return;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint64_t tok0 = (uint64_t)blockIdx.y * TOK;
+    const uint8_t *wrow = w + row * blocks * Q8_0_BYTES;  // rows are 2-byte aligned at least
+    float acc[TOK];
+#pragma unroll
+    for (int t = 0; t < TOK; ++t) acc[t] = 0.0f;
+    for (uint64_t b = lane; b < blocks; b += 32) {
+        const uint8_t *blk = wrow + b * Q8_0_BYTES;
+        // aligned words covering the block
+        const uintptr_t addr = reinterpret_cast<uintptr_t>(blk);
+        const uint32_t *aw = reinterpret_cast<const uint32_t *>(addr & ~(uintptr_t)3);
+        uint32_t raw[9];
+        const bool odd = (addr & 2) != 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) raw[i] = aw[i];
+        // the ninth word: an even block only owns its low half (never read past the tensor)
+        raw[8] = odd ? aw[8] : (uint32_t)*reinterpret_cast<const uint16_t *>(blk + 32);
+        uint32_t wq[8], scale_bits;
+        if (!odd) {  // [scale | q0 q1] [q2..q5] ... : the int8 data starts in the upper half of word 0
+            scale_bits = raw[0] & 0xFFFFu;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) wq[i] = __funnelshift_r(raw[i], raw[i + 1], 16);
+        } else {     // [.. | scale] [q0..q3] ...
+            scale_bits = raw[0] >> 16;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) wq[i] = raw[i + 1];
+        }
+        const float sw = f16_bits_to_f32(scale_bits, false);
+#pragma unroll
+        for (int t = 0; t < TOK; ++t) {
+            if (tok0 + t >= n_tok) break;
+            const uint4 *xv = reinterpret_cast<const uint4 *>(xq + ((tok0 + t) * blocks + b) * 32);
+            const uint4 x0 = xv[0], x1 = xv[1];
+            int dot = 0;
+            dot = __dp4a((int)wq[0], (int)x0.x, dot), dot = __dp4a((int)wq[1], (int)x0.y, dot);
+            dot = __dp4a((int)wq[2], (int)x0.z, dot), dot = __dp4a((int)wq[3], (int)x0.w, dot);
+            dot = __dp4a((int)wq[4], (int)x1.x, dot), dot = __dp4a((int)wq[5], (int)x1.y, dot);
+            dot = __dp4a((int)wq[6], (int)x1.z, dot), dot = __dp4a((int)wq[7], (int)x1.w, dot);
+            const float s = __fmul_rn(sw, xscale[(tok0 + t) * blocks + b]);
+            acc[t] = __fadd_rn(acc[t], __fmul_rn(s, (float)dot));
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < TOK; ++t) {
+        float v = acc[t];
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) v = __fadd_rn(v, __shfl_xor_sync(FULL, v, m));
+        if (lane == 0 && tok0 + t < n_tok) out[(tok0 + t) * out_dim + row] = v;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// swiglu: out = ((g / (1 + exp(-g))) * u) * weight with g clamped from above and u to [-clamp, clamp]
+// ---------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) swiglu_kernel(const float *__restrict__ gate, const float *__restrict__ up,
+                                                      float *__restrict__ out, uint64_t n, float clamp, float weight)
+{
+    const uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= n) return;
+    float g = gate[i], u = up[i];
+    if (clamp > 1.0e-6f) {
+        if (g > clamp) g = clamp;
+        if (u > clamp) u = clamp;
+        if (u < -clamp) u = -clamp;
+    }
+    out[i] = swiglu_weighted(g, u, weight);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// matmul_f16: out[tok][row] = dot(w[row], x[tok]). The reference sums with 256 threads striding the row and a
+// shared-memory halving tree. Here one warp does a (row, token): lane l owns the eight partial sums of threads
+// l, l+32, ..., l+224 (each over elements tx, tx+256, ... in order), folds them as the tree's strides 128, 64, 32 do
+// (partials tx and tx+stride sit in the same lane), and finishes strides 16..1 with shuffles.
+// ---------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) matmul_f16_kernel(const uint16_t *__restrict__ w, const float *__restrict__ x,
+                                                          float *__restrict__ out, uint64_t in_dim, uint64_t out_dim,
+                                                          uint64_t n_tok)
+{
+    const uint64_t row = (uint64_t)blockIdx.x * 8 + (threadIdx.x >> 5), tok = blockIdx.y;
+    if (row >= out_dim || tok >= n_tok) return;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint16_t *wr = w + row * in_dim;
+    const float *xr = x + tok * in_dim;
+    float p[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        float s = 0.0f;
+        for (uint64_t i = lane + 32 * k; i < in_dim; i += 256) s = __fadd_rn(s, __fmul_rn(f16_bits_to_f32(wr[i], false), xr[i]));
+        p[k] = s;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) p[k] = __fadd_rn(p[k], p[k + 4]);  // stride 128
+    p[0] = __fadd_rn(p[0], p[2]), p[1] = __fadd_rn(p[1], p[3]);    // stride 64
+    float v = __fadd_rn(p[0], p[1]);                               // stride 32
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) v = __fadd_rn(v, __shfl_down_sync(FULL, v, m));  // lanes below m hold the tree's values
+    if (lane == 0) out[tok * out_dim + row] = v;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+void launch_quantize_q8_0(cudaStream_t st, const float *x, int8_t *xq, float *xscale, uint64_t in_dim, uint64_t n_tok)
+{
+    const uint64_t blocks = (in_dim + 31) / 32, units = blocks * n_tok;
+    if (units == 0) return;
+    quantize_q8_0_kernel<<<(unsigned)((units + 7) / 8), 256, 0, st>>>(x, xq, xscale, in_dim, blocks, units);
+}
+
+void launch_matmul_q8_0(cudaStream_t st, const uint8_t *w, const int8_t *xq, const float *xscale, float *out,
+                        uint64_t in_dim, uint64_t out_dim, uint64_t n_tok)
+{
+    const uint64_t blocks = (in_dim + 31) / 32;
+    if (out_dim == 0 || n_tok == 0) return;
+    const unsigned gx = (unsigned)((out_dim + 7) / 8);
+    if (n_tok == 1) matmul_q8_0_kernel<1><<<dim3(gx, 1), 256, 0, st>>>(w, xq, xscale, out, out_dim, blocks, n_tok);
+    else matmul_q8_0_kernel<4><<<dim3(gx, (unsigned)((n_tok + 3) / 4)), 256, 0, st>>>(w, xq, xscale, out, out_dim, blocks, n_tok);
+}
+
+void launch_swiglu(cudaStream_t st, const float *gate, const float *up, float *out, uint64_t n, float clamp, float weight)
+{
+    if (n == 0) return;
+    swiglu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(gate, up, out, n, clamp, weight);
+}
+
+void launch_matmul_f16(cudaStream_t st, const uint16_t *w, const float *x, float *out, uint64_t in_dim, uint64_t out_dim,
+                       uint64_t n_tok)
+{
+    if (out_dim == 0 || n_tok == 0) return;
+    matmul_f16_kernel<<<dim3((unsigned)((out_dim + 7) / 8), (unsigned)n_tok), 256, 0, st>>>(w, x, out, in_dim, out_dim, n_tok);
+}
+
+}  // namespace dsmoe

@@ -138,6 +138,30 @@ class MoeKernels:
         """engine/src/kernels/moe.rs:983"""
         self._check(self.lib.dsmoe_moe_sum(self.h, _stream(), _ptr(down), _ptr(out), out_dim, n_expert, n_tokens))
 
+    # ---- router logits and shared expert (engine/src/session.rs:1894-2008) --------------------------------------
+
+    def quantize_q8_0(self, x, xq, xscale, in_dim: int, n_tokens: int):
+        """engine/src/kernels/quantize.rs:147 — x f32 [n_tokens, in_dim] -> int8 codes and f32 scales per 32."""
+        self._check(self.lib.dsmoe_quantize_q8_0(self.h, _stream(), _ptr(x), _ptr(xq), _ptr(xscale), in_dim, n_tokens))
+
+    def matmul_q8_0_preq_warp8(self, w, xq, xscale, out, in_dim: int, out_dim: int, n_tokens: int = 1):
+        """engine/src/kernels/matmul.rs:357 (n_tokens > 1: its batched twin)."""
+        self._check(self.lib.dsmoe_matmul_q8_0(self.h, _stream(), _ptr(w), _ptr(xq), _ptr(xscale), _ptr(out), in_dim,
+                                               out_dim, n_tokens))
+
+    def swiglu(self, gate, up, out, n: int, clamp: float, weight: float):
+        """engine/src/kernels/utils.rs:141"""
+        self._check(self.lib.dsmoe_swiglu(self.h, _stream(), _ptr(gate), _ptr(up), _ptr(out), n, clamp, weight))
+
+    def matmul_f16(self, w, x, out, in_dim: int, out_dim: int, n_tokens: int):
+        """engine/src/kernels/matmul.rs:57 — w: f16 bit patterns (uint16 / float16 tensor)."""
+        self._check(self.lib.dsmoe_matmul_f16(self.h, _stream(), _ptr(w), _ptr(x), _ptr(out), in_dim, out_dim, n_tokens))
+
+    def shared_expert(self, gate_w, up_w, down_w, x, n_tokens: int, out):
+        """The shared expert of engine/src/session.rs:1894-1986 in one call."""
+        self._check(self.lib.dsmoe_shared_expert(self.h, _stream(), _ptr(gate_w), _ptr(up_w), _ptr(down_w), _ptr(x),
+                                                 n_tokens, _ptr(out)))
+
     # ---- helpers with no reference kernel ------------------------------------------------------------------------
 
     def moe_sum_indexed(self, rows, pos, out, out_dim: int, n_expert: int, n_tokens: int):

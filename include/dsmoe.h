@@ -145,6 +145,33 @@ DSMOE_API int dsmoe_moe_sum(dsmoe_handle *h, dsmoe_stream stream, const float *d
 DSMOE_API int dsmoe_moe_sum_indexed(dsmoe_handle *h, dsmoe_stream stream, const float *rows, const int32_t *pos,
                                     float *out, uint32_t out_dim, uint32_t n_expert_used, uint32_t n_tokens);
 
+/* ---- the steps beside the routed experts: router logits and the shared expert (engine/src/session.rs:1894-2008) ---- */
+
+/* quantize_q8_0 (engine/src/kernels/quantize.rs:147-225; calls engine/src/session.rs:1896-1908, 1960-1972).
+ * x: f32 [n_tokens][in_dim] -> xq: int8 [n_tokens][ceil(in_dim/32)*32], xscale: f32 [n_tokens][ceil(in_dim/32)]. */
+DSMOE_API int dsmoe_quantize_q8_0(dsmoe_handle *h, dsmoe_stream stream, const float *x, int8_t *xq, float *xscale,
+                                  uint64_t in_dim, uint64_t n_tokens);
+
+/* matmul_q8_0_preq_warp8 / matmul_q8_0_preq_batch_warp8 (engine/src/kernels/matmul.rs:357-405 and the batched twin
+ * after it; calls engine/src/session.rs:1915-1944, 1973-1984). w: Q8_0 blocks [out_dim][ceil(in_dim/32)][34 bytes],
+ * 4-byte aligned; xq 16-byte aligned. out: f32 [n_tokens][out_dim]. */
+DSMOE_API int dsmoe_matmul_q8_0(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *w, const int8_t *xq,
+                                const float *xscale, float *out, uint64_t in_dim, uint64_t out_dim, uint64_t n_tokens);
+
+/* swiglu (engine/src/kernels/utils.rs:141-163; call engine/src/session.rs:1945-1953). */
+DSMOE_API int dsmoe_swiglu(dsmoe_handle *h, dsmoe_stream stream, const float *gate, const float *up, float *out,
+                           uint64_t n, float clamp, float weight);
+
+/* matmul_f16 (engine/src/kernels/matmul.rs:57-105; the router-logits call engine/src/session.rs:1995-2008).
+ * w: f16 bit patterns [out_dim][in_dim]; x: f32 [n_tokens][in_dim]; out: f32 [n_tokens][out_dim]. */
+DSMOE_API int dsmoe_matmul_f16(dsmoe_handle *h, dsmoe_stream stream, const uint16_t *w, const float *x, float *out,
+                               uint64_t in_dim, uint64_t out_dim, uint64_t n_tokens);
+
+/* The whole shared expert of engine/src/session.rs:1894-1986 for n_tokens rows (any count; scratch is library-owned):
+ * Q8_0 of x -> gate, up -> swiglu(clamp from the config, weight 1) -> Q8_0 -> down. out: f32 [n_tokens][n_embd]. */
+DSMOE_API int dsmoe_shared_expert(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *gate_w, const uint8_t *up_w,
+                                  const uint8_t *down_w, const float *x, uint32_t n_tokens, float *out);
+
 /* Dequantised weights. The reference has no such kernel; the values are defined by its block dots
  * (engine/src/kernels/quantize.rs:811, :900): IQ2_XXS w = (0.125*d) * (ls * +/-g); Q2_K w = d*(sc*q) - dmin*m.
  * blocks are in NATIVE order; out: f32 [n_blocks][256]. Bit-exact against the CPU oracle. */
