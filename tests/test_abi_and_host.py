@@ -81,3 +81,5 @@ def test_product_does_not_import_the_oracle():
             if fn.endswith((".py", ".cu", ".cuh", ".h", ".cpp")):
                 text = open(os.path.join(dirpath, fn)).read()
                 assert "import oracle" not in text and "from oracle" not in text and "dsmoe_oracle" not in text, fn
+                # nor the GPU baseline (the restated reference mapping), which is bench and test infrastructure too
+                assert "import baseline" not in text and "from baseline" not in text and "ref_mapping" not in text, fn
