@@ -63,6 +63,14 @@ __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t nthread
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// Programmatic dependent launch. A kernel launched with the programmatic-serialisation attribute may start while the
+// kernel before it in the stream is still running; pdl_wait() blocks until that kernel (and, transitively, everything
+// before it, as every kernel of a chain waits) has completed and its writes are visible. Before the wait a kernel may
+// only do work that touches no global data of its predecessors (shared-memory tables, barrier set-up).
+// pdl_launch_dependents() lets the next kernel's CTAs be scheduled early. Both do nothing in a plain launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 {
     uint32_t ok;

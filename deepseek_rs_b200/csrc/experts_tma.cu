@@ -126,6 +126,9 @@ __global__ void __launch_bounds__(32 * GU_MAX_WARPS, 1)
         for (int s = 0; s < GU_STAGES; ++s) mbar_init(&bars[s], 1);
         fence_async_smem();
     }
+    // the tables above depend on nothing; activations, routing and the output buffers do
+    pdl_launch_dependents();
+    pdl_wait();
     __syncthreads();
 
     // this warp's run of items; item i covers rows 2i, 2i+1 of the flattened [pair][row] space (mid_dim is even)
@@ -265,6 +268,8 @@ __global__ void __launch_bounds__(256, 2) down_m8_tma_kernel(const uint8_t *__re
     const uint32_t tok = blockIdx.y, pair = tok * k + slot;
     const uint32_t row_begin = blockIdx.x * rows_per_cta;
     const uint32_t n_rows = min((uint32_t)rows_per_cta, out_dim - row_begin);
+    pdl_launch_dependents();
+    pdl_wait();
     if (lane == 0) {
         const int32_t e = selected[pair];
         const uint64_t ex = e < 0 ? 0u : (uint64_t)e;
@@ -401,9 +406,9 @@ static void launch_gu_tma(cudaStream_t st, const GateUpArgs &a, int *status)
     }
     const uint32_t want = (n_items + best_w - 1) / best_w;
     const uint32_t grid = want < (uint32_t)sms ? want : (uint32_t)sms;
-    gate_up_x16_tma_kernel<LAYOUT><<<grid, 32 * best_w, smem, st>>>(a.gate_base, a.up_base, a.xq, a.selected, a.weights,
-                                                                    a.gate_out, a.up_out, a.mid_out, a.expert_bytes,
-                                                                    a.mid_dim, a.k, n_items, a.clamp, a.ieee, status);
+    launch_pdl(gate_up_x16_tma_kernel<LAYOUT>, dim3(grid), dim3(32 * best_w), smem, st, a.gate_base, a.up_base, a.xq,
+               a.selected, a.weights, a.gate_out, a.up_out, a.mid_out, a.expert_bytes, a.mid_dim, a.k, n_items, a.clamp,
+               a.ieee, status);
 }
 
 int launch_gate_up_mid_tma(cudaStream_t st, const GateUpArgs &a, int *status)
@@ -433,8 +438,8 @@ static void launch_dn_tma(cudaStream_t st, const DownArgs &a, int *status)
         attr_set = true;
     }
     dim3 grid((a.out_dim + rows_per_cta - 1) / rows_per_cta, a.n_tokens);
-    down_m8_tma_kernel<LAYOUT, SUM><<<grid, 32 * a.k, smem, st>>>(a.down_base, a.midq, a.selected, a.out, a.expert_bytes,
-                                                                  a.out_dim, a.k, a.ieee, rows_per_cta, status);
+    launch_pdl(down_m8_tma_kernel<LAYOUT, SUM>, grid, dim3(32 * a.k), smem, st, a.down_base, a.midq, a.selected, a.out,
+               a.expert_bytes, a.out_dim, a.k, a.ieee, rows_per_cta, status);
 }
 
 int launch_down_tma(cudaStream_t st, const DownArgs &a, int *status)

@@ -12,6 +12,8 @@
 //                         element: s_w is one scalar per tile and K block, s_a one per row) while the next block's
 //                         MMAs run. Operands reach shared memory by 16-byte cp.async in core-matrix order.
 //   fp8_matvec_kernel     M <= 8: bandwidth-bound, one warp per output feature, f32 accumulate.
+#include <stdlib.h>
+
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
@@ -136,7 +138,11 @@ __global__ void __launch_bounds__(256) fp8_matvec_kernel(const uint8_t *__restri
 // ---------------------------------------------------------------------------------------------------------------
 // GEMM: 128 (rows of A) x 128 (rows of W) output tile per CTA, 256 threads.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int F8_STAGES = 4;
+#ifndef F8_STAGES_N
+#define F8_STAGES_N 3
+#define F8_CTAS_PER_SM 2
+#endif
+constexpr int F8_STAGES = F8_STAGES_N;  // 3 stages x 32 KB: two CTAs share an SM and fill each other's waits
 constexpr int F8_TILE = 128 * 128;            // bytes of one operand stage (128 rows x 128 K, one byte each)
 constexpr int F8_SBO = (128 / 16) * 128;      // 1024: byte distance between 8-row groups
 constexpr int F8_SMEM = 2 * F8_STAGES * F8_TILE + 64;
@@ -146,7 +152,7 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void *src, 
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes) : "memory");
 }
 
-__global__ void __launch_bounds__(256, 1) fp8_gemm_kernel(const uint8_t *__restrict__ a, const float *__restrict__ a_scale,
+__global__ void __launch_bounds__(256, F8_CTAS_PER_SM) fp8_gemm_kernel(const uint8_t *__restrict__ a, const float *__restrict__ a_scale,
                                                            const uint8_t *__restrict__ w, const float *__restrict__ w_scale,
                                                            __nv_bfloat16 *__restrict__ out, uint32_t M, uint32_t N, uint32_t K,
                                                            int *status)
@@ -248,6 +254,195 @@ __global__ void __launch_bounds__(256, 1) fp8_gemm_kernel(const uint8_t *__restr
     if (warp == 0) tc05_dealloc(tmem, 256);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Large M: persistent, warp-specialised. One CTA per SM walks 128 x 256 output tiles; per 128-wide K block
+//   warps 8-11  producers  16-byte cp.async of the A (128 rows) and W (256 rows) blocks into a 4-stage ring in
+//                          core-matrix order, completion counted on the stage's "full" mbarrier;
+//   warp 12     issuer     four K=32 MMAs (M 128, N 256) into one of two TMEM accumulators, committed to the stage's
+//                          "free" and the accumulator's "full" mbarriers;
+//   warps 0-7   consumers  drain the accumulator (tcgen05.ld), hand it back, apply s_a[row][kb] * s_w[n/128][kb] with
+//                          one FMA per element into 128 registers; after the last K block write the bf16 row segment.
+// Registers move to the consumers with setmaxnreg. Every wait is bounded; the common exit frees TMEM.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int F8W_STAGES = 4, F8W_TN = 256, F8W_THREADS = 512, F8W_MAX_KB = 32;
+constexpr int F8W_STAGE_A = 128 * 128, F8W_STAGE_B = F8W_TN * 128;
+constexpr int F8W_SMEM_B = F8W_STAGES * F8W_STAGE_A;
+constexpr int F8W_SMEM_SA = F8W_SMEM_B + F8W_STAGES * F8W_STAGE_B;   // [kb][128 rows] activation scales of the tile
+constexpr int F8W_SMEM_SW = F8W_SMEM_SA + F8W_MAX_KB * 128 * 4;      // [2][kb] weight scales of the tile's two blocks
+constexpr int F8W_SMEM_BAR = F8W_SMEM_SW + 2 * F8W_MAX_KB * 4;
+constexpr int F8W_SMEM = F8W_SMEM_BAR + 128;
+static_assert(F8W_SMEM <= 232448, "shared memory per CTA");
+// compiled for 128 registers (512 threads); 8 warps release 56 each, the 8 consumer warps take them
+constexpr int F8W_REG_LAUNCH = 128, F8W_REG_CONSUMER = 184, F8W_REG_OTHER = 72;
+static_assert(256 * (F8W_REG_CONSUMER - F8W_REG_LAUNCH) <= 256 * (F8W_REG_LAUNCH - F8W_REG_OTHER), "setmaxnreg budget");
+
+__global__ void __launch_bounds__(F8W_THREADS, 1) fp8_gemm_ws_kernel(const uint8_t *__restrict__ a,
+                                                                     const float *__restrict__ a_scale,
+                                                                     const uint8_t *__restrict__ w,
+                                                                     const float *__restrict__ w_scale,
+                                                                     __nv_bfloat16 *__restrict__ out, uint32_t M, uint32_t N,
+                                                                     uint32_t K, int *status)
+{
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint64_t *bar_full = reinterpret_cast<uint64_t *>(smem + F8W_SMEM_BAR);  // [4] stage landed (128 producer threads)
+    uint64_t *bar_free = bar_full + F8W_STAGES;                               // [4] stage's MMAs retired
+    uint64_t *bar_acc_full = bar_free + F8W_STAGES;                           // [2]
+    uint64_t *bar_acc_free = bar_acc_full + 2;                                // [2] drained (8 warps)
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_acc_free + 2);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t nkb = K / 128, n_nt = N / F8W_TN, n_tiles = ((M + 127) / 128) * n_nt;
+
+    if (warp == 0) tc05_alloc(tmem_slot, 512);
+    if (tid == 0) {
+        for (int i = 0; i < F8W_STAGES; ++i) {
+            mbar_init(&bar_full[i], 128);
+            mbar_init(&bar_free[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bar_acc_full[i], 1);
+            mbar_init(&bar_acc_free[i], 8);
+        }
+        fence_async_smem();
+    }
+    tc05_fence_before_sync();
+    __syncthreads();
+    tc05_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp < 8) {
+        // ------------------------------------------------------------------------------------------- consumers
+        reg_alloc<F8W_REG_CONSUMER>();
+        const uint32_t arow = 32 * (warp & 3) + lane, half = warp >> 2, acol0 = 128 * half, tlane = (32u * (warp & 3)) << 16;
+        float *sA = reinterpret_cast<float *>(smem + F8W_SMEM_SA), *sW = reinterpret_cast<float *>(smem + F8W_SMEM_SW);
+        uint32_t g = 0;  // K blocks drained so far (accumulator buffer and mbarrier phase)
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+            const uint32_t mt = tile / n_nt, nt = tile - mt * n_nt, m0 = mt * 128, n0 = nt * F8W_TN, mrow = m0 + arow;
+            // the tile's scale tables, rewritten once every consumer warp is done with the previous tile's
+            ok = named_barrier_and(1, 256, ok);
+            if (!ok) break;
+            for (uint32_t i = tid; i < nkb * 128; i += 256) {
+                const uint32_t kb = i >> 7, r = i & 127;
+                sA[i] = m0 + r < M ? a_scale[(size_t)(m0 + r) * nkb + kb] : 0.0f;
+            }
+            for (uint32_t i = tid; i < 2 * nkb; i += 256) sW[i] = w_scale[(size_t)(2 * nt + i / nkb) * nkb + i % nkb];
+            named_barrier_sync(1, 256);
+            float acc[128];
+#pragma unroll
+            for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+            for (uint32_t kb = 0; kb < nkb; ++kb, ++g) {
+                if (!ok) break;
+                const uint32_t buf = g & 1u;
+                const float scale = sA[kb * 128 + arow] * sW[half * nkb + kb];
+                ok = mbar_wait_bounded(&bar_acc_full[buf], (g >> 1) & 1u, status);
+                ok = __all_sync(FULL, ok);
+                if (!ok) break;
+                tc05_fence_after_sync();
+#pragma unroll
+                for (int c0 = 0; c0 < 128; c0 += 16) {
+                    float v[16];
+                    tc05_ld16(tmem + tlane + buf * F8W_TN + acol0 + c0, v);
+                    tc05_wait_ld16(v);
+                    if (c0 == 112) {  // everything of this accumulator is in registers: hand it back
+                        tc05_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&bar_acc_free[buf]);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) acc[c0 + i] = fmaf(scale, v[i], acc[c0 + i]);
+                }
+            }
+            if (!ok) continue;
+            if (mrow < M) {
+                uint4 *o = reinterpret_cast<uint4 *>(out + (size_t)mrow * N + n0 + acol0);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    __nv_bfloat162 p[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) p[j] = __floats2bfloat162_rn(acc[8 * i + 2 * j], acc[8 * i + 2 * j + 1]);
+                    o[i] = *reinterpret_cast<uint4 *>(p);
+                }
+            }
+        }
+    } else {
+        reg_dealloc<F8W_REG_OTHER>();
+        if (warp < 12) {
+            // ------------------------------------------------------------------------------------------- producers
+            const uint32_t ptid = tid - 256;
+            uint32_t g = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+                const uint32_t mt = tile / n_nt, nt = tile - mt * n_nt, m0 = mt * 128, n0 = nt * F8W_TN;
+                for (uint32_t kb = 0; kb < nkb; ++kb, ++g) {
+                    const uint32_t s = g % F8W_STAGES, use = g / F8W_STAGES;
+                    if (use >= 1) ok = mbar_wait_bounded(&bar_free[s], (use - 1) & 1u, status);
+                    ok = __all_sync(FULL, ok);
+                    if (!ok) break;
+                    const uint32_t sa = smem_u32(smem + s * F8W_STAGE_A), sb = smem_u32(smem + F8W_SMEM_B + s * F8W_STAGE_B);
+                    // chunk q of an operand block: row r = q / 8, 16-byte column c = q % 8; a warp instruction
+                    // covers 4 rows x 128 contiguous bytes
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const uint32_t q = i * 128 + ptid, r = q >> 3, c = q & 7, m = m0 + r;
+                        cp_async_16(sa + (r >> 3) * F8_SBO + c * 128 + (r & 7) * 16,
+                                    a + (size_t)(m < M ? m : 0) * K + kb * 128 + 16 * c, m < M ? 16u : 0u);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const uint32_t q = i * 128 + ptid, r = q >> 3, c = q & 7;
+                        cp_async_16(sb + (r >> 3) * F8_SBO + c * 128 + (r & 7) * 16, w + (size_t)(n0 + r) * K + kb * 128 + 16 * c,
+                                    16u);
+                    }
+                    // arrives on the barrier when this thread's copies above have landed
+                    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&bar_full[s])) : "memory");
+                }
+            }
+            asm volatile("cp.async.wait_all;" ::: "memory");
+        } else if (warp == 12) {
+            // ------------------------------------------------------------------------------------------- issuer
+            const uint32_t idesc = tc05_idesc_e4m3(128, F8W_TN);
+            uint32_t g = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+                for (uint32_t kb = 0; kb < nkb; ++kb, ++g) {
+                    const uint32_t s = g % F8W_STAGES, buf = g & 1u;
+                    ok = mbar_wait_bounded(&bar_full[s], (g / F8W_STAGES) & 1u, status);
+                    if (g >= 2) ok = ok && mbar_wait_bounded(&bar_acc_free[buf], ((g >> 1) - 1) & 1u, status);
+                    ok = __all_sync(FULL, ok);
+                    fence_async_smem();  // the copies were written through the generic proxy
+                    tc05_fence_after_sync();
+                    if (elect_one()) {
+                        if (ok) {
+                            const uint64_t da = tc05_smem_desc(smem_u32(smem + s * F8W_STAGE_A), 128, F8_SBO);
+                            const uint64_t db = tc05_smem_desc(smem_u32(smem + F8W_SMEM_B + s * F8W_STAGE_B), 128, F8_SBO);
+#pragma unroll
+                            for (int ks = 0; ks < 4; ++ks)
+                                tc05_mma_f8(tmem + buf * F8W_TN, da + 16u * ks, db + 16u * ks, idesc, ks != 0);
+                        }
+                        tc05_commit(&bar_free[s]);
+                        tc05_commit(&bar_acc_full[buf]);
+                    }
+                    __syncwarp();
+                    if (!ok) break;
+                }
+            }
+        }
+    }
+    tc05_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tc05_dealloc(tmem, 512);
+}
+
+static bool fp8_ws_as_planned()
+{
+    static int state = -1;
+    if (state < 0) {
+        cudaFuncAttributes f;
+        state = cudaFuncGetAttributes(&f, fp8_gemm_ws_kernel) == cudaSuccess && f.numRegs == F8W_REG_LAUNCH ? 1 : 0;
+    }
+    return state == 1;
+}
+
 int launch_fp8_linear(cudaStream_t st, const uint8_t *a, const float *a_scale, const uint8_t *w, const float *w_scale,
                       void *out_bf16, uint32_t M, uint32_t N, uint32_t K, int *status)
 {
@@ -260,7 +455,23 @@ int launch_fp8_linear(cudaStream_t st, const uint8_t *a, const float *a_scale, c
     static bool attr_set = false;
     if (!attr_set) {
         cudaFuncSetAttribute(fp8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM);
+        cudaFuncSetAttribute(fp8_gemm_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F8W_SMEM);
         attr_set = true;
+    }
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    const char *no_ws = getenv("DSMOE_FP8_NO_WS");
+    const uint32_t tiles = ((M + 127) / 128) * (N / F8W_TN);
+    if (M > 256 && N % F8W_TN == 0 && K / 128 <= (uint32_t)F8W_MAX_KB && tiles >= (uint32_t)sms / 2 && fp8_ws_as_planned() &&
+        !(no_ws && no_ws[0] == '1')) {
+        fp8_gemm_ws_kernel<<<tiles < (uint32_t)sms ? tiles : (uint32_t)sms, F8W_THREADS, F8W_SMEM, st>>>(a, a_scale, w, w_scale,
+                                                                                                       out, M, N, K, status);
+        return 1;
     }
     fp8_gemm_kernel<<<dim3(N / 128, (M + 127) / 128), 256, F8_SMEM, st>>>(a, a_scale, w, w_scale, out, M, N, K, status);
     return 1;

@@ -7,6 +7,24 @@
 
 namespace dsmoe {
 
+// Launch with the programmatic-serialisation attribute (see pdl_wait() in async.cuh): the kernel may be scheduled
+// while its predecessor in the stream drains, and must call pdl_wait() before touching that kernel's data.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 void launch_q8k_quantize(cudaStream_t st, const float *x, uint8_t *out, uint32_t in_dim, uint32_t n_rows);
 
 void launch_router_select(cudaStream_t st, const float *logits, const float *bias, const int32_t *hash,

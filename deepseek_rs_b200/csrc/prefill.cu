@@ -40,9 +40,6 @@ static_assert(PF_COLS == 64, "the drain reads its 64 TMEM columns per thread wit
 // increase blocks until the CTA's warps have RELEASED as many registers as it asks for (registers the CTA never
 // allocated do not count), so the released total must cover the request or the consumers would wait for ever.
 constexpr int PF_REG_LAUNCH = 72;
-#ifndef PF_DRAIN_WIDE
-#define PF_DRAIN_WIDE 1
-#endif
 #ifndef PF_REG_CONSUMER
 #define PF_REG_CONSUMER 152
 #define PF_REG_PRODUCER 40
@@ -558,18 +555,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
                             acc[c0 + i + 1] = __fadd_rn(first ? 0.0f : acc[c0 + i + 1], t.y);
                         }
                     };
-                    if (!PF_DRAIN_WIDE) {  // 16 columns at a time, release at the end
-                        float v[16];
-#pragma unroll
-                        for (int c0 = 0; c0 < PF_COLS; c0 += 16) {
-                            if (acol0 + c0 >= rows16) break;
-                            tc05_ld16(tmem + tlane + acol0 + c0, v);
-                            tc05_wait_ld16(v);
-                            if (first_of_leaf) scaled(c0, v, true);
-                            else scaled(c0, v, false);
-                        }
-                        release();
-                    } else if (first_of_leaf) {  // acc is dead: load all 64 columns into it, release, scale in place
+                    if (first_of_leaf) {  // acc is dead: load all 64 columns into it, release, scale in place
                         if (acol0 < rows16) {  // warp-uniform: columns beyond the padded tile hold nothing
                             tc05_ld32(tmem + tlane + acol0, acc);
                             if (acol0 + 32 < rows16) tc05_ld32(tmem + tlane + acol0 + 32, acc + 32);

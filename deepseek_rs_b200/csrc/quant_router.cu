@@ -1,4 +1,5 @@
 // Q8_K activation quantiser, router top-k, dequantisers, upload-time re-layout and the slot sum.
+#include "async.cuh"
 #include "common.cuh"
 #include "launch.h"
 
@@ -75,6 +76,8 @@ __global__ void __launch_bounds__(256) q8k_quantize_kernel(const float *__restri
 {
     const int lane = threadIdx.x & 31;
     const uint64_t blk = (uint64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    pdl_launch_dependents();
+    pdl_wait();
     if (blk >= n_blocks_total) return;
     q8k_quantize_block(x + blk * QK_K, out + blk * Q8K_BYTES, lane);
 }
@@ -83,7 +86,7 @@ void launch_q8k_quantize(cudaStream_t st, const float *x, uint8_t *out, uint32_t
 {
     uint64_t nb = (uint64_t)(in_dim / QK_K) * n_rows;
     if (nb == 0) return;
-    q8k_quantize_kernel<<<(unsigned)((nb + 7) / 8), 256, 0, st>>>(x, out, nb);
+    launch_pdl(q8k_quantize_kernel, dim3((unsigned)((nb + 7) / 8)), dim3(256), 0, st, x, out, nb);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -222,6 +225,8 @@ __global__ void __launch_bounds__(256) router_q8k_fused_kernel(const float *__re
     __shared__ unsigned long long s_warp_best[8];
     __shared__ float s_w[MAX_K];
     __shared__ int s_sel[MAX_K];
+    pdl_launch_dependents();  // the expert kernel behind this one may set up its tables meanwhile
+    pdl_wait();
     const uint32_t t = blockIdx.x;
     const int e = threadIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float p = 0.0f;

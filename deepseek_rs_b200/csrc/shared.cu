@@ -64,40 +64,51 @@ __global__ void __launch_bounds__(256) matmul_q8_0_kernel(const uint8_t *__restr
     float acc[TOK];
 #pragma unroll
     for (int t = 0; t < TOK; ++t) acc[t] = 0.0f;
-    for (uint64_t b = lane; b < blocks; b += 32) {
-        const uint8_t *blk = wrow + b * Q8_0_BYTES;
-        // aligned words covering the block
-        const uintptr_t addr = reinterpret_cast<uintptr_t>(blk);
-        const uint32_t *aw = reinterpret_cast<const uint32_t *>(addr & ~(uintptr_t)3);
-        uint32_t raw[9];
-        const bool odd = (addr & 2) != 0;
+    // four blocks per lane and round: all their words are requested before any is used
+    for (uint64_t b0 = lane; b0 < blocks; b0 += 128) {
+        uint32_t raw[4][9];
+        bool odd[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) raw[i] = aw[i];
-        // the ninth word: an even block only owns its low half (never read past the tensor)
-        raw[8] = odd ? aw[8] : (uint32_t)*reinterpret_cast<const uint16_t *>(blk + 32);
-        uint32_t wq[8], scale_bits;
-        if (!odd) {  // [scale | q0 q1] [q2..q5] ... : the int8 data starts in the upper half of word 0
-            scale_bits = raw[0] & 0xFFFFu;
+        for (int u = 0; u < 4; ++u) {
+            const uint64_t b = b0 + 32 * u;
+            if (b >= blocks) break;
+            const uint8_t *blk = wrow + b * Q8_0_BYTES;
+            const uintptr_t addr = reinterpret_cast<uintptr_t>(blk);
+            const uint32_t *aw = reinterpret_cast<const uint32_t *>(addr & ~(uintptr_t)3);  // aligned words covering the block
+            odd[u] = (addr & 2) != 0;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) wq[i] = __funnelshift_r(raw[i], raw[i + 1], 16);
-        } else {     // [.. | scale] [q0..q3] ...
-            scale_bits = raw[0] >> 16;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) wq[i] = raw[i + 1];
+            for (int i = 0; i < 8; ++i) raw[u][i] = aw[i];
+            // the ninth word: an even block only owns its low half (never read past the tensor)
+            raw[u][8] = odd[u] ? aw[8] : (uint32_t)*reinterpret_cast<const uint16_t *>(blk + 32);
         }
-        const float sw = f16_bits_to_f32(scale_bits, false);
 #pragma unroll
-        for (int t = 0; t < TOK; ++t) {
-            if (tok0 + t >= n_tok) break;
-            const uint4 *xv = reinterpret_cast<const uint4 *>(xq + ((tok0 + t) * blocks + b) * 32);
-            const uint4 x0 = xv[0], x1 = xv[1];
-            int dot = 0;
-            dot = __dp4a((int)wq[0], (int)x0.x, dot), dot = __dp4a((int)wq[1], (int)x0.y, dot);
-            dot = __dp4a((int)wq[2], (int)x0.z, dot), dot = __dp4a((int)wq[3], (int)x0.w, dot);
-            dot = __dp4a((int)wq[4], (int)x1.x, dot), dot = __dp4a((int)wq[5], (int)x1.y, dot);
-            dot = __dp4a((int)wq[6], (int)x1.z, dot), dot = __dp4a((int)wq[7], (int)x1.w, dot);
-            const float s = __fmul_rn(sw, xscale[(tok0 + t) * blocks + b]);
-            acc[t] = __fadd_rn(acc[t], __fmul_rn(s, (float)dot));
+        for (int u = 0; u < 4; ++u) {
+            const uint64_t b = b0 + 32 * u;
+            if (b >= blocks) break;
+            uint32_t wq[8], scale_bits;
+            if (!odd[u]) {  // [scale | q0 q1] [q2..q5] ... : the int8 data starts in the upper half of word 0
+                scale_bits = raw[u][0] & 0xFFFFu;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) wq[i] = __funnelshift_r(raw[u][i], raw[u][i + 1], 16);
+            } else {        // [.. | scale] [q0..q3] ...
+                scale_bits = raw[u][0] >> 16;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) wq[i] = raw[u][i + 1];
+            }
+            const float sw = f16_bits_to_f32(scale_bits, false);
+#pragma unroll
+            for (int t = 0; t < TOK; ++t) {
+                if (tok0 + t >= n_tok) break;
+                const uint4 *xv = reinterpret_cast<const uint4 *>(xq + ((tok0 + t) * blocks + b) * 32);
+                const uint4 x0 = xv[0], x1 = xv[1];
+                int dot = 0;
+                dot = __dp4a((int)wq[0], (int)x0.x, dot), dot = __dp4a((int)wq[1], (int)x0.y, dot);
+                dot = __dp4a((int)wq[2], (int)x0.z, dot), dot = __dp4a((int)wq[3], (int)x0.w, dot);
+                dot = __dp4a((int)wq[4], (int)x1.x, dot), dot = __dp4a((int)wq[5], (int)x1.y, dot);
+                dot = __dp4a((int)wq[6], (int)x1.z, dot), dot = __dp4a((int)wq[7], (int)x1.w, dot);
+                const float sc = __fmul_rn(sw, xscale[(tok0 + t) * blocks + b]);
+                acc[t] = __fadd_rn(acc[t], __fmul_rn(sc, (float)dot));
+            }
         }
     }
 #pragma unroll
@@ -127,34 +138,47 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const float *__restrict__ g
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// matmul_f16: out[tok][row] = dot(w[row], x[tok]). The reference sums with 256 threads striding the row and a
-// shared-memory halving tree. Here one warp does a (row, token): lane l owns the eight partial sums of threads
-// l, l+32, ..., l+224 (each over elements tx, tx+256, ... in order), folds them as the tree's strides 128, 64, 32 do
-// (partials tx and tx+stride sit in the same lane), and finishes strides 16..1 with shuffles.
+// matmul_f16: out[tok][row] = dot(w[row], x[tok]). The reference sums with 256 threads striding the row (thread tx adds
+// elements tx, tx+256, ... in order) and a shared-memory halving tree. Here one warp does a (row, token): lane l owns
+// the partial sums of threads 8l .. 8l+7, whose elements at every step are 8 contiguous f16 (one 16-byte load). The
+// tree's strides 128 .. 8 pair lane l with lane l + stride/8 (shuffles), strides 4, 2, 1 fold the lane's own eight.
 // ---------------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) matmul_f16_kernel(const uint16_t *__restrict__ w, const float *__restrict__ x,
-                                                          float *__restrict__ out, uint64_t in_dim, uint64_t out_dim,
-                                                          uint64_t n_tok)
+__global__ void __launch_bounds__(64) matmul_f16_kernel(const uint16_t *__restrict__ w, const float *__restrict__ x,
+                                                         float *__restrict__ out, uint64_t in_dim, uint64_t out_dim,
+                                                         uint64_t n_tok)
 {
-    const uint64_t row = (uint64_t)blockIdx.x * 8 + (threadIdx.x >> 5), tok = blockIdx.y;
+    const uint64_t row = (uint64_t)blockIdx.x * 2 + (threadIdx.x >> 5), tok = blockIdx.y;
     if (row >= out_dim || tok >= n_tok) return;
     const uint32_t lane = threadIdx.x & 31;
     const uint16_t *wr = w + row * in_dim;
     const float *xr = x + tok * in_dim;
     float p[8];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        float s = 0.0f;
-        for (uint64_t i = lane + 32 * k; i < in_dim; i += 256) s = __fadd_rn(s, __fmul_rn(f16_bits_to_f32(wr[i], false), xr[i]));
-        p[k] = s;
+    for (int k = 0; k < 8; ++k) p[k] = 0.0f;
+    const bool vec = (in_dim & 7) == 0 && ((reinterpret_cast<uintptr_t>(wr) | reinterpret_cast<uintptr_t>(xr)) & 15) == 0;
+    for (uint64_t base = 8 * lane; base < in_dim; base += 256) {
+        if (vec) {
+            const uint4 wv = *reinterpret_cast<const uint4 *>(wr + base);
+            const float4 x0 = *reinterpret_cast<const float4 *>(xr + base), x1 = *reinterpret_cast<const float4 *>(xr + base + 4);
+            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+            const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                p[k] = __fadd_rn(p[k], __fmul_rn(f16_bits_to_f32((ww[k >> 1] >> (16 * (k & 1))) & 0xFFFFu, false), xs[k]));
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (base + k < in_dim) p[k] = __fadd_rn(p[k], __fmul_rn(f16_bits_to_f32(wr[base + k], false), xr[base + k]));
+        }
     }
 #pragma unroll
-    for (int k = 0; k < 4; ++k) p[k] = __fadd_rn(p[k], p[k + 4]);  // stride 128
-    p[0] = __fadd_rn(p[0], p[2]), p[1] = __fadd_rn(p[1], p[3]);    // stride 64
-    float v = __fadd_rn(p[0], p[1]);                               // stride 32
+    for (int m = 16; m > 0; m >>= 1)  // strides 128, 64, 32, 16, 8 of the tree; lanes below m hold its values
 #pragma unroll
-    for (int m = 16; m > 0; m >>= 1) v = __fadd_rn(v, __shfl_down_sync(FULL, v, m));  // lanes below m hold the tree's values
-    if (lane == 0) out[tok * out_dim + row] = v;
+        for (int k = 0; k < 8; ++k) p[k] = __fadd_rn(p[k], __shfl_down_sync(FULL, p[k], m));
+#pragma unroll
+    for (int k = 0; k < 4; ++k) p[k] = __fadd_rn(p[k], p[k + 4]);  // stride 4
+    p[0] = __fadd_rn(p[0], p[2]), p[1] = __fadd_rn(p[1], p[3]);    // stride 2
+    if (lane == 0) out[tok * out_dim + row] = __fadd_rn(p[0], p[1]);  // stride 1
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -185,7 +209,7 @@ void launch_matmul_f16(cudaStream_t st, const uint16_t *w, const float *x, float
                        uint64_t n_tok)
 {
     if (out_dim == 0 || n_tok == 0) return;
-    matmul_f16_kernel<<<dim3((unsigned)((out_dim + 7) / 8), (unsigned)n_tok), 256, 0, st>>>(w, x, out, in_dim, out_dim, n_tok);
+    matmul_f16_kernel<<<dim3((unsigned)((out_dim + 1) / 2), (unsigned)n_tok), 64, 0, st>>>(w, x, out, in_dim, out_dim, n_tok);
 }
 
 }  // namespace dsmoe

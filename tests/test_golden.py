@@ -66,14 +66,15 @@ def test_gpu_iq2xxs_matvec_fixture(torch_cuda, cases):
     from deepseek_rs_b200.kernels import MoeKernels
 
     c, g = cases["iq2xxs_matvec"], load("iq2xxs_matvec")
-    K = MoeKernels(device=0, n_expert=1, n_expert_used=1, max_tokens=1)
+    K = MoeKernels(device=0, n_expert=32, n_expert_used=1, max_tokens=1)
     xq = torch.empty((1, 16, 292), dtype=torch.uint8, device="cuda")
     K.q8k_quantize(dev(torch, c["x"]), xq, 4096, 1)
     w = dev(torch, c["w"])
     gate_out, up_out, mid = (torch.empty((1, 2048), device="cuda") for _ in range(3))
     sel = torch.zeros((1, 1), dtype=torch.int32, device="cuda")
     wt = torch.ones((1, 1), device="cuda")
-    K.moe_gate_up_mid_qwarp32(w, w, xq, sel, wt, gate_out, up_out, mid, 2048 * 16 * 66, 16 * 66, 16, 2048, 1, 10.0)
+    # clamp 0 switches the clamp off: gate_out / up_out are then the plain projections
+    K.moe_gate_up_mid_qwarp32(w, w, xq, sel, wt, gate_out, up_out, mid, 2048 * 16 * 66, 16 * 66, 16, 2048, 1, 0.0)
     torch.cuda.synchronize()
     assert same_bits(xq.cpu().numpy(), g["xq"])
     assert same_bits(gate_out.cpu().numpy(), g["y"]) and same_bits(up_out.cpu().numpy(), g["y"])
@@ -88,7 +89,7 @@ def test_gpu_q2k_matvec_fixture(torch_cuda, cases, T):
     from deepseek_rs_b200.kernels import MoeKernels
 
     c, g = cases["q2k_matvec"], load("q2k_matvec")
-    K = MoeKernels(device=0, n_expert=1, n_expert_used=1, max_tokens=16)
+    K = MoeKernels(device=0, n_expert=32, n_expert_used=1, max_tokens=16)
     xq = torch.empty((T, 16, 292), dtype=torch.uint8, device="cuda")
     K.q8k_quantize(dev(torch, c["x"][:T]), xq, 4096, T)
     out = torch.empty((T, 2048), device="cuda")

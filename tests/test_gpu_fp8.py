@@ -77,3 +77,22 @@ def test_fp8_linear(env, oracle, M, N, K):
     # the quantised product also tracks the unquantised one (sanity of the whole chain, loose)
     exact = a[rows].astype(np.float64) @ w.T.astype(np.float64)
     assert np.corrcoef(exact.ravel(), got[rows].ravel())[0, 1] > 0.995
+
+
+def test_fp8_linear_ragged_rows_on_the_persistent_kernel(env, oracle):
+    """M = 1000 is not a multiple of the 128-row tile and 80 tiles select the persistent warp-specialised kernel: the
+    last tile's missing rows are zero-filled on load and never stored; every row is checked."""
+    torch, Kh = env
+    M, N, K = 1000, 2560, 512
+    rng = np.random.default_rng(77)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = rng.standard_normal((N, K)).astype(np.float32)
+    ac, asc = _quant_gpu(torch, Kh, a, 1)
+    wc, wsc = _quant_gpu(torch, Kh, w, 128)
+    out = torch.full((M + 8, N), 7.0, dtype=torch.bfloat16, device="cuda")  # guard rows after the result
+    Kh.fp8_linear(ac, asc, wc, wsc, out, M, N, K)
+    assert Kh.device_status() == 0
+    got = out.float().cpu().numpy()
+    assert np.all(got[M:] == 7.0), "rows past M were written"
+    ref = oracle.fp8_gemm(ac.cpu().numpy(), asc.cpu().numpy(), wc.cpu().numpy(), wsc.cpu().numpy())
+    _check(got[:M], ref)
