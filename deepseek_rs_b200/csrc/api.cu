@@ -391,6 +391,10 @@ int dsmoe_shared_expert(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *gat
     const dsmoe_config &c = h->cfg;
     cudaStream_t st = (cudaStream_t)stream;
     int n = 0;
+    if (shared_fused_eligible(c.n_embd, c.n_ff, n_tokens) && n_tokens <= h->sh_chunk) {
+        n = launch_shared_fused(st, gate_w, up_w, down_w, x, h->sh_mid, out, c.n_embd, c.n_ff, n_tokens, c.swiglu_clamp);
+        return check_launch(h, "shared_expert", n);
+    }
     for (uint32_t t0 = 0; t0 < n_tokens; t0 += h->sh_chunk) {
         const uint32_t T = n_tokens - t0 < h->sh_chunk ? n_tokens - t0 : h->sh_chunk;
         const float *xc = x + (size_t)t0 * c.n_embd;

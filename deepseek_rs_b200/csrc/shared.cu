@@ -8,6 +8,7 @@
 // they are added) is kept, so the results equal the CPU oracle bit for bit; the thread mapping is new.
 #include <cuda_fp16.h>
 
+#include "async.cuh"
 #include "common.cuh"
 #include "launch.h"
 
@@ -156,20 +157,34 @@ __global__ void __launch_bounds__(64) matmul_f16_kernel(const uint16_t *__restri
 #pragma unroll
     for (int k = 0; k < 8; ++k) p[k] = 0.0f;
     const bool vec = (in_dim & 7) == 0 && ((reinterpret_cast<uintptr_t>(wr) | reinterpret_cast<uintptr_t>(xr)) & 15) == 0;
-    for (uint64_t base = 8 * lane; base < in_dim; base += 256) {
-        if (vec) {
-            const uint4 wv = *reinterpret_cast<const uint4 *>(wr + base);
-            const float4 x0 = *reinterpret_cast<const float4 *>(xr + base), x1 = *reinterpret_cast<const float4 *>(xr + base + 4);
-            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-            const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    if (vec) {
+        for (uint64_t base0 = 8 * lane; base0 < in_dim; base0 += 1024) {  // four rounds of loads in flight
+            uint4 wv[4];
+            float4 xa[4], xb[4];
 #pragma unroll
-            for (int k = 0; k < 8; ++k)
-                p[k] = __fadd_rn(p[k], __fmul_rn(f16_bits_to_f32((ww[k >> 1] >> (16 * (k & 1))) & 0xFFFFu, false), xs[k]));
-        } else {
+            for (int u = 0; u < 4; ++u) {
+                const uint64_t base = base0 + 256 * u;
+                if (base < in_dim) {
+                    wv[u] = *reinterpret_cast<const uint4 *>(wr + base);
+                    xa[u] = *reinterpret_cast<const float4 *>(xr + base);
+                    xb[u] = *reinterpret_cast<const float4 *>(xr + base + 4);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (base0 + 256 * u >= in_dim) break;
+                const uint32_t ww[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
+                const float xs[8] = {xa[u].x, xa[u].y, xa[u].z, xa[u].w, xb[u].x, xb[u].y, xb[u].z, xb[u].w};
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    p[k] = __fadd_rn(p[k], __fmul_rn(f16_bits_to_f32((ww[k >> 1] >> (16 * (k & 1))) & 0xFFFFu, false), xs[k]));
+            }
+        }
+    } else {
+        for (uint64_t base = 8 * lane; base < in_dim; base += 256)
 #pragma unroll
             for (int k = 0; k < 8; ++k)
                 if (base + k < in_dim) p[k] = __fadd_rn(p[k], __fmul_rn(f16_bits_to_f32(wr[base + k], false), xr[base + k]));
-        }
     }
 #pragma unroll
     for (int m = 16; m > 0; m >>= 1)  // strides 128, 64, 32, 16, 8 of the tree; lanes below m hold its values
@@ -179,6 +194,140 @@ __global__ void __launch_bounds__(64) matmul_f16_kernel(const uint16_t *__restri
     for (int k = 0; k < 4; ++k) p[k] = __fadd_rn(p[k], p[k + 4]);  // stride 4
     p[0] = __fadd_rn(p[0], p[2]), p[1] = __fadd_rn(p[1], p[3]);    // stride 2
     if (lane == 0) out[tok * out_dim + row] = __fadd_rn(p[0], p[1]);  // stride 1
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Small batches: the shared expert in two launches instead of six. Every CTA quantises the token's activation row to
+// Q8_0 itself, into shared memory (the same arithmetic as quantize_q8_0_kernel, so the same codes), and then its eight
+// warps each take one output row. FIRST: gate row r and up row r of the same warp meet in the SwiGLU, out = mid.
+// Otherwise: the down projection. Results equal the six-launch path bit for bit.
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void q8_0_block_words(const uint8_t *blk, uint32_t (&wq)[8], float &scale)
+{
+    const uintptr_t addr = reinterpret_cast<uintptr_t>(blk);
+    const uint32_t *aw = reinterpret_cast<const uint32_t *>(addr & ~(uintptr_t)3);
+    uint32_t raw[9];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) raw[i] = aw[i];
+    if (addr & 2) {
+        raw[8] = aw[8];
+        scale = f16_bits_to_f32(raw[0] >> 16, false);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) wq[i] = raw[i + 1];
+    } else {
+        raw[8] = (uint32_t)*reinterpret_cast<const uint16_t *>(blk + 32);
+        scale = f16_bits_to_f32(raw[0] & 0xFFFFu, false);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) wq[i] = __funnelshift_r(raw[i], raw[i + 1], 16);
+    }
+}
+
+__device__ __forceinline__ int q8_0_dot32(const uint32_t (&wq)[8], const int8_t *xq_blk)
+{
+    const uint4 x0 = reinterpret_cast<const uint4 *>(xq_blk)[0], x1 = reinterpret_cast<const uint4 *>(xq_blk)[1];
+    int dot = 0;
+    dot = __dp4a((int)wq[0], (int)x0.x, dot), dot = __dp4a((int)wq[1], (int)x0.y, dot);
+    dot = __dp4a((int)wq[2], (int)x0.z, dot), dot = __dp4a((int)wq[3], (int)x0.w, dot);
+    dot = __dp4a((int)wq[4], (int)x1.x, dot), dot = __dp4a((int)wq[5], (int)x1.y, dot);
+    dot = __dp4a((int)wq[6], (int)x1.z, dot), dot = __dp4a((int)wq[7], (int)x1.w, dot);
+    return dot;
+}
+
+constexpr int SHF_MAX_IN = 4096;  // widest activation row the fused kernels hold in shared memory
+
+template <bool FIRST>
+__global__ void __launch_bounds__(256) shared_fused_kernel(const uint8_t *__restrict__ w0, const uint8_t *__restrict__ w1,
+                                                            const float *__restrict__ x, float *__restrict__ out,
+                                                            uint32_t in_dim, uint32_t out_dim, float clamp)
+{
+    __shared__ __align__(16) int8_t s_xq[SHF_MAX_IN];
+    __shared__ float s_xs[SHF_MAX_IN / 32];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, tok = blockIdx.y, blocks = in_dim / 32;
+    pdl_launch_dependents();
+    pdl_wait();
+    const float *xr = x + (size_t)tok * in_dim;
+    // quantize_q8_0 of blocks warp, warp + 8, ...: all of the warp's values are requested first
+    float xv[SHF_MAX_IN / 256];
+#pragma unroll
+    for (int i = 0; i < SHF_MAX_IN / 256; ++i) {
+        const uint32_t b = warp + 8 * i;
+        xv[i] = b < blocks ? xr[b * 32 + lane] : 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < SHF_MAX_IN / 256; ++i) {
+        const uint32_t b = warp + 8 * i;
+        if (b >= blocks) break;
+        const float v = xv[i];
+        float amax = v < 0.0f ? -v : v;
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) {
+            const float o = __shfl_xor_sync(FULL, amax, m);
+            amax = o > amax ? o : amax;
+        }
+        const float d = __fdiv_rn(amax, 127.0f), id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+        const float raw = __fmul_rn(v, id);
+        int q = raw >= 0.0f ? (int)__fadd_rn(raw, 0.5f) : (int)__fsub_rn(raw, 0.5f);
+        q = q > 127 ? 127 : (q < -128 ? -128 : q);
+        s_xq[b * 32 + lane] = (int8_t)q;
+        if (lane == 0) s_xs[b] = d;
+    }
+    __syncthreads();
+    const uint32_t row = blockIdx.x * 8 + warp;
+    if (row >= out_dim) return;
+    const uint8_t *r0 = w0 + (size_t)row * blocks * Q8_0_BYTES, *r1 = FIRST ? w1 + (size_t)row * blocks * Q8_0_BYTES : nullptr;
+    float a0 = 0.0f, a1 = 0.0f;
+    // ascending blocks per lane (the reference's lane partials), four at a time with all their words requested first
+    for (uint32_t b0 = lane; b0 < blocks; b0 += 128) {
+        uint32_t wq0[4][8], wq1[4][8];
+        float sw0[4], sw1[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const uint32_t b = b0 + 32 * u;
+            if (b >= blocks) break;
+            q8_0_block_words(r0 + (size_t)b * Q8_0_BYTES, wq0[u], sw0[u]);
+            if (FIRST) q8_0_block_words(r1 + (size_t)b * Q8_0_BYTES, wq1[u], sw1[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const uint32_t b = b0 + 32 * u;
+            if (b >= blocks) break;
+            a0 = __fadd_rn(a0, __fmul_rn(__fmul_rn(sw0[u], s_xs[b]), (float)q8_0_dot32(wq0[u], s_xq + b * 32)));
+            if (FIRST) a1 = __fadd_rn(a1, __fmul_rn(__fmul_rn(sw1[u], s_xs[b]), (float)q8_0_dot32(wq1[u], s_xq + b * 32)));
+        }
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+        a0 = __fadd_rn(a0, __shfl_xor_sync(FULL, a0, m));
+        if (FIRST) a1 = __fadd_rn(a1, __shfl_xor_sync(FULL, a1, m));
+    }
+    if (lane == 0) {
+        if (FIRST) {
+            float g = a0, u = a1;
+            if (clamp > 1.0e-6f) {
+                if (g > clamp) g = clamp;
+                if (u > clamp) u = clamp;
+                if (u < -clamp) u = -clamp;
+            }
+            out[(size_t)tok * out_dim + row] = swiglu_weighted(g, u, 1.0f);
+        } else {
+            out[(size_t)tok * out_dim + row] = a0;
+        }
+    }
+}
+
+bool shared_fused_eligible(uint32_t n_embd, uint32_t n_ff, uint32_t n_tokens)
+{
+    return n_tokens <= 4 && n_embd % 32 == 0 && n_ff % 32 == 0 && n_embd <= (uint32_t)SHF_MAX_IN && n_ff <= (uint32_t)SHF_MAX_IN;
+}
+
+int launch_shared_fused(cudaStream_t st, const uint8_t *gate_w, const uint8_t *up_w, const uint8_t *down_w, const float *x,
+                        float *mid, float *out, uint32_t n_embd, uint32_t n_ff, uint32_t n_tokens, float clamp)
+{
+    launch_pdl(shared_fused_kernel<true>, dim3((n_ff + 7) / 8, n_tokens), dim3(256), 0, st, gate_w, up_w, x, mid, n_embd, n_ff,
+               clamp);
+    launch_pdl(shared_fused_kernel<false>, dim3((n_embd + 7) / 8, n_tokens), dim3(256), 0, st, down_w,
+               (const uint8_t *)nullptr, (const float *)mid, out, n_ff, n_embd, clamp);
+    return 2;
 }
 
 // ---------------------------------------------------------------------------------------------------------------

@@ -88,9 +88,10 @@ def test_matmul_f16_router_logits_bit_exact(torch_cuda, oracle, K, T, in_dim, ou
     assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
 
 
-@pytest.mark.parametrize("T", [1, 1300])
+@pytest.mark.parametrize("T", [1, 3, 1300])
 def test_shared_expert_whole(torch_cuda, oracle, K, T):
-    """The one-call shared expert against the oracle's four steps; 1300 tokens cross the library's 1024-token chunks."""
+    """The one-call shared expert against the oracle's four steps: 1 and 3 tokens take the fused two-launch kernels, 1300
+    tokens the six-launch path across the library's 1024-token chunks."""
     torch = torch_cuda
     rng = np.random.default_rng(T)
     n_embd, n_ff = 4096, 2048
