@@ -561,15 +561,38 @@ def run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, 
     per = N_EXPERT // world
     L, V = 2, 4
     K_route = MoeKernels(device=local_rank, max_tokens=T, max_layers=1)
-    K_owner = MoeKernels(device=local_rank, n_expert=per, n_expert_used=1, max_tokens=T_total * TOP_K, max_layers=L)
-    for il in range(L):
-        gate, up, down = gen_layer_gpu(torch, device, seed=1000 * rank + il, n_expert=per)
-        MoeLayer(K_owner, gate, up, down, layout=LAYOUT_ROWSOA, layer=il)
-        del gate, up, down
-    # expert popularity: the same on every rank. Tokens: weak = every rank its own chunk; strong = slices of one chunk
+    # expert popularity: the same on every rank (the bench's router subtracts 1.1 ln(popularity rank) from the logits)
     gen = torch.Generator(device=device)
     gen.manual_seed(7)
     rank_e = (torch.randperm(N_EXPERT, device=device, generator=gen) + 1).float()
+    # the R most popular experts are replicated on every rank: their pairs are computed where they are routed, which
+    # takes the hot experts' load off their owners (a serving system would take the ranking from running counts)
+    R = args.ep_replicate
+    hot = [int(e) for e in torch.argsort(rank_e)[:R].tolist()]
+    K_owner = MoeKernels(device=local_rank, n_expert=per + R, n_expert_used=1, max_tokens=T_total * TOP_K, max_layers=L)
+    g_exp, d_exp = N_FF * (N_EMBD // 256) * 66, N_EMBD * (N_FF // 256) * 84  # bytes per expert
+    for il in range(L):
+        gate, up, down = gen_layer_gpu(torch, device, seed=1000 * rank + il, n_expert=per)
+        if R:
+            reps = {}
+            for r in range(world):  # every owner broadcasts the slices of its hot experts
+                mine = [e for e in hot if e // per == r]
+                if not mine:
+                    continue
+                idx = torch.tensor([e % per for e in mine], device=device)
+                bufs = []
+                for t, nb in ((gate, g_exp), (up, g_exp), (down, d_exp)):
+                    buf = t.view(per, nb)[idx].contiguous() if r == rank else torch.empty((len(mine), nb), dtype=torch.uint8, device=device)
+                    dist.broadcast(buf, src=r)
+                    bufs.append(buf)
+                for i, e in enumerate(mine):
+                    reps[e] = tuple(bf[i] for bf in bufs)
+            gate = torch.cat([gate.view(per, g_exp)] + [reps[e][0][None] for e in hot]).reshape(-1)
+            up = torch.cat([up.view(per, g_exp)] + [reps[e][1][None] for e in hot]).reshape(-1)
+            down = torch.cat([down.view(per, d_exp)] + [reps[e][2][None] for e in hot]).reshape(-1)
+            del reps, bufs
+        MoeLayer(K_owner, gate, up, down, layout=LAYOUT_ROWSOA, layer=il)
+        del gate, up, down
     xl, ll = [], []
     for v in range(V):
         gen.manual_seed(100 + v if not weak else 100 + v + 1000 * rank)
@@ -582,7 +605,7 @@ def run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, 
     eps = []
     for il in range(L):
         rf, ef = gpu_functions(K_route, K_owner, layer=il)
-        eps.append(ExpertParallelMoe(rf, ef, N_EXPERT, TOP_K, N_EMBD, sum_fn=gpu_sum_function(K_route)))
+        eps.append(ExpertParallelMoe(rf, ef, N_EXPERT, TOP_K, N_EMBD, sum_fn=gpu_sum_function(K_route), replicated=hot))
     # the routing that comes out of the expert-parallel step must equal the single-GPU router's on the same tokens
     solo_route = gpu_functions(K_route, K_owner)[0]
     same = True
@@ -659,7 +682,7 @@ def run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, 
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.ep_scaling,
         "vs_baseline": None, "dtype": "f16 integer codes x int8 (exact), f32 accumulate in TMEM", "data": "synthetic",
         "config": {"workload": args.workload, "tokens_per_step_all_gpus": T_total, "tokens_per_step_per_gpu": T,
-                   "top_k": TOP_K, "n_expert": N_EXPERT, "experts_per_gpu": per, "n_embd": N_EMBD, "n_ff": N_FF,
+                   "top_k": TOP_K, "n_expert": N_EXPERT, "experts_per_gpu": per, "replicated_hot_experts": R, "n_embd": N_EMBD, "n_ff": N_FF,
                    "layout": "rowsoa", "router": "Zipf s=1.1 expert popularity",
                    "parallelism": f"ep{world}: NCCL all-to-all dispatch (Q8_K rows) + combine (f32 rows)",
                    "l2": f"inputs rotate over {L} layers x {V} routings",
@@ -687,6 +710,8 @@ def main():
     ap.add_argument("--layout", default="rowsoa", choices=["rowsoa", "native"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ref-mapping", action="store_true", help="skip the GPU baseline (restated reference mapping)")
+    ap.add_argument("--ep-replicate", type=int, default=32, choices=[0, 32, 64],
+                    help="N > 1: this many of the most popular experts are held by every rank (0 = pure sharding)")
     ap.add_argument("--ep-scaling", default="weak", choices=["weak", "strong"],
                     help="N > 1: every rank its own chunk (weak) or one chunk split over the ranks (strong)")
     ap.add_argument("--layers", type=int, default=0, help="layers to rotate over (0 = the workload's default; 1 keeps "

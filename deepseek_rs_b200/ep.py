@@ -33,10 +33,14 @@ class DispatchPlan:
     recv_counts: list
 
 
-def make_plan(selected: torch.Tensor, n_expert: int, world: int, group=None) -> DispatchPlan:
-    """selected: int32 [T, k] global expert ids (negative ids go to expert 0, as the kernels clamp them)."""
+def make_plan(selected: torch.Tensor, n_expert: int, world: int, group=None, stay_home=None, rank: int = 0) -> DispatchPlan:
+    """selected: int32 [T, k] global expert ids (negative ids go to expert 0, as the kernels clamp them).
+    stay_home: bool [n_expert] or None; pairs of those experts are computed on the rank that routed them."""
     per_rank = n_expert // world
-    dest = (selected.reshape(-1).clamp(min=0).to(torch.int64) // per_rank)
+    e = selected.reshape(-1).clamp(min=0).to(torch.int64)
+    dest = e // per_rank
+    if stay_home is not None:
+        dest = torch.where(stay_home[e], torch.full_like(dest, rank), dest)
     order = torch.sort(dest, stable=True).indices
     send = torch.bincount(dest, minlength=world).to(torch.int64)
     recv = torch.empty_like(send)
@@ -61,8 +65,12 @@ class ExpertParallelMoe:
         slots added in slot order (default: un-permute, then k torch additions)
     """
 
-    def __init__(self, route_fn, expert_fn, n_expert: int, k: int, n_embd: int, group=None, sum_fn=None):
+    def __init__(self, route_fn, expert_fn, n_expert: int, k: int, n_embd: int, group=None, sum_fn=None, replicated=None):
+        """replicated: global ids of experts every rank holds a copy of (the hottest ones), or None. Their pairs are
+        not dispatched: the routing rank computes them itself, with local expert id per_rank + position in the list.
+        The owner's expert table is then [own shard | replicas in list order]."""
         self.route_fn, self.expert_fn, self.sum_fn = route_fn, expert_fn, sum_fn
+        self.replicated = None if replicated is None or len(replicated) == 0 else [int(e) for e in replicated]
         self.n_expert, self.k, self.n_embd = n_expert, k, n_embd
         self.group = group
         self.world = dist.get_world_size(group)
@@ -79,7 +87,14 @@ class ExpertParallelMoe:
         mark("start")
         xq, selected, weights = self.route_fn(x, logits)
         mark("route")
-        plan = make_plan(selected, self.n_expert, self.world, self.group)
+        stay_home = replica_slot = None
+        if self.replicated is not None:
+            stay_home = torch.zeros(self.n_expert, dtype=torch.bool, device=selected.device)
+            replica_slot = torch.zeros(self.n_expert, dtype=torch.int64, device=selected.device)
+            ids = torch.tensor(self.replicated, dtype=torch.int64, device=selected.device)
+            stay_home[ids] = True
+            replica_slot[ids] = torch.arange(len(self.replicated), dtype=torch.int64, device=selected.device)
+        plan = make_plan(selected, self.n_expert, self.world, self.group, stay_home, self.rank)
         self.last_plan = plan
         mark("plan")
         pair_tok = plan.order // self.k
@@ -87,7 +102,10 @@ class ExpertParallelMoe:
         # int32 [pairs, 2] message
         xq_rows = xq.reshape(T, (self.n_embd // QK_K) * Q8K_BYTES)[pair_tok]
         sel_flat = selected.reshape(-1).clamp(min=0)[plan.order]
-        meta = torch.stack(((sel_flat % self.per_rank).to(torch.int32),
+        local_e = sel_flat.to(torch.int64) % self.per_rank
+        if stay_home is not None:
+            local_e = torch.where(stay_home[sel_flat.to(torch.int64)], self.per_rank + replica_slot[sel_flat.to(torch.int64)], local_e)
+        meta = torch.stack((local_e.to(torch.int32),
                             weights.reshape(-1)[plan.order].contiguous().view(torch.int32)), dim=1)
         r_xq = _exchange(xq_rows, plan.send_counts, plan.recv_counts, self.group)
         r_meta = _exchange(meta, plan.send_counts, plan.recv_counts, self.group)

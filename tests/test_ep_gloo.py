@@ -66,6 +66,23 @@ def _worker(rank, world, port, q):
         ok = ok and bool(np.array_equal(out2.numpy(), ref2))
     else:
         ok = ok and out2.shape == (0, n_embd)
+    # third step: experts 1 and 6 are replicated on both ranks (local ids per, per + 1); their pairs stay home and the
+    # result is still the single-rank layer's
+    rep = [6, 1]
+    def shard_with(t):
+        full = t.reshape(n_e, -1)
+        return np.concatenate([full[rank * per:(rank + 1) * per], full[rep]]).reshape(-1)
+    g3, u3, d3 = shard_with(lw.gate), shard_with(lw.up), shard_with(lw.down)
+
+    def expert_fn3(xq_rows, local_e, w):
+        _, _, mid = oracle.gate_up_mid(g3, u3, xq_rows.numpy(), local_e.numpy(), w.numpy(), n_ff, n_embd // 256)
+        return torch.from_numpy(oracle.down(d3, oracle.q8k_quantize(mid), local_e.numpy(), n_embd, n_ff // 256))
+
+    ep3 = ExpertParallelMoe(route_fn, expert_fn3, n_e, k, n_embd, replicated=rep)
+    out3, _ = ep3.forward(torch.from_numpy(x), torch.from_numpy(lg))
+    ok = ok and bool(np.array_equal(out3.numpy(), ref_out))
+    home = int(np.isin(ref_sel, rep).sum())  # pairs that must not have left this rank
+    ok = ok and ep3.last_plan.send_counts[rank] >= home
     q.put((rank, ok, sent, T * k))
     dist.barrier()
     dist.destroy_process_group()
