@@ -445,7 +445,7 @@ def run_fp8(args, torch, dist, K, device, rank, world, sampler):
         "config": {"workload": "fp8_linear", "M": 4096, "N": 4096, "K": 4096, "block_scales": "1x128 act, 128x128 weight",
                    "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
                    "l2": f"{R} weight matrices rotate (268 MB > 126 MB L2)"},
-        "roofline": {"bound": "tensor", "kernel": "fp8_gemm_ws_kernel (tcgen05 kind::f8f6f4, 128x256 tiles)", "achieved": head["tflops"],
+        "roofline": {"bound": "tensor", "kernel": "fp8_gemm_ws_kernel<TMA> (tcgen05 kind::f8f6f4, 128x256 tiles, tensor-map loads)", "achieved": head["tflops"],
                      "peak": peak_tf, "peak_kind": f"of {kind} bf16 GEMM (dense fp8 is nominally twice that)",
                      "unit": "TFLOP/s", "frac": head["tflops"] / peak_tf, "traffic": None, "avg_launch_ms": head["ms"]},
         "roofline_matvec": {"bound": "hbm", "kernel": "fp8_matvec_kernel (M = 1)", "achieved": mv["weight_gbs"],

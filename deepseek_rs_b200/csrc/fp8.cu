@@ -13,7 +13,9 @@
 //                         MMAs run. Operands reach shared memory by 16-byte cp.async in core-matrix order.
 //   fp8_matvec_kernel     M <= 8: bandwidth-bound, one warp per output feature, f32 accumulate.
 #include <stdlib.h>
+#include <string.h>
 
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
@@ -276,12 +278,41 @@ static_assert(F8W_SMEM <= 232448, "shared memory per CTA");
 constexpr int F8W_REG_LAUNCH = 128, F8W_REG_CONSUMER = 184, F8W_REG_OTHER = 72;
 static_assert(256 * (F8W_REG_CONSUMER - F8W_REG_LAUNCH) <= 256 * (F8W_REG_LAUNCH - F8W_REG_OTHER), "setmaxnreg budget");
 
+// Tensor-map (TMA) tile load into shared memory, completion counted in bytes on the mbarrier. Coordinates: x = byte
+// column (a multiple of 16), y = row. Rows outside the tensor arrive as zeros. Local memory only.
+__device__ __forceinline__ void tma_load_2d(void *dst_smem, const CUtensorMap *map, uint32_t x, uint32_t y, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Shared-memory descriptor of a K-major operand tile written by a 128-byte-swizzled tensor-map load: rows of 128
+// bytes, 8-row groups 1024 bytes apart, layout type 2 (128-byte swizzle), version 1. The tile must start on a
+// 1024-byte boundary; K advances inside the swizzle atom by adding the byte offset to the start address.
+__device__ __forceinline__ uint64_t tc05_smem_desc_sw128(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024u >> 4) << 32;
+    d |= 1ull << 46;
+    d |= 2ull << 61;
+    return d;
+}
+
+// TMA = true: one producer warp issues two tensor-map loads per stage (128-byte swizzle). TMA = false: four producer
+// warps copy 16 bytes at a time with cp.async into the unswizzled core-matrix order.
+template <bool TMA>
 __global__ void __launch_bounds__(F8W_THREADS, 1) fp8_gemm_ws_kernel(const uint8_t *__restrict__ a,
                                                                      const float *__restrict__ a_scale,
                                                                      const uint8_t *__restrict__ w,
                                                                      const float *__restrict__ w_scale,
                                                                      __nv_bfloat16 *__restrict__ out, uint32_t M, uint32_t N,
-                                                                     uint32_t K, int *status)
+                                                                     uint32_t K, int *status,
+                                                                     const __grid_constant__ CUtensorMap map_a,
+                                                                     const __grid_constant__ CUtensorMap map_w)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t *bar_full = reinterpret_cast<uint64_t *>(smem + F8W_SMEM_BAR);  // [4] stage landed (128 producer threads)
@@ -295,7 +326,7 @@ __global__ void __launch_bounds__(F8W_THREADS, 1) fp8_gemm_ws_kernel(const uint8
     if (warp == 0) tc05_alloc(tmem_slot, 512);
     if (tid == 0) {
         for (int i = 0; i < F8W_STAGES; ++i) {
-            mbar_init(&bar_full[i], 128);
+            mbar_init(&bar_full[i], TMA ? 1 : 128);
             mbar_init(&bar_free[i], 1);
         }
         for (int i = 0; i < 2; ++i) {
@@ -366,7 +397,26 @@ __global__ void __launch_bounds__(F8W_THREADS, 1) fp8_gemm_ws_kernel(const uint8
         }
     } else {
         reg_dealloc<F8W_REG_OTHER>();
-        if (warp < 12) {
+        if (TMA && warp == 8) {
+            // ------------------------------------------------------------------------------------------- producer (TMA)
+            uint32_t g = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+                const uint32_t mt = tile / n_nt, nt = tile - mt * n_nt, m0 = mt * 128, n0 = nt * F8W_TN;
+                for (uint32_t kb = 0; kb < nkb; ++kb, ++g) {
+                    const uint32_t s = g % F8W_STAGES, use = g / F8W_STAGES;
+                    if (use >= 1) ok = mbar_wait_bounded(&bar_free[s], (use - 1) & 1u, status);
+                    ok = __all_sync(FULL, ok);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        mbar_expect_tx(&bar_full[s], F8W_STAGE_A + F8W_STAGE_B);
+                        tma_load_2d(smem + s * F8W_STAGE_A, &map_a, kb * 128, m0, &bar_full[s]);
+                        tma_load_2d(smem + F8W_SMEM_B + s * F8W_STAGE_B, &map_w, kb * 128, n0, &bar_full[s]);
+                    }
+                    __syncwarp();
+                }
+            }
+        } else if (!TMA && warp < 12) {
             // ------------------------------------------------------------------------------------------- producers
             const uint32_t ptid = tid - 256;
             uint32_t g = 0;
@@ -413,11 +463,14 @@ __global__ void __launch_bounds__(F8W_THREADS, 1) fp8_gemm_ws_kernel(const uint8
                     tc05_fence_after_sync();
                     if (elect_one()) {
                         if (ok) {
-                            const uint64_t da = tc05_smem_desc(smem_u32(smem + s * F8W_STAGE_A), 128, F8_SBO);
-                            const uint64_t db = tc05_smem_desc(smem_u32(smem + F8W_SMEM_B + s * F8W_STAGE_B), 128, F8_SBO);
+                            const uint32_t pa = smem_u32(smem + s * F8W_STAGE_A), pb = smem_u32(smem + F8W_SMEM_B + s * F8W_STAGE_B);
+                            // unswizzled: K = 32 is two 128-byte core matrices = 256 bytes; swizzled: 32 bytes in the row
+                            const uint64_t da = TMA ? tc05_smem_desc_sw128(pa) : tc05_smem_desc(pa, 128, F8_SBO);
+                            const uint64_t db = TMA ? tc05_smem_desc_sw128(pb) : tc05_smem_desc(pb, 128, F8_SBO);
+                            const uint32_t kstep = TMA ? 2u : 16u;
 #pragma unroll
                             for (int ks = 0; ks < 4; ++ks)
-                                tc05_mma_f8(tmem + buf * F8W_TN, da + 16u * ks, db + 16u * ks, idesc, ks != 0);
+                                tc05_mma_f8(tmem + buf * F8W_TN, da + kstep * ks, db + kstep * ks, idesc, ks != 0);
                         }
                         tc05_commit(&bar_free[s]);
                         tc05_commit(&bar_acc_full[buf]);
@@ -438,9 +491,46 @@ static bool fp8_ws_as_planned()
     static int state = -1;
     if (state < 0) {
         cudaFuncAttributes f;
-        state = cudaFuncGetAttributes(&f, fp8_gemm_ws_kernel) == cudaSuccess && f.numRegs == F8W_REG_LAUNCH ? 1 : 0;
+        cudaFuncAttributes f2;
+        state = cudaFuncGetAttributes(&f, fp8_gemm_ws_kernel<false>) == cudaSuccess && f.numRegs == F8W_REG_LAUNCH &&
+                        cudaFuncGetAttributes(&f2, fp8_gemm_ws_kernel<true>) == cudaSuccess && f2.numRegs == F8W_REG_LAUNCH
+                    ? 1 : 0;
     }
     return state == 1;
+}
+
+// Tensor maps are encoded on the host by a driver function, looked up once through the runtime (no link-time
+// dependency on the driver library). Encoding allocates nothing and touches no device memory.
+typedef CUresult (*tensor_map_encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                         const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                         CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static tensor_map_encode_fn tensor_map_encoder()
+{
+    static tensor_map_encode_fn fn = nullptr;
+    static bool looked = false;
+    if (!looked) {
+        looked = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<tensor_map_encode_fn>(p);
+        cudaGetLastError();
+    }
+    return fn;
+}
+
+// bytes [rows][K] row-major, tiles of box_rows x 128 bytes, 128-byte swizzle, rows past the end read as zero
+static bool encode_u8_rows(CUtensorMap *map, const uint8_t *base, uint32_t rows, uint32_t K, uint32_t box_rows)
+{
+    tensor_map_encode_fn enc = tensor_map_encoder();
+    if (!enc || ((uintptr_t)base & 15) != 0 || K % 16 != 0) return false;
+    const cuuint64_t dims[2] = {K, rows}, strides[1] = {K};
+    const cuuint32_t box[2] = {128, box_rows}, estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 int launch_fp8_linear(cudaStream_t st, const uint8_t *a, const float *a_scale, const uint8_t *w, const float *w_scale,
@@ -455,7 +545,8 @@ int launch_fp8_linear(cudaStream_t st, const uint8_t *a, const float *a_scale, c
     static bool attr_set = false;
     if (!attr_set) {
         cudaFuncSetAttribute(fp8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM);
-        cudaFuncSetAttribute(fp8_gemm_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F8W_SMEM);
+        cudaFuncSetAttribute(fp8_gemm_ws_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8W_SMEM);
+        cudaFuncSetAttribute(fp8_gemm_ws_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8W_SMEM);
         attr_set = true;
     }
     static int sms = 0;
@@ -469,8 +560,15 @@ int launch_fp8_linear(cudaStream_t st, const uint8_t *a, const float *a_scale, c
     const uint32_t tiles = ((M + 127) / 128) * (N / F8W_TN);
     if (M > 256 && N % F8W_TN == 0 && K / 128 <= (uint32_t)F8W_MAX_KB && tiles >= (uint32_t)sms / 2 && fp8_ws_as_planned() &&
         !(no_ws && no_ws[0] == '1')) {
-        fp8_gemm_ws_kernel<<<tiles < (uint32_t)sms ? tiles : (uint32_t)sms, F8W_THREADS, F8W_SMEM, st>>>(a, a_scale, w, w_scale,
-                                                                                                       out, M, N, K, status);
+        const unsigned grid = tiles < (uint32_t)sms ? tiles : (uint32_t)sms;
+        const char *no_tma = getenv("DSMOE_FP8_NO_TMA");
+        CUtensorMap map_a, map_w;
+        memset(&map_a, 0, sizeof(map_a));
+        memset(&map_w, 0, sizeof(map_w));
+        if (!(no_tma && no_tma[0] == '1') && encode_u8_rows(&map_a, a, M, K, 128) && encode_u8_rows(&map_w, w, N, K, F8W_TN))
+            fp8_gemm_ws_kernel<true><<<grid, F8W_THREADS, F8W_SMEM, st>>>(a, a_scale, w, w_scale, out, M, N, K, status, map_a, map_w);
+        else
+            fp8_gemm_ws_kernel<false><<<grid, F8W_THREADS, F8W_SMEM, st>>>(a, a_scale, w, w_scale, out, M, N, K, status, map_a, map_w);
         return 1;
     }
     fp8_gemm_kernel<<<dim3(N / 128, (M + 127) / 128), 256, F8_SMEM, st>>>(a, a_scale, w, w_scale, out, M, N, K, status);
