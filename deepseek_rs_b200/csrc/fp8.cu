@@ -556,20 +556,23 @@ int launch_fp8_linear(cudaStream_t st, const uint8_t *a, const float *a_scale, c
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
     }
-    const char *no_ws = getenv("DSMOE_FP8_NO_WS");
+    const char *no_ws = getenv("DSMOE_FP8_NO_WS"), *no_tma = getenv("DSMOE_FP8_NO_TMA");
     const uint32_t tiles = ((M + 127) / 128) * (N / F8W_TN);
-    if (M > 256 && N % F8W_TN == 0 && K / 128 <= (uint32_t)F8W_MAX_KB && tiles >= (uint32_t)sms / 2 && fp8_ws_as_planned() &&
-        !(no_ws && no_ws[0] == '1')) {
+    if (N % F8W_TN == 0 && K / 128 <= (uint32_t)F8W_MAX_KB && fp8_ws_as_planned() && !(no_ws && no_ws[0] == '1')) {
         const unsigned grid = tiles < (uint32_t)sms ? tiles : (uint32_t)sms;
-        const char *no_tma = getenv("DSMOE_FP8_NO_TMA");
         CUtensorMap map_a, map_w;
         memset(&map_a, 0, sizeof(map_a));
         memset(&map_w, 0, sizeof(map_w));
-        if (!(no_tma && no_tma[0] == '1') && encode_u8_rows(&map_a, a, M, K, 128) && encode_u8_rows(&map_w, w, N, K, F8W_TN))
+        // with tensor-map loads the persistent kernel wins at every M (even on a handful of tiles it finishes a tile in
+        // half the lock-step kernel's time); with cp.async producers only when the tiles fill at least half the SMs
+        if (!(no_tma && no_tma[0] == '1') && encode_u8_rows(&map_a, a, M, K, 128) && encode_u8_rows(&map_w, w, N, K, F8W_TN)) {
             fp8_gemm_ws_kernel<true><<<grid, F8W_THREADS, F8W_SMEM, st>>>(a, a_scale, w, w_scale, out, M, N, K, status, map_a, map_w);
-        else
+            return 1;
+        }
+        if (M > 256 && tiles >= (uint32_t)sms / 2) {
             fp8_gemm_ws_kernel<false><<<grid, F8W_THREADS, F8W_SMEM, st>>>(a, a_scale, w, w_scale, out, M, N, K, status, map_a, map_w);
-        return 1;
+            return 1;
+        }
     }
     fp8_gemm_kernel<<<dim3(N / 128, (M + 127) / 128), 256, F8_SMEM, st>>>(a, a_scale, w, w_scale, out, M, N, K, status);
     return 1;
