@@ -56,6 +56,8 @@ SIGNATURES = {
     "dsmoe_moe_forward": (_int, [_vp, _vp, _u32, _vp, _vp, _u32, _vp, _vp, _vp]),
     "dsmoe_expert_ffn": (_int, [_vp, _vp, _u32, _vp, _vp, _vp, _u32, _vp]),
     "dsmoe_moe_forward_host": (_int, [_vp, _u32, _vp, _vp, _u32, _vp, _vp, _vp]),
+    "dsmoe_moe_forward_host_async": (_int, [_vp, _u32, _vp, _vp, _u32, _vp, _vp, _vp]),
+    "dsmoe_host_synchronize": (_int, [_vp]),
     "dsmoe_moe_forward_noalloc": (_int, [_vp, _vp, _vp, _vp, _int, _vp, _vp, _u32, _vp, _vp, _vp]),
 }
 

@@ -569,8 +569,24 @@ int dsmoe_expert_ffn(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, const
     return expert_ffn_impl(h, (cudaStream_t)stream, h->layers[layer], xq, selected, weights, n_tokens, out, 0, "expert_ffn");
 }
 
+int dsmoe_host_synchronize(dsmoe_handle *h)
+{
+    if (!h) return DSMOE_ERR_ARG;
+    const cudaError_t e = cudaStreamSynchronize(h->hstream);
+    if (e != cudaSuccess) return fail(h, DSMOE_ERR_CUDA, "host_synchronize: %s", cudaGetErrorString(e));
+    return DSMOE_OK;
+}
+
 int dsmoe_moe_forward_host(dsmoe_handle *h, uint32_t layer, const float *x_host, const float *logits_host,
                            uint32_t n_tokens, float *out_host, int32_t *selected_out_host, float *weights_out_host)
+{
+    const int rc = dsmoe_moe_forward_host_async(h, layer, x_host, logits_host, n_tokens, out_host, selected_out_host,
+                                                weights_out_host);
+    return rc != DSMOE_OK ? rc : dsmoe_host_synchronize(h);
+}
+
+int dsmoe_moe_forward_host_async(dsmoe_handle *h, uint32_t layer, const float *x_host, const float *logits_host,
+                                 uint32_t n_tokens, float *out_host, int32_t *selected_out_host, float *weights_out_host)
 {
     if (!h) return DSMOE_ERR_ARG;
     const dsmoe_config &c = h->cfg;
@@ -591,7 +607,6 @@ int dsmoe_moe_forward_host(dsmoe_handle *h, uint32_t layer, const float *x_host,
         e = cudaMemcpyAsync(selected_out_host, h->selected, n_tokens * k * 4, cudaMemcpyDeviceToHost, st);
     if (e == cudaSuccess && weights_out_host)
         e = cudaMemcpyAsync(weights_out_host, h->weights, n_tokens * k * 4, cudaMemcpyDeviceToHost, st);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return fail(h, DSMOE_ERR_CUDA, "moe_forward_host: copy out: %s", cudaGetErrorString(e));
     return DSMOE_OK;
 }

@@ -218,6 +218,21 @@ class MoeKernels:
         self._check(self.lib.dsmoe_moe_forward_host(self.h, layer, hp(x_host), hp(logits_host), n_tokens, hp(out_host),
                                                     hp(selected_host), hp(weights_host)))
 
+    def moe_forward_host_async(self, layer: int, x_host, logits_host, n_tokens: int, out_host, selected_host=None,
+                               weights_host=None):
+        """The same, queued on the handle's stream without waiting (pinned host tensors only); ``host_synchronize``
+        waits. One call in flight per handle; two handles used in turn overlap copies with kernels."""
+        def hp(t):
+            if t is None:
+                return None
+            assert (not t.is_cuda) and t.is_contiguous() and t.is_pinned()
+            return C.c_void_p(t.data_ptr())
+        self._check(self.lib.dsmoe_moe_forward_host_async(self.h, layer, hp(x_host), hp(logits_host), n_tokens,
+                                                          hp(out_host), hp(selected_host), hp(weights_host)))
+
+    def host_synchronize(self):
+        self._check(self.lib.dsmoe_host_synchronize(self.h))
+
 
 class MoeLayer:
     """One layer's routed experts resident on the device, with the upload-time re-layout applied.

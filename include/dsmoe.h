@@ -236,6 +236,16 @@ DSMOE_API int dsmoe_moe_forward_host(dsmoe_handle *h, uint32_t layer, const floa
                                      uint32_t n_tokens, float *out_host, int32_t *selected_out_host,
                                      float *weights_out_host);
 
+/* The same without the final wait: the copies and kernels are queued on the handle's internal stream and the call
+ * returns; dsmoe_host_synchronize waits for everything queued on that stream. The host buffers must be page-locked and
+ * stay untouched until then, and a handle takes one such call at a time (its staging buffers are per handle). Two
+ * handles used in turn overlap one chunk's copies with the other's kernels. No counterpart in the reference, which
+ * keeps its activations on the device. */
+DSMOE_API int dsmoe_moe_forward_host_async(dsmoe_handle *h, uint32_t layer, const float *x_host,
+                                           const float *logits_host, uint32_t n_tokens, float *out_host,
+                                           int32_t *selected_out_host, float *weights_out_host);
+DSMOE_API int dsmoe_host_synchronize(dsmoe_handle *h);
+
 /* ------------------------------------------------------------------------------------------------------------ */
 /* For callers that cannot allocate device memory                                                                 */
 /* ------------------------------------------------------------------------------------------------------------ */

@@ -413,6 +413,19 @@ def test_moe_forward_layer(torch_cuda, oracle, layout, T):
     oh = torch.zeros((T, 4096), dtype=torch.float32).pin_memory()
     Kl.moe_forward_host(0, xh, lh, T, oh)
     assert np.array_equal(oh.numpy(), out.cpu().numpy())
+    # the queued form on two handles in turn (copies of one overlap kernels of the other): same results
+    K2 = MoeKernels(device=0, n_expert=n_e, max_tokens=8)
+    K2.layer_register(0, layer.gate, layer.up, layer.down, layer.layout)
+    outs = [torch.zeros((T, 4096), dtype=torch.float32).pin_memory() for _ in range(4)]
+    for i, o in enumerate(outs):
+        hnd = (Kl, K2)[i % 2]
+        hnd.host_synchronize()
+        hnd.moe_forward_host_async(0, xh, lh, T, o)
+    Kl.host_synchronize()
+    K2.host_synchronize()
+    for o in outs:
+        assert np.array_equal(o.numpy(), out.cpu().numpy())
+    K2.close()
     # bounds and state errors come back as statuses, not crashes
     from deepseek_rs_b200.kernels import DsmoeError
     with pytest.raises(DsmoeError):
