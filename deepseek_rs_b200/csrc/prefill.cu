@@ -154,47 +154,52 @@ __global__ void __launch_bounds__(256) pf_gather_kernel(const uint8_t *__restric
                                                          float *__restrict__ S, __half *__restrict__ BS, uint32_t r_cap)
 {
     const uint32_t n_tiles = plan[0];
-    // one warp per (tile, padded row, Q8_K block); lane l converts elements 8l..8l+7 of the block
-    const uint32_t lane = threadIdx.x & 31;
+    // one warp per (tile, group of 8 padded rows, Q8_K block): lane = (row of the group r8, quarter q); in round j the
+    // lane converts elements 8c..8c+7, c = q + 4j, so that the eight rows' pieces of one core matrix (128 contiguous
+    // bytes of the operand tile) leave the warp together
+    const uint32_t lane = threadIdx.x & 31, r8 = lane & 7, q = lane >> 3;
     for (uint32_t t = blockIdx.y; t < n_tiles; t += gridDim.y) {
         const uint32_t rows = tile_rows[t], rows16 = (rows + 15u) & ~15u, boff = tile_boff[t], start = tile_start[t];
-        const uint32_t units = rows16 * kblocks;
+        const uint32_t units = (rows16 >> 3) * kblocks;
+        const size_t tile_base = (size_t)boff * kblocks * 512;
         for (uint32_t u = blockIdx.x * 8 + (threadIdx.x >> 5); u < units; u += gridDim.x * 8) {
-            const uint32_t r = u / kblocks, kb = u - r * kblocks;
-            uint32_t w0 = 0, w1 = 0;
-            float d = 0.0f;
-            uint32_t bsum = 0;
-            if (r < rows) {
-                const uint8_t *blk = q8k + ((size_t)(sorted[start + r] / div_k) * kblocks + kb) * Q8K_BYTES;
-                const uint32_t *qs = reinterpret_cast<const uint32_t *>(blk + 4);
-                w0 = qs[2 * lane];
-                w1 = qs[2 * lane + 1];
-                d = *reinterpret_cast<const float *>(blk);
-                if (lane < 16) bsum = reinterpret_cast<const uint16_t *>(blk + 260)[lane];
-            }
-            // int8 -> f16 exactly: byte ^ 0x80 is the value + 128; 0x6400 | b is 1024 + b as f16
-            w0 ^= 0x80808080u;
-            w1 ^= 0x80808080u;
+            const uint32_t g8 = u / kblocks, kb = u - g8 * kblocks, r = 8 * g8 + r8;
+            const bool valid = r < rows;
+            const uint8_t *blk = valid ? q8k + ((size_t)(sorted[start + r] / div_k) * kblocks + kb) * Q8K_BYTES : q8k;
+            const uint32_t *qs = reinterpret_cast<const uint32_t *>(blk + 4);
             const __half2 off = __floats2half2_rn(1152.0f, 1152.0f);
-            uint32_t h[4] = {__byte_perm(w0, 0x64646464u, 0x4140u), __byte_perm(w0, 0x64646464u, 0x4342u),
-                             __byte_perm(w1, 0x64646464u, 0x4140u), __byte_perm(w1, 0x64646464u, 0x4342u)};
-            uint4 o;
-            uint32_t *op = reinterpret_cast<uint32_t *>(&o);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                __half2 v = __hsub2(*reinterpret_cast<__half2 *>(&h[i]), off);
-                op[i] = *reinterpret_cast<uint32_t *>(&v);
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t c = q + 4 * j;
+                uint32_t w0 = valid ? qs[2 * c] : 0u, w1 = valid ? qs[2 * c + 1] : 0u;
+                // int8 -> f16 exactly: byte ^ 0x80 is the value + 128; 0x6400 | b is 1024 + b as f16
+                w0 ^= 0x80808080u;
+                w1 ^= 0x80808080u;
+                uint32_t h[4] = {__byte_perm(w0, 0x64646464u, 0x4140u), __byte_perm(w0, 0x64646464u, 0x4342u),
+                                 __byte_perm(w1, 0x64646464u, 0x4140u), __byte_perm(w1, 0x64646464u, 0x4342u)};
+                uint4 o;
+                uint32_t *op = reinterpret_cast<uint32_t *>(&o);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    __half2 v = __hsub2(*reinterpret_cast<__half2 *>(&h[i]), off);
+                    op[i] = *reinterpret_cast<uint32_t *>(&v);
+                }
+                // element k = 256 kb + 8 c: stage 2 kb + c / 16, core column c % 16
+                const size_t off_b = tile_base + (size_t)(2 * kb + (c >> 4)) * rows16 * 256 + (size_t)g8 * PF_SBO + (c & 15) * 128 +
+                                     r8 * 16;
+                *reinterpret_cast<uint4 *>(B + off_b) = o;
             }
-            // element k = 256 kb + 8 lane: stage 2 kb + lane / 16, core column lane % 16
-            const size_t tile_base = (size_t)boff * kblocks * 512;
-            const size_t off_b = tile_base + (size_t)(2 * kb + (lane >> 4)) * rows16 * 256 + (size_t)(r >> 3) * PF_SBO +
-                                 (lane & 15) * 128 + (r & 7) * 16;
-            *reinterpret_cast<uint4 *>(B + off_b) = o;
-            if (lane == 0) S[(size_t)kb * r_cap + boff + r] = d;
-            if (BS && lane < 16) {
+            if (q == 0) S[(size_t)kb * r_cap + boff + r] = valid ? *reinterpret_cast<const float *>(blk) : 0.0f;
+            if (BS) {  // bsums 4q .. 4q+3 of the row, as f16, in core-matrix order [row / 8][j / 8][row % 8][j % 8]
+                const uint32_t *bp = reinterpret_cast<const uint32_t *>(blk + 260);  // 4-byte aligned, not 8
+                const uint2 raw = valid ? make_uint2(bp[2 * q], bp[2 * q + 1]) : make_uint2(0u, 0u);
+                const __half2 lo = __halves2half2(__short2half_rn((short)(raw.x & 0xFFFFu)), __short2half_rn((short)(raw.x >> 16)));
+                const __half2 hi = __halves2half2(__short2half_rn((short)(raw.y & 0xFFFFu)), __short2half_rn((short)(raw.y >> 16)));
                 const size_t bs_tile = ((size_t)kb * r_cap + boff) * 16;
-                BS[bs_tile + (size_t)(r >> 3) * 128 + (lane >> 3) * 64 + (r & 7) * 8 + (lane & 7)] =
-                    __short2half_rn((short)(int16_t)(uint16_t)bsum);
+                uint2 out2;
+                out2.x = *reinterpret_cast<const uint32_t *>(&lo);
+                out2.y = *reinterpret_cast<const uint32_t *>(&hi);
+                *reinterpret_cast<uint2 *>(BS + bs_tile + (size_t)g8 * 128 + (q >> 1) * 64 + r8 * 8 + (q & 1) * 4) = out2;
             }
         }
     }
