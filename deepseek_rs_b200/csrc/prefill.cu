@@ -80,21 +80,37 @@ __global__ void __launch_bounds__(256) pf_count_kernel(const int32_t *__restrict
 }
 
 // offsets (exclusive prefix of counts) and the tile list: expert e contributes ceil(count / PF_TN) tiles.
-// plan[0] = n_tiles, plan[1] = total padded rows. One thread: 256 experts.
-__global__ void pf_plan_kernel(const uint32_t *__restrict__ counts, int n_expert, uint32_t *__restrict__ offsets,
-                               uint32_t *__restrict__ tile_expert, uint32_t *__restrict__ tile_start,
-                               uint32_t *__restrict__ tile_rows, uint32_t *__restrict__ tile_boff,
-                               uint32_t *__restrict__ plan)
+// plan[0] = n_tiles, plan[1] = total padded rows. One warp: lane l owns a run of consecutive experts; three warp scans
+// (pairs, tiles, padded rows) give each lane the bases its experts' entries start from.
+__global__ void __launch_bounds__(32) pf_plan_kernel(const uint32_t *__restrict__ counts, int n_expert,
+                                                      uint32_t *__restrict__ offsets, uint32_t *__restrict__ tile_expert,
+                                                      uint32_t *__restrict__ tile_start, uint32_t *__restrict__ tile_rows,
+                                                      uint32_t *__restrict__ tile_boff, uint32_t *__restrict__ plan)
 {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
-    uint32_t sum = 0, nt = 0, boff = 0;
-    for (int e = 0; e < n_expert; ++e) {
+    if (blockIdx.x != 0) return;
+    const int lane = threadIdx.x, per = (n_expert + 31) / 32, e0 = lane * per, e1 = min(n_expert, e0 + per);
+    uint32_t pairs = 0, tiles = 0, padded = 0;
+    for (int e = e0; e < e1; ++e) {
+        const uint32_t c = counts[e];
+        pairs += c;
+        tiles += (c + PF_TN - 1) / PF_TN;
+        const uint32_t tail = c % PF_TN;
+        padded += (c / PF_TN) * PF_TN + ((tail + 15u) & ~15u);
+    }
+    uint32_t sp = pairs, st = tiles, sb = padded;  // inclusive scans
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t a = __shfl_up_sync(FULL, sp, d), b = __shfl_up_sync(FULL, st, d), c = __shfl_up_sync(FULL, sb, d);
+        if (lane >= d) sp += a, st += b, sb += c;
+    }
+    uint32_t sum = sp - pairs, nt = st - tiles, boff = sb - padded;
+    for (int e = e0; e < e1; ++e) {
         offsets[e] = sum;
         const uint32_t c = counts[e];
-        for (uint32_t s = 0; s < c; s += PF_TN) {
-            const uint32_t rows = min((uint32_t)PF_TN, c - s);
+        for (uint32_t s0 = 0; s0 < c; s0 += PF_TN) {
+            const uint32_t rows = min((uint32_t)PF_TN, c - s0);
             tile_expert[nt] = (uint32_t)e;
-            tile_start[nt] = sum + s;
+            tile_start[nt] = sum + s0;
             tile_rows[nt] = rows;
             tile_boff[nt] = boff;
             boff += (rows + 15u) & ~15u;
@@ -102,38 +118,39 @@ __global__ void pf_plan_kernel(const uint32_t *__restrict__ counts, int n_expert
         }
         sum += c;
     }
-    offsets[n_expert] = sum;
-    tile_boff[nt] = boff;
-    plan[0] = nt;
-    plan[1] = boff;
+    if (lane == 31) {
+        offsets[n_expert] = sp;
+        tile_boff[st] = sb;
+        plan[0] = st;
+        plan[1] = sb;
+    }
 }
 
-// sorted[offsets[e] + rank] = pair, rank = number of earlier pairs of the same expert. One CTA per expert.
+// sorted[offsets[e] + rank] = pair, rank = number of earlier pairs of the same expert. One CTA per expert; warp w
+// owns the w-th contiguous eighth of the pairs: a first pass counts its hits, a prefix over the eight counts gives its
+// base, a second pass places them (ballot ranks inside the warp, running count across its rounds).
 __global__ void __launch_bounds__(256) pf_place_kernel(const int32_t *__restrict__ selected, uint32_t n_pairs,
                                                         const uint32_t *__restrict__ offsets,
                                                         uint32_t *__restrict__ sorted)
 {
     __shared__ uint32_t s_warp[8];
-    __shared__ uint32_t s_base;
     const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (threadIdx.x == 0) s_base = offsets[e];
+    const uint32_t seg = ((n_pairs + 7) / 8 + 31) & ~31u, p_lo = min(n_pairs, warp * seg), p_hi = min(n_pairs, p_lo + seg);
+    uint32_t cnt = 0;
+    for (uint32_t p0 = p_lo; p0 < p_hi; p0 += 32) {
+        const uint32_t p = p0 + lane;
+        cnt += __popc(__ballot_sync(FULL, p < p_hi && pf_expert_of(selected, p) == e));
+    }
+    if (lane == 0) s_warp[warp] = cnt;
     __syncthreads();
-    for (uint32_t p0 = 0; p0 < n_pairs; p0 += 256) {
-        const uint32_t p = p0 + threadIdx.x;
-        const bool hit = p < n_pairs && pf_expert_of(selected, p) == e;
+    uint32_t base = offsets[e];
+    for (int w = 0; w < warp; ++w) base += s_warp[w];
+    for (uint32_t p0 = p_lo; p0 < p_hi; p0 += 32) {
+        const uint32_t p = p0 + lane;
+        const bool hit = p < p_hi && pf_expert_of(selected, p) == e;
         const uint32_t ballot = __ballot_sync(FULL, hit);
-        if (lane == 0) s_warp[warp] = __popc(ballot);
-        __syncthreads();
-        uint32_t before = 0, total = 0;
-#pragma unroll
-        for (int w = 0; w < 8; ++w) {
-            before += w < warp ? s_warp[w] : 0u;
-            total += s_warp[w];
-        }
-        if (hit) sorted[s_base + before + __popc(ballot & ((1u << lane) - 1u))] = p;
-        __syncthreads();
-        if (threadIdx.x == 0) s_base += total;
-        __syncthreads();
+        if (hit) sorted[base + __popc(ballot & ((1u << lane) - 1u))] = p;
+        base += __popc(ballot);
     }
 }
 
