@@ -119,28 +119,10 @@ class ClockSampler:
 
 
 def gen_layer_gpu(torch, device, seed: int, n_expert: int = 0):
-    """One layer's expert tensors generated on the device: uniform bytes give uniform codebook / sign / scale /
-    quant fields; the f16 scales are |N(0,1)| * 1e-3."""
-    g = torch.Generator(device=device)
-    g.manual_seed(seed)
+    """One layer's expert tensors generated on the device (see formats.random_layer_device)."""
+    from deepseek_rs_b200.formats import random_layer_device
 
-    def scales(n):
-        return (torch.randn(n, device=device, generator=g).abs() * 1e-3).to(torch.float16).view(torch.uint8).view(n, 2)
-
-    def iq2(n):
-        t = torch.randint(0, 256, (n, 66), dtype=torch.uint8, device=device, generator=g)
-        t[:, 0:2] = scales(n)
-        return t.view(-1)
-
-    def q2k(n):
-        t = torch.randint(0, 256, (n, 84), dtype=torch.uint8, device=device, generator=g)
-        t[:, 80:82] = scales(n)
-        t[:, 82:84] = scales(n)
-        return t.view(-1)
-
-    ne = n_expert or N_EXPERT
-    nb_gate, nb_down = ne * N_FF * (N_EMBD // 256), ne * N_EMBD * (N_FF // 256)
-    return iq2(nb_gate), iq2(nb_gate), q2k(nb_down)
+    return random_layer_device(torch, device, seed, n_expert or N_EXPERT, N_EMBD, N_FF)
 
 
 def run_reference(args, rank: int, world: int):

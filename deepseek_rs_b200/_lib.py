@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(HERE, "libdsmoe.so")
 OK = 0
 ERR_ARG, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_BOUNDS, ERR_NOMEM, ERR_STATE = -1, -2, -3, -4, -5, -6, -7
 LAYOUT_NATIVE, LAYOUT_ROWSOA = 0, 1
+DEBUG_WAIT_LIMIT_KCLOCKS, DEBUG_DROP_ONE_COPY, DEBUG_CLEAR_STATUS = 1, 2, 3
 
 
 class Config(C.Structure):
@@ -59,6 +60,8 @@ SIGNATURES = {
     "dsmoe_moe_forward_host_async": (_int, [_vp, _u32, _vp, _vp, _u32, _vp, _vp, _vp]),
     "dsmoe_host_synchronize": (_int, [_vp]),
     "dsmoe_moe_forward_noalloc": (_int, [_vp, _vp, _vp, _vp, _int, _vp, _vp, _u32, _vp, _vp, _vp]),
+    "dsmoe_noalloc_device_status": (_int, [_vp, _vp]),
+    "dsmoe_debug_set": (_int, [_vp, _int, _int]),
 }
 
 _lib = None

@@ -5,6 +5,7 @@
 #include <cstring>
 #include <new>
 
+#include "async.cuh"
 #include "common.cuh"
 #include "launch.h"
 
@@ -29,7 +30,7 @@ struct dsmoe_handle {
     // staging for the host-buffer call
     cudaStream_t hstream;
     float *d_x, *d_logits, *d_out;
-    int *d_status;  // device status word: 0, or the first device-side error code (a bounded wait that expired)
+    int *d_status;  // device status block (STATUS_WORDS ints, async.cuh): [0] first device-side error code, [1] wait limit
     bool use_tma;   // stage packed rows with bulk asynchronous copies where the shapes allow (default on)
     // batched (tcgen05 grouped GEMM) path: used by the tier-2 call from prefill_min_tokens tokens upwards (default:
     // 4.5 pairs per expert; DSMOE_PREFILL_MIN_TOKENS overrides)
@@ -67,6 +68,10 @@ int check_launch(dsmoe_handle *h, const char *what, int n_launched)
 
 bool aligned(const void *p, size_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
 
+// A handle's pointers and streams belong to its device: a call made while another device is current would launch
+// there with this device's pointers. Such calls are refused.
+int check_device(const dsmoe_handle *h);
+
 int check_layout(const dsmoe_handle *h, int layout)
 {
     if (layout != DSMOE_LAYOUT_NATIVE && layout != DSMOE_LAYOUT_ROWSOA)
@@ -81,10 +86,25 @@ cudaError_t dev_alloc(T **p, size_t n)
     return n ? cudaMalloc((void **)p, n * sizeof(T)) : cudaSuccess;
 }
 
+#define DSMOE_ENTER(h)                              \
+    do {                                            \
+        if (!(h)) return DSMOE_ERR_ARG;             \
+        if (int rc_ = check_device(h)) return rc_;  \
+    } while (0)
+
 #define DSMOE_REQUIRE(h, cond, ...) \
     do {                            \
         if (!(cond)) return fail((h), DSMOE_ERR_ARG, __VA_ARGS__); \
     } while (0)
+
+int check_device(const dsmoe_handle *h)
+{
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess) return fail(h, DSMOE_ERR_CUDA, "cudaGetDevice failed");
+    if (cur != h->device)
+        return fail(h, DSMOE_ERR_STATE, "the handle belongs to device %d but device %d is current", h->device, cur);
+    return DSMOE_OK;
+}
 
 }  // namespace
 
@@ -120,7 +140,13 @@ int dsmoe_create(const dsmoe_config *cfg, int device, dsmoe_handle **out)
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return DSMOE_ERR_CUDA;
     if (prop.major != 10) return DSMOE_ERR_CUDA;  // the kernels are sm_100a machine code only
+    int caller_device = -1;
+    cudaGetDevice(&caller_device);
     if (cudaSetDevice(device) != cudaSuccess) return DSMOE_ERR_CUDA;
+    struct RestoreDevice {  // the caller's current device is put back on every way out
+        int d;
+        ~RestoreDevice() { if (d >= 0) cudaSetDevice(d); }
+    } restore{caller_device};
 
     dsmoe_handle *h = new (std::nothrow) dsmoe_handle();
     if (!h) return DSMOE_ERR_NOMEM;
@@ -142,6 +168,7 @@ int dsmoe_create(const dsmoe_config *cfg, int device, dsmoe_handle **out)
     ok = ok && dev_alloc(&h->d_out, T * cfg->n_embd) == cudaSuccess;
     {
         h->sh_chunk = cfg->max_tokens < 1024u ? cfg->max_tokens : 1024u;
+        if (h->sh_chunk == 0) h->sh_chunk = 1;  // a handle for the tier-1 calls only may be created with max_tokens 0
         const size_t C = h->sh_chunk, wide = cfg->n_embd > cfg->n_ff ? cfg->n_embd : cfg->n_ff;
         ok = ok && dev_alloc(&h->sh_xq, C * wide) == cudaSuccess;
         ok = ok && dev_alloc(&h->sh_xscale, C * ((wide + 31) / 32)) == cudaSuccess;
@@ -150,7 +177,8 @@ int dsmoe_create(const dsmoe_config *cfg, int device, dsmoe_handle **out)
         ok = ok && dev_alloc(&h->sh_mid, C * cfg->n_ff) == cudaSuccess;
     }
     ok = ok && cudaStreamCreateWithFlags(&h->hstream, cudaStreamNonBlocking) == cudaSuccess;
-    ok = ok && dev_alloc(&h->d_status, 1) == cudaSuccess && cudaMemset(h->d_status, 0, sizeof(int)) == cudaSuccess;
+    ok = ok && dev_alloc(&h->d_status, STATUS_WORDS) == cudaSuccess &&
+         cudaMemset(h->d_status, 0, STATUS_WORDS * sizeof(int)) == cudaSuccess;
     {
         const size_t pf_bytes = prefill_scratch_bytes(cfg->max_tokens, cfg->n_expert_used, cfg->n_expert, cfg->n_embd,
                                                       cfg->n_ff, &h->pf_lay);
@@ -176,6 +204,8 @@ int dsmoe_create(const dsmoe_config *cfg, int device, dsmoe_handle **out)
 int dsmoe_destroy(dsmoe_handle *h)
 {
     if (!h) return DSMOE_OK;
+    int caller_device = -1;
+    cudaGetDevice(&caller_device);
     cudaSetDevice(h->device);
     if (h->hstream) cudaStreamDestroy(h->hstream);
     cudaFree(h->probs);
@@ -196,6 +226,7 @@ int dsmoe_destroy(dsmoe_handle *h)
     cudaFree(h->sh_mid);
     delete[] h->layers;
     delete h;
+    if (caller_device >= 0) cudaSetDevice(caller_device);
     return DSMOE_OK;
 }
 
@@ -203,7 +234,7 @@ const char *dsmoe_last_error(const dsmoe_handle *h) { return h ? h->err : "null 
 
 int dsmoe_set_phase_events(dsmoe_handle *h, void **events, int n_events)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     if (!events || n_events == 0) {
         h->phase_events_set = false;
         return DSMOE_OK;
@@ -217,6 +248,7 @@ int dsmoe_set_phase_events(dsmoe_handle *h, void **events, int n_events)
 int dsmoe_device_status(dsmoe_handle *h, dsmoe_stream stream, int *code_out)
 {
     if (!h || !code_out) return DSMOE_ERR_ARG;
+    if (int rc = check_device(h)) return rc;
     cudaError_t e = cudaMemcpyAsync(code_out, h->d_status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
     if (e != cudaSuccess) return fail(h, DSMOE_ERR_CUDA, "device_status: %s", cudaGetErrorString(e));
@@ -225,6 +257,20 @@ int dsmoe_device_status(dsmoe_handle *h, dsmoe_stream stream, int *code_out)
 }
 uint64_t dsmoe_launch_count(const dsmoe_handle *h) { return h ? h->launches : 0; }
 
+int dsmoe_debug_set(dsmoe_handle *h, int what, int value)
+{
+    DSMOE_ENTER(h);
+    DSMOE_REQUIRE(h, what == DSMOE_DEBUG_WAIT_LIMIT_KCLOCKS || what == DSMOE_DEBUG_DROP_ONE_COPY || what == DSMOE_DEBUG_CLEAR_STATUS,
+                  "debug_set: unknown item %d", what);
+    DSMOE_REQUIRE(h, value >= 0, "debug_set: negative value");
+    const int word = what == DSMOE_DEBUG_WAIT_LIMIT_KCLOCKS ? 1 : what == DSMOE_DEBUG_DROP_ONE_COPY ? 2 : 0;
+    if (what == DSMOE_DEBUG_CLEAR_STATUS) value = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess ||
+        cudaMemcpy(h->d_status + word, &value, sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess)
+        return fail(h, DSMOE_ERR_CUDA, "debug_set: %s", cudaGetErrorString(cudaGetLastError()));
+    return DSMOE_OK;
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // tier 1
 // ---------------------------------------------------------------------------------------------------------------
@@ -232,7 +278,7 @@ uint64_t dsmoe_launch_count(const dsmoe_handle *h) { return h ? h->launches : 0;
 int dsmoe_q8k_quantize(dsmoe_handle *h, dsmoe_stream stream, const float *x, uint8_t *out, uint32_t in_dim,
                        uint32_t n_rows)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     DSMOE_REQUIRE(h, in_dim % QK_K == 0, "q8k_quantize: in_dim %u is not a multiple of 256", in_dim);
     if (n_rows == 0 || in_dim == 0) return DSMOE_OK;
     DSMOE_REQUIRE(h, x && out, "q8k_quantize: null pointer");
@@ -246,7 +292,7 @@ int dsmoe_router_select(dsmoe_handle *h, dsmoe_stream stream, const float *logit
                         int32_t token_scalar, uint32_t hash_rows, uint32_t n_tokens, uint32_t has_bias,
                         uint32_t hash_mode)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     if (n_tokens == 0) return DSMOE_OK;
     DSMOE_REQUIRE(h, logits && probs && selected && weights, "router_select: null pointer");
     DSMOE_REQUIRE(h, !has_bias || bias, "router_select: has_bias set but bias is null");
@@ -262,7 +308,7 @@ int dsmoe_gate_up_mid(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *gate_
                       float *mid_out, uint64_t gate_expert_bytes, uint64_t gate_row_bytes, uint32_t xq_blocks,
                       uint32_t expert_mid_dim, uint32_t n_expert_used, uint32_t n_tokens, float clamp, int layout)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     if (int rc = check_layout(h, layout)) return rc;
     if (n_tokens == 0 || expert_mid_dim == 0) return DSMOE_OK;
     DSMOE_REQUIRE(h, gate_base && up_base && xq && selected && weights && mid_out, "gate_up_mid: null pointer");
@@ -286,7 +332,7 @@ static int down_common(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *down
                        uint32_t midq_blocks, uint32_t out_dim, uint32_t n_expert_used, uint32_t n_tokens, int layout,
                        int sum_slots)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     if (int rc = check_layout(h, layout)) return rc;
     if (n_tokens == 0 || out_dim == 0) return DSMOE_OK;
     DSMOE_REQUIRE(h, down_base && midq && selected && out, "down: null pointer");
@@ -322,7 +368,7 @@ int dsmoe_down_sum(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *down_bas
 int dsmoe_moe_sum(dsmoe_handle *h, dsmoe_stream stream, const float *down, float *out, uint32_t out_dim,
                   uint32_t n_expert_used, uint32_t n_tokens)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     if (n_tokens == 0 || out_dim == 0) return DSMOE_OK;
     DSMOE_REQUIRE(h, down && out, "moe_sum: null pointer");
     launch_moe_sum((cudaStream_t)stream, down, nullptr, out, out_dim, n_expert_used, n_tokens);
@@ -332,7 +378,7 @@ int dsmoe_moe_sum(dsmoe_handle *h, dsmoe_stream stream, const float *down, float
 int dsmoe_moe_sum_indexed(dsmoe_handle *h, dsmoe_stream stream, const float *rows, const int32_t *pos, float *out,
                           uint32_t out_dim, uint32_t n_expert_used, uint32_t n_tokens)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     if (n_tokens == 0 || out_dim == 0) return DSMOE_OK;
     DSMOE_REQUIRE(h, rows && pos && out, "moe_sum_indexed: null pointer");
     launch_moe_sum((cudaStream_t)stream, rows, pos, out, out_dim, n_expert_used, n_tokens);
@@ -342,7 +388,7 @@ int dsmoe_moe_sum_indexed(dsmoe_handle *h, dsmoe_stream stream, const float *row
 int dsmoe_quantize_q8_0(dsmoe_handle *h, dsmoe_stream stream, const float *x, int8_t *xq, float *xscale, uint64_t in_dim,
                         uint64_t n_tokens)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     if (n_tokens == 0 || in_dim == 0) return DSMOE_OK;
     DSMOE_REQUIRE(h, x && xq && xscale, "quantize_q8_0: null pointer");
     launch_quantize_q8_0((cudaStream_t)stream, x, xq, xscale, in_dim, n_tokens);
@@ -352,7 +398,7 @@ int dsmoe_quantize_q8_0(dsmoe_handle *h, dsmoe_stream stream, const float *x, in
 int dsmoe_matmul_q8_0(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *w, const int8_t *xq, const float *xscale,
                       float *out, uint64_t in_dim, uint64_t out_dim, uint64_t n_tokens)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     if (n_tokens == 0 || out_dim == 0) return DSMOE_OK;
     DSMOE_REQUIRE(h, w && xq && xscale && out, "matmul_q8_0: null pointer");
     DSMOE_REQUIRE(h, ((uintptr_t)w & 3) == 0 && ((uintptr_t)xq & 15) == 0, "matmul_q8_0: w needs 4-byte, xq 16-byte alignment");
@@ -363,7 +409,7 @@ int dsmoe_matmul_q8_0(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *w, co
 int dsmoe_swiglu(dsmoe_handle *h, dsmoe_stream stream, const float *gate, const float *up, float *out, uint64_t n,
                  float clamp, float weight)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     if (n == 0) return DSMOE_OK;
     DSMOE_REQUIRE(h, gate && up && out, "swiglu: null pointer");
     launch_swiglu((cudaStream_t)stream, gate, up, out, n, clamp, weight);
@@ -373,7 +419,7 @@ int dsmoe_swiglu(dsmoe_handle *h, dsmoe_stream stream, const float *gate, const 
 int dsmoe_matmul_f16(dsmoe_handle *h, dsmoe_stream stream, const uint16_t *w, const float *x, float *out, uint64_t in_dim,
                      uint64_t out_dim, uint64_t n_tokens)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     if (n_tokens == 0 || out_dim == 0) return DSMOE_OK;
     DSMOE_REQUIRE(h, w && x && out, "matmul_f16: null pointer");
     DSMOE_REQUIRE(h, n_tokens <= 65535, "matmul_f16: at most 65535 tokens per call");
@@ -384,7 +430,7 @@ int dsmoe_matmul_f16(dsmoe_handle *h, dsmoe_stream stream, const uint16_t *w, co
 int dsmoe_shared_expert(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *gate_w, const uint8_t *up_w,
                         const uint8_t *down_w, const float *x, uint32_t n_tokens, float *out)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     if (n_tokens == 0) return DSMOE_OK;
     DSMOE_REQUIRE(h, gate_w && up_w && down_w && x && out, "shared_expert: null pointer");
     DSMOE_REQUIRE(h, (((uintptr_t)gate_w | (uintptr_t)up_w | (uintptr_t)down_w) & 3) == 0, "shared_expert: weights need 4-byte alignment");
@@ -411,7 +457,7 @@ int dsmoe_shared_expert(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *gat
 
 int dsmoe_dequant_iq2xxs(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *blocks, uint64_t n_blocks, float *out)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     if (n_blocks == 0) return DSMOE_OK;
     DSMOE_REQUIRE(h, blocks && out && aligned(blocks, 2), "dequant_iq2xxs: null or misaligned pointer");
     launch_dequant_iq2xxs((cudaStream_t)stream, blocks, n_blocks, out, (int)h->cfg.f16_ieee);
@@ -420,7 +466,7 @@ int dsmoe_dequant_iq2xxs(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *bl
 
 int dsmoe_dequant_q2k(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *blocks, uint64_t n_blocks, float *out)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     if (n_blocks == 0) return DSMOE_OK;
     DSMOE_REQUIRE(h, blocks && out && aligned(blocks, 2), "dequant_q2k: null or misaligned pointer");
     launch_dequant_q2k((cudaStream_t)stream, blocks, n_blocks, out, (int)h->cfg.f16_ieee);
@@ -430,7 +476,7 @@ int dsmoe_dequant_q2k(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *block
 int dsmoe_relayout_iq2xxs(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *src, uint8_t *dst, uint64_t n_rows,
                           uint32_t blocks_per_row, int inverse)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     if (n_rows == 0 || blocks_per_row == 0) return DSMOE_OK;
     DSMOE_REQUIRE(h, src && dst && src != dst && aligned(src, 2) && aligned(dst, 2),
                   "relayout_iq2xxs: null, aliased or misaligned pointer");
@@ -441,7 +487,7 @@ int dsmoe_relayout_iq2xxs(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *s
 int dsmoe_relayout_q2k(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *src, uint8_t *dst, uint64_t n_rows,
                        uint32_t blocks_per_row, int inverse)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     if (n_rows == 0 || blocks_per_row == 0) return DSMOE_OK;
     DSMOE_REQUIRE(h, src && dst && src != dst && aligned(src, 4) && aligned(dst, 4),
                   "relayout_q2k: null, aliased or misaligned pointer");
@@ -456,7 +502,7 @@ int dsmoe_relayout_q2k(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *src,
 int dsmoe_fp8_quantize(dsmoe_handle *h, dsmoe_stream stream, const float *x, uint8_t *codes, float *scales,
                        uint32_t rows, uint32_t cols, int rows_per_block)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     DSMOE_REQUIRE(h, rows_per_block == 1 || rows_per_block == 128, "fp8_quantize: rows_per_block must be 1 or 128");
     DSMOE_REQUIRE(h, cols % 128 == 0, "fp8_quantize: cols %u is not a multiple of 128", cols);
     if (rows == 0 || cols == 0) return DSMOE_OK;
@@ -468,7 +514,7 @@ int dsmoe_fp8_quantize(dsmoe_handle *h, dsmoe_stream stream, const float *x, uin
 int dsmoe_fp8_linear(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *a_fp8, const float *a_scale,
                      const uint8_t *w_fp8, const float *w_scale, void *out_bf16, uint32_t M, uint32_t N, uint32_t K)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     DSMOE_REQUIRE(h, K % 128 == 0 && N % 128 == 0 && K > 0, "fp8_linear: N %u and K %u must be multiples of 128", N, K);
     if (M == 0 || N == 0) return DSMOE_OK;
     DSMOE_REQUIRE(h, a_fp8 && a_scale && w_fp8 && w_scale && out_bf16, "fp8_linear: null pointer");
@@ -484,7 +530,7 @@ int dsmoe_fp8_linear(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *a_fp8,
 int dsmoe_layer_register(dsmoe_handle *h, uint32_t layer, const uint8_t *gate, const uint8_t *up, const uint8_t *down,
                          int layout)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     if (int rc = check_layout(h, layout)) return rc;
     const uint32_t L = h->cfg.max_layers ? h->cfg.max_layers : 1;
     DSMOE_REQUIRE(h, layer < L, "layer_register: layer %u beyond max_layers %u", layer, L);
@@ -515,17 +561,21 @@ static int expert_ffn_impl(dsmoe_handle *h, cudaStream_t st, const dsmoe_layer_s
                     (uint64_t)xb * IQ2XXS_BYTES, xb, c.n_ff, k, n_tokens, c.swiglu_clamp, ly.layout, (int)c.f16_ieee};
     n += ((h->use_tma && gate_up_tma_eligible(g)) ? launch_gate_up_mid_tma(st, g, h->d_status)
                                                   : launch_gate_up_mid(st, g));
+    if (int rc = check_launch(h, what, n)) return rc;
+    n = 1;
     launch_q8k_quantize(st, h->mid, h->midq, c.n_ff, n_tokens * k);
+    if (int rc = check_launch(h, what, n)) return rc;
+    n = 0;
     DownArgs d = {ly.down, h->midq, sel, out, (uint64_t)c.n_embd * mb * Q2K_BYTES, (uint64_t)mb * Q2K_BYTES, mb,
                   c.n_embd, k, n_tokens, ly.layout, (int)c.f16_ieee, 1};
-    n += 1 + ((h->use_tma && down_tma_eligible(d)) ? launch_down_tma(st, d, h->d_status) : launch_down(st, d));
+    n += ((h->use_tma && down_tma_eligible(d)) ? launch_down_tma(st, d, h->d_status) : launch_down(st, d));
     return check_launch(h, what, n);
 }
 
 int dsmoe_moe_forward(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, const float *x, const float *logits,
                       uint32_t n_tokens, float *out, int32_t *selected_out, float *weights_out)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     const dsmoe_config &c = h->cfg;
     const uint32_t L = c.max_layers ? c.max_layers : 1;
     if (layer >= L || !h->layers[layer].set) return fail(h, DSMOE_ERR_STATE, "moe_forward: layer %u not registered", layer);
@@ -557,7 +607,7 @@ int dsmoe_moe_forward(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, cons
 int dsmoe_expert_ffn(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, const uint8_t *xq, const int32_t *selected,
                      const float *weights, uint32_t n_tokens, float *out)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     const dsmoe_config &c = h->cfg;
     const uint32_t L = c.max_layers ? c.max_layers : 1;
     if (layer >= L || !h->layers[layer].set) return fail(h, DSMOE_ERR_STATE, "expert_ffn: layer %u not registered", layer);
@@ -571,7 +621,7 @@ int dsmoe_expert_ffn(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, const
 
 int dsmoe_host_synchronize(dsmoe_handle *h)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     const cudaError_t e = cudaStreamSynchronize(h->hstream);
     if (e != cudaSuccess) return fail(h, DSMOE_ERR_CUDA, "host_synchronize: %s", cudaGetErrorString(e));
     return DSMOE_OK;
@@ -588,7 +638,7 @@ int dsmoe_moe_forward_host(dsmoe_handle *h, uint32_t layer, const float *x_host,
 int dsmoe_moe_forward_host_async(dsmoe_handle *h, uint32_t layer, const float *x_host, const float *logits_host,
                                  uint32_t n_tokens, float *out_host, int32_t *selected_out_host, float *weights_out_host)
 {
-    if (!h) return DSMOE_ERR_ARG;
+    DSMOE_ENTER(h);
     const dsmoe_config &c = h->cfg;
     if (n_tokens > c.max_tokens)
         return fail(h, DSMOE_ERR_BOUNDS, "moe_forward_host: n_tokens %u exceeds max_tokens %u", n_tokens, c.max_tokens);

@@ -86,14 +86,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
     return ok != 0;
 }
 
-// Waits for the given phase with a time limit (about two seconds of SM clocks). On expiry records
-// DEV_ERR_MBAR_TIMEOUT in *status (if it was still 0) and returns false; the caller stops using the buffer.
+// The status block every bounded-wait kernel receives: four ints in device memory.
+//   [0] first device-side error code (0 = none); kernels only ever change it from 0
+//   [1] wait limit in units of 1024 SM clocks; 0 = the default of about two seconds
+//   [2] test hook: non-zero makes down_m8_tma_kernel leave one of its copies out, so that a wait runs out
+//   [3] unused
+constexpr int STATUS_WORDS = 4;
+constexpr long long DEFAULT_WAIT_CLOCKS = 4000000000LL;
+
+// Waits for the given phase with a time limit (status[1], default about two seconds of SM clocks). On expiry records
+// DEV_ERR_MBAR_TIMEOUT in status[0] (if it was still 0) and returns false; the caller stops using the buffer.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int *status)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
+    long long limit = DEFAULT_WAIT_CLOCKS;
+    if (status) {
+        const int kclk = *reinterpret_cast<volatile int *>(status + 1);
+        if (kclk > 0) limit = (long long)kclk << 10;
+    }
     while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > 4000000000LL) {
+        if (clock64() - t0 > limit) {
             if (status) atomicCAS(status, 0, DEV_ERR_MBAR_TIMEOUT);
             return false;
         }

@@ -279,8 +279,11 @@ __global__ void __launch_bounds__(256, 2) down_m8_tma_kernel(const uint8_t *__re
         fence_async_smem();
         // everything is requested up front, four rows per mbarrier, so that the first rows can be consumed while
         // the later ones are still arriving
+        // test hook (status[2], normally 0): the second group of rows is never requested, so the wait for it runs out
+        const bool drop_one = status != nullptr && *reinterpret_cast<volatile int *>(status + 2) != 0;
         for (uint32_t s = 0; 4 * s < n_rows; ++s) {
             const uint32_t rows = min(4u, n_rows - 4 * s), bytes = rows * DN_ROW_BYTES + (s == 0 ? DN_ACT_BYTES : 0);
+            if (drop_one && s == 1) continue;
             mbar_expect_tx(&bars[s], bytes);
             if (s == 0) bulk_g2s(abuf, midq + (size_t)pair * DN_ACT_BYTES, DN_ACT_BYTES, &bars[0]);
             bulk_g2s(wbuf + 4 * s * DN_ROW_BYTES, src + (uint64_t)4 * s * DN_ROW_BYTES, rows * DN_ROW_BYTES, &bars[s]);
@@ -365,19 +368,6 @@ __global__ void __launch_bounds__(256, 2) down_m8_tma_kernel(const uint8_t *__re
 // launchers
 // ---------------------------------------------------------------------------------------------------------------
 
-static int g_sm_count = 0;
-
-static int sm_count()
-{
-    if (g_sm_count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (g_sm_count <= 0) g_sm_count = 148;
-    }
-    return g_sm_count;
-}
-
 bool gate_up_tma_eligible(const GateUpArgs &a)
 {
     return a.xq_blocks == 16 && a.row_bytes == (uint64_t)GU_ROW_BYTES && a.mid_dim % GU_ITEM_ROWS == 0 &&
@@ -388,7 +378,7 @@ template <int LAYOUT>
 static void launch_gu_tma(cudaStream_t st, const GateUpArgs &a, int *status)
 {
     const uint32_t n_items = a.n_tokens * a.k * (a.mid_dim / GU_ITEM_ROWS);
-    const int sms = sm_count();
+    const int sms = sm_count_current();
     // warps per CTA: as many as fit, unless a smaller count wastes clearly fewer warp-slots in the last round of items
     auto eff_of = [&](int w) {
         const uint32_t nw = (uint32_t)sms * w, chunk = (n_items + nw - 1) / nw;
@@ -398,12 +388,10 @@ static void launch_gu_tma(cudaStream_t st, const GateUpArgs &a, int *status)
     for (int w = GU_MAX_WARPS - 1; w >= 8; --w)
         if (eff_of(w) > eff_of(best_w) + 0.08) best_w = w;
     const size_t smem = GU_TABLE_BYTES + (size_t)best_w * GU_STAGES * GU_ITEM_BYTES + (size_t)best_w * GU_STAGES * 8;
-    static bool attr_set[2] = {false, false};
-    if (!attr_set[LAYOUT]) {
+    static OncePerDevice attr;  // one per template instance
+    if (attr.first())
         cudaFuncSetAttribute(gate_up_x16_tma_kernel<LAYOUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              GU_TABLE_BYTES + GU_MAX_WARPS * GU_STAGES * (GU_ITEM_BYTES + 8));
-        attr_set[LAYOUT] = true;
-    }
     const uint32_t want = (n_items + best_w - 1) / best_w;
     const uint32_t grid = want < (uint32_t)sms ? want : (uint32_t)sms;
     launch_pdl(gate_up_x16_tma_kernel<LAYOUT>, dim3(grid), dim3(32 * best_w), smem, st, a.gate_base, a.up_base, a.xq,
@@ -431,12 +419,10 @@ static void launch_dn_tma(cudaStream_t st, const DownArgs &a, int *status)
     // small batches: short chunks so that one wave of CTAs covers all rows; large batches: longer chunks
     const int rows_per_cta = 16;  // 256 CTAs per token at out_dim 4096: one wave at two CTAs per SM
     const size_t smem = (size_t)a.k * (rows_per_cta * DN_ROW_BYTES + DN_ACT_BYTES) + MAX_K * DN_ROWS_MAX * 4 + MAX_K * DN_STAGES * 8;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static OncePerDevice attr;  // one per template instance
+    if (attr.first())
         cudaFuncSetAttribute(down_m8_tma_kernel<LAYOUT, SUM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              MAX_K * (DN_ROWS_MAX * DN_ROW_BYTES + DN_ACT_BYTES) + MAX_K * DN_ROWS_MAX * 4 + MAX_K * DN_STAGES * 8);
-        attr_set = true;
-    }
     dim3 grid((a.out_dim + rows_per_cta - 1) / rows_per_cta, a.n_tokens);
     launch_pdl(down_m8_tma_kernel<LAYOUT, SUM>, grid, dim3(32 * a.k), smem, st, a.down_base, a.midq, a.selected, a.out,
                a.expert_bytes, a.out_dim, a.k, a.ieee, rows_per_cta, status);

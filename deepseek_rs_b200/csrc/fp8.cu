@@ -542,20 +542,13 @@ int launch_fp8_linear(cudaStream_t st, const uint8_t *a, const float *a_scale, c
         fp8_matvec_kernel<<<(N + 7) / 8, 256, 0, st>>>(a, a_scale, w, w_scale, out, M, N, K);
         return 1;
     }
-    static bool attr_set = false;
-    if (!attr_set) {
+    static OncePerDevice attr;
+    if (attr.first()) {
         cudaFuncSetAttribute(fp8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM);
         cudaFuncSetAttribute(fp8_gemm_ws_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8W_SMEM);
         cudaFuncSetAttribute(fp8_gemm_ws_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8W_SMEM);
-        attr_set = true;
     }
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (sms <= 0) sms = 148;
-    }
+    const int sms = sm_count_current();
     const char *no_ws = getenv("DSMOE_FP8_NO_WS"), *no_tma = getenv("DSMOE_FP8_NO_TMA");
     const uint32_t tiles = ((M + 127) / 128) * (N / F8W_TN);
     if (N % F8W_TN == 0 && K / 128 <= (uint32_t)F8W_MAX_KB && fp8_ws_as_planned() && !(no_ws && no_ws[0] == '1')) {

@@ -7,6 +7,39 @@
 
 namespace dsmoe {
 
+// Per-device host state. Function attributes (the dynamic shared-memory limit of a kernel) and device properties
+// belong to one device, while a process may create handles on several: everything cached on the host is therefore
+// kept per device ordinal, looked up from the CURRENT device at the time of the launch.
+constexpr int MAX_DEVICES = 64;
+inline int current_device_slot()
+{
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= MAX_DEVICES) d = 0;
+    return d;
+}
+// True the first time it is asked on each device.
+struct OncePerDevice {
+    bool done[MAX_DEVICES] = {};
+    bool first()
+    {
+        const int d = current_device_slot();
+        if (done[d]) return false;
+        done[d] = true;
+        return true;
+    }
+};
+// Multiprocessor count of the current device (cached per device).
+inline int sm_count_current()
+{
+    static int n[MAX_DEVICES] = {};
+    const int d = current_device_slot();
+    if (n[d] == 0) {
+        cudaDeviceGetAttribute(&n[d], cudaDevAttrMultiProcessorCount, d);
+        if (n[d] <= 0) n[d] = 148;
+    }
+    return n[d];
+}
+
 // Launch with the programmatic-serialisation attribute (see pdl_wait() in async.cuh): the kernel may be scheduled
 // while its predecessor in the stream drains, and must call pdl_wait() before touching that kernel's data.
 template <typename... KArgs, typename... Args>

@@ -6,6 +6,7 @@
 // dsmoe_create() allocates the scratch of dsmoe_moe_forward() with cudaMalloc, so those callers cannot even obtain a
 // handle. This entry point needs no handle: its scratch is a fixed array in the library's own device image, which
 // every GPU that loads the library carries from load until the process exits.
+#include "async.cuh"
 #include "common.cuh"
 #include "launch.h"
 
@@ -20,7 +21,7 @@ constexpr uint32_t NA_XB = NA_EMBD / QK_K, NA_MB = NA_FF / QK_K;
 constexpr uint32_t NA_T = DSMOE_NOALLOC_MAX_TOKENS;
 
 // Scratch layout (byte offsets, all multiples of 256): the intermediates of one call for up to NA_T tokens.
-constexpr size_t OFF_STATUS = 0;                                              // int, bounded-wait status word
+constexpr size_t OFF_STATUS = 0;                                              // STATUS_WORDS ints, bounded-wait status block
 constexpr size_t OFF_PROBS = 256;                                             // f32 [T][256]
 constexpr size_t OFF_SEL = OFF_PROBS + (size_t)NA_T * NA_EXPERT * 4;          // i32 [T][6] (padded)
 constexpr size_t OFF_WTS = OFF_SEL + 256;                                     // f32 [T][6] (padded)
@@ -33,7 +34,6 @@ static_assert(NA_T * NA_K * 4 <= 256, "selection / weight slots are 256 bytes");
 // About 0.55 MB. In host code this name is only a stand-in for the symbol, never a device address.
 static __device__ __align__(256) unsigned char g_noalloc_scratch[SCRATCH_BYTES];
 
-constexpr int MAX_DEVICES = 64;
 unsigned char *g_scratch_ptr[MAX_DEVICES] = {};  // per device: the array's device address, looked up once
 
 }  // namespace
@@ -72,9 +72,9 @@ extern "C" int dsmoe_moe_forward_noalloc(dsmoe_stream stream, const uint8_t *gat
     float *mid = reinterpret_cast<float *>(s + OFF_MID);
     uint8_t *midq = s + OFF_MIDQ;
 
-    // The status word is the only part of the array that must start at zero: every other region is completely
+    // The status block is the only part of the array that must start at zero: every other region is completely
     // rewritten for rows [0, n_tokens) before it is read.
-    if (cudaMemsetAsync(status, 0, sizeof(int), st) != cudaSuccess) return DSMOE_ERR_CUDA;
+    if (cudaMemsetAsync(status, 0, STATUS_WORDS * sizeof(int), st) != cudaSuccess) return DSMOE_ERR_CUDA;
     launch_router_q8k_fused(st, logits, x, probs, sel, wts, xq, n_tokens, (int)NA_K, (int)NA_EXPERT, NA_EMBD,
                             NA_ROUTE_SCALE);
     GateUpArgs g = {gate, up, xq, sel, wts, nullptr, nullptr, mid, (uint64_t)NA_FF * NA_XB * IQ2XXS_BYTES,
@@ -87,4 +87,17 @@ extern "C" int dsmoe_moe_forward_noalloc(dsmoe_stream stream, const uint8_t *gat
     if (down_tma_eligible(d)) launch_down_tma(st, d, status);
     else launch_down(st, d);
     return cudaGetLastError() == cudaSuccess ? DSMOE_OK : DSMOE_ERR_CUDA;
+}
+
+extern "C" int dsmoe_noalloc_device_status(dsmoe_stream stream, int *code_out)
+{
+    if (!code_out) return DSMOE_ERR_ARG;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return DSMOE_ERR_CUDA;
+    if (!g_scratch_ptr[dev]) return DSMOE_ERR_STATE;  // the entry point has not run on this device
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemcpyAsync(code_out, g_scratch_ptr[dev] + OFF_STATUS, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return DSMOE_ERR_CUDA;
+    return *code_out == 0 ? DSMOE_OK : DSMOE_ERR_TIMEOUT;
 }

@@ -17,7 +17,6 @@
 //   5 grouped_gemm<Q2K>                     down, min-term as a second K=16 MMA -> per-pair rows
 //   6 moe_sum                               slots summed in slot order
 #include <cuda_fp16.h>
-#include <stdio.h>
 
 #include "common.cuh"
 #include "launch.h"
@@ -227,8 +226,12 @@ __global__ void __launch_bounds__(256) pf_gather_kernel(const uint8_t *__restric
 //
 // One persistent CTA per SM (896 threads) walks items = (token tile, M tile). Four roles run asynchronously and meet
 // only on mbarriers:
-//   warps 8-23  producers  decode 128 weight rows x 128 K per stage (half a superblock) into a two-stage ring in
-//                          shared memory as exact f16 integers, 8 rows per warp;
+//   warps 8-23  producers  decode 128 weight rows x 128 K per stage (half a superblock) into a two-stage ring as
+//                          exact f16 integers. Q2_K: the ring is in shared memory, 8 rows per warp. IQ2_XXS: the ring
+//                          is in TENSOR memory (the MMA takes its A operand from there): a thread owns one row
+//                          (= its TMEM lane), decodes one 32-weight group per stage in registers and writes it with
+//                          one tcgen05.st, so the decoded weights never cross the shared-memory pipe, which the
+//                          codebook lookups already keep busy;
 //   warp 25     loader     bulk-copies the matching activation blocks (already f16, already in operand layout) into a
 //                          three-stage ring, running ahead of the decode;
 //   warp 24     issuer     one elected lane issues the stage's eight K=16 MMAs once both operands are there, and
@@ -239,8 +242,12 @@ __global__ void __launch_bounds__(256) pf_gather_kernel(const uint8_t *__restric
 //                          result while the other roles already work on the next item.
 // Registers move between the roles with setmaxnreg.
 // TMEM (512 columns). Q2_K: two accumulator buffers (D at 0/128, min-term D2 at 256/384), so superblock j is drained
-// while j+1 is contracted. IQ2_XXS: one accumulator (columns 0-127) and three spill sets P1/P2/P3 (128.., 256.., 384..)
-// that hold the upper levels of the reference's reduction tree, private to the draining thread.
+// while j+1 is contracted. IQ2_XXS: two accumulator buffers as well (columns 0-127 and 128-255), one spill set X
+// (256..) and the two-stage ring of decoded weights (384.., 64 columns = 128 f16 per row and stage). The reference's
+// reduction tree needs up to three spill sets, private to the draining thread: X, a second one (Y) in shared memory
+// (64 KB, where the Q2_K kernel has its weight ring), and a third only while the tree's last leaf is being contracted:
+// for that window (the last two superblocks of an item; the last one when a row has 8 blocks) accumulator buffer 1 is
+// the spill set and buffer 0 works alone.
 // IQ2_XXS tile rows: row 2r is gate row r and row 2r+1 the same row of up, so the two inputs of SwiGLU sit in
 // neighbouring lanes of one warp and are exchanged with shuffles.
 // Q2_K: the min term -dmin * d_x * sum_j bsums[j] * sc_hi[j] is a second accumulator fed by one K=16 MMA per
@@ -265,7 +272,9 @@ struct PfGemmArgs {
 };
 
 constexpr int PF_A_STAGES = 2, PF_B_STAGES = 3;
-constexpr int PF_SMEM_A = 0;                                          // 2 x 32 KB decoded weights
+constexpr int PF_SMEM_A = 0;                                          // Q2K: 2 x 32 KB decoded weights; IQ2: spill set Y
+constexpr uint32_t PF_TMEM_X = 256, PF_TMEM_A = 384;                    // IQ2: TMEM columns of spill set X and of the weight ring
+constexpr uint32_t PF_TMEM_A_STAGE = PF_KS / 2;                          // 64 columns: 128 f16 per row
 constexpr int PF_SMEM_B = PF_A_STAGES * PF_STAGE_A;                   // 3 x 32 KB activations
 constexpr int PF_SMEM_LUT = PF_SMEM_B + PF_B_STAGES * PF_STAGE_A;     // IQ2: codebook (f16, 32 KB) + signs (16 KB), 8 copies each
 constexpr int PF_SMEM_A2 = PF_SMEM_LUT;                               // Q2K (no tables): 2 x 4 KB sc_hi tile, one per TMEM buffer
@@ -279,20 +288,6 @@ constexpr int PF_SMEM_TOTAL = PF_SMEM_BAR + 128;
 static_assert(PF_SMEM_TOTAL <= 232448, "shared memory per CTA");
 
 enum { PF_IQ2 = 0, PF_Q2K = 1 };
-
-// Optional in-kernel phase timing (diagnostic builds only, -DPF_PROFILE): cycles per role and phase, one record per CTA.
-#ifdef PF_PROFILE
-__device__ long long g_pf_prof[2][160][32];
-#define PF_T0() long long pf_t_ = clock64()
-#define PF_ACC(i) do { const long long pf_n_ = clock64(); pf_c_[i] += pf_n_ - pf_t_; pf_t_ = pf_n_; } while (0)
-#define PF_DECL() long long pf_c_[8] = {0, 0, 0, 0, 0, 0, 0, 0}
-#define PF_DUMP(cond, base) do { if (cond) for (int q_ = 0; q_ < 8; ++q_) g_pf_prof[KIND][blockIdx.x][(base) + q_] = pf_c_[q_]; } while (0)
-#else
-#define PF_T0() do { } while (0)
-#define PF_ACC(i) do { } while (0)
-#define PF_DECL() do { } while (0)
-#define PF_DUMP(cond, base) do { } while (0)
-#endif
 
 // 8 unsigned bytes (two words) -> 8 exact f16 integers; 0x6400 | b is 1024 + b
 __device__ __forceinline__ uint4 pf_bytes_to_f16x8(uint32_t lo, uint32_t hi)
@@ -346,25 +341,23 @@ __device__ __forceinline__ uint4 pf_load_q2k_scales16(const uint8_t *row, int la
     return make_uint4(q[0], q[1], q[2], q[3]);
 }
 
-// IQ2_XXS: decode one 32-weight group into four core-matrix rows (8 f16 each) at dst + u * 128, u = 0..3
 // The tables hold 8 copies of every entry (entry stride 128 bytes); lane7 = lane & 7 picks this lane's copy, so the
 // eight lanes of a shared-memory wavefront never share a bank group.
-__device__ __forceinline__ void pf_decode_iq2(uint2 pk, uint8_t *dst, const uint4 *lut_grid, const uint4 *lut_sign,
-                                              uint32_t lane7)
+// IQ2_XXS for the tensor-memory ring: decode one 32-weight group into 16 words (f16 pairs in K order).
+__device__ __forceinline__ void pf_decode_iq2_regs(uint2 pk, uint32_t (&w)[16], const uint4 *lut_grid, const uint4 *lut_sign,
+                                                   uint32_t lane7)
 {
     const uint32_t aux0 = pk.x, aux1 = pk.y;
     const __half2 ls = __float2half2_rn((float)(2u * (aux1 >> 28) + 1u));
     const uint32_t ls2 = *reinterpret_cast<const uint32_t *>(&ls);
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-        const uint4 g = lut_grid[((aux0 >> (8 * u)) & 255u) * 8 + lane7];   // magnitudes as f16
-        const uint4 s = lut_sign[((aux1 >> (7 * u)) & 127u) * 8 + lane7];   // +1 / -1 as f16
-        uint4 w;
-        w.x = pf_hmul2(g.x, pf_hmul2(s.x, ls2));
-        w.y = pf_hmul2(g.y, pf_hmul2(s.y, ls2));
-        w.z = pf_hmul2(g.z, pf_hmul2(s.z, ls2));
-        w.w = pf_hmul2(g.w, pf_hmul2(s.w, ls2));
-        *reinterpret_cast<uint4 *>(dst + u * 128) = w;
+        const uint4 g = lut_grid[((aux0 >> (8 * u)) & 255u) * 8 + lane7];
+        const uint4 s = lut_sign[((aux1 >> (7 * u)) & 127u) * 8 + lane7];
+        w[4 * u + 0] = pf_hmul2(g.x, pf_hmul2(s.x, ls2));
+        w[4 * u + 1] = pf_hmul2(g.y, pf_hmul2(s.y, ls2));
+        w[4 * u + 2] = pf_hmul2(g.z, pf_hmul2(s.z, ls2));
+        w[4 * u + 3] = pf_hmul2(g.w, pf_hmul2(s.w, ls2));
     }
 }
 
@@ -394,6 +387,20 @@ __device__ __forceinline__ uint32_t pf_visit_block(uint32_t kblocks, uint32_t j)
     const uint32_t l = (0x73516240u >> (4 * leaf)) & 7u;
     return kblocks == 16 ? l + 8 * (j & 1) : l;
 }
+
+// Accumulator buffer (0 or 1) that superblock j of an item is contracted into. gsb = superblocks this CTA has started
+// before it. Q2_K alternates for ever. IQ2_XXS alternates inside an item up to the blocks of the tree's last leaf,
+// which use buffer 0 only: buffer 1 then holds a spill set (see the TMEM note above).
+template <int KIND>
+__device__ __forceinline__ uint32_t pf_acc_buf(uint32_t kblocks, uint32_t j, uint32_t gsb)
+{
+    if (KIND == PF_Q2K) return gsb & 1u;
+    const uint32_t single_from = kblocks == 16 ? 14u : kblocks - 1u;
+    return j < single_from ? (j & 1u) : 0u;
+}
+// IQ2_XXS: the last superblock of an item that is contracted into buffer 1. The consumers hand buffer 1 back only at
+// the end of the item, after the spill set parked in it has been read.
+__device__ __forceinline__ uint32_t pf_last_buf1_block(uint32_t kblocks) { return kblocks == 16 ? 13u : kblocks - 3u; }
 
 // Weight row behind row `rl` of an item's 128-row operand tile.
 template <int KIND>
@@ -437,7 +444,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     constexpr uint32_t TMEM_COLS = 512u;
-    constexpr uint32_t NBUF = KIND == PF_IQ2 ? 1u : 2u;      // accumulator buffers in TMEM
     constexpr uint32_t M_OUT = KIND == PF_IQ2 ? 64u : 128u;  // output rows per tile
     const bool ieee = a.ieee != 0;
 
@@ -486,10 +492,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
         // accumulator row (TMEM lane) and column half of this thread
         const uint32_t arow = 32 * (warp & 3) + lane, acol0 = PF_COLS * (warp >> 2);
         const uint32_t tlane = (32u * (warp & 3)) << 16;
-        uint32_t gsb = 0;  // superblocks drained so far (TMEM buffer and mbarrier phase)
+        uint32_t gsb = 0, use0 = 0, use1 = 0;  // superblocks drained so far, and per accumulator buffer (mbarrier phase)
         bool ok = true;
-        PF_DECL();
-        PF_T0();
 
         for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x) {
             const uint32_t tile = item / n_mtiles, mt = item - tile * n_mtiles;
@@ -521,7 +525,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
                 if (KIND == PF_IQ2) sW[tid] = a.weights[pair];
             }
             named_barrier_sync(1, 32 * PF_DRAIN_WARPS);
-            PF_ACC(0);
 
             // Q2K: running sum. IQ2: the current leaf's partial a_l, after the last leaf the row total
             float acc[PF_COLS];
@@ -530,18 +533,19 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
 
             for (uint32_t j = 0; j < a.kblocks; ++j) {
                 if (!ok) break;  // keeps walking the items, so that every warp reaches the item barriers
-                const uint32_t buf = gsb % NBUF, use = gsb / NBUF, kb = pf_visit_block<KIND>(a.kblocks, j);
+                const uint32_t buf = pf_acc_buf<KIND>(a.kblocks, j, gsb), use = buf ? use1 : use0;
+                const uint32_t kb = pf_visit_block<KIND>(a.kblocks, j);
+                // IQ2: buffer 1 stays with the consumers after its last superblock of the item (it becomes a spill set)
+                const bool keep_buf = KIND == PF_IQ2 && j == pf_last_buf1_block(a.kblocks);
                 // IQ2: position of this block in the reference's reduction tree
                 const uint32_t leaf = a.kblocks == 16 ? (j >> 1) : j;
                 const bool first_of_leaf = a.kblocks == 16 ? (j & 1) == 0 : true;
                 const bool last_of_leaf = a.kblocks == 16 ? (j & 1) == 1 : true;
                 const uint32_t sc_bits = sD[kb * PF_TN + arow];
-                PF_ACC(1);
                 ok = mbar_wait_bounded(&bar_acc_full[buf], use & 1u, a.status);
                 ok = __all_sync(FULL, ok);
                 if (!ok) break;
                 tc05_fence_after_sync();
-                PF_ACC(2);
                 float dw, dmin = 0.0f;
                 if (KIND == PF_IQ2) {
                     dw = __fmul_rn(0.125f, f16_bits_to_f32(sc_bits, ieee));
@@ -555,6 +559,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
                     // registers, so that the next superblock's MMAs overlap the arithmetic.
                     // ((0.125 d_w) d_x) bsum is added to 0 (first block of a leaf) or to the leaf's first block.
                     auto release = [&]() {
+                        if (keep_buf) return;
                         tc05_fence_before_sync();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&bar_acc_free[buf]);
@@ -579,8 +584,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
                     };
                     if (first_of_leaf) {  // acc is dead: load all 64 columns into it, release, scale in place
                         if (acol0 < rows16) {  // warp-uniform: columns beyond the padded tile hold nothing
-                            tc05_ld32(tmem + tlane + acol0, acc);
-                            if (acol0 + 32 < rows16) tc05_ld32(tmem + tlane + acol0 + 32, acc + 32);
+                            tc05_ld32(tmem + tlane + buf * PF_TN + acol0, acc);
+                            if (acol0 + 32 < rows16) tc05_ld32(tmem + tlane + buf * PF_TN + acol0 + 32, acc + 32);
                             tc05_wait_ld32(acc);
                             tc05_wait_ld32(acc + 32);
                         }
@@ -595,7 +600,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
                             if (acol0 + 32 * h < rows16) {
-                                tc05_ld32(tmem + tlane + acol0 + 32 * h, v);
+                                tc05_ld32(tmem + tlane + buf * PF_TN + acol0 + 32 * h, v);
                                 tc05_wait_ld32(v);
                             }
                             if (h == 1) release();
@@ -636,46 +641,61 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
                     if (lane == 0) mbar_arrive(&bar_acc_free[buf]);
                 }
                 ++gsb;
-                PF_ACC(3);
+                if (buf) ++use1;
+                else ++use0;
 
                 if (KIND == PF_IQ2 && last_of_leaf) {
-                    // fold the finished leaf a_l (in acc) into the tree. P1 = pair sums, P2 = quad sums, P3 = the even
-                    // half: TMEM columns 128.., 256.., 384.. of this thread's lane, used as spill space
+                    // Fold the finished leaf a_l (in acc) into the tree ((a0+a4)+(a2+a6)) + ((a1+a5)+(a3+a7)); the
+                    // leaves arrive in the order 0 4 2 6 1 5 3 7. Spill sets of this thread: X in its TMEM lane, Y in
+                    // shared memory (column-major, so that the 32 lanes of a warp touch 32 different banks), and for
+                    // the last leaf accumulator buffer 1, whose last superblock of the item has been drained by then.
+                    // Stores to the spill sets are only waited for here, right before the next access to them.
+                    float *ys = reinterpret_cast<float *>(smem + PF_SMEM_A) + arow;
+                    tc05_wait_st();
 #pragma unroll
-                    for (int c0 = 0; c0 < PF_COLS; c0 += 16) {
+                    for (int c0 = 0; c0 < PF_COLS; c0 += 32) {
                         if (acol0 + c0 >= rows16) break;
-                        const uint32_t t1 = tmem + tlane + 128u + acol0 + c0, t2 = t1 + 128u, t3 = t1 + 256u;
-                        float w[16], e[16];
-                        if ((leaf & 1) == 0) {                     // first leaf of a pair
+                        const uint32_t tx = tmem + tlane + PF_TMEM_X + acol0 + c0, tz = tmem + tlane + PF_TN + acol0 + c0;
+                        float *y = ys + (acol0 + c0) * 128;
+                        float e[32];
+                        if (leaf == 0 || leaf == 6) {              // a0 -> X, a3 -> buffer 1
+                            tc05_st32(leaf == 0 ? tx : tz, acc + c0);
+                        } else if (leaf == 2 || leaf == 4) {       // a2 -> Y, a1 -> Y
 #pragma unroll
-                            for (int i = 0; i < 16; ++i) w[i] = acc[c0 + i];
-                            tc05_st16(t1, w);
-                        } else if (leaf == 1 || leaf == 5) {       // pair sum, the first of its half: P2
-                            tc05_ld16(t1, w);
-                            tc05_wait_ld16(w);
+                            for (int i = 0; i < 32; ++i) y[i * 128] = acc[c0 + i];
+                        } else if (leaf == 1) {                    // X = a0 + a4
+                            tc05_ld32(tx, e);
+                            tc05_wait_ld32(e);
 #pragma unroll
-                            for (int i = 0; i < 16; ++i) w[i] = __fadd_rn(w[i], acc[c0 + i]);
-                            tc05_st16(t2, w);
-                        } else {                                   // leaf 3 or 7: quad sum = P2 + (P1 + a_l)
-                            tc05_ld16(t1, w);
-                            tc05_ld16(t2, e);
-                            tc05_wait_ld16(w);
-                            tc05_wait_ld16(e);
+                            for (int i = 0; i < 32; ++i) e[i] = __fadd_rn(e[i], acc[c0 + i]);
+                            tc05_st32(tx, e);
+                        } else if (leaf == 5) {                    // Y = a1 + a5
 #pragma unroll
-                            for (int i = 0; i < 16; ++i) w[i] = __fadd_rn(e[i], __fadd_rn(w[i], acc[c0 + i]));
-                            if (leaf == 3) {                       // even half done: park it in P3
-                                tc05_st16(t3, w);
-                            } else {                               // row total = even half + odd half
-                                tc05_ld16(t3, e);
-                                tc05_wait_ld16(e);
+                            for (int i = 0; i < 32; ++i) y[i * 128] = __fadd_rn(y[i * 128], acc[c0 + i]);
+                        } else if (leaf == 3) {                    // X = (a0 + a4) + (a2 + a6): the even half
+                            tc05_ld32(tx, e);
+                            tc05_wait_ld32(e);
 #pragma unroll
-                                for (int i = 0; i < 16; ++i) acc[c0 + i] = __fadd_rn(e[i], w[i]);
-                            }
+                            for (int i = 0; i < 32; ++i) e[i] = __fadd_rn(e[i], __fadd_rn(y[i * 128], acc[c0 + i]));
+                            tc05_st32(tx, e);
+                        } else {                                   // row total = X + ((a1 + a5) + (a3 + a7))
+                            tc05_ld32(tz, e);
+                            tc05_wait_ld32(e);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) acc[c0 + i] = __fadd_rn(y[i * 128], __fadd_rn(e[i], acc[c0 + i]));
+                            tc05_ld32(tx, e);
+                            tc05_wait_ld32(e);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) acc[c0 + i] = __fadd_rn(e[i], acc[c0 + i]);
                         }
                     }
-                    tc05_wait_st();
                 }
-                PF_ACC(4);
+                if (KIND == PF_IQ2 && last_of_leaf && leaf == 7) {
+                    // the spill set in buffer 1 has been read: the issuer may have the buffer again
+                    tc05_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bar_acc_free[1]);
+                }
             }
             if (!ok) continue;
 
@@ -733,47 +753,60 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
                         if (acol0 + i0 + k < rows) orow[(size_t)pr[k] * a.out_dim] = acc[i0 + k];
                 }
             }
-            PF_ACC(5);
         }
-        PF_DUMP(tid == 0, 0);
     } else if (warp < PF_DRAIN_WARPS + PF_DECODE_WARPS) {
         // ------------------------------------------------------------------------------------------- producers
         reg_dealloc<PF_REG_PRODUCER>();
         const uint32_t dwarp = warp - PF_DRAIN_WARPS, dtid = tid - 32 * PF_DRAIN_WARPS;
-        // this thread in the decode: lane = c * 8 + r8 -> quarter c of the stage, tile row 8 dwarp + r8
-        const uint32_t dc = lane >> 3, dr8 = lane & 7, rl = 8 * dwarp + dr8;
+        // This thread in the decode. Q2_K: lane = c * 8 + r8 -> quarter c of the stage, tile row 8 dwarp + r8.
+        // IQ2_XXS: a warp can only write the TMEM lanes of its own quadrant (warp index mod 4), so the thread's row is
+        // 32 * (warp % 4) + lane and the warp's quarter of the stage is dwarp / 4.
+        const uint32_t dc = KIND == PF_IQ2 ? (dwarp >> 2) : (lane >> 3), dr8 = lane & 7;
+        const uint32_t rl = KIND == PF_IQ2 ? 32u * (warp & 3u) + lane : 8 * dwarp + dr8;
         uint32_t gs = 0, gsb = 0;  // stages / superblocks started so far by this CTA (ring slot and mbarrier phase)
         bool ok = true;
-        PF_DECL();
-        PF_T0();
 
-        if (blockIdx.x < n_items) pf_prefetch_item<KIND>(a, blockIdx.x, n_mtiles, row_bytes, dtid, 32 * PF_DECODE_WARPS);
-        for (uint32_t item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
-            if (item + gridDim.x < n_items)
-                pf_prefetch_item<KIND>(a, item + gridDim.x, n_mtiles, row_bytes, dtid, 32 * PF_DECODE_WARPS);
+        // Row pointer of this thread in an item's operand tile
+        auto item_row = [&](uint32_t item) -> const uint8_t * {
             const uint32_t tile = item / n_mtiles, mt = item - tile * n_mtiles;
-            const uint64_t ebase = (uint64_t)a.tile_expert[tile] * a.expert_bytes;
-            const uint8_t *drow = pf_tile_row<KIND>(a, ebase, mt, rl, row_bytes);
-            // Packed bytes are fetched one stage ahead and Q2_K scale bytes one superblock ahead. The loop is written
-            // two superblocks at a time over two register sets, so that a fetched value is first touched by the
-            // decode that needs it (a register copy at the end of a stage would wait for the load there).
-            uint2 pkA = pf_load_packed<KIND>(drow, a.layout, pf_visit_block<KIND>(a.kblocks, 0), 0, dc), pkB = pkA;
-            uint4 scA = make_uint4(0, 0, 0, 0), scB = scA;
-            if (KIND == PF_Q2K) scA = pf_load_q2k_scales16(drow, a.layout, pf_visit_block<KIND>(a.kblocks, 0));
+            return pf_tile_row<KIND>(a, (uint64_t)a.tile_expert[tile] * a.expert_bytes, mt, rl, row_bytes);
+        };
+        // Packed bytes (and Q2_K scale bytes) are requested one whole superblock ahead, across item boundaries too, and
+        // BEFORE the wait for a free ring slot: a load from L2 takes about as long as a stage, so a request made only
+        // once the slot is free would sit on the critical path of every stage. Two register sets (A: even superblocks,
+        // B: odd ones; a row has an even number of superblocks) alternate, so that a fetched value is first touched by
+        // the decode that needs it.
+        uint2 pA0 = make_uint2(0, 0), pA1 = pA0, pB0 = pA0, pB1 = pA0;
+        uint4 scA = make_uint4(0, 0, 0, 0), scB = scA;
+        const uint8_t *drow = nullptr;
+        if (blockIdx.x < n_items) {
+            pf_prefetch_item<KIND>(a, blockIdx.x, n_mtiles, row_bytes, dtid, 32 * PF_DECODE_WARPS);
+            drow = item_row(blockIdx.x);
+            const uint32_t kb0 = pf_visit_block<KIND>(a.kblocks, 0);
+            pA0 = pf_load_packed<KIND>(drow, a.layout, kb0, 0, dc);
+            pA1 = pf_load_packed<KIND>(drow, a.layout, kb0, 1, dc);
+            if (KIND == PF_Q2K) scA = pf_load_q2k_scales16(drow, a.layout, kb0);
+        }
+        for (uint32_t item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+            const bool has_next = item + gridDim.x < n_items;
+            if (has_next) pf_prefetch_item<KIND>(a, item + gridDim.x, n_mtiles, row_bytes, dtid, 32 * PF_DECODE_WARPS);
+            const uint8_t *drow_next = has_next ? item_row(item + gridDim.x) : nullptr;
 
-            auto stage = [&](uint32_t s, const uint2 &cur, uint2 &nxt, const uint4 &sc) -> bool {
+            auto stage = [&](uint32_t s, const uint2 &cur, const uint4 &sc) -> bool {
                 const uint32_t b = gs & 1u, half = s & 1u;
                 // the ring slot is free once the MMAs of the stage issued two stages ago have retired
-                PF_ACC(0);
                 if (gs >= 2) ok = mbar_wait_bounded(&bar_a_free[b], ((gs >> 1) - 1) & 1u, a.status);
                 ok = __all_sync(FULL, ok);
                 if (!ok) return false;
-                PF_ACC(1);
-                if (s + 1 < n_stages)
-                    nxt = pf_load_packed<KIND>(drow, a.layout, pf_visit_block<KIND>(a.kblocks, (s + 1) >> 1), (s + 1) & 1, dc);
+                if (KIND == PF_IQ2) tc05_fence_after_sync();  // the MMAs that read this TMEM stage have retired
                 uint8_t *dst = smem + PF_SMEM_A + b * PF_STAGE_A + (rl >> 3) * PF_SBO + (rl & 7) * 16;
                 if (KIND == PF_IQ2) {
-                    pf_decode_iq2(cur, dst + dc * 512, lut_grid, lut_sign, dr8);
+                    // group dc of the stage -> K elements 32 dc .. 32 dc + 31 -> 16 columns of this row's TMEM lane
+                    uint32_t wreg[16];
+                    pf_decode_iq2_regs(cur, wreg, lut_grid, lut_sign, dr8);
+                    tc05_st16_u32(tmem + ((32u * (warp & 3u)) << 16) + PF_TMEM_A + b * PF_TMEM_A_STAGE + 16u * dc, wreg);
+                    tc05_wait_st();
+                    tc05_fence_before_sync();
                 } else {
                     pf_decode_q2k(cur, half ? make_uint2(sc.z, sc.w) : make_uint2(sc.x, sc.y), dc, dst + dc * 128);
                     if (half == 0 && dc < 2) {  // sc_hi of sub-blocks 8 dc .. 8 dc + 7 -> min-term operand, core dc
@@ -784,49 +817,51 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
                     }
                 }
                 // generic-proxy writes -> visible to the tensor core (async proxy); this warp's share is done
-                fence_async_smem();
+                if (KIND == PF_Q2K) fence_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bar_a_full[b]);
                 if (half == 1) ++gsb;
                 ++gs;
-                PF_ACC(2);
                 return true;
             };
-            auto superblock = [&](uint32_t j, const uint4 &sc_cur, uint4 &sc_nxt) -> bool {
-                if (KIND == PF_Q2K && j + 1 < a.kblocks)
-                    sc_nxt = pf_load_q2k_scales16(drow, a.layout, pf_visit_block<KIND>(a.kblocks, j + 1));
-                return stage(2 * j, pkA, pkB, sc_cur) && stage(2 * j + 1, pkB, pkA, sc_cur);
+            // superblock j from the register set (c0, c1, sc_cur); the other set is filled for superblock j + 1 of this
+            // item or superblock 0 of the next
+            auto superblock = [&](uint32_t j, const uint2 &c0, const uint2 &c1, const uint4 &sc_cur, uint2 &n0, uint2 &n1,
+                                  uint4 &sc_nxt) -> bool {
+                const uint8_t *nrow = j + 1 < a.kblocks ? drow : drow_next;
+                if (nrow != nullptr) {
+                    const uint32_t kbn = pf_visit_block<KIND>(a.kblocks, j + 1 < a.kblocks ? j + 1 : 0);
+                    n0 = pf_load_packed<KIND>(nrow, a.layout, kbn, 0, dc);
+                    n1 = pf_load_packed<KIND>(nrow, a.layout, kbn, 1, dc);
+                    if (KIND == PF_Q2K) sc_nxt = pf_load_q2k_scales16(nrow, a.layout, kbn);
+                }
+                return stage(2 * j, c0, sc_cur) && stage(2 * j + 1, c1, sc_cur);
             };
             for (uint32_t j = 0; j < a.kblocks; j += 2) {
-                if (!superblock(j, scA, scB)) break;
-                if (j + 1 < a.kblocks && !superblock(j + 1, scB, scA)) break;
+                if (!superblock(j, pA0, pA1, scA, pB0, pB1, scB)) break;
+                if (!superblock(j + 1, pB0, pB1, scB, pA0, pA1, scA)) break;
             }
+            drow = drow_next;
         }
-        PF_DUMP(dtid == 0, 16);
     } else {
         // ------------------------------------------------------------------------------------ issuer and loader
         reg_dealloc<PF_REG_AUX>();
         const uint32_t awarp = warp - PF_DRAIN_WARPS - PF_DECODE_WARPS;
         if (awarp == 0) {
             // issuer: the whole warp walks the stages, one elected lane issues
-            uint32_t gs = 0, gsb = 0, bslot = 0, bpar = 0;
+            uint32_t gs = 0, gsb = 0, use0 = 0, use1 = 0, bslot = 0, bpar = 0;
             bool ok = true;
-            PF_DECL();
-            PF_T0();
             for (uint32_t item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
                 const uint32_t tile = item / n_mtiles;
                 const uint32_t rows16 = (a.tile_rows[tile] + 15u) & ~15u;
                 const uint32_t idesc = tc05_idesc_f16(128, rows16);
                 for (uint32_t s = 0; s < n_stages; ++s, ++gs) {
-                    const uint32_t b = gs & 1u, half = s & 1u, buf = gsb % NBUF, use = gsb / NBUF;
-                    PF_ACC(0);
+                    const uint32_t b = gs & 1u, half = s & 1u;
+                    const uint32_t buf = pf_acc_buf<KIND>(a.kblocks, s >> 1, gsb), use = buf ? use1 : use0;
                     ok = mbar_wait_bounded(&bar_a_full[b], (gs >> 1) & 1u, a.status);
-                    PF_ACC(1);
                     ok = ok && mbar_wait_bounded(&bar_b_full[bslot], bpar, a.status);
-                    PF_ACC(2);
                     // at the start of a superblock the consumers must have handed the accumulator buffer back
-                    if (half == 0 && gsb >= NBUF) ok = ok && mbar_wait_bounded(&bar_acc_free[buf], (use - 1u) & 1u, a.status);
-                    PF_ACC(3);
+                    if (half == 0 && use >= 1u) ok = ok && mbar_wait_bounded(&bar_acc_free[buf], (use - 1u) & 1u, a.status);
                     ok = __all_sync(FULL, ok);
                     tc05_fence_after_sync();
                     if (elect_one()) {
@@ -835,8 +870,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
                             const uint64_t da = tc05_smem_desc(smem_u32(smem + PF_SMEM_A + b * PF_STAGE_A), 128, PF_SBO);
                             const uint64_t db = tc05_smem_desc(smem_u32(smem + PF_SMEM_B + bslot * PF_STAGE_A), 128, PF_SBO);
 #pragma unroll
-                            for (int ks = 0; ks < PF_KS / 16; ++ks)  // K advances 256 bytes = 16 descriptor units
-                                tc05_mma_f16(d_tmem, da + 16u * ks, db + 16u * ks, idesc, (half | ks) != 0);
+                            for (int ks = 0; ks < PF_KS / 16; ++ks) {  // K advances 256 bytes = 16 descriptor units
+                                if (KIND == PF_IQ2)  // A from tensor memory: 16 f16 = 8 columns per K step
+                                    tc05_mma_f16_ts(d_tmem, tmem + PF_TMEM_A + b * PF_TMEM_A_STAGE + 8u * ks, db + 16u * ks, idesc,
+                                                    (half | ks) != 0);
+                                else
+                                    tc05_mma_f16(d_tmem, da + 16u * ks, db + 16u * ks, idesc, (half | ks) != 0);
+                            }
                             if (KIND == PF_Q2K && half == 1)
                                 tc05_mma_f16(tmem + 256u + buf * PF_TN,
                                              tc05_smem_desc(smem_u32(smem + PF_SMEM_A2 + (gsb & 1u) * 4096), 128, 256),
@@ -848,13 +888,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
                         if (half == 1) tc05_commit(&bar_acc_full[buf]);
                     }
                     __syncwarp();
-                    if (half == 1) ++gsb;
+                    if (half == 1) {
+                        ++gsb;
+                        if (buf) ++use1;
+                        else ++use0;
+                    }
                     if (++bslot == PF_B_STAGES) bslot = 0, bpar ^= 1u;
-                    PF_ACC(4);
                     if (!ok) break;
                 }
             }
-            PF_DUMP(lane == 0, 8);
         } else if (awarp == 1) {
             // loader: activation blocks (and, for Q2_K, the superblock's bsums tile) into the three-stage ring
             uint32_t gs = 0, gsb = 0, bslot = 0, bpar = 0;
@@ -954,31 +996,18 @@ bool prefill_eligible(uint32_t n_embd, uint32_t n_ff, const uint8_t *gate, const
            (layout == DSMOE_LAYOUT_NATIVE || ((n_embd / QK_K * IQ2XXS_BYTES) % 16 == 0 && (n_ff / QK_K * Q2K_BYTES) % 16 == 0));
 }
 
-static int pf_sm_count()
-{
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-        if (n <= 0) n = 148;
-    }
-    return n;
-}
-
 int launch_prefill_experts(cudaStream_t st, const PrefillArgs &p)
 {
     uint8_t *w = p.scratch;
     const PrefillScratch &L = p.lay;
     auto u32p = [&](size_t o) { return reinterpret_cast<uint32_t *>(w + o); };
     const uint32_t P = p.n_tokens * p.k, xb = p.n_embd / QK_K, mb = p.n_ff / QK_K;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static OncePerDevice attr;
+    if (attr.first()) {
         cudaFuncSetAttribute(pf_grouped_gemm_kernel<PF_IQ2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM_TOTAL);
         cudaFuncSetAttribute(pf_grouped_gemm_kernel<PF_Q2K>, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM_TOTAL);
-        attr_set = true;
     }
-    const int sms = pf_sm_count();
+    const int sms = sm_count_current();
     int n = 0;
     auto mark = [&](int i) {
         if (p.phase_events) cudaEventRecord(p.phase_events[i], st);
@@ -1023,20 +1052,6 @@ int launch_prefill_experts(cudaStream_t st, const PrefillArgs &p)
     // 6. slots summed in slot order
     launch_moe_sum(st, reinterpret_cast<const float *>(w + L.down_pair), nullptr, p.out, p.n_embd, p.k, p.n_tokens);
     mark(5);
-#ifdef PF_PROFILE
-    {
-        static long long h[2][160][32];
-        cudaStreamSynchronize(st);
-        cudaMemcpyFromSymbol(h, g_pf_prof, sizeof(h));
-        for (int k = 0; k < 2; ++k) {
-            double sum[32] = {0};
-            for (int c = 0; c < sms; ++c)
-                for (int q = 0; q < 32; ++q) sum[q] += (double)h[k][c][q] / sms / 1e3;
-            fprintf(stderr, "pf_prof kind %d (kcycles/CTA): consumer tab %.0f scale %.0f wait_full %.0f drain %.0f fold %.0f epi %.0f | issuer loop %.0f wait_a %.0f wait_b %.0f wait_acc %.0f issue %.0f | producer loop %.0f wait_free %.0f decode %.0f\n",
-                    k, sum[0], sum[1], sum[2], sum[3], sum[4], sum[5], sum[8], sum[9], sum[10], sum[11], sum[12], sum[16], sum[17], sum[18]);
-        }
-    }
-#endif
     return n + 6;
 }
 

@@ -155,3 +155,29 @@ class ExpertLayer:
     @property
     def packed_bytes_per_expert(self) -> int:
         return 2 * self.gate_expert_bytes + self.down_expert_bytes
+
+
+def random_layer_device(torch, device, seed: int, n_expert: int = N_EXPERT, n_embd: int = N_EMBD, n_ff: int = N_FF_EXP):
+    """One layer's expert tensors (gate, up, down; NATIVE byte order, flat uint8) generated on a CUDA device with the
+    distributions of ``ExpertLayer``: uniform bytes give uniform codebook / sign / scale / quant fields, the f16 scales
+    are |N(0,1)| * 1e-3. A full 256-expert layer is 1.8 GB, which numpy takes minutes to draw; the device takes
+    milliseconds. The bytes differ from ``ExpertLayer(seed)``: a consumer that needs them on the host copies them back."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+
+    def scales(n):
+        return (torch.randn(n, device=device, generator=g).abs() * 1e-3).to(torch.float16).view(torch.uint8).view(n, 2)
+
+    def iq2(n):
+        t = torch.randint(0, 256, (n, IQ2XXS_BYTES), dtype=torch.uint8, device=device, generator=g)
+        t[:, 0:2] = scales(n)
+        return t.view(-1)
+
+    def q2k(n):
+        t = torch.randint(0, 256, (n, Q2K_BYTES), dtype=torch.uint8, device=device, generator=g)
+        t[:, 80:82] = scales(n)
+        t[:, 82:84] = scales(n)
+        return t.view(-1)
+
+    nb_gate, nb_down = n_expert * n_ff * (n_embd // QK_K), n_expert * n_embd * (n_ff // QK_K)
+    return iq2(nb_gate), iq2(nb_gate), q2k(nb_down)

@@ -85,6 +85,10 @@ class MoeKernels:
         arr = (C.c_void_p * 6)(*[C.c_void_p(e.cuda_event) for e in events])
         self._check(self.lib.dsmoe_set_phase_events(self.h, arr, 6))
 
+    def debug_set(self, what: int, value: int):
+        """Test hook for the bounded-wait error path (see dsmoe_debug_set in include/dsmoe.h)."""
+        self._check(self.lib.dsmoe_debug_set(self.h, what, value))
+
     @property
     def launch_count(self) -> int:
         return int(self.lib.dsmoe_launch_count(self.h))

@@ -16,7 +16,12 @@
  *     and nothing throws across the boundary.
  *   - Packed weight pointers must be 16-byte aligned for the ROWSOA layout and 2-byte (IQ2_XXS) / 4-byte (Q2_K)
  *     aligned for the NATIVE layout; Q8_K buffers must be 4-byte aligned.
- *   - A handle belongs to one device and one host thread at a time.
+ *   - A handle belongs to one device and one host thread at a time. Calls that take a handle must be made with the
+ *     handle's device current (cudaSetDevice); otherwise they return DSMOE_ERR_STATE. dsmoe_create and dsmoe_destroy
+ *     switch to the handle's device themselves and put the caller's current device back before they return.
+ *   - The decode kernels index (token, slot) pairs with 16 bits: tier-1 gate/up/down calls and the tier-2 call below
+ *     its batched threshold take at most 65535 pairs (n_tokens * n_expert_used) per call and return DSMOE_ERR_ARG /
+ *     DSMOE_ERR_BOUNDS beyond that. The batched (grouped GEMM) path has no such limit.
  *
  * Block formats (little-endian): IQ2_XXS 66 B, Q2_K 84 B, Q8_K 292 B per 256 values
  * (engine/src/kernels/moe.rs:601-611).
@@ -93,6 +98,18 @@ DSMOE_API int dsmoe_device_status(dsmoe_handle *h, dsmoe_stream stream, int *cod
 DSMOE_API int dsmoe_set_phase_events(dsmoe_handle *h, void **events, int n_events);
 /* Number of kernels this handle has launched since creation (bookkeeping for benchmarks). */
 DSMOE_API uint64_t dsmoe_launch_count(const dsmoe_handle *h);
+
+/* Test hooks for the bounded-wait error path; no counterpart in the reference (which has no device-side waits).
+ * Synchronises the device, then writes one word of the handle's device status block:
+ *   DSMOE_DEBUG_WAIT_LIMIT_KCLOCKS  value = limit of every device-side wait in units of 1024 SM clocks (0 = default,
+ *                                   about two seconds)
+ *   DSMOE_DEBUG_DROP_ONE_COPY       value != 0: the TMA-staged down kernel leaves one of its bulk copies out, so the
+ *                                   wait for it runs out; the kernel records the code and returns, nothing hangs
+ *   DSMOE_DEBUG_CLEAR_STATUS        clears a recorded error code
+ * A test sets a short limit and the drop flag, runs dsmoe_down_sum, and expects dsmoe_device_status to return
+ * DSMOE_ERR_TIMEOUT. Production code never calls this. */
+enum { DSMOE_DEBUG_WAIT_LIMIT_KCLOCKS = 1, DSMOE_DEBUG_DROP_ONE_COPY = 2, DSMOE_DEBUG_CLEAR_STATUS = 3 };
+DSMOE_API int dsmoe_debug_set(dsmoe_handle *h, int what, int value);
 
 /* ------------------------------------------------------------------------------------------------------------ */
 /* Tier 1: kernel-for-kernel                                                                                      */
@@ -272,6 +289,14 @@ DSMOE_API int dsmoe_host_synchronize(dsmoe_handle *h);
 DSMOE_API int dsmoe_moe_forward_noalloc(dsmoe_stream stream, const uint8_t *gate, const uint8_t *up,
                                         const uint8_t *down, int layout, const float *x, const float *logits,
                                         uint32_t n_tokens, float *out, int32_t *selected_out, float *weights_out);
+
+/* The device status word of dsmoe_moe_forward_noalloc on the CURRENT device (no counterpart in the reference). The
+ * kernels of that call bound their waits on asynchronous copies like every other kernel here; the word lives in the
+ * same static array as the scratch, so there is no handle to ask. Waits for `stream`, copies the word back (no
+ * allocation: a plain cudaMemcpyAsync from the array's looked-up address) and returns DSMOE_OK with *code_out == 0,
+ * or DSMOE_ERR_TIMEOUT with the code if a wait expired during the most recent call (each call clears the word
+ * first). Returns DSMOE_ERR_STATE if dsmoe_moe_forward_noalloc has not run on this device yet. */
+DSMOE_API int dsmoe_noalloc_device_status(dsmoe_stream stream, int *code_out);
 
 #ifdef __cplusplus
 }
