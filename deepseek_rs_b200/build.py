@@ -11,15 +11,15 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libdsmoe.so")
-SOURCES = ["api.cu", "quant_router.cu", "experts.cu", "experts_tma.cu", "noalloc.cu", "prefill.cu", "fp8.cu", "shared.cu"]
-HEADERS = ["common.cuh", "launch.h", "async.cuh", "tc05.cuh", os.path.join("..", "..", "include", "dsmoe.h"),
+SOURCES = ["api.cu", "quant_router.cu", "experts.cu", "experts_tma.cu", "noalloc.cu", "prefill.cu", "fp8.cu", "shared.cu", "gguf.cu", "ep.cu"]
+HEADERS = ["common.cuh", "launch.h", "async.cuh", "tc05.cuh", "ep.h", os.path.join("..", "..", "include", "dsmoe.h"),
            os.path.join("..", "..", "include", "dsmoe_iq2_tables.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     # no fused multiply-add contraction: the f32 epilogues must round each operation like the reference's
     "-fmad=false", "-prec-div=true", "-prec-sqrt=true",
-    "-Xcompiler", "-fPIC,-fvisibility=hidden", "-cudart", "static", "--shared",
+    "-Xcompiler", "-fPIC,-fvisibility=hidden", "-cudart", "static", "--shared", "-ldl",
 ]
 
 

@@ -7,6 +7,7 @@
 
 #include "async.cuh"
 #include "common.cuh"
+#include "ep.h"
 #include "launch.h"
 
 using namespace dsmoe;
@@ -15,6 +16,12 @@ struct dsmoe_layer_slot {
     const uint8_t *gate, *up, *down;
     int layout;
     bool set;
+    // the tensors beside the routed experts (dsmoe_layer_register_extras); any of them may be null
+    const uint16_t *router_f16;
+    const float *router_bias;
+    const int32_t *hash_table;
+    uint32_t hash_rows;
+    const uint8_t *sh_gate, *sh_up, *sh_down;
 };
 
 struct dsmoe_handle {
@@ -43,6 +50,15 @@ struct dsmoe_handle {
     uint32_t sh_chunk;
     int8_t *sh_xq;
     float *sh_xscale, *sh_gate, *sh_up, *sh_mid;
+    // dsmoe_ffn_forward: logits computed here, shared-expert output when the caller does not want it, widened bf16 input;
+    // the shared expert runs on a side stream between two events
+    float *ffn_logits, *ffn_shared, *ffn_x32;
+    cudaStream_t sstream;
+    cudaEvent_t ev_fork, ev_join;
+    // expert-parallel state (dsmoe_ep_init), or null
+    EpState *ep;
+    cudaEvent_t ep_events[6];
+    bool ep_events_set;
 };
 
 namespace {
@@ -177,6 +193,12 @@ int dsmoe_create(const dsmoe_config *cfg, int device, dsmoe_handle **out)
         ok = ok && dev_alloc(&h->sh_mid, C * cfg->n_ff) == cudaSuccess;
     }
     ok = ok && cudaStreamCreateWithFlags(&h->hstream, cudaStreamNonBlocking) == cudaSuccess;
+    ok = ok && dev_alloc(&h->ffn_logits, T * cfg->n_expert) == cudaSuccess;
+    ok = ok && dev_alloc(&h->ffn_shared, T * cfg->n_embd) == cudaSuccess;
+    ok = ok && dev_alloc(&h->ffn_x32, T * cfg->n_embd) == cudaSuccess;
+    ok = ok && cudaStreamCreateWithFlags(&h->sstream, cudaStreamNonBlocking) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming) == cudaSuccess;
     ok = ok && dev_alloc(&h->d_status, STATUS_WORDS) == cudaSuccess &&
          cudaMemset(h->d_status, 0, STATUS_WORDS * sizeof(int)) == cudaSuccess;
     {
@@ -207,7 +229,14 @@ int dsmoe_destroy(dsmoe_handle *h)
     int caller_device = -1;
     cudaGetDevice(&caller_device);
     cudaSetDevice(h->device);
+    if (h->ep) ep_destroy(h->ep);
     if (h->hstream) cudaStreamDestroy(h->hstream);
+    if (h->sstream) cudaStreamDestroy(h->sstream);
+    if (h->ev_fork) cudaEventDestroy(h->ev_fork);
+    if (h->ev_join) cudaEventDestroy(h->ev_join);
+    cudaFree(h->ffn_logits);
+    cudaFree(h->ffn_shared);
+    cudaFree(h->ffn_x32);
     cudaFree(h->probs);
     cudaFree(h->weights);
     cudaFree(h->selected);
@@ -427,6 +456,9 @@ int dsmoe_matmul_f16(dsmoe_handle *h, dsmoe_stream stream, const uint16_t *w, co
     return check_launch(h, "matmul_f16", 1);
 }
 
+static int shared_expert_impl(dsmoe_handle *h, cudaStream_t st, const uint8_t *gate_w, const uint8_t *up_w,
+                              const uint8_t *down_w, const float *x, uint32_t n_tokens, float *out);
+
 int dsmoe_shared_expert(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *gate_w, const uint8_t *up_w,
                         const uint8_t *down_w, const float *x, uint32_t n_tokens, float *out)
 {
@@ -434,8 +466,13 @@ int dsmoe_shared_expert(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *gat
     if (n_tokens == 0) return DSMOE_OK;
     DSMOE_REQUIRE(h, gate_w && up_w && down_w && x && out, "shared_expert: null pointer");
     DSMOE_REQUIRE(h, (((uintptr_t)gate_w | (uintptr_t)up_w | (uintptr_t)down_w) & 3) == 0, "shared_expert: weights need 4-byte alignment");
+    return shared_expert_impl(h, (cudaStream_t)stream, gate_w, up_w, down_w, x, n_tokens, out);
+}
+
+static int shared_expert_impl(dsmoe_handle *h, cudaStream_t st, const uint8_t *gate_w, const uint8_t *up_w,
+                              const uint8_t *down_w, const float *x, uint32_t n_tokens, float *out)
+{
     const dsmoe_config &c = h->cfg;
-    cudaStream_t st = (cudaStream_t)stream;
     int n = 0;
     if (shared_fused_eligible(c.n_embd, c.n_ff, n_tokens) && n_tokens <= h->sh_chunk) {
         n = launch_shared_fused(st, gate_w, up_w, down_w, x, h->sh_mid, out, c.n_embd, c.n_ff, n_tokens, c.swiglu_clamp);
@@ -538,21 +575,41 @@ int dsmoe_layer_register(dsmoe_handle *h, uint32_t layer, const uint8_t *gate, c
     const size_t al = layout == DSMOE_LAYOUT_ROWSOA ? 16 : 4;
     DSMOE_REQUIRE(h, aligned(gate, al) && aligned(up, al) && aligned(down, al),
                   "layer_register: tensors must be %zu-byte aligned for this layout", al);
-    h->layers[layer] = {gate, up, down, layout, true};
+    dsmoe_layer_slot &ly = h->layers[layer];
+    ly.gate = gate, ly.up = up, ly.down = down, ly.layout = layout, ly.set = true;
+    return DSMOE_OK;
+}
+
+int dsmoe_layer_register_extras(dsmoe_handle *h, uint32_t layer, const uint16_t *router_f16, const float *router_bias,
+                                const int32_t *hash_table, uint32_t hash_rows, const uint8_t *shared_gate,
+                                const uint8_t *shared_up, const uint8_t *shared_down)
+{
+    DSMOE_ENTER(h);
+    const uint32_t L = h->cfg.max_layers ? h->cfg.max_layers : 1;
+    DSMOE_REQUIRE(h, layer < L, "layer_register_extras: layer %u beyond max_layers %u", layer, L);
+    DSMOE_REQUIRE(h, (hash_table == nullptr) == (hash_rows == 0), "layer_register_extras: hash table and hash_rows must come together");
+    const bool any_sh = shared_gate || shared_up || shared_down, all_sh = shared_gate && shared_up && shared_down;
+    DSMOE_REQUIRE(h, any_sh == all_sh, "layer_register_extras: the shared expert needs all three tensors");
+    DSMOE_REQUIRE(h, (((uintptr_t)shared_gate | (uintptr_t)shared_up | (uintptr_t)shared_down) & 3) == 0 && aligned(router_f16, 2),
+                  "layer_register_extras: shared-expert tensors need 4-byte, the router 2-byte alignment");
+    dsmoe_layer_slot &ly = h->layers[layer];
+    ly.router_f16 = router_f16, ly.router_bias = router_bias, ly.hash_table = hash_table, ly.hash_rows = hash_rows;
+    ly.sh_gate = shared_gate, ly.sh_up = shared_up, ly.sh_down = shared_down;
     return DSMOE_OK;
 }
 
 // Everything after the router and the Q8_K of x: gate/up/SwiGLU -> Q8_K(mid) -> down -> slot sum, on the decode
 // kernels or, from prefill_min_tokens rows upwards, on the grouped GEMM.
 static int expert_ffn_impl(dsmoe_handle *h, cudaStream_t st, const dsmoe_layer_slot &ly, const uint8_t *xq,
-                           const int32_t *sel, const float *wts, uint32_t n_tokens, float *out, int n, const char *what)
+                           const int32_t *sel, const float *wts, uint32_t n_tokens, float *out, int n, const char *what,
+                           const HcEpilogue *hc = nullptr, cudaEvent_t before_sum = nullptr)
 {
     const dsmoe_config &c = h->cfg;
     const uint32_t k = c.n_expert_used, xb = c.n_embd / QK_K, mb = c.n_ff / QK_K;
     if (n_tokens >= h->prefill_min_tokens && prefill_eligible(c.n_embd, c.n_ff, ly.gate, ly.up, ly.down, ly.layout)) {
         PrefillArgs p = {ly.gate, ly.up, ly.down, xq, sel, wts, h->mid, h->midq, out, h->pf_scratch, h->pf_lay,
                          n_tokens, k, c.n_expert, c.n_embd, c.n_ff, c.swiglu_clamp, ly.layout, (int)c.f16_ieee,
-                         h->d_status, h->phase_events_set ? h->phase_events : nullptr};
+                         h->d_status, h->phase_events_set ? h->phase_events : nullptr, hc, before_sum};
         n += launch_prefill_experts(st, p);
         return check_launch(h, what, n);
     }
@@ -569,6 +626,11 @@ static int expert_ffn_impl(dsmoe_handle *h, cudaStream_t st, const dsmoe_layer_s
     DownArgs d = {ly.down, h->midq, sel, out, (uint64_t)c.n_embd * mb * Q2K_BYTES, (uint64_t)mb * Q2K_BYTES, mb,
                   c.n_embd, k, n_tokens, ly.layout, (int)c.f16_ieee, 1};
     n += ((h->use_tma && down_tma_eligible(d)) ? launch_down_tma(st, d, h->d_status) : launch_down(st, d));
+    if (before_sum) cudaStreamWaitEvent(st, before_sum, 0);
+    if (hc && hc->out_hc) {
+        launch_hc_expand(st, out, c.n_embd, n_tokens, *hc);
+        n += 1;
+    }
     return check_launch(h, what, n);
 }
 
@@ -617,6 +679,207 @@ int dsmoe_expert_ffn(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, const
     DSMOE_REQUIRE(h, xq && selected && weights && out, "expert_ffn: null pointer");
     DSMOE_REQUIRE(h, aligned(xq, 16), "expert_ffn: xq must be 16-byte aligned");
     return expert_ffn_impl(h, (cudaStream_t)stream, h->layers[layer], xq, selected, weights, n_tokens, out, 0, "expert_ffn");
+}
+
+int dsmoe_hc_expand(dsmoe_handle *h, dsmoe_stream stream, const float *block_out, const float *block_add,
+                    const float *residual_hc, const float *split, float *out_hc, uint32_t n_embd, uint32_t n_hc,
+                    uint32_t n_tokens, uint32_t mix_hc, uint32_t has_add)
+{
+    DSMOE_ENTER(h);
+    if (n_tokens == 0 || n_embd == 0 || n_hc == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, block_out && residual_hc && split && out_hc && (!has_add || block_add), "hc_expand: null pointer");
+    DSMOE_REQUIRE(h, mix_hc >= 2 * n_hc + n_hc * n_hc, "hc_expand: mix_hc %u shorter than pre + post + comb of n_hc %u", mix_hc, n_hc);
+    const HcEpilogue hc = {block_out, residual_hc, split, out_hc, n_hc, mix_hc};
+    launch_hc_expand((cudaStream_t)stream, has_add ? block_add : nullptr, n_embd, n_tokens, hc);
+    return check_launch(h, "hc_expand", 1);
+}
+
+int dsmoe_ffn_forward(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, const dsmoe_ffn_args *a)
+{
+    DSMOE_ENTER(h);
+    DSMOE_REQUIRE(h, a != nullptr, "ffn_forward: null arguments");
+    const dsmoe_config &c = h->cfg;
+    const uint32_t L = c.max_layers ? c.max_layers : 1;
+    if (layer >= L || !h->layers[layer].set) return fail(h, DSMOE_ERR_STATE, "ffn_forward: layer %u not registered", layer);
+    const dsmoe_layer_slot &ly = h->layers[layer];
+    const uint32_t T = a->n_tokens, k = c.n_expert_used;
+    if (T > c.max_tokens) return fail(h, DSMOE_ERR_BOUNDS, "ffn_forward: n_tokens %u exceeds max_tokens %u", T, c.max_tokens);
+    if (T == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, a->x && a->routed_out, "ffn_forward: x and routed_out are required");
+    DSMOE_REQUIRE(h, a->x_dtype == DSMOE_DTYPE_F32 || a->x_dtype == DSMOE_DTYPE_BF16, "ffn_forward: unknown x_dtype %d", a->x_dtype);
+    DSMOE_REQUIRE(h, a->logits || ly.router_f16, "ffn_forward: no logits given and no router matrix registered");
+    DSMOE_REQUIRE(h, !a->hash_mode || ly.hash_table, "ffn_forward: hash_mode set but the layer has no hash table");
+    const bool want_shared = a->shared_out != nullptr || a->out_hc != nullptr;
+    DSMOE_REQUIRE(h, !want_shared || ly.sh_gate, "ffn_forward: shared-expert output wanted but no shared expert registered");
+    DSMOE_REQUIRE(h, !a->out_hc || (a->residual_hc && a->hc_split && a->n_hc > 0 && a->mix_hc >= 2 * a->n_hc + a->n_hc * a->n_hc),
+                  "ffn_forward: the hyper-connection merge needs residual_hc, hc_split, n_hc and mix_hc >= 2 n_hc + n_hc^2");
+    cudaStream_t st = (cudaStream_t)stream;
+    int n = 0;
+
+    // hidden states: f32 as the reference keeps them, or bf16 widened exactly
+    const float *x = static_cast<const float *>(a->x);
+    if (a->x_dtype == DSMOE_DTYPE_BF16) {
+        DSMOE_REQUIRE(h, aligned(a->x, 2), "ffn_forward: bf16 x must be 2-byte aligned");
+        launch_bf16_to_f32(st, static_cast<const uint16_t *>(a->x), h->ffn_x32, (uint64_t)T * c.n_embd);
+        x = h->ffn_x32;
+        n += 1;
+    } else {
+        DSMOE_REQUIRE(h, aligned(a->x, 16), "ffn_forward: x must be 16-byte aligned");
+    }
+
+    // shared expert on the side stream (engine/src/session.rs:1894-1987), concurrent with the routed path
+    float *shared = a->shared_out ? a->shared_out : h->ffn_shared;
+    if (want_shared) {
+        if (cudaEventRecord(h->ev_fork, st) != cudaSuccess || cudaStreamWaitEvent(h->sstream, h->ev_fork, 0) != cudaSuccess)
+            return fail(h, DSMOE_ERR_CUDA, "ffn_forward: fork: %s", cudaGetErrorString(cudaGetLastError()));
+        if (int rc = shared_expert_impl(h, h->sstream, ly.sh_gate, ly.sh_up, ly.sh_down, x, T, shared)) return rc;
+        if (cudaEventRecord(h->ev_join, h->sstream) != cudaSuccess)
+            return fail(h, DSMOE_ERR_CUDA, "ffn_forward: join: %s", cudaGetErrorString(cudaGetLastError()));
+    }
+
+    // router logits (engine/src/session.rs:1995-2008) unless the caller brings them
+    const float *logits = a->logits;
+    if (!logits) {
+        DSMOE_REQUIRE(h, T <= 65535u, "ffn_forward: at most 65535 tokens per call when the logits are computed here");
+        launch_matmul_f16(st, ly.router_f16, x, h->ffn_logits, c.n_embd, c.n_expert, T);
+        logits = h->ffn_logits;
+        n += 1;
+    }
+    int32_t *sel = a->selected_out ? a->selected_out : h->selected;
+    float *wts = a->weights_out ? a->weights_out : h->weights;
+    const bool plain_router = !ly.router_bias && !a->hash_mode && c.n_expert <= 256;
+    if (plain_router) {
+        launch_router_q8k_fused(st, logits, x, h->probs, sel, wts, h->xq, T, (int)k, (int)c.n_expert, c.n_embd, c.route_scale);
+        n += 1;
+    } else {  // bias and / or hash routing (engine/src/kernels/moe.rs:211-228)
+        launch_router_select(st, logits, ly.router_bias, a->hash_mode ? ly.hash_table : nullptr, a->tokens, h->probs, sel, wts,
+                             a->token_scalar, a->hash_mode ? ly.hash_rows : 0, T, ly.router_bias != nullptr, a->hash_mode != 0,
+                             (int)k, (int)c.n_expert, c.route_scale);
+        launch_q8k_quantize(st, x, h->xq, c.n_embd, T);
+        n += 2;
+    }
+    HcEpilogue hc = {shared, a->residual_hc, a->hc_split, a->out_hc, a->n_hc, a->mix_hc};
+    const int rc = expert_ffn_impl(h, st, ly, h->xq, sel, wts, T, a->routed_out, n, "ffn_forward", a->out_hc ? &hc : nullptr,
+                                   want_shared ? h->ev_join : nullptr);
+    return rc;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// expert parallel
+// ---------------------------------------------------------------------------------------------------------------
+
+int dsmoe_ep_get_unique_id(uint8_t *id128)
+{
+    if (!id128) return DSMOE_ERR_ARG;
+    return ep_get_unique_id(id128);
+}
+
+static int ep_init_common(dsmoe_handle *h, const uint8_t *id128, void *comm, int rank, int world, uint32_t max_replicas,
+                          uint32_t recv_capacity_rows)
+{
+    DSMOE_ENTER(h);
+    if (h->ep) return fail(h, DSMOE_ERR_STATE, "ep_init: already initialised");
+    DSMOE_REQUIRE(h, id128 || comm, "ep_init: neither a unique id nor a communicator");
+    char msg[384] = {0};
+    const int rc = ep_create(h->cfg, h->device, id128, comm, rank, world, max_replicas, recv_capacity_rows, &h->ep, msg, sizeof(msg));
+    if (rc != DSMOE_OK) return fail(h, rc, "%s", msg);
+    return DSMOE_OK;
+}
+
+int dsmoe_ep_init(dsmoe_handle *h, const uint8_t *id128, int rank, int world, uint32_t max_replicas,
+                  uint32_t recv_capacity_rows)
+{
+    return ep_init_common(h, id128, nullptr, rank, world, max_replicas, recv_capacity_rows);
+}
+
+int dsmoe_ep_init_comm(dsmoe_handle *h, void *nccl_comm, int rank, int world, uint32_t max_replicas,
+                       uint32_t recv_capacity_rows)
+{
+    return ep_init_common(h, nullptr, nccl_comm, rank, world, max_replicas, recv_capacity_rows);
+}
+
+#define DSMOE_NEED_EP(h, what) \
+    do {                       \
+        if (!(h)->ep) return fail((h), DSMOE_ERR_STATE, "%s: dsmoe_ep_init has not run on this handle", what); \
+    } while (0)
+
+int dsmoe_ep_layer_register(dsmoe_handle *h, uint32_t layer, const uint8_t *gate, const uint8_t *up, const uint8_t *down,
+                            int layout)
+{
+    DSMOE_ENTER(h);
+    DSMOE_NEED_EP(h, "ep_layer_register");
+    dsmoe_handle *o = ep_owner(h->ep);
+    const int rc = dsmoe_layer_register(o, layer, gate, up, down, layout);
+    if (rc != DSMOE_OK) return fail(h, rc, "ep_layer_register: %s", dsmoe_last_error(o));
+    return DSMOE_OK;
+}
+
+int dsmoe_ep_set_replicas(dsmoe_handle *h, const int32_t *expert_ids, uint32_t n)
+{
+    DSMOE_ENTER(h);
+    DSMOE_NEED_EP(h, "ep_set_replicas");
+    DSMOE_REQUIRE(h, n == 0 || expert_ids, "ep_set_replicas: null list");
+    const int rc = ep_set_replicas(h->ep, h->cfg.n_expert, expert_ids, n);
+    if (rc != DSMOE_OK) return fail(h, rc, "%s", ep_last_error(h->ep));
+    return DSMOE_OK;
+}
+
+int dsmoe_ep_expert_counts(dsmoe_handle *h, dsmoe_stream stream, uint64_t *counts_host, int reset)
+{
+    DSMOE_ENTER(h);
+    DSMOE_NEED_EP(h, "ep_expert_counts");
+    DSMOE_REQUIRE(h, counts_host, "ep_expert_counts: null pointer");
+    const int rc = ep_expert_counts(h->ep, (cudaStream_t)stream, h->cfg.n_expert, counts_host, reset);
+    if (rc != DSMOE_OK) return fail(h, rc, "%s", ep_last_error(h->ep));
+    return DSMOE_OK;
+}
+
+int dsmoe_ep_last_recv_rows(dsmoe_handle *h, int32_t *rows_per_rank)
+{
+    DSMOE_ENTER(h);
+    DSMOE_NEED_EP(h, "ep_last_recv_rows");
+    DSMOE_REQUIRE(h, rows_per_rank, "ep_last_recv_rows: null pointer");
+    return ep_last_recv_rows(h->ep, rows_per_rank);
+}
+
+int dsmoe_ep_set_phase_events(dsmoe_handle *h, void **events, int n_events)
+{
+    DSMOE_ENTER(h);
+    if (!events || n_events == 0) {
+        h->ep_events_set = false;
+        return DSMOE_OK;
+    }
+    if (n_events != 6) return fail(h, DSMOE_ERR_ARG, "ep_set_phase_events: expected 6 events, got %d", n_events);
+    for (int i = 0; i < 6; ++i) h->ep_events[i] = (cudaEvent_t)events[i];
+    h->ep_events_set = true;
+    return DSMOE_OK;
+}
+
+int dsmoe_moe_forward_ep(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, const float *x, const float *logits,
+                         uint32_t n_tokens, float *out, int32_t *selected_out, float *weights_out)
+{
+    DSMOE_ENTER(h);
+    DSMOE_NEED_EP(h, "moe_forward_ep");
+    const dsmoe_config &c = h->cfg;
+    if (n_tokens > c.max_tokens)
+        return fail(h, DSMOE_ERR_BOUNDS, "moe_forward_ep: n_tokens %u exceeds max_tokens %u", n_tokens, c.max_tokens);
+    DSMOE_REQUIRE(h, n_tokens == 0 || (x && logits && out), "moe_forward_ep: null pointer");
+    DSMOE_REQUIRE(h, aligned(x, 16), "moe_forward_ep: x must be 16-byte aligned");
+    DSMOE_REQUIRE(h, c.n_expert <= 256, "moe_forward_ep: at most 256 experts");
+    cudaStream_t st = (cudaStream_t)stream;
+    int32_t *sel = selected_out ? selected_out : h->selected;
+    float *wts = weights_out ? weights_out : h->weights;
+    int n = 0;
+    if (n_tokens) {  // the same router kernel on the same logits as the single-GPU call: routing is bit-identical
+        launch_router_q8k_fused(st, logits, x, h->probs, sel, wts, h->xq, n_tokens, (int)c.n_expert_used, (int)c.n_expert,
+                                c.n_embd, c.route_scale);
+        n = 1;
+    }
+    // a rank without tokens still takes part in the exchanges
+    const int rc = ep_forward(h->ep, st, layer, h->xq, sel, wts, n_tokens, c.n_expert_used, c.n_embd, out, &n,
+                              h->ep_events_set ? h->ep_events : nullptr);
+    if (rc != DSMOE_OK) return fail(h, rc, "%s", ep_last_error(h->ep));
+    return check_launch(h, "moe_forward_ep", n);
 }
 
 int dsmoe_host_synchronize(dsmoe_handle *h)

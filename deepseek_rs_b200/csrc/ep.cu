@@ -1,0 +1,427 @@
+// Expert-parallel execution of the routed-expert step behind the C ABI.
+//
+// The reference is single-GPU (one context, one stream: engine/src/engine.rs:73-74); sharding is new here and is
+// defined by "same result as one GPU". Rank r of G owns experts [r * E / G, (r + 1) * E / G) and routes its own tokens
+// with the same router kernel as the single-GPU call, so routing is bit-identical. One exchange each way:
+//   dispatch  every (token, slot) pair goes to the rank that owns its expert, as the token's Q8_K row (4672 B instead
+//             of 16 KB of f32) plus its expert id local to the owner and its router weight;
+//   combine   the owner returns the pair's down-projection row (f32 [n_embd]); the source sums a token's k rows in
+//             slot order straight from the receive buffer, so the result does not depend on arrival order.
+// Experts named by dsmoe_ep_set_replicas are held by every rank: their pairs stay on the rank that routed them.
+//
+// Everything between the router and the slot sum is device work on the caller's stream: the pairs are counted and
+// placed by destination rank with the same stable counting sort as the batched single-GPU path, the rows are gathered
+// by a kernel, and NCCL moves them (grouped ncclSend / ncclRecv over NVLink). The only host synchronisation of a step
+// is the read of the G x G count matrix that sizes the transfers; every rank sees the whole matrix, so a receive
+// buffer that would overflow is reported by all ranks alike and no rank is left waiting in a collective.
+//
+// NCCL is reached through dlsym on the libnccl.so.2 that is already loaded in the process (the one torch brings, when
+// the host is Python), so the library never links a second NCCL beside it.
+#include <dlfcn.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+#include "ep.h"
+#include "launch.h"
+
+namespace dsmoe {
+
+// ---- NCCL entry points, resolved at run time -------------------------------------------------------------------
+typedef struct { char internal[128]; } nccl_unique_id;  // ncclUniqueId
+typedef void *nccl_comm;                                 // ncclComm_t
+enum { NCCL_UINT8 = 1, NCCL_INT32 = 2 };                 // ncclDataType_t values used here
+struct NcclApi {
+    int (*GetUniqueId)(nccl_unique_id *);
+    int (*CommInitRank)(nccl_comm *, int, nccl_unique_id, int);
+    int (*CommDestroy)(nccl_comm);
+    int (*AllGather)(const void *, void *, size_t, int, nccl_comm, cudaStream_t);
+    int (*Send)(const void *, size_t, int, int, nccl_comm, cudaStream_t);
+    int (*Recv)(void *, size_t, int, int, nccl_comm, cudaStream_t);
+    int (*GroupStart)();
+    int (*GroupEnd)();
+    const char *(*GetErrorString)(int);
+    bool ok = false;
+};
+
+static const NcclApi *nccl_api()
+{
+    static NcclApi api;
+    static bool looked = false;
+    if (looked) return api.ok ? &api : nullptr;
+    looked = true;
+    void *lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);  // the copy the process already has, if any
+    if (!lib) lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!lib) return nullptr;
+#define DSMOE_NCCL_SYM(field, name)                                         \
+    *reinterpret_cast<void **>(&api.field) = dlsym(lib, name);              \
+    if (!api.field) return nullptr;
+    DSMOE_NCCL_SYM(GetUniqueId, "ncclGetUniqueId")
+    DSMOE_NCCL_SYM(CommInitRank, "ncclCommInitRank")
+    DSMOE_NCCL_SYM(CommDestroy, "ncclCommDestroy")
+    DSMOE_NCCL_SYM(AllGather, "ncclAllGather")
+    DSMOE_NCCL_SYM(Send, "ncclSend")
+    DSMOE_NCCL_SYM(Recv, "ncclRecv")
+    DSMOE_NCCL_SYM(GroupStart, "ncclGroupStart")
+    DSMOE_NCCL_SYM(GroupEnd, "ncclGroupEnd")
+    DSMOE_NCCL_SYM(GetErrorString, "ncclGetErrorString")
+#undef DSMOE_NCCL_SYM
+    api.ok = true;
+    return &api;
+}
+
+// ---- device side: destination of a pair, counts, stable placement, row gather -------------------------------------
+struct EpRoute {
+    const int32_t *selected;      // [n_pairs] global expert ids (negative -> expert 0, engine/src/kernels/moe.rs:645-648)
+    const int32_t *replica_slot;  // [n_expert]: -1, or the position of the expert in the replica list
+    uint32_t n_pairs, per_rank, rank, world;
+};
+
+__device__ __forceinline__ void ep_route(const EpRoute &r, uint32_t p, uint32_t *dest, int32_t *local)
+{
+    int32_t e = r.selected[p];
+    if (e < 0) e = 0;
+    const int32_t rs = r.replica_slot[e];
+    if (rs >= 0) {
+        *dest = r.rank;
+        *local = (int32_t)r.per_rank + rs;
+    } else {
+        *dest = (uint32_t)e / r.per_rank;
+        *local = e % (int32_t)r.per_rank;
+    }
+}
+
+// counts[d] = pairs this rank sends to rank d (one CTA per destination). CTA 0 also adds the step's selections to
+// the running per-expert histogram from which a host may choose the experts to replicate.
+__global__ void __launch_bounds__(256) ep_count_kernel(EpRoute r, int32_t *__restrict__ counts,
+                                                        unsigned long long *__restrict__ hist)
+{
+    __shared__ uint32_t s_warp[8];
+    const uint32_t d = blockIdx.x;
+    uint32_t c = 0;
+    for (uint32_t p = threadIdx.x; p < r.n_pairs; p += 256) {
+        uint32_t dest;
+        int32_t local;
+        ep_route(r, p, &dest, &local);
+        c += dest == d;
+        if (d == 0 && hist) {
+            const int32_t e = r.selected[p];
+            atomicAdd(&hist[e < 0 ? 0 : e], 1ull);
+        }
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) c += __shfl_xor_sync(FULL, c, m);
+    if ((threadIdx.x & 31) == 0) s_warp[threadIdx.x >> 5] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t t = 0;
+        for (int w = 0; w < 8; ++w) t += s_warp[w];
+        counts[d] = (int32_t)t;
+    }
+}
+
+// pos[p] = position of pair p in send order (grouped by destination, ascending pair id inside a group), order = its
+// inverse. One CTA per destination; same two-pass ballot placement as the batched path's pair grouping.
+__global__ void __launch_bounds__(256) ep_place_kernel(EpRoute r, const int32_t *__restrict__ counts,
+                                                        int32_t *__restrict__ pos, uint32_t *__restrict__ order)
+{
+    __shared__ uint32_t s_warp[8];
+    const uint32_t d = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t seg = ((r.n_pairs + 7) / 8 + 31) & ~31u, p_lo = min(r.n_pairs, warp * seg), p_hi = min(r.n_pairs, p_lo + seg);
+    auto hit_at = [&](uint32_t p) {
+        if (p >= p_hi) return false;
+        uint32_t dest;
+        int32_t local;
+        ep_route(r, p, &dest, &local);
+        return dest == d;
+    };
+    uint32_t cnt = 0;
+    for (uint32_t p0 = p_lo; p0 < p_hi; p0 += 32) cnt += __popc(__ballot_sync(FULL, hit_at(p0 + lane)));
+    if (lane == 0) s_warp[warp] = cnt;
+    __syncthreads();
+    uint32_t base = 0;
+    for (uint32_t i = 0; i < d; ++i) base += (uint32_t)counts[i];
+    for (uint32_t w = 0; w < warp; ++w) base += s_warp[w];
+    for (uint32_t p0 = p_lo; p0 < p_hi; p0 += 32) {
+        const uint32_t p = p0 + lane;
+        const bool hit = hit_at(p);
+        const uint32_t ballot = __ballot_sync(FULL, hit);
+        if (hit) {
+            const uint32_t at = base + __popc(ballot & ((1u << lane) - 1u));
+            pos[p] = (int32_t)at;
+            order[at] = p;
+        }
+        base += __popc(ballot);
+    }
+}
+
+// send buffers in send order: the pair's token row of Q8_K blocks (16-byte pieces), its owner-local expert id and its
+// router weight. One warp per row.
+__global__ void __launch_bounds__(256) ep_gather_kernel(EpRoute r, const uint32_t *__restrict__ order,
+                                                         const uint8_t *__restrict__ xq, const float *__restrict__ weights,
+                                                         uint32_t k, uint32_t row_bytes, uint8_t *__restrict__ send_xq,
+                                                         int32_t *__restrict__ send_sel, float *__restrict__ send_w)
+{
+    const uint32_t lane = threadIdx.x & 31, i = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (i >= r.n_pairs) return;
+    const uint32_t p = order[i];
+    const uint4 *src = reinterpret_cast<const uint4 *>(xq + (size_t)(p / k) * row_bytes);
+    uint4 *dst = reinterpret_cast<uint4 *>(send_xq + (size_t)i * row_bytes);
+    for (uint32_t j = lane; j < row_bytes / 16; j += 32) dst[j] = src[j];
+    if (lane == 0) {
+        uint32_t dest;
+        int32_t local;
+        ep_route(r, p, &dest, &local);
+        send_sel[i] = local;
+        send_w[i] = weights[p];
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------------------------------------
+struct EpState {
+    const NcclApi *nccl = nullptr;
+    nccl_comm comm = nullptr;
+    bool own_comm = false;
+    int rank = 0, world = 1;
+    uint32_t per_rank = 0, max_replicas = 0, recv_cap = 0, max_pairs = 0, row_bytes = 0;
+    dsmoe_handle *owner = nullptr;  // n_expert = per_rank + max_replicas, n_expert_used = 1: runs the received rows
+    // device
+    int32_t *replica_slot = nullptr, *send_counts = nullptr, *count_matrix = nullptr, *pos = nullptr, *send_sel = nullptr,
+            *recv_sel = nullptr;
+    uint32_t *order = nullptr;
+    unsigned long long *hist = nullptr;
+    uint8_t *send_xq = nullptr, *recv_xq = nullptr;
+    float *send_w = nullptr, *recv_w = nullptr, *rows = nullptr, *back = nullptr;
+    // pinned host
+    int32_t *h_matrix = nullptr;
+    std::vector<int32_t> last_recv;  // rows received from each rank in the most recent step
+    char err[384] = {0};
+};
+
+static int ep_fail(EpState *s, int code, const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(s->err, sizeof(s->err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+const char *ep_last_error(const EpState *s) { return s ? s->err : ""; }
+
+void ep_destroy(EpState *s)
+{
+    if (!s) return;
+    if (s->comm && s->own_comm && s->nccl) s->nccl->CommDestroy(s->comm);
+    if (s->owner) dsmoe_destroy(s->owner);
+    cudaFree(s->replica_slot), cudaFree(s->send_counts), cudaFree(s->count_matrix), cudaFree(s->pos), cudaFree(s->send_sel);
+    cudaFree(s->recv_sel), cudaFree(s->order), cudaFree(s->hist), cudaFree(s->send_xq), cudaFree(s->recv_xq);
+    cudaFree(s->send_w), cudaFree(s->recv_w), cudaFree(s->rows), cudaFree(s->back);
+    if (s->h_matrix) cudaFreeHost(s->h_matrix);
+    delete s;
+}
+
+int ep_get_unique_id(uint8_t *id128)
+{
+    const NcclApi *api = nccl_api();
+    if (!api) return DSMOE_ERR_NCCL;
+    nccl_unique_id id;
+    if (api->GetUniqueId(&id) != 0) return DSMOE_ERR_NCCL;
+    memcpy(id128, id.internal, 128);
+    return DSMOE_OK;
+}
+
+int ep_create(const dsmoe_config &cfg, int device, const uint8_t *id128, void *adopt_comm, int rank, int world,
+              uint32_t max_replicas, uint32_t recv_capacity_rows, EpState **out, char *err, size_t err_len)
+{
+    auto fail_early = [&](int code, const char *msg) {
+        snprintf(err, err_len, "%s", msg);
+        return code;
+    };
+    *out = nullptr;
+    if (world < 1 || rank < 0 || rank >= world || cfg.n_expert % (uint32_t)world) return fail_early(DSMOE_ERR_ARG, "ep_init: bad rank / world, or the experts do not divide evenly over the ranks");
+    const uint32_t per = cfg.n_expert / (uint32_t)world;
+    if ((per + max_replicas) % 32 || per + max_replicas > 512) return fail_early(DSMOE_ERR_ARG, "ep_init: experts per rank + replicas must be a multiple of 32, at most 512");
+    const NcclApi *api = nccl_api();
+    if (!api) return fail_early(DSMOE_ERR_NCCL, "ep_init: libnccl.so.2 could not be loaded");
+    EpState *s = new (std::nothrow) EpState();
+    if (!s) return fail_early(DSMOE_ERR_NOMEM, "ep_init: out of host memory");
+    s->nccl = api, s->rank = rank, s->world = world, s->per_rank = per, s->max_replicas = max_replicas;
+    s->max_pairs = cfg.max_tokens * cfg.n_expert_used;
+    s->recv_cap = recv_capacity_rows ? recv_capacity_rows : 2u * s->max_pairs;
+    s->row_bytes = cfg.n_embd / QK_K * Q8K_BYTES;
+    if (s->row_bytes % 16) {
+        delete s;
+        return fail_early(DSMOE_ERR_ARG, "ep_init: the Q8_K row of a token must be a multiple of 16 bytes (n_embd a multiple of 1024)");
+    }
+    if (adopt_comm) {
+        s->comm = adopt_comm;
+    } else {
+        nccl_unique_id id;
+        memcpy(id.internal, id128, 128);
+        const int rc = api->CommInitRank(&s->comm, world, id, rank);
+        if (rc != 0) {
+            snprintf(err, err_len, "ep_init: ncclCommInitRank: %s", api->GetErrorString(rc));
+            delete s;
+            return DSMOE_ERR_NCCL;
+        }
+        s->own_comm = true;
+    }
+    dsmoe_config oc = cfg;
+    oc.n_expert = per + max_replicas, oc.n_expert_used = 1, oc.max_tokens = s->recv_cap;
+    if (int rc = dsmoe_create(&oc, device, &s->owner)) {
+        ep_destroy(s);
+        return fail_early(rc, "ep_init: could not create the owner-side handle (receive capacity too large for the device?)");
+    }
+    const size_t P = s->max_pairs ? s->max_pairs : 1, C = s->recv_cap, W = (size_t)world;
+    bool ok = true;
+    auto alloc = [&](auto **p, size_t n) { ok = ok && cudaMalloc((void **)p, n * sizeof(**p)) == cudaSuccess; };
+    alloc(&s->replica_slot, cfg.n_expert), alloc(&s->send_counts, W), alloc(&s->count_matrix, W * W), alloc(&s->pos, P);
+    alloc(&s->order, P), alloc(&s->hist, cfg.n_expert), alloc(&s->send_sel, P), alloc(&s->recv_sel, C);
+    alloc(&s->send_xq, P * s->row_bytes), alloc(&s->recv_xq, C * s->row_bytes), alloc(&s->send_w, P), alloc(&s->recv_w, C);
+    alloc(&s->rows, C * cfg.n_embd), alloc(&s->back, P * cfg.n_embd);
+    ok = ok && cudaMallocHost((void **)&s->h_matrix, W * W * sizeof(int32_t)) == cudaSuccess;
+    ok = ok && cudaMemset(s->replica_slot, 0xFF, cfg.n_expert * sizeof(int32_t)) == cudaSuccess;
+    ok = ok && cudaMemset(s->hist, 0, cfg.n_expert * sizeof(unsigned long long)) == cudaSuccess;
+    if (!ok) {
+        cudaGetLastError();
+        ep_destroy(s);
+        return fail_early(DSMOE_ERR_NOMEM, "ep_init: device allocation failed");
+    }
+    s->last_recv.assign(W, 0);
+    *out = s;
+    return DSMOE_OK;
+}
+
+dsmoe_handle *ep_owner(EpState *s) { return s->owner; }
+int ep_rank(const EpState *s) { return s->rank; }
+int ep_world(const EpState *s) { return s->world; }
+
+int ep_set_replicas(EpState *s, uint32_t n_expert, const int32_t *ids, uint32_t n)
+{
+    if (n > s->max_replicas) return ep_fail(s, DSMOE_ERR_BOUNDS, "ep_set_replicas: %u replicas, the handle was initialised for %u", n, s->max_replicas);
+    std::vector<int32_t> slot(n_expert, -1);
+    for (uint32_t i = 0; i < n; ++i) {
+        if (ids[i] < 0 || (uint32_t)ids[i] >= n_expert || slot[ids[i]] >= 0) return ep_fail(s, DSMOE_ERR_ARG, "ep_set_replicas: bad or repeated expert id %d", ids[i]);
+        slot[ids[i]] = (int32_t)i;
+    }
+    if (cudaDeviceSynchronize() != cudaSuccess ||
+        cudaMemcpy(s->replica_slot, slot.data(), n_expert * sizeof(int32_t), cudaMemcpyHostToDevice) != cudaSuccess)
+        return ep_fail(s, DSMOE_ERR_CUDA, "ep_set_replicas: %s", cudaGetErrorString(cudaGetLastError()));
+    return DSMOE_OK;
+}
+
+int ep_expert_counts(EpState *s, cudaStream_t st, uint32_t n_expert, uint64_t *host_out, int reset)
+{
+    cudaError_t e = cudaMemcpyAsync(host_out, s->hist, n_expert * sizeof(uint64_t), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess && reset) e = cudaMemsetAsync(s->hist, 0, n_expert * sizeof(uint64_t), st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    return e == cudaSuccess ? DSMOE_OK : ep_fail(s, DSMOE_ERR_CUDA, "ep_expert_counts: %s", cudaGetErrorString(e));
+}
+
+int ep_last_recv_rows(const EpState *s, int32_t *per_rank_out)
+{
+    for (int i = 0; i < s->world; ++i) per_rank_out[i] = s->last_recv[(size_t)i];
+    return DSMOE_OK;
+}
+
+#define EP_NCCL(call, what)                                                                        \
+    do {                                                                                           \
+        const int rc_ = (call);                                                                    \
+        if (rc_ != 0) return ep_fail(s, DSMOE_ERR_NCCL, "%s: %s", what, s->nccl->GetErrorString(rc_)); \
+    } while (0)
+#define EP_CUDA(call, what)                                                                        \
+    do {                                                                                           \
+        const cudaError_t e_ = (call);                                                             \
+        if (e_ != cudaSuccess) return ep_fail(s, DSMOE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e_)); \
+    } while (0)
+
+// Dispatch, owner compute, combine and slot sum for rows that are already routed and quantised on this rank.
+// selected / weights: [n_tokens][k]; xq: Q8_K rows [n_tokens]; out: [n_tokens][n_embd]. Collective: every rank calls it.
+int ep_forward(EpState *s, cudaStream_t st, uint32_t layer, const uint8_t *xq, const int32_t *selected, const float *weights,
+               uint32_t n_tokens, uint32_t k, uint32_t n_embd, float *out, int *n_launched, cudaEvent_t *marks)
+{
+    const uint32_t P = n_tokens * k, W = (uint32_t)s->world;
+    if (P > s->max_pairs) return ep_fail(s, DSMOE_ERR_BOUNDS, "moe_forward_ep: %u pairs, the handle was created for %u", P, s->max_pairs);
+    auto mark = [&](int i) {
+        if (marks) cudaEventRecord(marks[i], st);
+    };
+    const EpRoute r = {selected, s->replica_slot, P, s->per_rank, (uint32_t)s->rank, W};
+    mark(0);
+    // 1. counts by destination, gathered from every rank; placement and row gather run while the matrix travels
+    ep_count_kernel<<<W, 256, 0, st>>>(r, s->send_counts, s->hist);
+    EP_NCCL(s->nccl->AllGather(s->send_counts, s->count_matrix, W, NCCL_INT32, s->comm, st), "count exchange");
+    EP_CUDA(cudaMemcpyAsync(s->h_matrix, s->count_matrix, (size_t)W * W * sizeof(int32_t), cudaMemcpyDeviceToHost, st), "count read");
+    if (P) {
+        ep_place_kernel<<<W, 256, 0, st>>>(r, s->send_counts, s->pos, s->order);
+        ep_gather_kernel<<<(P + 7) / 8, 256, 0, st>>>(r, s->order, xq, weights, k, s->row_bytes, s->send_xq, s->send_sel, s->send_w);
+    }
+    EP_CUDA(cudaGetLastError(), "plan launch");
+    *n_launched += P ? 3 : 1;
+    EP_CUDA(cudaStreamSynchronize(st), "count read");
+    mark(1);
+    // 2. sizes; every rank evaluates every rank's receive total, so an overflow is reported by all of them alike
+    const int32_t *M = s->h_matrix;  // M[src * W + dst]
+    for (uint32_t d = 0; d < W; ++d) {
+        uint64_t total = 0;
+        for (uint32_t src = 0; src < W; ++src) total += (uint32_t)M[src * W + d];
+        if (total > s->recv_cap)
+            return ep_fail(s, DSMOE_ERR_BOUNDS, "moe_forward_ep: rank %u would receive %llu rows, its buffer holds %u (raise recv_capacity_rows or replicate the hot experts)",
+                           d, (unsigned long long)total, s->recv_cap);
+    }
+    std::vector<size_t> soff(W + 1, 0), roff(W + 1, 0);
+    for (uint32_t i = 0; i < W; ++i) {
+        soff[i + 1] = soff[i] + (uint32_t)M[(uint32_t)s->rank * W + i];
+        roff[i + 1] = roff[i] + (uint32_t)M[i * W + (uint32_t)s->rank];
+        s->last_recv[i] = M[i * W + (uint32_t)s->rank];
+    }
+    const size_t R = roff[W];
+    // 3. dispatch
+    EP_NCCL(s->nccl->GroupStart(), "dispatch");
+    for (uint32_t peer = 0; peer < W; ++peer) {
+        const size_t sc = soff[peer + 1] - soff[peer], rc = roff[peer + 1] - roff[peer];
+        if (sc) {
+            EP_NCCL(s->nccl->Send(s->send_xq + soff[peer] * s->row_bytes, sc * s->row_bytes, NCCL_UINT8, (int)peer, s->comm, st), "dispatch send");
+            EP_NCCL(s->nccl->Send(s->send_sel + soff[peer], sc, NCCL_INT32, (int)peer, s->comm, st), "dispatch send");
+            EP_NCCL(s->nccl->Send(s->send_w + soff[peer], sc * 4, NCCL_UINT8, (int)peer, s->comm, st), "dispatch send");
+        }
+        if (rc) {
+            EP_NCCL(s->nccl->Recv(s->recv_xq + roff[peer] * s->row_bytes, rc * s->row_bytes, NCCL_UINT8, (int)peer, s->comm, st), "dispatch recv");
+            EP_NCCL(s->nccl->Recv(s->recv_sel + roff[peer], rc, NCCL_INT32, (int)peer, s->comm, st), "dispatch recv");
+            EP_NCCL(s->nccl->Recv(s->recv_w + roff[peer], rc * 4, NCCL_UINT8, (int)peer, s->comm, st), "dispatch recv");
+        }
+    }
+    EP_NCCL(s->nccl->GroupEnd(), "dispatch");
+    mark(2);
+    // 4. the owner's compute: every received row is one (token, slot) pair of one local expert
+    if (R) {
+        const uint64_t before = dsmoe_launch_count(s->owner);
+        const int rc = dsmoe_expert_ffn(s->owner, st, layer, s->recv_xq, s->recv_sel, s->recv_w, (uint32_t)R, s->rows);
+        if (rc != DSMOE_OK) return ep_fail(s, rc, "moe_forward_ep: owner compute: %s", dsmoe_last_error(s->owner));
+        *n_launched += (int)(dsmoe_launch_count(s->owner) - before);
+    }
+    mark(3);
+    // 5. combine: the rows travel back along the same splits and land in send order
+    EP_NCCL(s->nccl->GroupStart(), "combine");
+    for (uint32_t peer = 0; peer < W; ++peer) {
+        const size_t sc = soff[peer + 1] - soff[peer], rc = roff[peer + 1] - roff[peer];
+        if (rc) EP_NCCL(s->nccl->Send(s->rows + roff[peer] * n_embd, rc * n_embd * 4, NCCL_UINT8, (int)peer, s->comm, st), "combine send");
+        if (sc) EP_NCCL(s->nccl->Recv(s->back + soff[peer] * n_embd, sc * n_embd * 4, NCCL_UINT8, (int)peer, s->comm, st), "combine recv");
+    }
+    EP_NCCL(s->nccl->GroupEnd(), "combine");
+    mark(4);
+    // 6. slots summed in slot order, each row read where it landed
+    if (P) {
+        launch_moe_sum(st, s->back, s->pos, out, n_embd, k, n_tokens);
+        EP_CUDA(cudaGetLastError(), "slot sum");
+        *n_launched += 1;
+    }
+    mark(5);
+    return DSMOE_OK;
+}
+
+}  // namespace dsmoe

@@ -74,8 +74,19 @@ void launch_dequant_iq2xxs(cudaStream_t st, const uint8_t *blocks, uint64_t n_bl
 void launch_dequant_q2k(cudaStream_t st, const uint8_t *blocks, uint64_t n_blocks, float *out, int ieee);
 void launch_relayout_iq2xxs(cudaStream_t st, const uint8_t *src, uint8_t *dst, uint64_t n_rows, uint32_t xb, int inverse);
 void launch_relayout_q2k(cudaStream_t st, const uint8_t *src, uint8_t *dst, uint64_t n_rows, uint32_t mb, int inverse);
+// Operands of the hyper-connection merge that follows the routed experts in the reference (hc_expand,
+// engine/src/kernels/hc.rs:212-251). out_hc == nullptr: no merge.
+struct HcEpilogue {
+    const float *shared;     // block_out: the shared expert's output [n_tokens][n_embd]
+    const float *residual;   // residual_hc [n_tokens][n_hc][n_embd]
+    const float *split;      // [n_tokens][mix_hc]: pre (n_hc), post (n_hc), comb (n_hc * n_hc)
+    float *out_hc;           // [n_tokens][n_hc][n_embd]
+    uint32_t n_hc, mix_hc;
+};
 void launch_moe_sum(cudaStream_t st, const float *down, const int32_t *pos, float *out, uint32_t out_dim, uint32_t k,
-                    uint32_t n_tokens);
+                    uint32_t n_tokens, const HcEpilogue *hc = nullptr);
+void launch_hc_expand(cudaStream_t st, const float *block_add, uint32_t n_embd, uint32_t n_tokens, const HcEpilogue &hc);
+void launch_bf16_to_f32(cudaStream_t st, const uint16_t *in, float *out, uint64_t n);
 
 // Router logits and shared expert (shared.cu)
 void launch_quantize_q8_0(cudaStream_t st, const float *x, int8_t *xq, float *xscale, uint64_t in_dim, uint64_t n_tok);
@@ -143,6 +154,8 @@ struct PrefillArgs {
     int layout, ieee;
     int *status;
     cudaEvent_t *phase_events;         // optional, 6 events: start, grouped+gathered, gate/up, q8k+gather, down, sum
+    const HcEpilogue *hc;              // optional: hc_expand fused into the slot sum
+    cudaEvent_t before_sum;            // optional: the stream waits for this event before the slot sum (shared expert done)
 };
 // Everything after the router and the Q8_K of x. Returns the number of kernels launched.
 int launch_prefill_experts(cudaStream_t st, const PrefillArgs &p);

@@ -1050,7 +1050,8 @@ int launch_prefill_experts(cudaStream_t st, const PrefillArgs &p)
     pf_grouped_gemm_kernel<PF_Q2K><<<sms, PF_THREADS, PF_SMEM_TOTAL, st>>>(d);
     mark(4);
     // 6. slots summed in slot order
-    launch_moe_sum(st, reinterpret_cast<const float *>(w + L.down_pair), nullptr, p.out, p.n_embd, p.k, p.n_tokens);
+    if (p.before_sum) cudaStreamWaitEvent(st, p.before_sum, 0);
+    launch_moe_sum(st, reinterpret_cast<const float *>(w + L.down_pair), nullptr, p.out, p.n_embd, p.k, p.n_tokens, p.hc);
     mark(5);
     return n + 6;
 }

@@ -397,9 +397,28 @@ void launch_relayout_q2k(cudaStream_t st, const uint8_t *src, uint8_t *dst, uint
 // ---------------------------------------------------------------------------------------------------------------
 // out[tok] = ((0 + r_0) + r_1) + ... over the token's k slot rows, r_e = down[pos ? pos[tok*k+e] : tok*k+e].
 // VEC = 4: one float4 per thread (out_dim a multiple of 4, pointers 16-byte aligned); VEC = 1 otherwise.
+// With hc.out_hc set, the hyper-connection merge that consumes the sum in the reference (hc_expand,
+// engine/src/kernels/hc.rs:212-251; call engine/src/session.rs:2162-2175) runs in the same thread, so the routed sum
+// is not read back from memory: block_v = shared[t][d] + routed[t][d];
+// out_hc[t][dst][d] = block_v * post[dst] + sum over src of comb[dst + src * n_hc] * residual[t][src][d], post and comb
+// taken from the token's split row at offsets n_hc and 2 n_hc, every multiplication and addition rounded on its own.
+__device__ __forceinline__ void hc_expand_elem(const HcEpilogue &hc, uint64_t tok, uint64_t d, uint32_t n_embd, float routed)
+{
+    const float block_v = __fadd_rn(hc.shared[tok * n_embd + d], routed);
+    const float *sp = hc.split + tok * hc.mix_hc;
+    for (uint32_t dst = 0; dst < hc.n_hc; ++dst) {
+        float acc = __fmul_rn(block_v, sp[hc.n_hc + dst]);
+        for (uint32_t src = 0; src < hc.n_hc; ++src)
+            acc = __fadd_rn(acc, __fmul_rn(sp[2 * hc.n_hc + dst + src * hc.n_hc],
+                                           hc.residual[(tok * hc.n_hc + src) * n_embd + d]));
+        hc.out_hc[(tok * hc.n_hc + dst) * n_embd + d] = acc;
+    }
+}
+
 template <int VEC>
 __global__ void __launch_bounds__(256) moe_sum_kernel(const float *__restrict__ down, const int32_t *__restrict__ pos,
-                                                       float *__restrict__ out, uint32_t out_dim, uint32_t k, uint64_t n)
+                                                       float *__restrict__ out, uint32_t out_dim, uint32_t k, uint64_t n,
+                                                       HcEpilogue hc)
 {
     const uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (gid >= n) return;
@@ -421,16 +440,65 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(const float *__restrict__ 
     }
     if (VEC == 4) *reinterpret_cast<float4 *>(out + tok * out_dim + col) = make_float4(acc[0], acc[1], acc[2], acc[3]);
     else out[tok * out_dim + col] = acc[0];
+    if (hc.out_hc != nullptr) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) hc_expand_elem(hc, tok, col + i, out_dim, acc[i]);
+    }
 }
 
 void launch_moe_sum(cudaStream_t st, const float *down, const int32_t *pos, float *out, uint32_t out_dim, uint32_t k,
-                    uint32_t n_tokens)
+                    uint32_t n_tokens, const HcEpilogue *hc)
 {
     if (n_tokens == 0 || out_dim == 0) return;
+    HcEpilogue h = {};
+    if (hc) h = *hc;
     const bool vec = out_dim % 4 == 0 && (((uintptr_t)down | (uintptr_t)out) & 15) == 0;
     const uint64_t n = (uint64_t)n_tokens * (vec ? out_dim / 4 : out_dim);
-    if (vec) moe_sum_kernel<4><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(down, pos, out, out_dim, k, n);
-    else moe_sum_kernel<1><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(down, pos, out, out_dim, k, n);
+    if (vec) moe_sum_kernel<4><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(down, pos, out, out_dim, k, n, h);
+    else moe_sum_kernel<1><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(down, pos, out, out_dim, k, n, h);
+}
+
+// hc_expand on its own (engine/src/kernels/hc.rs:212-251): one thread per (token, d); block_add may be null
+// (has_add == 0: the routed experts did not run).
+__global__ void __launch_bounds__(256) hc_expand_kernel(const float *__restrict__ block_add, uint32_t n_embd, uint64_t n,
+                                                         HcEpilogue hc)
+{
+    const uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= n) return;
+    const uint64_t tok = gid / n_embd, d = gid - tok * n_embd;
+    if (block_add != nullptr) {
+        hc_expand_elem(hc, tok, d, n_embd, block_add[gid]);
+        return;
+    }
+    const float block_v = hc.shared[gid];
+    const float *sp = hc.split + tok * hc.mix_hc;
+    for (uint32_t dst = 0; dst < hc.n_hc; ++dst) {
+        float acc = __fmul_rn(block_v, sp[hc.n_hc + dst]);
+        for (uint32_t src = 0; src < hc.n_hc; ++src)
+            acc = __fadd_rn(acc, __fmul_rn(sp[2 * hc.n_hc + dst + src * hc.n_hc],
+                                           hc.residual[(tok * hc.n_hc + src) * n_embd + d]));
+        hc.out_hc[(tok * hc.n_hc + dst) * n_embd + d] = acc;
+    }
+}
+
+void launch_hc_expand(cudaStream_t st, const float *block_add, uint32_t n_embd, uint32_t n_tokens, const HcEpilogue &hc)
+{
+    const uint64_t n = (uint64_t)n_tokens * n_embd;
+    if (n == 0) return;
+    hc_expand_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(block_add, n_embd, n, hc);
+}
+
+// bf16 -> f32, exact (the bf16 bit pattern is the upper half of the f32 one)
+__global__ void __launch_bounds__(256) bf16_to_f32_kernel(const uint16_t *__restrict__ in, float *__restrict__ out, uint64_t n)
+{
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __uint_as_float((uint32_t)in[i] << 16);
+}
+
+void launch_bf16_to_f32(cudaStream_t st, const uint16_t *in, float *out, uint64_t n)
+{
+    if (n == 0) return;
+    bf16_to_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(in, out, n);
 }
 
 }  // namespace dsmoe

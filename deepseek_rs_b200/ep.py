@@ -9,10 +9,12 @@ tokens. One exchange each way:
   combine   the owner returns the pair's down-projection row (f32 [n_embd]); the source sums a token's k rows in slot
             order, so the result does not depend on arrival order.
 
-The exchanges are ``torch.distributed.all_to_all_single`` (NCCL over NVLink on GPUs, gloo in the CPU tests); the
-compute on each side goes through the C ABI (``MoeKernels``). Split sizes are exchanged first and read on the host,
-which costs one synchronisation per step. ``route_fn`` / ``expert_fn`` can be replaced, which is how the CPU tests run
-the same plan with the oracle standing in for the kernels.
+Two implementations of the same plan live here. ``ExpertParallelHandle`` is the product path: a thin caller of the C
+ABI (``dsmoe_ep_init`` / ``dsmoe_moe_forward_ep``), where counting, placement, row gather, the NCCL exchanges, the
+owner's compute and the slot sum all happen inside the library on one stream. ``ExpertParallelMoe`` expresses the plan
+with ``torch.distributed.all_to_all_single`` and replaceable ``route_fn`` / ``expert_fn``: it runs on gloo without a
+GPU, with the oracle standing in for the kernels, which is how the CPU tests check the plan itself (dispatch order,
+replicas, combine positions) with two ranks.
 """
 from __future__ import annotations
 
@@ -22,6 +24,81 @@ import torch
 import torch.distributed as dist
 
 from .formats import Q8K_BYTES, QK_K
+
+
+class ExpertParallelHandle:
+    """Expert-parallel state of one rank behind the C ABI. ``kernels``: a MoeKernels created with the model's n_expert
+    and top-k and max_tokens = the tokens this rank routes per call. The NCCL communicator is created inside the library
+    from a unique id that rank 0 makes and ``torch.distributed`` (any backend) carries to the other ranks."""
+
+    def __init__(self, kernels, rank: int, world: int, max_replicas: int = 0, recv_capacity_rows: int = 0, group=None):
+        import ctypes as C
+
+        self.k, self.rank, self.world, self.max_replicas = kernels, rank, world, max_replicas
+        self.per_rank = kernels.cfg.n_expert // world
+        lib = kernels.lib
+        uid = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            buf = (C.c_uint8 * 128)()
+            kernels._check(lib.dsmoe_ep_get_unique_id(buf))
+            uid = torch.tensor(list(buf), dtype=torch.uint8)
+        if world > 1:
+            dev = torch.device("cuda", kernels.device) if dist.get_backend(group) == "nccl" else torch.device("cpu")
+            uid = uid.to(dev)
+            dist.broadcast(uid, src=0, group=group)
+            uid = uid.cpu()
+        ids = (C.c_uint8 * 128)(*uid.tolist())
+        kernels._check(lib.dsmoe_ep_init(kernels.h, ids, rank, world, max_replicas, recv_capacity_rows))
+
+    def layer_register(self, layer: int, gate, up, down, layout: int):
+        """The rank's shard [own experts | replicas], per_rank + max_replicas experts long, already in ``layout``."""
+        import ctypes as C
+
+        p = lambda t: C.c_void_p(t.data_ptr())
+        self.k._check(self.k.lib.dsmoe_ep_layer_register(self.k.h, layer, p(gate), p(up), p(down), layout))
+
+    def set_replicas(self, expert_ids):
+        import ctypes as C
+
+        arr = (C.c_int32 * len(expert_ids))(*[int(e) for e in expert_ids])
+        self.k._check(self.k.lib.dsmoe_ep_set_replicas(self.k.h, arr, len(expert_ids)))
+
+    def expert_counts(self, reset: bool = False) -> torch.Tensor:
+        """Running selections per expert on this rank (int64 [n_expert], host)."""
+        import ctypes as C
+
+        out = torch.zeros(self.k.cfg.n_expert, dtype=torch.int64)
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        self.k._check(self.k.lib.dsmoe_ep_expert_counts(self.k.h, stream, C.c_void_p(out.data_ptr()), int(reset)))
+        return out
+
+    def last_recv_rows(self) -> list:
+        import ctypes as C
+
+        arr = (C.c_int32 * self.world)()
+        self.k._check(self.k.lib.dsmoe_ep_last_recv_rows(self.k.h, arr))
+        return list(arr)
+
+    def set_phase_events(self, events):
+        import ctypes as C
+
+        if not events:
+            self.k._check(self.k.lib.dsmoe_ep_set_phase_events(self.k.h, None, 0))
+            return
+        arr = (C.c_void_p * 6)(*[C.c_void_p(e.cuda_event) for e in events])
+        self.k._check(self.k.lib.dsmoe_ep_set_phase_events(self.k.h, arr, 6))
+
+    def forward(self, layer: int, x, logits, out=None, selected_out=None, weights_out=None):
+        import ctypes as C
+
+        T = x.shape[0]
+        if out is None:
+            out = torch.empty((T, self.k.cfg.n_embd), dtype=torch.float32, device=x.device)
+        p = lambda t: None if t is None else C.c_void_p(t.data_ptr())
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        self.k._check(self.k.lib.dsmoe_moe_forward_ep(self.k.h, stream, layer, p(x), p(logits), T, p(out), p(selected_out),
+                                                     p(weights_out)))
+        return out
 
 
 @dataclass

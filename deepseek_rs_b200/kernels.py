@@ -202,6 +202,37 @@ class MoeKernels:
     def layer_register(self, layer: int, gate, up, down, layout: int):
         self._check(self.lib.dsmoe_layer_register(self.h, layer, _ptr(gate), _ptr(up), _ptr(down), layout))
 
+    def layer_register_extras(self, layer: int, router_f16=None, router_bias=None, hash_table=None, shared_gate=None,
+                              shared_up=None, shared_down=None):
+        """The tensors beside the routed experts (router matrix, bias, hash table, shared expert); any may be None."""
+        hash_rows = 0 if hash_table is None else hash_table.numel() // self.cfg.n_expert_used
+        self._check(self.lib.dsmoe_layer_register_extras(self.h, layer, _ptr(router_f16), _ptr(router_bias),
+                                                         _ptr(hash_table), hash_rows, _ptr(shared_gate), _ptr(shared_up),
+                                                         _ptr(shared_down)))
+
+    def ffn_forward(self, layer: int, x, routed_out, logits=None, tokens=None, token_scalar: int = 0, hash_mode: int = 0,
+                    shared_out=None, residual_hc=None, hc_split=None, out_hc=None, selected_out=None, weights_out=None):
+        """Steps g, h, i of Session::decode_attn_out_and_ffn (engine/src/session.rs:1894-2180) in one call. x: f32 or
+        bfloat16 [T, n_embd]."""
+        p = lambda t: None if t is None else t.data_ptr()
+        a = _lib.FfnArgs()
+        a.x, a.x_dtype, a.n_tokens = p(x), (_lib.DTYPE_BF16 if x.dtype == torch.bfloat16 else _lib.DTYPE_F32), x.shape[0]
+        a.logits, a.tokens, a.token_scalar, a.hash_mode = p(logits), p(tokens), token_scalar, hash_mode
+        a.routed_out, a.shared_out = p(routed_out), p(shared_out)
+        a.residual_hc, a.hc_split, a.out_hc = p(residual_hc), p(hc_split), p(out_hc)
+        if out_hc is not None:
+            a.n_hc, a.mix_hc = residual_hc.shape[1], hc_split.shape[1]
+        a.selected_out, a.weights_out = p(selected_out), p(weights_out)
+        for t in (x, logits, tokens, routed_out, shared_out, residual_hc, hc_split, out_hc, selected_out, weights_out):
+            assert t is None or (t.is_cuda and t.is_contiguous())
+        self._check(self.lib.dsmoe_ffn_forward(self.h, _stream(), layer, C.byref(a)))
+
+    def hc_expand(self, block_out, block_add, residual_hc, split, out_hc, n_embd: int, n_hc: int, n_tokens: int,
+                  mix_hc: int, has_add: int):
+        """engine/src/kernels/hc.rs:212"""
+        self._check(self.lib.dsmoe_hc_expand(self.h, _stream(), _ptr(block_out), _ptr(block_add), _ptr(residual_hc),
+                                             _ptr(split), _ptr(out_hc), n_embd, n_hc, n_tokens, mix_hc, has_add))
+
     def moe_forward(self, layer: int, x, logits, n_tokens: int, out, selected_out=None, weights_out=None):
         self._check(self.lib.dsmoe_moe_forward(self.h, _stream(), layer, _ptr(x), _ptr(logits), n_tokens, _ptr(out),
                                                _ptr(selected_out), _ptr(weights_out)))

@@ -49,7 +49,7 @@ typedef enum dsmoe_status {
     DSMOE_OK = 0,
     DSMOE_ERR_ARG = -1,     /* bad pointer, size, alignment or enum */
     DSMOE_ERR_CUDA = -2,    /* a CUDA runtime call or launch failed */
-    DSMOE_ERR_NCCL = -3,    /* reserved for the expert-parallel path */
+    DSMOE_ERR_NCCL = -3,    /* an NCCL call failed, or libnccl.so.2 could not be loaded (expert-parallel calls) */
     DSMOE_ERR_TIMEOUT = -4, /* a bounded device-side wait expired */
     DSMOE_ERR_BOUNDS = -5,  /* a size exceeds what the handle was created for */
     DSMOE_ERR_NOMEM = -6,
@@ -247,6 +247,58 @@ DSMOE_API int dsmoe_moe_forward(dsmoe_handle *h, dsmoe_stream stream, uint32_t l
 DSMOE_API int dsmoe_expert_ffn(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, const uint8_t *xq,
                                const int32_t *selected, const float *weights, uint32_t n_tokens, float *out);
 
+/* The tensors beside the routed experts of one layer, all optional (NULL / 0), borrowed like the expert tensors:
+ *   router_f16    blk.{il}.ffn_gate_inp.weight, f16 bit patterns [n_expert][n_embd] (engine/src/engine.rs:178); with it
+ *                 dsmoe_ffn_forward computes the logits itself (matmul_f16, engine/src/session.rs:1995-2008)
+ *   router_bias   f32 [n_expert], added to the selection score only (engine/src/kernels/moe.rs:229-262); the reference
+ *                 binds none for this model (engine/src/engine.rs:179)
+ *   hash_table    blk.{il}.ffn_gate_tid2eid, i32 [hash_rows][n_expert_used] (engine/src/engine.rs:177); layers below
+ *                 N_HASH_LAYER = 3 carry one (engine/src/model.rs:19)
+ *   shared_*      blk.{il}.ffn_{gate,up,down}_shexp.weight, Q8_0 blocks (engine/src/session.rs:1894-1987) */
+DSMOE_API int dsmoe_layer_register_extras(dsmoe_handle *h, uint32_t layer, const uint16_t *router_f16,
+                                          const float *router_bias, const int32_t *hash_table, uint32_t hash_rows,
+                                          const uint8_t *shared_gate, const uint8_t *shared_up,
+                                          const uint8_t *shared_down);
+
+enum { DSMOE_DTYPE_F32 = 0, DSMOE_DTYPE_BF16 = 1 };
+
+/* Operands of dsmoe_ffn_forward. Unused optional pointers are NULL. */
+typedef struct dsmoe_ffn_args {
+    const void *x;             /* hidden states (ffn_norm) [n_tokens][n_embd]: f32 as the reference keeps them, or bf16,
+                                  which is widened exactly before the same Q8_K / Q8_0 steps */
+    int32_t x_dtype;           /* DSMOE_DTYPE_F32 or DSMOE_DTYPE_BF16 */
+    uint32_t n_tokens;
+    const float *logits;       /* optional [n_tokens][n_expert]; NULL: computed from the registered router matrix */
+    const int32_t *tokens;     /* optional token ids [n_tokens] for hash routing (NULL: token_scalar for every row) */
+    int32_t token_scalar;
+    uint32_t hash_mode;        /* 0: score routing (what the reference's live call passes, engine/src/session.rs:2056);
+                                  1: selected = hash_table[token] (engine/src/kernels/moe.rs:211-228) */
+    float *routed_out;         /* required: slot sum of the routed experts [n_tokens][n_embd] (Session::routed_out) */
+    float *shared_out;         /* optional: shared-expert output [n_tokens][n_embd] (Session::shared_out) */
+    /* optional hyper-connection merge, hc_expand (engine/src/kernels/hc.rs:212-251, call engine/src/session.rs:2162-2175):
+     * out_hc[t][dst][d] = (shared + routed)[t][d] * post[dst] + sum_src comb[dst + src * n_hc] * residual_hc[t][src][d],
+     * post / comb at offsets n_hc / 2 n_hc of the token's hc_split row. Needs a registered shared expert. */
+    const float *residual_hc;  /* [n_tokens][n_hc][n_embd] (Session::after_attn_hc) */
+    const float *hc_split;     /* [n_tokens][mix_hc] */
+    float *out_hc;             /* [n_tokens][n_hc][n_embd] (Session::after_ffn_hc) */
+    uint32_t n_hc, mix_hc;
+    int32_t *selected_out;     /* optional [n_tokens][n_expert_used] */
+    float *weights_out;        /* optional [n_tokens][n_expert_used] */
+} dsmoe_ffn_args;
+
+/* Steps g, h and i of Session::decode_attn_out_and_ffn (engine/src/session.rs:1894-2180) for n_tokens rows in one call:
+ * shared expert (on an internal side stream, concurrently with the routed path), router logits, router_select (score,
+ * bias or hash mode), Q8_K, routed experts, slot sum and, when out_hc is set, the hyper-connection merge fused into the
+ * slot sum (batched path) or run right after it. On return the caller's stream has been made to wait for the side
+ * stream, so every output is ordered on `stream` like the other calls. */
+DSMOE_API int dsmoe_ffn_forward(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, const dsmoe_ffn_args *args);
+
+/* hc_expand on its own (engine/src/kernels/hc.rs:212-251): block_out / block_add f32 [n_tokens][n_embd] (block_add is
+ * read when has_add != 0), residual_hc [n_tokens][n_hc][n_embd], split [n_tokens][mix_hc], out_hc like residual_hc. */
+DSMOE_API int dsmoe_hc_expand(dsmoe_handle *h, dsmoe_stream stream, const float *block_out, const float *block_add,
+                              const float *residual_hc, const float *split, float *out_hc, uint32_t n_embd,
+                              uint32_t n_hc, uint32_t n_tokens, uint32_t mix_hc, uint32_t has_add);
+
 /* Same with host buffers: copies x and logits in, runs dsmoe_moe_forward on an internal stream, copies out (and the
  * optional routing) back and waits. Host buffers should be page-locked for full copy speed. */
 DSMOE_API int dsmoe_moe_forward_host(dsmoe_handle *h, uint32_t layer, const float *x_host, const float *logits_host,
@@ -262,6 +314,98 @@ DSMOE_API int dsmoe_moe_forward_host_async(dsmoe_handle *h, uint32_t layer, cons
                                            const float *logits_host, uint32_t n_tokens, float *out_host,
                                            int32_t *selected_out_host, float *weights_out_host);
 DSMOE_API int dsmoe_host_synchronize(dsmoe_handle *h);
+
+/* ------------------------------------------------------------------------------------------------------------ */
+/* Expert parallel: experts sharded over the GPUs of one box, NCCL dispatch and combine                           */
+/* ------------------------------------------------------------------------------------------------------------ */
+
+/* No counterpart in the reference, which is single-GPU (one context, one stream: engine/src/engine.rs:73-74); defined by
+ * "same result as one GPU". Rank r of `world` owns experts [r * n_expert / world, (r + 1) * n_expert / world) and routes
+ * its own tokens with the same router kernel as dsmoe_moe_forward, so routing is bit-identical.
+ *
+ * Set-up: the handle is created with the MODEL's n_expert / n_expert_used and max_tokens = the most tokens this rank
+ * routes per call. Rank 0 calls dsmoe_ep_get_unique_id and hands the 128 bytes to every rank over any host channel;
+ * every rank then calls dsmoe_ep_init (it creates the NCCL communicator: collective, all ranks must call it), or
+ * dsmoe_ep_init_comm with an ncclComm_t it already has. NCCL is looked up with dlsym in the libnccl.so.2 the process
+ * has loaded, so no second NCCL is linked beside the host's. max_replicas: room for that many replicated experts
+ * (n_expert / world + max_replicas must be a multiple of 32); recv_capacity_rows: rows this rank can receive per call
+ * (0 = twice the pairs it routes itself). dsmoe_ep_layer_register takes the rank's shard in the order
+ * [own experts | replicas in dsmoe_ep_set_replicas order], (n_expert / world + max_replicas) experts long.
+ *
+ * dsmoe_moe_forward_ep is collective: every rank calls it, in the same order, also with n_tokens == 0. It makes ONE host
+ * synchronisation per call (it reads the world x world count matrix that sizes the transfers). Every rank sees the whole
+ * matrix, so if any rank's receive buffer would overflow, every rank returns DSMOE_ERR_BOUNDS before any data moves and
+ * none is left waiting. Operands as in dsmoe_moe_forward. */
+#define DSMOE_EP_UNIQUE_ID_BYTES 128
+DSMOE_API int dsmoe_ep_get_unique_id(uint8_t *id128);
+DSMOE_API int dsmoe_ep_init(dsmoe_handle *h, const uint8_t *id128, int rank, int world, uint32_t max_replicas,
+                            uint32_t recv_capacity_rows);
+DSMOE_API int dsmoe_ep_init_comm(dsmoe_handle *h, void *nccl_comm, int rank, int world, uint32_t max_replicas,
+                                 uint32_t recv_capacity_rows);
+DSMOE_API int dsmoe_ep_layer_register(dsmoe_handle *h, uint32_t layer, const uint8_t *gate, const uint8_t *up,
+                                      const uint8_t *down, int layout);
+/* Experts every rank holds a copy of: their pairs are computed on the rank that routed them and never dispatched, which
+ * takes the load of a few very popular experts off their owners. Results do not change. Synchronises the device. */
+DSMOE_API int dsmoe_ep_set_replicas(dsmoe_handle *h, const int32_t *expert_ids, uint32_t n);
+/* Running count of selections per expert over this rank's dsmoe_moe_forward_ep calls (uint64 [n_expert], copied to the
+ * host; reset != 0 clears it): what a server picks its replicas from. Synchronises the stream. */
+DSMOE_API int dsmoe_ep_expert_counts(dsmoe_handle *h, dsmoe_stream stream, uint64_t *counts_host, int reset);
+/* Rows this rank received from each rank in its most recent dsmoe_moe_forward_ep (int32 [world]). */
+DSMOE_API int dsmoe_ep_last_recv_rows(dsmoe_handle *h, int32_t *rows_per_rank);
+/* Measurement aid: six cudaEvent_t recorded at start, plan done, dispatch done, owner compute done, combine done, slot
+ * sum done. NULL / 0 clears. */
+DSMOE_API int dsmoe_ep_set_phase_events(dsmoe_handle *h, void **events, int n_events);
+DSMOE_API int dsmoe_moe_forward_ep(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, const float *x,
+                                   const float *logits, uint32_t n_tokens, float *out, int32_t *selected_out,
+                                   float *weights_out);
+
+/* ------------------------------------------------------------------------------------------------------------ */
+/* GGUF expert-tensor ingestion                                                                                   */
+/* ------------------------------------------------------------------------------------------------------------ */
+
+/* Replaces GgufFile (engine/src/gguf.rs:23-122) and the verbatim tensor upload of Engine::open
+ * (engine/src/engine.rs:77-90, names bound at :176-185) for the tensors of this path. Host-side calls; they need no
+ * handle and, except dsmoe_gguf_upload_experts, no GPU. Tensor type ids as in engine/src/model.rs:29-39. */
+enum { DSMOE_GGUF_F32 = 0, DSMOE_GGUF_F16 = 1, DSMOE_GGUF_Q8_0 = 8, DSMOE_GGUF_Q2_K = 10, DSMOE_GGUF_Q4_K = 12,
+       DSMOE_GGUF_IQ2_XXS = 16, DSMOE_GGUF_I32 = 26 };
+
+typedef struct dsmoe_gguf dsmoe_gguf;
+typedef struct dsmoe_gguf_tensor {
+    const char *name;       /* owned by the dsmoe_gguf object */
+    uint32_t type, n_dims;  /* type id as stored in the file */
+    uint64_t dims[4];       /* fastest-varying dimension first, as GGUF stores them; unused entries are 1 */
+    uint64_t offset;        /* from the start of the data section */
+    uint64_t bytes;         /* ceil(elements / block elements) * block bytes (engine/src/model.rs:41-75) */
+    const void *host_data;  /* the tensor's bytes inside the mapping */
+} dsmoe_gguf_tensor;
+
+/* Maps the file read-only and parses header, metadata (skipped) and tensor table; the data section starts at the next
+ * 32-byte boundary (engine/src/gguf.rs:101-102). *out is set even when parsing fails, so that dsmoe_gguf_last_error
+ * can be read; close it in either case. DSMOE_ERR_ARG: bad magic, version outside 2..3, unknown tensor type id.
+ * DSMOE_ERR_BOUNDS: the file ends inside the header or table, or a tensor's bytes run past its end. */
+DSMOE_API int dsmoe_gguf_open(const char *path, dsmoe_gguf **out);
+/* The same over bytes the caller keeps alive (the reference's parser tests build their files in memory,
+ * engine/tests/gguf_parse.rs:12-77). */
+DSMOE_API int dsmoe_gguf_open_memory(const void *data, size_t bytes, dsmoe_gguf **out);
+DSMOE_API int dsmoe_gguf_close(dsmoe_gguf *g);
+DSMOE_API const char *dsmoe_gguf_last_error(const dsmoe_gguf *g);
+DSMOE_API uint64_t dsmoe_gguf_tensor_count(const dsmoe_gguf *g);
+DSMOE_API uint64_t dsmoe_gguf_data_offset(const dsmoe_gguf *g);
+DSMOE_API int dsmoe_gguf_tensor_at(const dsmoe_gguf *g, uint64_t index, dsmoe_gguf_tensor *out);
+/* GgufFile::find (engine/src/gguf.rs:118-121); DSMOE_ERR_STATE when there is no such tensor. */
+DSMOE_API int dsmoe_gguf_find_tensor(const dsmoe_gguf *g, const char *name, dsmoe_gguf_tensor *out);
+
+/* Device bytes of expert_count experts of one layer: gate (= up) and down. */
+DSMOE_API int dsmoe_gguf_expert_shard_bytes(const dsmoe_config *cfg, uint32_t expert_count, uint64_t *gate_up_bytes,
+                                            uint64_t *down_bytes);
+/* Validates blk.{gguf_layer}.ffn_{gate,up,down}_exps.weight (type ids 16 / 16 / 10, dims [in, out, n_expert] against
+ * cfg, byte sizes against the block formats) and copies experts [expert_begin, expert_begin + expert_count) - one
+ * expert-parallel shard, or all of them - into the caller's device buffers on `stream`, permuted to ROWSOA on the way
+ * when `layout` says so (staging_dev: a device buffer of at least the down shard's bytes; unused for NATIVE). The
+ * buffers are then ready for dsmoe_layer_register. Nothing is copied unless all three tensors validate. */
+DSMOE_API int dsmoe_gguf_upload_experts(const dsmoe_gguf *g, const dsmoe_config *cfg, dsmoe_stream stream,
+                                        uint32_t gguf_layer, uint32_t expert_begin, uint32_t expert_count, int layout,
+                                        uint8_t *gate_dev, uint8_t *up_dev, uint8_t *down_dev, uint8_t *staging_dev);
 
 /* ------------------------------------------------------------------------------------------------------------ */
 /* For callers that cannot allocate device memory                                                                 */

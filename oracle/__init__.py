@@ -94,6 +94,7 @@ def _declare(L: C.CDLL) -> None:
     L.orc_e4m3_decode.argtypes = [C.c_uint8]
     L.orc_fp8_quantize.argtypes = [_f32p, _u8p, _f32p, C.c_int64, C.c_int64, C.c_int]
     L.orc_fp8_gemm.argtypes = [_u8p, _f32p, _u8p, _f32p, _f32p, C.c_int64, C.c_int64, C.c_int64]
+    L.orc_hc_expand.argtypes = [_f32p, _f32p, _f32p, _f32p, _f32p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int]
     L.orc_num_threads.restype = C.c_int
     L.orc_set_num_threads.argtypes = [C.c_int]
 
@@ -326,6 +327,19 @@ def fp8_gemm(a: np.ndarray, a_scale: np.ndarray, w: np.ndarray, w_scale: np.ndar
     N = w.shape[0]
     out = np.empty((M, N), np.float32)
     lib().orc_fp8_gemm(_p(a, _u8p), _p(a_scale, _f32p), _p(w, _u8p), _p(w_scale, _f32p), _p(out, _f32p), M, N, K)
+    return out
+
+
+def hc_expand(block_out: np.ndarray, block_add, residual_hc: np.ndarray, split: np.ndarray) -> np.ndarray:
+    """hc_expand of engine/src/kernels/hc.rs:212-251. block_out / block_add [T, n_embd] (block_add may be None),
+    residual_hc [T, n_hc, n_embd], split [T, mix_hc]. Returns out_hc [T, n_hc, n_embd]."""
+    bo, res, sp = _c(block_out, np.float32), _c(residual_hc, np.float32), _c(split, np.float32)
+    ba = None if block_add is None else _c(block_add, np.float32)
+    T, n_hc, n_embd = res.shape
+    out = np.empty_like(res)
+    if T:
+        lib().orc_hc_expand(_p(bo, _f32p), _p(ba, _f32p), _p(res, _f32p), _p(sp, _f32p), _p(out, _f32p), n_embd, n_hc, T,
+                            sp.shape[1], int(ba is not None))
     return out
 
 

@@ -770,6 +770,27 @@ void orc_fp8_gemm(const uint8_t *a, const float *a_scale, const uint8_t *w, cons
 
 /* ------------------------------------------------------------------------------------------------------------ */
 
+/* hc_expand, engine/src/kernels/hc.rs:212-251: block_v = block_out (+ block_add); out = block_v * post[dst] +
+ * sum over src of comb[dst + src * n_hc] * residual[src], with post at split[n_hc ..] and comb at split[2 n_hc ..] of the
+ * token's row of mix_hc floats. Multiplications and additions are separate f32 operations, as in the Rust source. */
+void orc_hc_expand(const float *block_out, const float *block_add, const float *residual_hc, const float *split,
+                   float *out_hc, int64_t n_embd, int64_t n_hc, int64_t n_tokens, int64_t mix_hc, int has_add)
+{
+    for (int64_t t = 0; t < n_tokens; ++t)
+        for (int64_t dst = 0; dst < n_hc; ++dst)
+            for (int64_t d = 0; d < n_embd; ++d) {
+                float block_v = block_out[t * n_embd + d];
+                if (has_add) block_v += block_add[t * n_embd + d];
+                const float *sp = split + t * mix_hc;
+                float acc = block_v * sp[n_hc + dst];
+                for (int64_t src = 0; src < n_hc; ++src) {
+                    const float prod = sp[2 * n_hc + dst + src * n_hc] * residual_hc[(t * n_hc + src) * n_embd + d];
+                    acc += prod;
+                }
+                out_hc[(t * n_hc + dst) * n_embd + d] = acc;
+            }
+}
+
 int orc_num_threads(void)
 {
 #if defined(_OPENMP)

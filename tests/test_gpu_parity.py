@@ -531,3 +531,53 @@ def test_expert_parallel_world1_matches_forward(torch_cuda, oracle):
     finally:
         if created:
             dist.destroy_process_group()
+
+
+def test_expert_parallel_c_abi_world1_and_replicas(torch_cuda, oracle):
+    """dsmoe_moe_forward_ep on a one-rank NCCL communicator: counting, placement, gather, self send/recv, owner compute
+    and the indexed slot sum must reproduce dsmoe_moe_forward bit for bit when both sides run the decode kernels, with
+    and without replicated experts (replicas change where a pair is computed, never the result)."""
+    torch = torch_cuda
+    import os
+
+    from deepseek_rs_b200.ep import ExpertParallelHandle
+    from deepseek_rs_b200.kernels import LAYOUT_ROWSOA, MoeKernels, MoeLayer
+
+    n_e, T = 32, 9
+    lw = F.ExpertLayer(seed=51, n_expert=n_e)
+    rng = np.random.default_rng(52)
+    x = dev(torch, F.bf16_round(rng.standard_normal((T, 4096)).astype(np.float32)))
+    logits = dev(torch, rng.standard_normal((T, n_e)).astype(np.float32))
+    K_full = MoeKernels(device=0, n_expert=n_e, max_tokens=T)
+    layer = MoeLayer(K_full, lw.gate, lw.up, lw.down, layout=LAYOUT_ROWSOA)
+    sel_want = torch.zeros((T, 6), dtype=torch.int32, device="cuda")
+    want = layer.forward(x, logits, selected_out=sel_want)
+    ge, de = lw.gate_expert_bytes, lw.down_expert_bytes
+    for replicas in ([], [3, 17, 4]):
+        os.environ["DSMOE_PREFILL_MIN_TOKENS"] = "1000000"  # owner side on the decode kernels as well
+        try:
+            K = MoeKernels(device=0, n_expert=n_e, max_tokens=T)
+            ep = ExpertParallelHandle(K, 0, 1, max_replicas=32)
+        finally:
+            del os.environ["DSMOE_PREFILL_MIN_TOKENS"]
+        # shard = all 32 experts, then the replica slots (unused slots stay zero)
+        def shard(t, per):
+            buf = torch.zeros((n_e + 32) * per, dtype=torch.uint8, device="cuda")
+            buf[: n_e * per] = t
+            for i, e in enumerate(replicas):
+                buf[(n_e + i) * per:(n_e + i + 1) * per] = t[e * per:(e + 1) * per]
+            return buf
+        g, u, d = shard(layer.gate, ge), shard(layer.up, ge), shard(layer.down, de)
+        ep.layer_register(0, g, u, d, LAYOUT_ROWSOA)
+        ep.set_replicas(replicas)
+        sel = torch.zeros((T, 6), dtype=torch.int32, device="cuda")
+        out = ep.forward(0, x, logits, selected_out=sel)
+        torch.cuda.synchronize()
+        assert K.device_status() == 0
+        assert torch.equal(sel, sel_want)
+        assert torch.equal(out, want)
+        assert sum(ep.last_recv_rows()) == T * 6
+        counts = ep.expert_counts()
+        assert int(counts.sum()) == T * 6 and torch.equal(counts, torch.bincount(sel_want.flatten().cpu().long(), minlength=n_e))
+        K.close()
+    K_full.close()
