@@ -60,15 +60,21 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up decode kernel, from the ncu captures summarised
-# in profiles/decode_gate_up_and_down_ncu.md (batch 1: equal to the algorithmic bytes; batch 64: 1.79 x, pairs of one
-# expert are not yet grouped) and, for the prefill workload, of the gate/up grouped GEMM
-# (profiles/prefill_grouped_gemm_ncu.md: the packed weights once per token tile plus activations and mid)
-NCU_TRAFFIC = {"moe_decode_b1": 25999616, "moe_decode_b64": 1552575072, "moe_prefill_4096": 989383936}
-
-
 def ncu_traffic(workload: str):
-    return NCU_TRAFFIC.get(workload)
+    """(bytes, source) of dram__bytes_read.sum + dram__bytes_write.sum per launch of the workload's dominant kernel, from
+    the committed ncu capture record. The record names the kernel's source file and its SHA-256 at capture time: when
+    the file has changed since, the figure no longer describes the code that runs and is withheld."""
+    import hashlib
+
+    try:
+        rec = json.load(open(os.path.join(ROOT, "profiles", "traffic.json")))[workload]
+        src = os.path.join(ROOT, rec["source_file"])
+        digest = hashlib.sha256(open(src, "rb").read()).hexdigest()
+        if digest != rec["source_sha256"]:
+            return None, f"withheld: {rec['source_file']} has changed since the capture at commit {rec['commit']}"
+        return rec["dram_bytes_per_launch"], f"ncu capture at commit {rec['commit']} ({rec['summary']})"
+    except Exception as e:  # no record for this workload
+        return None, f"no capture on record ({type(e).__name__})"
 
 
 class ClockSampler:
@@ -101,6 +107,10 @@ class ClockSampler:
                 self.proc.wait(timeout=5)
             except Exception:
                 pass
+        return self.peek(window)
+
+    def peek(self, window=None):
+        """The summary of the samples so far (the sampler keeps running)."""
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for ts, r in self.rows:
@@ -136,8 +146,11 @@ def run_reference(args, rank: int, world: int):
 
     oracle.build()
     wl = WORKLOADS[args.workload]
+    # the launcher of a multi-rank run sets OMP_NUM_THREADS=1 for its children: this arm uses every host core at any N
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    oracle.set_num_threads(cores)
     cores = oracle.num_threads()
-    sample_tokens = min(wl["tokens"], max(1, 2 * cores))
+    sample_tokens = min(wl["tokens"], 64)  # the same sample at every N
     n_exp = 32  # full-size experts, fewer of them: the CPU path's cost per token does not depend on the expert count
     lw = F.ExpertLayer(seed=1, n_expert=n_exp)
     rng = np.random.default_rng(0)
@@ -169,6 +182,7 @@ def cpu_baseline(workload: str):
     from deepseek_rs_b200 import formats as F
 
     oracle.build()
+    oracle.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     cores = oracle.num_threads()
     n_tok, n_exp = max(4, 4 * cores), 32
     lw = F.ExpertLayer(seed=1, n_expert=n_exp)
@@ -245,12 +259,20 @@ def run_prefill(args, torch, dist, K, layers, layout, device, rank, world, sampl
     lgs = (torch.randn((V, T, N_EXPERT), device=device, generator=gen) - 1.1 * torch.log(rank_e)[None, None, :]).contiguous()
     out = torch.empty((T, N_EMBD), device=device)
     sel = torch.empty((T, TOP_K), dtype=torch.int32, device=device)
-    distinct, max_share = [], 0.0
+    distinct, max_share, near_ties = [], 0.0, 0
+    probs = torch.empty((T, N_EXPERT), device=device)
+    sel2, w2 = torch.empty_like(sel), torch.empty((T, TOP_K), device=device)
     for v in range(V):
         K.moe_forward(v % L, xs[v], lgs[v], T, out, sel, None)
         cnt = torch.bincount(sel.flatten().clamp(min=0), minlength=N_EXPERT)
         distinct.append(int((cnt > 0).sum()))
         max_share = max(max_share, float(cnt.max()) / (T * TOP_K))
+        # near ties: tokens whose 6th and 7th selection scores are fewer than 4 f32 steps apart. Only there could an
+        # exp / ln implementation that rounds differently from this one pick another expert.
+        K.router_select_parallel(lgs[v], None, None, None, probs, sel2, w2, 0, 0, T, 0, 0)
+        top = torch.topk(probs, TOP_K + 1, dim=1).values  # scores are positive: their bit patterns order like the values
+        gap = top[:, TOP_K - 1].contiguous().view(torch.int32) - top[:, TOP_K].contiguous().view(torch.int32)
+        near_ties += int((gap < 4).sum())
     torch.cuda.synchronize()
     assert K.device_status() == 0
 
@@ -263,17 +285,24 @@ def run_prefill(args, torch, dist, K, layers, layout, device, rank, world, sampl
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
+    # The K timed steps are repeated (each repeat between its own pair of events) until about a second of device time
+    # has been measured; the value is taken over all repeats and their spread is reported.
     launches0 = K.launch_count
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        step(args.warmup + i)
-    e1.record()
-    torch.cuda.synchronize()
+    rep_ms = []
+    while len(rep_ms) < 5 or (sum(rep_ms) < 1000.0 and len(rep_ms) < 200):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            step(args.warmup + i)
+        e1.record()
+        torch.cuda.synchronize()
+        rep_ms.append(e0.elapsed_time(e1))
+        if len(rep_ms) == 1:
+            launches = K.launch_count - launches0
     if world > 1:
         dist.barrier()
-    ms_total = e0.elapsed_time(e1)
-    launches = K.launch_count - launches0
+    repeats = len(rep_ms)
+    ms_total = sum(rep_ms) / repeats
 
     # phase times from events recorded inside the library between its kernels
     evs = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
@@ -305,26 +334,48 @@ def run_prefill(args, torch, dist, K, layers, layout, device, rank, world, sampl
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    t0 = time.perf_counter()
-    e2e_steps = min(args.steps, 20)
-    for i in range(e2e_steps):
-        h = hk[i % 2]
-        h.host_synchronize()
-        h.moe_forward_host_async(i % L, xh[i % V], lh[i % V], T, ohs[i % 2])
-    for h in hk:
-        h.host_synchronize()
-    e2e_ms_step = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    e2e_steps, e2e_reps = min(args.steps, 20), []
+    for _ in range(6):
+        t0 = time.perf_counter()
+        for i in range(e2e_steps):
+            h = hk[i % 2]
+            h.host_synchronize()
+            h.moe_forward_host_async(i % L, xh[i % V], lh[i % V], T, ohs[i % 2])
+        for h in hk:
+            h.host_synchronize()
+        e2e_reps.append((time.perf_counter() - t0) * 1e3 / e2e_steps)
+    e2e_ms_step = statistics.median(e2e_reps)
     assert K2.device_status() == 0
     K2.close()
     while time.time() - t_load0 < 2.0:
         step(0)
         torch.cuda.synchronize()
-    clocks = sampler.stop(window=(t_load0, time.time()))
+    clocks = sampler.peek(window=(t_load0, time.time()))
 
     times = torch.tensor([ms_total, e2e_ms_step] + phase, dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms_total, e2e_ms_step, *phase = (float(v) for v in times.tolist())
+    # the decode workloads (batch 1, 8, 64) on the same layers: the packed-weight bandwidth half of the metric
+    decode = []
+    if world == 1 and not args.no_decode_block:
+        for t in (1, 8, 64):
+            Kd = MoeKernels(device=device.index, max_tokens=t, max_layers=L)
+            for il, (gate, up, down) in enumerate(layers):
+                Kd.layer_register(il, gate, up, down, layout)
+            d = run_decode(args, torch, dist, Kd, layers, layout, device, rank, world, sampler, t, L, f"moe_decode_b{t}",
+                           emit=False, steps=200)
+            Kd.close()
+            decode.append({"workload": d["config"]["workload"], "tokens_per_step": t, "ms_per_step": d["ms_per_step"],
+                           "tokens_per_s": d["value"], "distinct_experts_per_step": d["config"]["distinct_experts_per_step"],
+                           "packed_weight_gbs": d["packed_weight_gbs"],
+                           "frac_of_measured_hbm": d["packed_weight_frac_of_measured_hbm"],
+                           "frac_of_8000": d["packed_weight_frac_of_8000"],
+                           "gate_up": {k: d["roofline"][k] for k in ("kernel", "achieved", "frac", "avg_launch_ms", "traffic")},
+                           "down": {k: d["roofline_down"][k] for k in ("kernel", "achieved", "frac", "avg_launch_ms")},
+                           "e2e_tokens_per_s": d["e2e"]["value"], "gpu_launches_per_step": d["gpu_launches"] / d["steps"],
+                           "clocks": d["clocks"]})
+    sampler.stop()
     if rank != 0:
         return
     peak_tf, peak_kind = measured_tflops()
@@ -342,12 +393,14 @@ def run_prefill(args, torch, dist, K, layers, layout, device, rank, world, sampl
                    "n_embd": N_EMBD, "n_ff": N_FF, "layout": args.layout, "router": "Zipf s=1.1 expert popularity",
                    "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
                    "l2": f"inputs rotate over {L} layers (1.8 GB each) x {V} routings: larger than the 126 MB L2",
-                   "distinct_experts_per_step": u_mean, "largest_expert_share_of_pairs": max_share},
+                   "distinct_experts_per_step": u_mean, "largest_expert_share_of_pairs": max_share,
+                   "near_tie_tokens_lt_4ulp": near_ties, "tokens_checked_for_near_ties": V * T},
+        "repeats": repeats, "ms_per_step_min": min(rep_ms) / args.steps, "ms_per_step_max": max(rep_ms) / args.steps,
         "packed_weight_gbs": u_mean * EXPERT_BYTES * world / (ms_step * 1e-3) / 1e9,
         "roofline": {"bound": "tensor", "kernel": "pf_grouped_gemm_kernel<IQ2> (gate+up+SwiGLU, tcgen05 kind::f16)",
                      "achieved": gu_flops / (phase[1] * 1e-3) / 1e12, "peak": peak_tf, "peak_kind": f"of {peak_kind}",
                      "unit": "TFLOP/s", "frac": gu_flops / (phase[1] * 1e-3) / 1e12 / peak_tf,
-                     "traffic": ncu_traffic(args.workload) if L >= 1 else None,
+                     "traffic": ncu_traffic(args.workload)[0], "traffic_source": ncu_traffic(args.workload)[1],
                      "algorithmic_flops_per_launch": gu_flops, "avg_launch_ms": phase[1]},
         "roofline_down": {"bound": "tensor", "kernel": "pf_grouped_gemm_kernel<Q2K> (down, tcgen05 kind::f16)",
                           "achieved": dn_flops / (phase[3] * 1e-3) / 1e12, "peak": peak_tf, "unit": "TFLOP/s",
@@ -355,9 +408,13 @@ def run_prefill(args, torch, dist, K, layers, layout, device, rank, world, sampl
         "phases_ms": {"group+gather": phase[0], "gate_up_gemm": phase[1], "q8k_mid+gather": phase[2],
                       "down_gemm": phase[3], "slot_sum": phase[4]},
         "e2e": {"value": T * world / (e2e_ms_step * 1e-3), "unit": UNIT,
-                "h2d_bytes_per_step": T * (N_EMBD + N_EXPERT) * 4, "d2h_bytes_per_step": T * N_EMBD * 4},
-        "gpu_launches": launches, "timed_with": "CUDA events around K back-to-back steps", "clocks": clocks,
+                "h2d_bytes_per_step": T * (N_EMBD + N_EXPERT) * 4, "d2h_bytes_per_step": T * N_EMBD * 4,
+                "repeats": len(e2e_reps), "value_min": T * world / (max(e2e_reps) * 1e-3),
+                "value_max": T * world / (min(e2e_reps) * 1e-3)},
+        "gpu_launches": launches, "timed_with": f"CUDA events around K back-to-back steps, {repeats} repeats", "clocks": clocks,
     }
+    if decode:
+        line["decode"] = decode
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(args.workload)
     if world == 1 and not args.no_ref_mapping:
@@ -444,7 +501,9 @@ def run_fp8(args, torch, dist, K, device, rank, world, sampler):
                    "l2": f"{R} weight matrices rotate (268 MB > 126 MB L2)"},
         "roofline": {"bound": "tensor", "kernel": "fp8_gemm_ws_kernel<TMA> (tcgen05 kind::f8f6f4, 128x256 tiles, tensor-map loads)", "achieved": head["tflops"],
                      "peak": peak_tf, "peak_kind": f"of {kind} bf16 GEMM (dense fp8 is nominally twice that)",
-                     "unit": "TFLOP/s", "frac": head["tflops"] / peak_tf, "traffic": None, "avg_launch_ms": head["ms"]},
+                     "unit": "TFLOP/s", "frac": head["tflops"] / peak_tf, "traffic": None, "avg_launch_ms": head["ms"],
+                     "fp8_peak_nominal": 2.0 * peak_tf, "frac_of_fp8_peak_nominal": head["tflops"] / (2.0 * peak_tf),
+                     "fp8_peak_kind": "2 x the measured bf16 burst (no fp8 measurement exists for this pool; nominal ratio)"},
         "roofline_matvec": {"bound": "hbm", "kernel": "fp8_matvec_kernel (M = 1)", "achieved": mv["weight_gbs"],
                             "peak": hbm, "unit": "GB/s", "frac": mv["weight_gbs"] / hbm, "avg_launch_ms": mv["ms"]},
         "shapes": results,
@@ -546,145 +605,192 @@ def run_shared(args, torch, dist, K, device, rank, world, sampler):
 
 
 def run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, T_chunk):
-    """Expert-parallel prefill: rank r owns experts [r*256/G, (r+1)*256/G) and routes its own tokens; NCCL all-to-all
-    dispatch (Q8_K rows) and combine (f32 rows). Weak scaling (default): every rank brings its own 4096-token chunk.
-    --ep-scaling strong: one 4096-token chunk split evenly over the ranks."""
-    from deepseek_rs_b200.ep import ExpertParallelMoe, gpu_functions, gpu_sum_function
-    from deepseek_rs_b200.kernels import LAYOUT_ROWSOA, MoeKernels, MoeLayer
+    """Expert-parallel prefill through the C ABI (dsmoe_ep_init / dsmoe_moe_forward_ep): rank r owns experts
+    [r*256/G, (r+1)*256/G) and routes its own tokens; counting, placement, row gather, NCCL dispatch (Q8_K rows) and
+    combine (f32 rows), the owner's grouped GEMM and the slot sum all run inside the library. `value` is weak scaling
+    (every rank brings its own 4096-token chunk); the same line carries the strong-scaling figure (ONE 4096-token chunk
+    split evenly over the ranks), the figure without replicated experts, and a comparison of the outputs with a
+    single-GPU run of the same layer on rank 0."""
+    from deepseek_rs_b200.ep import ExpertParallelHandle
+    from deepseek_rs_b200.kernels import LAYOUT_ROWSOA, MoeKernels
 
-    weak = args.ep_scaling == "weak"
-    T_total = T_chunk * world if weak else T_chunk
-    T = T_total // world
-    per = N_EXPERT // world
+    T, per, R = T_chunk, N_EXPERT // world, args.ep_replicate
     L, V = 2, 4
-    K_route = MoeKernels(device=local_rank, max_tokens=T, max_layers=1)
-    # expert popularity: the same on every rank (the bench's router subtracts 1.1 ln(popularity rank) from the logits)
+    K = MoeKernels(device=local_rank, max_tokens=T, max_layers=L)
+    ep = ExpertParallelHandle(K, rank, world, max_replicas=R, recv_capacity_rows=3 * T * TOP_K)
+    g_exp, d_exp = GATE_EXPERT_BYTES, DOWN_EXPERT_BYTES
+    shards = []
+    for il in range(L):  # shard of layer il in ROWSOA order, with R empty replica slots behind the rank's own experts
+        gate, up, down = gen_layer_gpu(torch, device, seed=1000 * rank + il, n_expert=per)
+        bufs = []
+        for t, nb, relay, rows, blocks in ((gate, g_exp, K.relayout_iq2xxs, per * N_FF, N_EMBD // 256),
+                                          (up, g_exp, K.relayout_iq2xxs, per * N_FF, N_EMBD // 256),
+                                          (down, d_exp, K.relayout_q2k, per * N_EMBD, N_FF // 256)):
+            buf = torch.zeros((per + R) * nb, dtype=torch.uint8, device=device)
+            relay(t, buf[: per * nb], rows, blocks)
+            bufs.append(buf)
+        torch.cuda.synchronize()
+        del gate, up, down
+        ep.layer_register(il, bufs[0], bufs[1], bufs[2], LAYOUT_ROWSOA)
+        shards.append(bufs)
+
+    # expert popularity is the same on every rank (the router subtracts 1.1 ln(popularity rank) from the logits); the
+    # library is never told: replicas are chosen below from its own running counts of `selected`
     gen = torch.Generator(device=device)
     gen.manual_seed(7)
     rank_e = (torch.randperm(N_EXPERT, device=device, generator=gen) + 1).float()
-    # the R most popular experts are replicated on every rank: their pairs are computed where they are routed, which
-    # takes the hot experts' load off their owners (a serving system would take the ranking from running counts)
-    R = args.ep_replicate
-    hot = [int(e) for e in torch.argsort(rank_e)[:R].tolist()]
-    K_owner = MoeKernels(device=local_rank, n_expert=per + R, n_expert_used=1, max_tokens=T_total * TOP_K, max_layers=L)
-    g_exp, d_exp = N_FF * (N_EMBD // 256) * 66, N_EMBD * (N_FF // 256) * 84  # bytes per expert
-    for il in range(L):
-        gate, up, down = gen_layer_gpu(torch, device, seed=1000 * rank + il, n_expert=per)
-        if R:
-            reps = {}
-            for r in range(world):  # every owner broadcasts the slices of its hot experts
-                mine = [e for e in hot if e // per == r]
-                if not mine:
-                    continue
-                idx = torch.tensor([e % per for e in mine], device=device)
-                bufs = []
-                for t, nb in ((gate, g_exp), (up, g_exp), (down, d_exp)):
-                    buf = t.view(per, nb)[idx].contiguous() if r == rank else torch.empty((len(mine), nb), dtype=torch.uint8, device=device)
-                    dist.broadcast(buf, src=r)
-                    bufs.append(buf)
-                for i, e in enumerate(mine):
-                    reps[e] = tuple(bf[i] for bf in bufs)
-            gate = torch.cat([gate.view(per, g_exp)] + [reps[e][0][None] for e in hot]).reshape(-1)
-            up = torch.cat([up.view(per, g_exp)] + [reps[e][1][None] for e in hot]).reshape(-1)
-            down = torch.cat([down.view(per, d_exp)] + [reps[e][2][None] for e in hot]).reshape(-1)
-            del reps, bufs
-        MoeLayer(K_owner, gate, up, down, layout=LAYOUT_ROWSOA, layer=il)
-        del gate, up, down
     xl, ll = [], []
     for v in range(V):
-        gen.manual_seed(100 + v if not weak else 100 + v + 1000 * rank)
-        n_gen, lo = (T, 0) if weak else (T_total, rank * T)
-        x = torch.randn((n_gen, N_EMBD), device=device, generator=gen).to(torch.bfloat16).to(torch.float32)
-        lg = torch.randn((n_gen, N_EXPERT), device=device, generator=gen) - 1.1 * torch.log(rank_e)[None, :]
-        xl.append(x[lo:lo + T].contiguous())
-        ll.append(lg[lo:lo + T].contiguous())
-        del x, lg
-    eps = []
-    for il in range(L):
-        rf, ef = gpu_functions(K_route, K_owner, layer=il)
-        eps.append(ExpertParallelMoe(rf, ef, N_EXPERT, TOP_K, N_EMBD, sum_fn=gpu_sum_function(K_route), replicated=hot))
-    # the routing that comes out of the expert-parallel step must equal the single-GPU router's on the same tokens
-    solo_route = gpu_functions(K_route, K_owner)[0]
-    same = True
-    for v in range(V):
-        _, sel_solo, _ = solo_route(xl[v], ll[v])
-        _, sel = eps[0].forward(xl[v], ll[v])
-        same = same and bool(torch.equal(sel, sel_solo))
-    flag = torch.tensor([1 if same else 0], device=device)
-    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        gen.manual_seed(100 + v + 1000 * rank)
+        x = torch.randn((T, N_EMBD), device=device, generator=gen).to(torch.bfloat16).to(torch.float32)
+        lg = torch.randn((T, N_EXPERT), device=device, generator=gen) - 1.1 * torch.log(rank_e)[None, :]
+        xl.append(x.contiguous())
+        ll.append(lg.contiguous())
+    out = torch.empty((T, N_EMBD), device=device)
+    sel = torch.empty((T, TOP_K), dtype=torch.int32, device=device)
 
-    def step(i):
-        return eps[i % L].forward(xl[i % V], ll[i % V])[0]
+    def step(i, n_tok=T):
+        ep.forward(i % L, xl[i % V][:n_tok], ll[i % V][:n_tok], out=out[:n_tok])
+
+    def timed(n_steps, n_tok=T):
+        for i in range(max(3, args.warmup // 2)):
+            step(i, n_tok)
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(n_steps):
+            step(args.warmup + i, n_tok)
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1) / n_steps], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
     t_load0 = time.time()
-    for i in range(args.warmup):
-        step(i)
-    torch.cuda.synchronize()
-    dist.barrier()
-    l0 = K_route.launch_count + K_owner.launch_count
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        step(args.warmup + i)
-    e1.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    ms_total = e0.elapsed_time(e1)
-    launches = K_route.launch_count + K_owner.launch_count - l0
-    recv_pairs = sum(eps[0].last_plan.recv_counts)
-    assert K_owner.device_status() == 0
+    # pure sharding first: its time is reported, and its steps fill the running per-expert counts
+    ms_unreplicated = timed(min(args.steps, 10))
+    max_recv_unrep = torch.tensor([float(sum(ep.last_recv_rows()))], dtype=torch.float64, device=device)
+    dist.all_reduce(max_recv_unrep, op=dist.ReduceOp.MAX)
+    hot = []
+    if R:
+        counts = ep.expert_counts().to(device)
+        dist.all_reduce(counts)  # every rank sees the same totals, hence picks the same replicas
+        hot = [int(e) for e in torch.argsort(counts, descending=True, stable=True)[:R].tolist()]
+        for il in range(L):  # each owner broadcasts the (already re-laid) bytes of its hot experts into everyone's slots
+            for slot, e in enumerate(hot):
+                for buf, nb in zip(shards[il], (g_exp, g_exp, d_exp)):
+                    piece = buf[(per + slot) * nb:(per + slot + 1) * nb]
+                    if e // per == rank:
+                        piece.copy_(buf[(e % per) * nb:(e % per + 1) * nb])
+                    dist.broadcast(piece, src=e // per)
+        torch.cuda.synchronize()
+        ep.set_replicas(hot)
 
-    # phase times on this rank (events at the phase boundaries of the step)
-    names = ["route", "plan", "dispatch", "experts", "combine", "sum"]
+    # correctness before timing: routing against the single-GPU router, outputs against a single-GPU run of the layer
+    K_solo = MoeKernels(device=local_rank, max_tokens=T, max_layers=1)
+    probs = torch.empty((T, N_EXPERT), device=device)
+    sel_solo, w_solo = torch.empty_like(sel), torch.empty((T, TOP_K), device=device)
+    same_routing = True
+    for v in range(V):
+        ep.forward(0, xl[v], ll[v], out=out, selected_out=sel)
+        K_solo.router_select_parallel(ll[v], None, None, None, probs, sel_solo, w_solo, 0, 0, T, 0, 0)
+        same_routing = same_routing and bool(torch.equal(sel, sel_solo))
+    out_match, out_maxdiff = True, 0.0
+    if rank == 0:  # all shards of layer 0 regenerated from their seeds: 1.8 GB + its re-laid copy, freed afterwards
+        parts = [gen_layer_gpu(torch, device, seed=1000 * r + 0, n_expert=per) for r in range(world)]
+        full = [torch.cat([p[i] for p in parts]) for i in range(3)]
+        del parts
+        g2, u2, d2 = (torch.empty_like(t) for t in full)
+        K_solo.relayout_iq2xxs(full[0], g2, N_EXPERT * N_FF, N_EMBD // 256)
+        K_solo.relayout_iq2xxs(full[1], u2, N_EXPERT * N_FF, N_EMBD // 256)
+        K_solo.relayout_q2k(full[2], d2, N_EXPERT * N_EMBD, N_FF // 256)
+        torch.cuda.synchronize()
+        del full
+        K_solo.layer_register(0, g2, u2, d2, LAYOUT_ROWSOA)
+        want = torch.empty((T, N_EMBD), device=device)
+        K_solo.moe_forward(0, xl[1], ll[1], T, want, None, None)
+        torch.cuda.synchronize()
+    ep.forward(0, xl[1], ll[1], out=out)  # collective: every rank takes part
+    torch.cuda.synchronize()
+    if rank == 0:
+        out_match = bool(torch.equal(out, want))
+        out_maxdiff = float((out - want).abs().max() / want.abs().max())
+        del g2, u2, d2, want
+    K_solo.close()
+    flags = torch.tensor([1 if same_routing else 0, 1 if out_match else 0], device=device)
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    if not int(flags[0].item()):
+        raise SystemExit("expert-parallel routing differs from the single-GPU router")
+    if rank == 0 and out_maxdiff > 1e-5:
+        raise SystemExit(f"expert-parallel output differs from the single-GPU layer (max diff {out_maxdiff} of scale)")
+
+    # timed: weak scaling (the line's value), then strong scaling (one chunk split over the ranks)
+    l0 = K.launch_count
+    ms_step = timed(args.steps)
+    launches = K.launch_count - l0  # the route-side handle; the owner-side launches are counted inside the library call
+    recv_rows = float(sum(ep.last_recv_rows()))
+    ms_strong = timed(args.steps, T // world)
+    assert K.device_status() == 0
+
+    # phase times on this rank from events recorded inside the library
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+    for e in evs:
+        e.record()
+    ep.set_phase_events(evs)
+    names = ["plan", "dispatch", "experts", "combine", "sum"]
     phase = {n: 0.0 for n in names}
     reps = min(args.steps, 5)
     for i in range(reps):
-        evs = {}
-
-        def mark(name):
-            evs[name] = torch.cuda.Event(enable_timing=True)
-            evs[name].record()
-
-        eps[i % L].forward(xl[i % V], ll[i % V], mark=mark)
+        step(i)
         torch.cuda.synchronize()
-        prev = "start"
-        for n in names:
-            phase[n] += evs[prev].elapsed_time(evs[n]) / reps
-            prev = n
+        for j, n in enumerate(names):
+            phase[n] += evs[j].elapsed_time(evs[j + 1]) / reps
+    ep.set_phase_events(None)
 
     # end to end: pinned host slices in, result back on the host, every step
     xh = [t.cpu().pin_memory() for t in xl]
     lh = [t.cpu().pin_memory() for t in ll]
     oh = torch.empty((T, N_EMBD)).pin_memory()
+    xd, ld = torch.empty_like(xl[0]), torch.empty_like(ll[0])
     dist.barrier()
     t0 = time.perf_counter()
     e2e_steps = min(args.steps, 20)
     for i in range(e2e_steps):
-        o = eps[i % L].forward(xh[i % V].to(device, non_blocking=True), lh[i % V].to(device, non_blocking=True))[0]
-        oh.copy_(o, non_blocking=True)
+        xd.copy_(xh[i % V], non_blocking=True)
+        ld.copy_(lh[i % V], non_blocking=True)
+        ep.forward(i % L, xd, ld, out=out)
+        oh.copy_(out, non_blocking=True)
         torch.cuda.synchronize()
     e2e_ms_step = (time.perf_counter() - t0) * 1e3 / e2e_steps
     while time.time() - t_load0 < 2.0:
         step(0)
         torch.cuda.synchronize()
     clocks = sampler.stop(window=(t_load0, time.time()))
-    times = torch.tensor([ms_total, e2e_ms_step, float(recv_pairs)], dtype=torch.float64, device=device)
+    times = torch.tensor([e2e_ms_step, recv_rows], dtype=torch.float64, device=device)
     dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms_step, max_recv = (float(v) for v in times.tolist())
+    e2e_ms_step, max_recv = (float(v) for v in times.tolist())
     if rank != 0:
         return
-    ms_step = ms_total / args.steps
+    T_total = T * world
     line = {
         "metric": METRIC, "value": T_total / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.ep_scaling,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16 integer codes x int8 (exact), f32 accumulate in TMEM", "data": "synthetic",
         "config": {"workload": args.workload, "tokens_per_step_all_gpus": T_total, "tokens_per_step_per_gpu": T,
-                   "top_k": TOP_K, "n_expert": N_EXPERT, "experts_per_gpu": per, "replicated_hot_experts": R, "n_embd": N_EMBD, "n_ff": N_FF,
-                   "layout": "rowsoa", "router": "Zipf s=1.1 expert popularity",
-                   "parallelism": f"ep{world}: NCCL all-to-all dispatch (Q8_K rows) + combine (f32 rows)",
+                   "top_k": TOP_K, "n_expert": N_EXPERT, "experts_per_gpu": per, "replicated_hot_experts": R,
+                   "replicas_chosen_from": "running counts of `selected` inside the library over the unreplicated steps",
+                   "n_embd": N_EMBD, "n_ff": N_FF, "layout": "rowsoa", "router": "Zipf s=1.1 expert popularity",
+                   "parallelism": f"ep{world}: dsmoe_moe_forward_ep, NCCL send/recv dispatch (Q8_K rows) + combine (f32 rows)",
                    "l2": f"inputs rotate over {L} layers x {V} routings",
-                   "routing_bit_exact_vs_single_gpu": bool(int(flag.item())),
-                   "max_pairs_received_by_a_rank": int(max_recv), "mean_pairs_per_rank": T_total * TOP_K // world},
+                   "routing_bit_exact_vs_single_gpu": bool(int(flags[0].item())),
+                   "outputs_match_single_gpu": bool(int(flags[1].item())), "outputs_max_diff_of_scale": out_maxdiff,
+                   "max_pairs_received_by_a_rank": int(max_recv), "mean_pairs_per_rank": T * TOP_K},
+        "strong": {"tokens_per_step_all_gpus": T, "ms_per_step": ms_strong, "value": T / (ms_strong * 1e-3), "unit": UNIT,
+                   "note": "one 4096-token chunk split evenly over the ranks"},
+        "unreplicated": {"ms_per_step": ms_unreplicated, "value": T_total / (ms_unreplicated * 1e-3), "unit": UNIT,
+                         "max_pairs_received_by_a_rank": int(max_recv_unrep.item())},
         "roofline": {"bound": "tensor", "kernel": "pf_grouped_gemm_kernel<IQ2> (per-rank shard)", "achieved": None,
                      "peak": measured_tflops()[0], "unit": "TFLOP/s", "frac": None, "traffic": None,
                      "note": "kernel-level figures are reported by the 1-GPU run; this line is the whole EP step"},
@@ -697,86 +803,11 @@ def run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, 
     print(json.dumps(line), flush=True)
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=0, help="timed steps (default 200, or 20 for the prefill workload)")
-    ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layout", default="rowsoa", choices=["rowsoa", "native"])
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-ref-mapping", action="store_true", help="skip the GPU baseline (restated reference mapping)")
-    ap.add_argument("--ep-replicate", type=int, default=32, choices=[0, 32, 64],
-                    help="N > 1: this many of the most popular experts are held by every rank (0 = pure sharding)")
-    ap.add_argument("--ep-scaling", default="weak", choices=["weak", "strong"],
-                    help="N > 1: every rank its own chunk (weak) or one chunk split over the ranks (strong)")
-    ap.add_argument("--layers", type=int, default=0, help="layers to rotate over (0 = the workload's default; 1 keeps "
-                    "device memory small for profiler captures)")
-    args = ap.parse_args()
-    args.warmup = max(args.warmup, 3)
-    if args.steps <= 0:
-        args.steps = 20 if WORKLOADS[args.workload]["tokens"] >= 1024 else 200
-    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-
-    if args.impl == "reference":
-        if args.steps <= 0:
-            args.steps = 5
-        run_reference(args, rank, world)
-        return
-
-    import torch
-    import torch.distributed as dist
-
-    from deepseek_rs_b200.kernels import LAYOUT_NATIVE, LAYOUT_ROWSOA, MoeKernels
-
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-
-    sampler = ClockSampler(local_rank)
-    sampler.start()  # started early (nvidia-smi takes a while to come up); samples are filtered to the load window
-    wl = WORKLOADS[args.workload]
-    if args.workload == "shared_expert":
-        run_shared(args, torch, dist, MoeKernels(device=local_rank, max_tokens=64), device, rank, world, sampler)
-        if world > 1:
-            dist.destroy_process_group()
-        return
-    if args.workload == "fp8_linear":
-        run_fp8(args, torch, dist, MoeKernels(device=local_rank, max_tokens=1), device, rank, world, sampler)
-        if world > 1:
-            dist.destroy_process_group()
-        return
-    if wl["tokens"] >= 1024 and world > 1:
-        run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, wl["tokens"])
-        dist.destroy_process_group()
-        return
-    T, L = wl["tokens"], (args.layers if args.layers > 0 else wl["layers"])
-    K = MoeKernels(device=local_rank, max_tokens=T, max_layers=L)
-    layout = LAYOUT_ROWSOA if args.layout == "rowsoa" else LAYOUT_NATIVE
-    layers = []
-    for il in range(L):
-        gate, up, down = gen_layer_gpu(torch, device, seed=1000 * rank + il)
-        if layout == LAYOUT_ROWSOA:
-            g2, u2, d2 = torch.empty_like(gate), torch.empty_like(up), torch.empty_like(down)
-            K.relayout_iq2xxs(gate, g2, N_EXPERT * N_FF, N_EMBD // 256)
-            K.relayout_iq2xxs(up, u2, N_EXPERT * N_FF, N_EMBD // 256)
-            K.relayout_q2k(down, d2, N_EXPERT * N_EMBD, N_FF // 256)
-            torch.cuda.synchronize()
-            gate, up, down = g2, u2, d2
-        K.layer_register(il, gate, up, down, layout)
-        layers.append((gate, up, down))
-
-    if wl["tokens"] >= 1024:
-        run_prefill(args, torch, dist, K, layers, layout, device, rank, world, sampler, T, L)
-        if world > 1:
-            dist.destroy_process_group()
-        return
-
+def run_decode(args, torch, dist, K, layers, layout, device, rank, world, sampler, T, L, workload, emit=True, steps=0):
+    """A decode workload (batch T): the whole step replayed from a CUDA graph, the two dominant kernels timed alone, the
+    host-buffer call end to end. Returns the JSON line (rank 0; printed when `emit`)."""
+    if steps:
+        args = argparse.Namespace(**{**vars(args), "steps": steps})
     # routing / activation variants: enough of them that (layer, routing) pairs repeat only after far more than the
     # L2 capacity has streamed through
     V = 16
@@ -909,7 +940,7 @@ def main():
         for _ in range(8):
             graph.replay()
         torch.cuda.synchronize()
-    clocks = sampler.stop(window=(t_load0, time.time()))
+    clocks = sampler.stop(window=(t_load0, time.time())) if emit else sampler.peek(window=(t_load0, time.time()))
 
     # max over ranks
     times = torch.tensor([ms_total, e2e_s * 1e3, gu_ms_mean], dtype=torch.float64, device=device)
@@ -917,6 +948,7 @@ def main():
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms_total, e2e_ms, gu_ms_mean = (float(v) for v in times.tolist())
 
+    line = None
     if rank == 0:
         peak, peak_kind = measured_peaks()
         tokens = T * args.steps * world
@@ -928,7 +960,7 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int8 x 2-bit codes, f32 accumulate", "data": "synthetic",
-            "config": {"workload": args.workload, "tokens_per_step_per_gpu": T, "top_k": TOP_K, "n_expert": N_EXPERT,
+            "config": {"workload": workload, "tokens_per_step_per_gpu": T, "top_k": TOP_K, "n_expert": N_EXPERT,
                        "n_embd": N_EMBD, "n_ff": N_FF, "layout": args.layout,
                        "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
                        "l2": f"inputs rotate over {L} layers x {V} routings; packed bytes between reuse >> 126 MB L2",
@@ -938,7 +970,7 @@ def main():
             "packed_weight_frac_of_8000": layer_gbs / world / 8000.0,
             "roofline": {"bound": "hbm", "kernel": "gate_up_x16_kernel (IQ2_XXS gate+up+SwiGLU)", "achieved": achieved,
                          "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": ncu_traffic(args.workload), "algorithmic_bytes_per_launch": gu_bytes,
+                         "traffic": ncu_traffic(workload)[0], "traffic_source": ncu_traffic(workload)[1], "algorithmic_bytes_per_launch": gu_bytes,
                          "avg_launch_ms": gu_ms_mean},
             "roofline_down": {"bound": "hbm", "kernel": "down_m8_kernel (Q2_K down + slot sum)",
                               "achieved": u_mean * DOWN_EXPERT_BYTES / (dn_ms_mean * 1e-3) / 1e9, "peak": peak,
@@ -949,11 +981,97 @@ def main():
             "gpu_launches": launches, "timed_with": f"CUDA graph of {G} steps replayed {args.steps // G} times",
             "clocks": clocks,
         }
-        if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(args.workload)
-        if world == 1 and not args.no_ref_mapping:
+        if emit and world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(workload)
+        if emit and world == 1 and not args.no_ref_mapping:
             line["ref_mapping_gpu"] = ref_mapping_gpu(torch, device, K, T, ms_total / args.steps)
-        print(json.dumps(line), flush=True)
+        if emit:
+            print(json.dumps(line), flush=True)
+    return line
+
+
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=0, help="timed steps (default 200, or 20 for the prefill workload)")
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layout", default="rowsoa", choices=["rowsoa", "native"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-ref-mapping", action="store_true", help="skip the GPU baseline (restated reference mapping)")
+    ap.add_argument("--no-decode-block", action="store_true", help="prefill workload: skip the batch 1 / 8 / 64 decode block")
+    ap.add_argument("--ep-replicate", type=int, default=32, choices=[0, 32, 64],
+                    help="N > 1: this many of the most popular experts are held by every rank (0 = pure sharding)")
+    ap.add_argument("--layers", type=int, default=0, help="layers to rotate over (0 = the workload's default; 1 keeps "
+                    "device memory small for profiler captures)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.steps <= 0:
+        args.steps = 20 if WORKLOADS[args.workload]["tokens"] >= 1024 else 200
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if args.steps <= 0:
+            args.steps = 5
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from deepseek_rs_b200.kernels import LAYOUT_NATIVE, LAYOUT_ROWSOA, MoeKernels
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()  # started early (nvidia-smi takes a while to come up); samples are filtered to the load window
+    wl = WORKLOADS[args.workload]
+    if args.workload == "shared_expert":
+        run_shared(args, torch, dist, MoeKernels(device=local_rank, max_tokens=64), device, rank, world, sampler)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if args.workload == "fp8_linear":
+        run_fp8(args, torch, dist, MoeKernels(device=local_rank, max_tokens=1), device, rank, world, sampler)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if wl["tokens"] >= 1024 and world > 1:
+        run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, wl["tokens"])
+        dist.destroy_process_group()
+        return
+    T, L = wl["tokens"], (args.layers if args.layers > 0 else wl["layers"])
+    K = MoeKernels(device=local_rank, max_tokens=T, max_layers=L)
+    layout = LAYOUT_ROWSOA if args.layout == "rowsoa" else LAYOUT_NATIVE
+    layers = []
+    for il in range(L):
+        gate, up, down = gen_layer_gpu(torch, device, seed=1000 * rank + il)
+        if layout == LAYOUT_ROWSOA:
+            g2, u2, d2 = torch.empty_like(gate), torch.empty_like(up), torch.empty_like(down)
+            K.relayout_iq2xxs(gate, g2, N_EXPERT * N_FF, N_EMBD // 256)
+            K.relayout_iq2xxs(up, u2, N_EXPERT * N_FF, N_EMBD // 256)
+            K.relayout_q2k(down, d2, N_EXPERT * N_EMBD, N_FF // 256)
+            torch.cuda.synchronize()
+            gate, up, down = g2, u2, d2
+        K.layer_register(il, gate, up, down, layout)
+        layers.append((gate, up, down))
+
+    if wl["tokens"] >= 1024:
+        run_prefill(args, torch, dist, K, layers, layout, device, rank, world, sampler, T, L)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    run_decode(args, torch, dist, K, layers, layout, device, rank, world, sampler, T, L, args.workload)
     if world > 1:
         dist.destroy_process_group()
 
