@@ -75,6 +75,8 @@ SIGNATURES = {
     "dsmoe_layer_register": (_int, [_vp, _u32, _vp, _vp, _vp, _int]),
     "dsmoe_layer_register_extras": (_int, [_vp, _u32, _vp, _vp, _vp, _u32, _vp, _vp, _vp]),
     "dsmoe_ffn_forward": (_int, [_vp, _vp, _u32, C.POINTER(FfnArgs)]),
+    "dsmoe_hc_split_weighted_sum_norm": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _f32,
+                                                _f32]),
     "dsmoe_hc_expand": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32]),
     "dsmoe_moe_forward": (_int, [_vp, _vp, _u32, _vp, _vp, _u32, _vp, _vp, _vp]),
     "dsmoe_expert_ffn": (_int, [_vp, _vp, _u32, _vp, _vp, _vp, _u32, _vp]),

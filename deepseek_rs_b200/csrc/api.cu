@@ -694,6 +694,20 @@ int dsmoe_hc_expand(dsmoe_handle *h, dsmoe_stream stream, const float *block_out
     return check_launch(h, "hc_expand", 1);
 }
 
+int dsmoe_hc_split_weighted_sum_norm(dsmoe_handle *h, dsmoe_stream stream, const float *mix, const float *scale,
+                                     const float *base, const float *residual_hc, const float *norm_w, float *split,
+                                     float *out, float *norm_out, uint32_t n_embd, uint32_t n_hc, uint32_t n_rows,
+                                     uint32_t sinkhorn_iters, float epsv, float norm_eps)
+{
+    DSMOE_ENTER(h);
+    if (n_rows == 0 || n_embd == 0) return DSMOE_OK;
+    DSMOE_REQUIRE(h, n_hc == 4, "hc_split_weighted_sum_norm: n_hc must be 4 (the reference kernel returns early otherwise)");
+    DSMOE_REQUIRE(h, mix && scale && base && residual_hc && norm_w && split && out && norm_out, "hc_split_weighted_sum_norm: null pointer");
+    launch_hc_split_weighted_sum_norm((cudaStream_t)stream, mix, scale, base, residual_hc, norm_w, split, out, norm_out,
+                                      n_embd, n_rows, sinkhorn_iters, epsv, norm_eps);
+    return check_launch(h, "hc_split_weighted_sum_norm", 1);
+}
+
 int dsmoe_ffn_forward(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, const dsmoe_ffn_args *a)
 {
     DSMOE_ENTER(h);

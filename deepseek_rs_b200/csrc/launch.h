@@ -87,6 +87,12 @@ void launch_moe_sum(cudaStream_t st, const float *down, const int32_t *pos, floa
                     uint32_t n_tokens, const HcEpilogue *hc = nullptr);
 void launch_hc_expand(cudaStream_t st, const float *block_add, uint32_t n_embd, uint32_t n_tokens, const HcEpilogue &hc);
 void launch_bf16_to_f32(cudaStream_t st, const uint16_t *in, float *out, uint64_t n);
+// hc_split_weighted_sum_norm_fused (engine/src/kernels/hc.rs:313-394), n_hc = 4: split [n_rows][24], out and norm_out
+// [n_rows][n_embd].
+void launch_hc_split_weighted_sum_norm(cudaStream_t st, const float *mix, const float *scale, const float *base,
+                                       const float *residual_hc, const float *norm_w, float *split, float *out,
+                                       float *norm_out, uint32_t n_embd, uint32_t n_rows, uint32_t iters, float epsv,
+                                       float norm_eps);
 
 // Router logits and shared expert (shared.cu)
 void launch_quantize_q8_0(cudaStream_t st, const float *x, int8_t *xq, float *xscale, uint64_t in_dim, uint64_t n_tok);

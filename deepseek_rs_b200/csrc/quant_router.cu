@@ -488,6 +488,106 @@ void launch_hc_expand(cudaStream_t st, const float *block_add, uint32_t n_embd, 
     hc_expand_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(block_add, n_embd, n, hc);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// FFN pre-norm producer: hc_split_weighted_sum_norm_fused (engine/src/kernels/hc.rs:313-394) with hc4_split_one
+// (hc.rs:17-100). One CTA of 256 threads per row, as the reference launches it (engine/src/session.rs:1865-1892).
+// Thread 0 computes the 24-value split (4 pre-weights: sigmoid + eps; 4 post-weights: 2 sigmoid; 4 x 4 comb matrix: row
+// softmax + eps, then Sinkhorn normalisation), all threads the weighted sum over the 4 residual streams, then the RMS
+// norm with the reference's 256-wide halving tree. Every operation is rounded on its own and in the reference's order;
+// exp is the correctly rounded f32 exponential this library uses everywhere (the reference's comes from its compiler's
+// math library, whose rounding no test pins).
+// ---------------------------------------------------------------------------------------------------------------
+__device__ void hc4_split_one(float *out, const float *mix, const float *scale, const float *base, uint32_t iters, float epsv)
+{
+    const float pre_s = scale[0], post_s = scale[1], comb_s = scale[2];
+    for (int i = 0; i < 4; ++i) {
+        const float z = __fadd_rn(__fmul_rn(mix[i], pre_s), base[i]);
+        out[i] = __fadd_rn(__fdiv_rn(1.0f, __fadd_rn(1.0f, expf_cr(-z))), epsv);
+    }
+    for (int i = 0; i < 4; ++i) {
+        const float z = __fadd_rn(__fmul_rn(mix[4 + i], post_s), base[4 + i]);
+        out[4 + i] = __fdiv_rn(2.0f, __fadd_rn(1.0f, expf_cr(-z)));
+    }
+    float c[16];
+    for (int r = 0; r < 4; ++r) {
+        float m = -INFINITY;
+        for (int col = 0; col < 4; ++col) {
+            const float v = __fadd_rn(__fmul_rn(mix[8 + r * 4 + col], comb_s), base[8 + r * 4 + col]);
+            c[r * 4 + col] = v;
+            if (v > m) m = v;
+        }
+        float sum = 0.0f;
+        for (int col = 0; col < 4; ++col) {
+            const float v = expf_cr(__fsub_rn(c[r * 4 + col], m));
+            c[r * 4 + col] = v;
+            sum = __fadd_rn(sum, v);
+        }
+        for (int col = 0; col < 4; ++col) c[r * 4 + col] = __fadd_rn(__fdiv_rn(c[r * 4 + col], sum), epsv);
+    }
+    for (int col = 0; col < 4; ++col) {
+        float sum = epsv;
+        for (int r = 0; r < 4; ++r) sum = __fadd_rn(sum, c[r * 4 + col]);
+        for (int r = 0; r < 4; ++r) c[r * 4 + col] = __fdiv_rn(c[r * 4 + col], sum);
+    }
+    for (uint32_t it = 1; it < iters; ++it) {
+        for (int r = 0; r < 4; ++r) {
+            float sum = epsv;
+            for (int col = 0; col < 4; ++col) sum = __fadd_rn(sum, c[r * 4 + col]);
+            for (int col = 0; col < 4; ++col) c[r * 4 + col] = __fdiv_rn(c[r * 4 + col], sum);
+        }
+        for (int col = 0; col < 4; ++col) {
+            float sum = epsv;
+            for (int r = 0; r < 4; ++r) sum = __fadd_rn(sum, c[r * 4 + col]);
+            for (int r = 0; r < 4; ++r) c[r * 4 + col] = __fdiv_rn(c[r * 4 + col], sum);
+        }
+    }
+    for (int i = 0; i < 16; ++i) out[8 + i] = c[i];
+}
+
+__global__ void __launch_bounds__(256) hc_split_weighted_sum_norm_kernel(
+    const float *__restrict__ mix, const float *__restrict__ scale, const float *__restrict__ base,
+    const float *__restrict__ residual_hc, const float *__restrict__ norm_w, float *__restrict__ split,
+    float *__restrict__ out, float *__restrict__ norm_out, uint32_t n_embd, uint32_t iters, float epsv, float norm_eps)
+{
+    __shared__ float s_split[24];
+    __shared__ float s_partial[256];
+    const uint32_t t = blockIdx.x, d = threadIdx.x;
+    if (d == 0) {
+        hc4_split_one(s_split, mix + (size_t)t * 24, scale, base, iters, epsv);
+        for (int i = 0; i < 24; ++i) split[(size_t)t * 24 + i] = s_split[i];
+    }
+    __syncthreads();
+    float sum_sq = 0.0f;
+    for (uint32_t col = d; col < n_embd; col += 256) {
+        float acc = 0.0f;
+        for (uint32_t h = 0; h < 4; ++h)
+            acc = __fadd_rn(acc, __fmul_rn(residual_hc[((size_t)t * 4 + h) * n_embd + col], s_split[h]));
+        out[(size_t)t * n_embd + col] = acc;
+        sum_sq = __fadd_rn(sum_sq, __fmul_rn(acc, acc));
+    }
+    s_partial[d] = sum_sq;
+    __syncthreads();
+    for (uint32_t stride = 128; stride > 0; stride >>= 1) {
+        if (d < stride) s_partial[d] = __fadd_rn(s_partial[d], s_partial[d + stride]);
+        __syncthreads();
+    }
+    const float norm_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(s_partial[0], (float)n_embd), norm_eps)));
+    for (uint32_t col = d; col < n_embd; col += 256) {
+        const size_t off = (size_t)t * n_embd + col;
+        norm_out[off] = __fmul_rn(__fmul_rn(out[off], norm_scale), norm_w[col]);
+    }
+}
+
+void launch_hc_split_weighted_sum_norm(cudaStream_t st, const float *mix, const float *scale, const float *base,
+                                       const float *residual_hc, const float *norm_w, float *split, float *out,
+                                       float *norm_out, uint32_t n_embd, uint32_t n_rows, uint32_t iters, float epsv,
+                                       float norm_eps)
+{
+    if (n_rows == 0) return;
+    hc_split_weighted_sum_norm_kernel<<<n_rows, 256, 0, st>>>(mix, scale, base, residual_hc, norm_w, split, out, norm_out,
+                                                              n_embd, iters, epsv, norm_eps);
+}
+
 // bf16 -> f32, exact (the bf16 bit pattern is the upper half of the f32 one)
 __global__ void __launch_bounds__(256) bf16_to_f32_kernel(const uint16_t *__restrict__ in, float *__restrict__ out, uint64_t n)
 {

@@ -227,6 +227,14 @@ class MoeKernels:
             assert t is None or (t.is_cuda and t.is_contiguous())
         self._check(self.lib.dsmoe_ffn_forward(self.h, _stream(), layer, C.byref(a)))
 
+    def hc_split_weighted_sum_norm_fused(self, mix, scale, base, residual_hc, norm_w, split, out, norm_out, n_embd: int,
+                                         n_hc: int, n_rows: int, sinkhorn_iters: int, epsv: float, norm_eps: float):
+        """engine/src/kernels/hc.rs:313 - the producer of ffn_norm"""
+        self._check(self.lib.dsmoe_hc_split_weighted_sum_norm(self.h, _stream(), _ptr(mix), _ptr(scale), _ptr(base),
+                                                              _ptr(residual_hc), _ptr(norm_w), _ptr(split), _ptr(out),
+                                                              _ptr(norm_out), n_embd, n_hc, n_rows, sinkhorn_iters, epsv,
+                                                              norm_eps))
+
     def hc_expand(self, block_out, block_add, residual_hc, split, out_hc, n_embd: int, n_hc: int, n_tokens: int,
                   mix_hc: int, has_add: int):
         """engine/src/kernels/hc.rs:212"""

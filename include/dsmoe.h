@@ -299,6 +299,18 @@ DSMOE_API int dsmoe_hc_expand(dsmoe_handle *h, dsmoe_stream stream, const float 
                               const float *residual_hc, const float *split, float *out_hc, uint32_t n_embd,
                               uint32_t n_hc, uint32_t n_tokens, uint32_t mix_hc, uint32_t has_add);
 
+/* hc_split_weighted_sum_norm_fused (engine/src/kernels/hc.rs:313-394 with hc4_split_one, :17-100; call
+ * engine/src/session.rs:1865-1892): the producer of ffn_norm, the input of this path. Per row: the 24-value split
+ * (pre = sigmoid + epsv, post = 2 sigmoid, comb = row softmax + epsv then sinkhorn_iters rounds of Sinkhorn
+ * normalisation), out = sum over the 4 residual streams weighted by pre, norm_out = out * rsqrt(mean(out^2) + norm_eps)
+ * * norm_w. mix [n_rows][24], scale [3], base [24], residual_hc [n_rows][4][n_embd], norm_w [n_embd]; split
+ * [n_rows][24] is the hc_split buffer dsmoe_ffn_forward and dsmoe_hc_expand read (mix_hc = 24). n_hc must be 4. */
+DSMOE_API int dsmoe_hc_split_weighted_sum_norm(dsmoe_handle *h, dsmoe_stream stream, const float *mix,
+                                               const float *scale, const float *base, const float *residual_hc,
+                                               const float *norm_w, float *split, float *out, float *norm_out,
+                                               uint32_t n_embd, uint32_t n_hc, uint32_t n_rows,
+                                               uint32_t sinkhorn_iters, float epsv, float norm_eps);
+
 /* Same with host buffers: copies x and logits in, runs dsmoe_moe_forward on an internal stream, copies out (and the
  * optional routing) back and waits. Host buffers should be page-locked for full copy speed. */
 DSMOE_API int dsmoe_moe_forward_host(dsmoe_handle *h, uint32_t layer, const float *x_host, const float *logits_host,

@@ -95,6 +95,8 @@ def _declare(L: C.CDLL) -> None:
     L.orc_fp8_quantize.argtypes = [_f32p, _u8p, _f32p, C.c_int64, C.c_int64, C.c_int]
     L.orc_fp8_gemm.argtypes = [_u8p, _f32p, _u8p, _f32p, _f32p, C.c_int64, C.c_int64, C.c_int64]
     L.orc_hc_expand.argtypes = [_f32p, _f32p, _f32p, _f32p, _f32p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int]
+    L.orc_hc_split_weighted_sum_norm.argtypes = [_f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, C.c_int64,
+                                                 C.c_int64, C.c_int, C.c_float, C.c_float]
     L.orc_num_threads.restype = C.c_int
     L.orc_set_num_threads.argtypes = [C.c_int]
 
@@ -341,6 +343,23 @@ def hc_expand(block_out: np.ndarray, block_add, residual_hc: np.ndarray, split: 
         lib().orc_hc_expand(_p(bo, _f32p), _p(ba, _f32p), _p(res, _f32p), _p(sp, _f32p), _p(out, _f32p), n_embd, n_hc, T,
                             sp.shape[1], int(ba is not None))
     return out
+
+
+def hc_split_weighted_sum_norm(mix, scale, base, residual_hc, norm_w, iters: int = 20, epsv: float = 1e-6,
+                               norm_eps: float = 1e-6):
+    """hc_split_weighted_sum_norm_fused of engine/src/kernels/hc.rs:313-394. mix [T, 24], scale [3], base [24], residual_hc
+    [T, 4, n_embd], norm_w [n_embd]. Returns (split [T, 24], out [T, n_embd], norm_out [T, n_embd])."""
+    mix, scale, base = _c(mix, np.float32), _c(scale, np.float32), _c(base, np.float32)
+    res, nw = _c(residual_hc, np.float32), _c(norm_w, np.float32)
+    T, _, n_embd = res.shape
+    split = np.empty((T, 24), np.float32)
+    out = np.empty((T, n_embd), np.float32)
+    norm_out = np.empty_like(out)
+    if T:
+        lib().orc_hc_split_weighted_sum_norm(_p(mix, _f32p), _p(scale, _f32p), _p(base, _f32p), _p(res, _f32p), _p(nw, _f32p),
+                                             _p(split, _f32p), _p(out, _f32p), _p(norm_out, _f32p), n_embd, T, iters, epsv,
+                                             norm_eps)
+    return split, out, norm_out
 
 
 def check_div_rn(n: int, seed: int = 1):

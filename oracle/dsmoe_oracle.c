@@ -791,6 +791,88 @@ void orc_hc_expand(const float *block_out, const float *block_add, const float *
             }
 }
 
+/* hc4_split_one, engine/src/kernels/hc.rs:17-100 */
+static void orc_hc4_split_one(float *out, const float *mix, const float *scale, const float *base, int iters, float epsv)
+{
+    const float pre_s = scale[0], post_s = scale[1], comb_s = scale[2];
+    for (int i = 0; i < 4; ++i) {
+        const float z = mix[i] * pre_s + base[i];
+        out[i] = 1.0f / (1.0f + orc_expf(-z)) + epsv;
+    }
+    for (int i = 0; i < 4; ++i) {
+        const float z = mix[4 + i] * post_s + base[4 + i];
+        out[4 + i] = 2.0f / (1.0f + orc_expf(-z));
+    }
+    float c[16];
+    for (int r = 0; r < 4; ++r) {
+        float m = -INFINITY;
+        for (int col = 0; col < 4; ++col) {
+            const float v = mix[8 + r * 4 + col] * comb_s + base[8 + r * 4 + col];
+            c[r * 4 + col] = v;
+            if (v > m) m = v;
+        }
+        float s = 0.0f;
+        for (int col = 0; col < 4; ++col) {
+            const float v = orc_expf(c[r * 4 + col] - m);
+            c[r * 4 + col] = v;
+            s += v;
+        }
+        for (int col = 0; col < 4; ++col) c[r * 4 + col] = c[r * 4 + col] / s + epsv;
+    }
+    for (int col = 0; col < 4; ++col) {
+        float s = epsv;
+        for (int r = 0; r < 4; ++r) s += c[r * 4 + col];
+        for (int r = 0; r < 4; ++r) c[r * 4 + col] /= s;
+    }
+    for (int it = 1; it < iters; ++it) {
+        for (int r = 0; r < 4; ++r) {
+            float s = epsv;
+            for (int col = 0; col < 4; ++col) s += c[r * 4 + col];
+            for (int col = 0; col < 4; ++col) c[r * 4 + col] /= s;
+        }
+        for (int col = 0; col < 4; ++col) {
+            float s = epsv;
+            for (int r = 0; r < 4; ++r) s += c[r * 4 + col];
+            for (int r = 0; r < 4; ++r) c[r * 4 + col] /= s;
+        }
+    }
+    for (int i = 0; i < 16; ++i) out[8 + i] = c[i];
+}
+
+/* hc_split_weighted_sum_norm_fused, engine/src/kernels/hc.rs:313-394: 256 "threads" per row, each summing the squares of
+ * its columns d, d + 256, ..., then the halving tree over the 256 partial sums. */
+void orc_hc_split_weighted_sum_norm(const float *mix, const float *scale, const float *base, const float *residual_hc,
+                                    const float *norm_w, float *split, float *out, float *norm_out, int64_t n_embd,
+                                    int64_t n_rows, int iters, float epsv, float norm_eps)
+{
+    for (int64_t t = 0; t < n_rows; ++t) {
+        float *sp = split + t * 24;
+        orc_hc4_split_one(sp, mix + t * 24, scale, base, iters, epsv);
+        float partial[256];
+        for (int d = 0; d < 256; ++d) {
+            float sum_sq = 0.0f;
+            for (int64_t col = d; col < n_embd; col += 256) {
+                float acc = 0.0f;
+                for (int h = 0; h < 4; ++h) {
+                    const float prod = residual_hc[(t * 4 + h) * n_embd + col] * sp[h];
+                    acc += prod;
+                }
+                out[t * n_embd + col] = acc;
+                const float sq = acc * acc;
+                sum_sq += sq;
+            }
+            partial[d] = sum_sq;
+        }
+        for (int stride = 128; stride > 0; stride >>= 1)
+            for (int d = 0; d < stride; ++d) partial[d] += partial[d + stride];
+        const float norm_scale = 1.0f / sqrtf(partial[0] / (float)n_embd + norm_eps);
+        for (int64_t col = 0; col < n_embd; ++col) {
+            const float v = out[t * n_embd + col] * norm_scale;
+            norm_out[t * n_embd + col] = v * norm_w[col];
+        }
+    }
+}
+
 int orc_num_threads(void)
 {
 #if defined(_OPENMP)

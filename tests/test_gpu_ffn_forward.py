@@ -131,3 +131,33 @@ def test_hc_expand_kernel_bit_exact(torch_cuda, oracle):
         torch.cuda.synchronize()
         assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
     K.close()
+
+
+def test_ffn_pre_norm_producer_bit_exact(torch_cuda, oracle):
+    """hc_split_weighted_sum_norm_fused (the kernel that produces ffn_norm and hc_split) against the oracle, then the
+    whole neighbourhood of the path in sequence: producer -> dsmoe_ffn_forward -> merged residual streams."""
+    torch = torch_cuda
+    from deepseek_rs_b200.kernels import MoeKernels
+
+    K = MoeKernels(device=0, n_expert=32, max_tokens=4)
+    rng = np.random.default_rng(77)
+    for T, n_embd in ((1, 4096), (3, 1000)):
+        mix = rng.standard_normal((T, 24)).astype(np.float32) * 2
+        scale = np.array([0.7, 1.3, 0.9], np.float32)
+        base = (rng.standard_normal(24) * 0.5).astype(np.float32)
+        res = rng.standard_normal((T, 4, n_embd)).astype(np.float32)
+        nw = (1.0 + 0.1 * rng.standard_normal(n_embd)).astype(np.float32)
+        want_split, want_out, want_norm = oracle.hc_split_weighted_sum_norm(mix, scale, base, res, nw, 20, 1e-6, 1e-6)
+        split = torch.zeros((T, 24), device="cuda")
+        out = torch.zeros((T, n_embd), device="cuda")
+        norm = torch.zeros((T, n_embd), device="cuda")
+        K.hc_split_weighted_sum_norm_fused(dev(torch, mix), dev(torch, scale), dev(torch, base), dev(torch, res), dev(torch, nw),
+                                           split, out, norm, n_embd, 4, T, 20, 1e-6, 1e-6)
+        torch.cuda.synchronize()
+        assert np.array_equal(split.cpu().numpy().view(np.uint32), want_split.view(np.uint32))
+        assert np.array_equal(out.cpu().numpy().view(np.uint32), want_out.view(np.uint32))
+        assert np.array_equal(norm.cpu().numpy().view(np.uint32), want_norm.view(np.uint32))
+        # the comb matrix is doubly stochastic up to the eps terms
+        comb = want_split[:, 8:].reshape(T, 4, 4)
+        assert np.allclose(comb.sum(axis=1), 1.0, atol=1e-4) and np.allclose(comb.sum(axis=2), 1.0, atol=1e-3)
+    K.close()

@@ -61,6 +61,30 @@ def test_noalloc_matches_handle_path_twice_in_a_row():
         assert np.all(err <= ABS + REL * np.abs(want)), f"max abs err {err.max()}"
         assert np.array_equal(got, want)
 
+    # NATIVE byte order, the weights output, and a call that asks for neither routing output
+    from deepseek_rs_b200.kernels import LAYOUT_NATIVE
+
+    native = MoeLayer(K, gate, up, down, layout=LAYOUT_NATIVE)
+    r = np.random.default_rng(3)
+    T = 5
+    x = F.bf16_round(r.standard_normal((T, 4096)).astype(np.float32))
+    logits = np.full((T, n_e), -30.0, np.float32)
+    logits[:, :used] = r.standard_normal((T, used))
+    xd, ld = torch.from_numpy(x).cuda(), torch.from_numpy(logits).cuda()
+    w_ref = torch.zeros((T, 6), device="cuda")
+    ref = native.forward(xd, ld, weights_out=w_ref)
+    for want_outputs in (True, False):
+        out = torch.full((T, 4096), float("nan"), device="cuda")
+        wts = torch.zeros((T, 6), device="cuda")
+        rc = lib.dsmoe_moe_forward_noalloc(stream, p(native.gate), p(native.up), p(native.down), LAYOUT_NATIVE, p(xd),
+                                           p(ld), T, p(out), None, p(wts) if want_outputs else None)
+        assert rc == 0
+        code = C.c_int(-1)
+        assert lib.dsmoe_noalloc_device_status(stream, C.byref(code)) == 0 and code.value == 0  # no wait expired
+        assert torch.equal(out, ref)
+        if want_outputs:
+            assert torch.equal(wts, w_ref)
+
     # sizes beyond the static scratch are refused, not truncated
     big = torch.zeros((9, 4096), device="cuda")
     rc = lib.dsmoe_moe_forward_noalloc(stream, p(layer.gate), p(layer.up), p(layer.down), LAYOUT_ROWSOA, p(big),
