@@ -8,7 +8,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libdsmoe.so")
+# DSMOE_CHECKED_BUILD=1 loads the checked variant (python -m deepseek_rs_b200.build --bounds) instead
+LIB_PATH = os.path.join(HERE, "libdsmoe_bounds.so" if os.environ.get("DSMOE_CHECKED_BUILD") == "1" else "libdsmoe.so")
 
 OK = 0
 ERR_ARG, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_BOUNDS, ERR_NOMEM, ERR_STATE = -1, -2, -3, -4, -5, -6, -7

@@ -11,6 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libdsmoe.so")
+LIB_BOUNDS = os.path.join(HERE, "libdsmoe_bounds.so")  # the checked build (-DDSMOE_BOUNDS)
 SOURCES = ["api.cu", "quant_router.cu", "experts.cu", "experts_tma.cu", "noalloc.cu", "prefill.cu", "fp8.cu", "shared.cu", "gguf.cu", "ep.cu"]
 HEADERS = ["common.cuh", "launch.h", "async.cuh", "tc05.cuh", "ep.h", os.path.join("..", "..", "include", "dsmoe.h"),
            os.path.join("..", "..", "include", "dsmoe_iq2_tables.h")]
@@ -30,19 +31,22 @@ def _nvcc() -> str:
     return "nvcc"
 
 
-def needs_build() -> bool:
-    if not os.path.exists(LIB):
+def needs_build(lib: str = LIB) -> bool:
+    if not os.path.exists(lib):
         return True
-    t = os.path.getmtime(LIB)
+    t = os.path.getmtime(lib)
     deps = [os.path.join(CSRC, s) for s in SOURCES + HEADERS] + [os.path.abspath(__file__)]
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and not needs_build():
-        return LIB
-    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + \
-          [os.path.join(CSRC, s) for s in SOURCES]
+def build(force: bool = False, verbose: bool = False, bounds: bool = False) -> str:
+    """bounds=True builds the checked variant: expert indices handed to the tier-2 calls are copied, range-checked and
+    replaced by 0 when outside the layer, with the violation recorded in the status word (no trap, no fault)."""
+    lib = LIB_BOUNDS if bounds else LIB
+    if not force and not needs_build(lib):
+        return lib
+    cmd = [_nvcc()] + NVCC_FLAGS + (["-DDSMOE_BOUNDS"] if bounds else []) + (["-Xptxas", "-v"] if verbose else []) + \
+          ["-o", lib] + [os.path.join(CSRC, s) for s in SOURCES]
     env = dict(os.environ)
     env.pop("CC", None)
     env.pop("CXX", None)
@@ -50,10 +54,9 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if verbose or r.returncode != 0:
         sys.stderr.write(r.stdout + r.stderr)
     if r.returncode != 0:
-        raise RuntimeError("nvcc failed building libdsmoe.so")
-    return LIB
+        raise RuntimeError(f"nvcc failed building {os.path.basename(lib)}")
+    return lib
 
 
 if __name__ == "__main__":
-    build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
-    print(LIB)
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, bounds="--bounds" in sys.argv))

@@ -126,7 +126,14 @@ int check_device(const dsmoe_handle *h)
 
 extern "C" {
 
-const char *dsmoe_version(void) { return "dsmoe 0.1 (sm_100a)"; }
+const char *dsmoe_version(void)
+{
+#ifdef DSMOE_BOUNDS
+    return "dsmoe 0.2 (sm_100a, checked build)";
+#else
+    return "dsmoe 0.2 (sm_100a)";
+#endif
+}
 
 void dsmoe_default_config(dsmoe_config *cfg)
 {
@@ -281,6 +288,8 @@ int dsmoe_device_status(dsmoe_handle *h, dsmoe_stream stream, int *code_out)
     cudaError_t e = cudaMemcpyAsync(code_out, h->d_status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
     if (e != cudaSuccess) return fail(h, DSMOE_ERR_CUDA, "device_status: %s", cudaGetErrorString(e));
+    if (*code_out == DEV_ERR_INDEX_RANGE)
+        return fail(h, DSMOE_ERR_BOUNDS, "an expert index outside the layer was replaced by 0 (checked build, code %d)", *code_out);
     if (*code_out != 0) return fail(h, DSMOE_ERR_TIMEOUT, "a bounded device-side wait expired (code %d)", *code_out);
     return DSMOE_OK;
 }
@@ -606,6 +615,12 @@ static int expert_ffn_impl(dsmoe_handle *h, cudaStream_t st, const dsmoe_layer_s
 {
     const dsmoe_config &c = h->cfg;
     const uint32_t k = c.n_expert_used, xb = c.n_embd / QK_K, mb = c.n_ff / QK_K;
+#ifdef DSMOE_BOUNDS
+    // checked build: the kernels only ever see indices inside the layer (a copy in the handle's own selection buffer)
+    launch_sanitize_indices(st, sel, h->selected, (uint64_t)n_tokens * k, (int32_t)c.n_expert, h->d_status);
+    sel = h->selected;
+    n += 1;
+#endif
     if (n_tokens >= h->prefill_min_tokens && prefill_eligible(c.n_embd, c.n_ff, ly.gate, ly.up, ly.down, ly.layout)) {
         PrefillArgs p = {ly.gate, ly.up, ly.down, xq, sel, wts, h->mid, h->midq, out, h->pf_scratch, h->pf_lay,
                          n_tokens, k, c.n_expert, c.n_embd, c.n_ff, c.swiglu_clamp, ly.layout, (int)c.f16_ieee,

@@ -7,6 +7,7 @@ namespace dsmoe {
 
 // Device-side error codes written to the handle's status word (first error wins).
 constexpr int DEV_ERR_MBAR_TIMEOUT = 1;
+constexpr int DEV_ERR_INDEX_RANGE = 2;  // checked build only: an expert index outside [.., n_expert) was replaced by 0
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

@@ -87,6 +87,8 @@ void launch_moe_sum(cudaStream_t st, const float *down, const int32_t *pos, floa
                     uint32_t n_tokens, const HcEpilogue *hc = nullptr);
 void launch_hc_expand(cudaStream_t st, const float *block_add, uint32_t n_embd, uint32_t n_tokens, const HcEpilogue &hc);
 void launch_bf16_to_f32(cudaStream_t st, const uint16_t *in, float *out, uint64_t n);
+// dst[i] = src[i] < hi ? src[i] : 0, recording DEV_ERR_INDEX_RANGE in *status on a replacement (checked build).
+void launch_sanitize_indices(cudaStream_t st, const int32_t *src, int32_t *dst, uint64_t n, int32_t hi, int *status);
 // hc_split_weighted_sum_norm_fused (engine/src/kernels/hc.rs:313-394), n_hc = 4: split [n_rows][24], out and norm_out
 // [n_rows][n_embd].
 void launch_hc_split_weighted_sum_norm(cudaStream_t st, const float *mix, const float *scale, const float *base,

@@ -588,6 +588,28 @@ void launch_hc_split_weighted_sum_norm(cudaStream_t st, const float *mix, const 
                                                               n_embd, iters, epsv, norm_eps);
 }
 
+// Checked build (-DDSMOE_BOUNDS): expert indices are copied before use, any index >= hi is replaced by 0 and recorded in
+// the status word, so an index that would address memory outside the registered tensors never reaches a kernel.
+// Negative indices are left alone: the kernels map them to expert 0 as the reference does (moe.rs:645-648).
+__global__ void __launch_bounds__(256) sanitize_indices_kernel(const int32_t *src, int32_t *dst,  // may alias
+                                                                uint64_t n, int32_t hi, int *status)
+{
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int32_t v = src[i];
+    if (v >= hi) {
+        v = 0;
+        if (status) atomicCAS(status, 0, 2 /* DEV_ERR_INDEX_RANGE */);
+    }
+    dst[i] = v;
+}
+
+void launch_sanitize_indices(cudaStream_t st, const int32_t *src, int32_t *dst, uint64_t n, int32_t hi, int *status)
+{
+    if (n == 0) return;
+    sanitize_indices_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(src, dst, n, hi, status);
+}
+
 // bf16 -> f32, exact (the bf16 bit pattern is the upper half of the f32 one)
 __global__ void __launch_bounds__(256) bf16_to_f32_kernel(const uint16_t *__restrict__ in, float *__restrict__ out, uint64_t n)
 {

@@ -101,3 +101,49 @@ def test_zero_max_tokens_handle_serves_tier1_calls():
     K.q8k_quantize(x, out, 256, 2)
     torch.cuda.synchronize()
     K.close()
+
+
+def test_checked_build_catches_an_out_of_range_expert_index(oracle):
+    """The checked build (-DDSMOE_BOUNDS) in a child process: an expert index beyond the layer handed to dsmoe_expert_ffn is
+    replaced by 0 before any kernel sees it, the output equals the run with index 0, and the status word reports
+    DSMOE_ERR_BOUNDS. Output buffers carry canary rows on both sides, which must come back untouched."""
+    import os
+    import subprocess
+    import sys
+    import textwrap
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = textwrap.dedent("""
+        import numpy as np, torch
+        from deepseek_rs_b200 import _lib, formats as F
+        from deepseek_rs_b200.kernels import DsmoeError, LAYOUT_ROWSOA, MoeKernels, MoeLayer
+        assert b"checked" in _lib.load().dsmoe_version()
+        n_e, T = 32, 4
+        K = MoeKernels(device=0, n_expert=n_e, n_expert_used=1, max_tokens=T)
+        lw = F.ExpertLayer(seed=3, n_expert=n_e)
+        layer = MoeLayer(K, lw.gate, lw.up, lw.down, layout=LAYOUT_ROWSOA)
+        rng = np.random.default_rng(4)
+        x = torch.from_numpy(rng.standard_normal((T, 4096)).astype(np.float32)).cuda()
+        xq = torch.empty((T, 16, 292), dtype=torch.uint8, device="cuda")
+        K.q8k_quantize(x, xq, 4096, T)
+        w = torch.ones((T, 1), device="cuda")
+        def run(sel):
+            guard = torch.full((T + 2, 4096), 7.25, device="cuda")  # canary rows before and after the output
+            K.expert_ffn(0, xq, torch.tensor(sel, dtype=torch.int32, device="cuda").reshape(T, 1), w, T, guard[1:T + 1])
+            torch.cuda.synchronize()
+            assert bool((guard[0] == 7.25).all()) and bool((guard[T + 1] == 7.25).all()), "canary overwritten"
+            return guard[1:T + 1].clone()
+        good = run([3, 0, 9, 31])
+        assert K.device_status() == 0
+        bad = run([3, n_e + 5, 9, 31])  # would address memory behind the layer's tensors
+        try:
+            K.device_status()
+            raise SystemExit("the out-of-range index was not reported")
+        except DsmoeError as e:
+            assert e.code == _lib.ERR_BOUNDS, e
+        assert torch.equal(bad, good)
+        print("checked build ok")
+    """)
+    env = dict(os.environ, DSMOE_CHECKED_BUILD="1", PYTHONPATH=root)
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, cwd=root, timeout=600)
+    assert r.returncode == 0 and "checked build ok" in r.stdout, r.stdout + r.stderr
