@@ -39,6 +39,7 @@ _SIGS = {
     "refmap_gate_up_mid": [_vp] * 9 + [_u64, _u64, _u32, _u32, _u32, _u32, _f],
     "refmap_down_sum6": [_vp] * 5 + [_u64, _u64, _u32, _u32],
     "refmap_tokens": [_vp] * 11 + [_u32, _u32, _u32, _f],
+    "refmap_batched": [_vp] * 13 + [_u32, _u32, _u32, _f],
 }
 
 
@@ -89,3 +90,23 @@ class RefMapping:
                                            self._p(selected), self._p(weights), self._p(xq), self._p(mid), self._p(midq),
                                            self._p(out), n_embd, n_ff, n_tokens, clamp))
 
+
+    def batched(self, gate, up, down, x, selected, weights, out, n_embd: int, n_ff: int, n_tokens: int, clamp: float):
+        """One chunk through the reference's sorted-pair kernels (the batched form it contains but never calls); scratch
+        is allocated here, outside any timed region of the caller if it passes the returned tuple back in."""
+        torch = self.torch
+        dev, P = x.device, n_tokens * 6
+        scratch = (torch.empty(n_tokens * (n_embd // 256) * 292, dtype=torch.uint8, device=dev),
+                   torch.empty((P, n_ff), device=dev),
+                   torch.empty(P * (n_ff // 256) * 292, dtype=torch.uint8, device=dev),
+                   torch.empty((P, n_embd), device=dev),
+                   torch.empty(770 + P, dtype=torch.int32, device=dev))
+        self.batched_with(scratch, gate, up, down, x, selected, weights, out, n_embd, n_ff, n_tokens, clamp)
+        return scratch
+
+    def batched_with(self, scratch, gate, up, down, x, selected, weights, out, n_embd: int, n_ff: int, n_tokens: int,
+                     clamp: float):
+        xq, mid, midq, rows, idx = scratch
+        self._check(self.lib.refmap_batched(self._stream(), self._p(gate), self._p(up), self._p(down), self._p(x),
+                                            self._p(selected), self._p(weights), self._p(xq), self._p(mid), self._p(midq),
+                                            self._p(rows), self._p(idx), self._p(out), n_embd, n_ff, n_tokens, clamp))

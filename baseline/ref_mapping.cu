@@ -2,12 +2,17 @@
 // written to have a GPU number to put beside the product's on the same B200. It is NOT the reference's binary (its
 // cuda-oxide toolchain is not available) and not part of the product: only tests and the bench load it.
 //
-// What is restated (one kernel each, launched as the reference launches them, i.e. once per token):
+// Two forms are restated. The LIVE form: one kernel each, launched as the reference launches them, i.e. once per token:
 //   q8k_quantize             engine/src/kernels/quantize.rs:309-417   CTA per 256-block, shared-memory max tree
 //   moe_gate_up_mid_qwarp32  engine/src/kernels/moe.rs:622-715        8 lanes per row, 4 rows per quarter-warp, lane b
 //                                                                     walks blocks b, b+8; tables in global memory
 //   moe_down_sum6_qwarp32    engine/src/kernels/moe.rs:922-970        8 lanes per row, the 6 slots in sequence
-// with the block dots of engine/src/kernels/quantize.rs:763-901 in scalar form (byte loads, no dp4a, no vector
+// The BATCHED form, which the reference contains but never calls (its only formulation of a whole chunk at once):
+//   moe_count / prefix / scatter_sorted_pairs  moe.rs:299-362  histogram with global atomics, serial 256-prefix,
+//                                                              atomic-cursor scatter of pair ids into expert order
+//   moe_gate_up_mid_sorted_qwarp32             moe.rs:721-815  the gate/up kernel with the pair read from sorted_pairs
+//   moe_down_sorted_qwarp32 + moe_sum          moe.rs:871-916, 983-1005
+// Both with the block dots of engine/src/kernels/quantize.rs:763-901 in scalar form (byte loads, no dp4a, no vector
 // loads), and the f16 conversion of engine/src/kernels/utils.rs:16-29 (subnormals flush to zero). Arithmetic order is
 // the reference's, each f32 operation rounded separately, so the results equal the CPU oracle bit for bit.
 #include <cuda_runtime.h>
@@ -151,9 +156,11 @@ __global__ void __launch_bounds__(256) gate_up_mid_kernel(const uint8_t *gate, c
                                                            const int32_t *selected, const float *weights, float *gate_out,
                                                            float *up_out, float *mid_out, uint64_t expert_bytes,
                                                            uint64_t row_bytes, uint32_t xq_blocks, uint32_t mid_dim,
-                                                           uint32_t k, float clamp)
+                                                           uint32_t k, float clamp, const uint32_t *sorted_pairs)
 {
-    const uint32_t lane = threadIdx.x & 7, rlane = threadIdx.x >> 3, pair = blockIdx.y, tok = pair / k;
+    // sorted_pairs != null: moe_gate_up_mid_sorted_qwarp32 (moe.rs:721), which differs only in where the pair id comes from
+    const uint32_t lane = threadIdx.x & 7, rlane = threadIdx.x >> 3, pair = sorted_pairs ? sorted_pairs[blockIdx.y] : blockIdx.y;
+    const uint32_t tok = pair / k;
     const int32_t e = selected[pair];
     const uint64_t expert = e < 0 ? 0u : (uint64_t)e;
     const uint8_t *act = xq + (size_t)tok * xq_blocks * Q8K_BYTES;
@@ -205,6 +212,64 @@ __global__ void __launch_bounds__(256) down_sum6_kernel(const uint8_t *down, con
     if (lane == 0) out[row] = total;
 }
 
+// ---- the batched form (engine/src/kernels/moe.rs:299-362, 871-916, 983-1005) -----------------------------------
+__global__ void count_sorted_pairs_kernel(const int32_t *selected, uint32_t *counts, uint32_t pair_count)
+{
+    const uint32_t pair = blockIdx.x * blockDim.x + threadIdx.x;
+    if (pair >= pair_count) return;
+    const int32_t e = selected[pair];
+    atomicAdd(&counts[e < 0 ? 0 : e], 1u);
+}
+
+__global__ void prefix_sorted_pairs_kernel(const uint32_t *counts, uint32_t *offsets, uint32_t *cursors)
+{
+    if (threadIdx.x != 0) return;
+    uint32_t sum = 0;
+    for (int e = 0; e < 256; ++e) {
+        offsets[e] = sum;
+        cursors[e] = sum;
+        sum += counts[e];
+    }
+    offsets[256] = sum;
+}
+
+__global__ void scatter_sorted_pairs_kernel(const int32_t *selected, uint32_t *cursors, uint32_t *sorted_pairs, uint32_t pair_count)
+{
+    const uint32_t pair = blockIdx.x * blockDim.x + threadIdx.x;
+    if (pair >= pair_count) return;
+    const int32_t e = selected[pair];
+    sorted_pairs[atomicAdd(&cursors[e < 0 ? 0 : e], 1u)] = pair;
+}
+
+// grid (ceil(out_dim / 32), n_pairs), 256 threads: quarter-warp per output row of one pair
+__global__ void __launch_bounds__(256) down_sorted_kernel(const uint8_t *down, const uint8_t *midq, const uint32_t *sorted_pairs,
+                                                           const int32_t *selected, float *down_out, uint64_t expert_bytes,
+                                                           uint64_t row_bytes, uint32_t midq_blocks, uint32_t out_dim)
+{
+    const uint32_t lane = threadIdx.x & 7, row = blockIdx.x * 32 + (threadIdx.x >> 3);
+    if (row >= out_dim) return;
+    const uint32_t pair = sorted_pairs[blockIdx.y];
+    const int32_t e = selected[pair];
+    const size_t off = (e < 0 ? 0u : (uint64_t)e) * expert_bytes + (size_t)row * row_bytes;
+    const uint8_t *act = midq + (size_t)pair * midq_blocks * Q8K_BYTES;
+    float acc = 0.0f;
+    for (uint32_t b = lane; b < midq_blocks; b += 8)
+        acc = __fadd_rn(acc, dot_q2k(down + off + (size_t)b * Q2K_BYTES, act + (size_t)b * Q8K_BYTES));
+    acc = sum8(acc);
+    if (lane == 0) down_out[(size_t)pair * out_dim + row] = acc;
+}
+
+// moe_sum (moe.rs:983-1005): one thread per (token, row), slots added in slot order
+__global__ void __launch_bounds__(256) moe_sum_kernel(const float *down, float *out, uint32_t out_dim, uint32_t k, uint64_t n)
+{
+    const uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= n) return;
+    const uint64_t tok = gid / out_dim, row = gid - tok * out_dim;
+    float acc = 0.0f;
+    for (uint32_t slot = 0; slot < k; ++slot) acc = __fadd_rn(acc, down[(tok * k + slot) * out_dim + row]);
+    out[gid] = acc;
+}
+
 }  // namespace refmap
 
 #define REFMAP_API extern "C" __attribute__((visibility("default")))
@@ -229,7 +294,7 @@ REFMAP_API int refmap_gate_up_mid(void *stream, const uint8_t *gate, const uint8
 {
     if (n_tokens == 0) return 0;
     refmap::gate_up_mid_kernel<<<dim3((mid_dim + 127) / 128, n_tokens * k), 256, 0, (cudaStream_t)stream>>>(
-        gate, up, xq, selected, weights, gate_out, up_out, mid_out, expert_bytes, row_bytes, xq_blocks, mid_dim, k, clamp);
+        gate, up, xq, selected, weights, gate_out, up_out, mid_out, expert_bytes, row_bytes, xq_blocks, mid_dim, k, clamp, nullptr);
     return (int)cudaGetLastError();
 }
 
@@ -257,5 +322,35 @@ REFMAP_API int refmap_tokens(void *stream, const uint8_t *gate, const uint8_t *u
         refmap_down_sum6(stream, down, midq, selected + 6 * t, out + (size_t)t * n_embd,
                          (uint64_t)n_embd * mb * refmap::Q2K_BYTES, (uint64_t)mb * refmap::Q2K_BYTES, mb, n_embd);
     }
+    return (int)cudaGetLastError();
+}
+
+// The batched form for one chunk of n_tokens tokens: pairs counted, prefixed and scattered into expert order, then one
+// launch each of Q8_K(x), sorted gate/up/mid, Q8_K(mid), sorted down and the slot sum. Scratch (device): xq
+// [n_tokens][n_embd/256][292], mid f32 [n_tokens*6][n_ff], midq [n_tokens*6][n_ff/256][292], down_rows f32
+// [n_tokens*6][n_embd], idx u32 [257 + 257 + 256 + n_tokens*6] (counts, offsets, cursors, sorted pairs).
+REFMAP_API int refmap_batched(void *stream, const uint8_t *gate, const uint8_t *up, const uint8_t *down, const float *x,
+                              const int32_t *selected, const float *weights, uint8_t *xq, float *mid, uint8_t *midq,
+                              float *down_rows, uint32_t *idx, float *out, uint32_t n_embd, uint32_t n_ff, uint32_t n_tokens,
+                              float clamp)
+{
+    if (n_tokens == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint32_t xb = n_embd / 256, mb = n_ff / 256, k = 6, P = n_tokens * k;
+    uint32_t *counts = idx, *offsets = idx + 257, *cursors = idx + 514, *sorted = idx + 770;
+    cudaMemsetAsync(counts, 0, 257 * sizeof(uint32_t), st);
+    refmap::count_sorted_pairs_kernel<<<(P + 255) / 256, 256, 0, st>>>(selected, counts, P);
+    refmap::prefix_sorted_pairs_kernel<<<1, 1, 0, st>>>(counts, offsets, cursors);
+    refmap::scatter_sorted_pairs_kernel<<<(P + 255) / 256, 256, 0, st>>>(selected, cursors, sorted, P);
+    refmap_q8k_quantize(stream, x, xq, n_embd, n_tokens);
+    refmap::gate_up_mid_kernel<<<dim3((n_ff + 127) / 128, P), 256, 0, st>>>(
+        gate, up, xq, selected, weights, nullptr, nullptr, mid, (uint64_t)n_ff * xb * refmap::IQ2_BYTES,
+        (uint64_t)xb * refmap::IQ2_BYTES, xb, n_ff, k, clamp, sorted);
+    refmap_q8k_quantize(stream, mid, midq, n_ff, P);
+    refmap::down_sorted_kernel<<<dim3((n_embd + 31) / 32, P), 256, 0, st>>>(down, midq, sorted, selected, down_rows,
+                                                                             (uint64_t)n_embd * mb * refmap::Q2K_BYTES,
+                                                                             (uint64_t)mb * refmap::Q2K_BYTES, mb, n_embd);
+    const uint64_t n = (uint64_t)n_tokens * n_embd;
+    refmap::moe_sum_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(down_rows, out, n_embd, k, n);
     return (int)cudaGetLastError();
 }

@@ -94,6 +94,7 @@ SIGNATURES = {
     "dsmoe_ep_expert_counts": (_int, [_vp, _vp, _vp, _int]),
     "dsmoe_ep_last_recv_rows": (_int, [_vp, _vp]),
     "dsmoe_ep_set_phase_events": (_int, [_vp, C.POINTER(_vp), _int]),
+    "dsmoe_ep_combine_is_fused": (_int, [_vp]),
     "dsmoe_moe_forward_ep": (_int, [_vp, _vp, _u32, _vp, _vp, _u32, _vp, _vp, _vp]),
     "dsmoe_gguf_open": (_int, [C.c_char_p, C.POINTER(_vp)]),
     "dsmoe_gguf_open_memory": (_int, [_vp, C.c_size_t, C.POINTER(_vp)]),

@@ -611,7 +611,7 @@ int dsmoe_layer_register_extras(dsmoe_handle *h, uint32_t layer, const uint16_t 
 // kernels or, from prefill_min_tokens rows upwards, on the grouped GEMM.
 static int expert_ffn_impl(dsmoe_handle *h, cudaStream_t st, const dsmoe_layer_slot &ly, const uint8_t *xq,
                            const int32_t *sel, const float *wts, uint32_t n_tokens, float *out, int n, const char *what,
-                           const HcEpilogue *hc = nullptr, cudaEvent_t before_sum = nullptr)
+                           const HcEpilogue *hc = nullptr, cudaEvent_t before_sum = nullptr, float *const *row_ptr = nullptr)
 {
     const dsmoe_config &c = h->cfg;
     const uint32_t k = c.n_expert_used, xb = c.n_embd / QK_K, mb = c.n_ff / QK_K;
@@ -624,7 +624,7 @@ static int expert_ffn_impl(dsmoe_handle *h, cudaStream_t st, const dsmoe_layer_s
     if (n_tokens >= h->prefill_min_tokens && prefill_eligible(c.n_embd, c.n_ff, ly.gate, ly.up, ly.down, ly.layout)) {
         PrefillArgs p = {ly.gate, ly.up, ly.down, xq, sel, wts, h->mid, h->midq, out, h->pf_scratch, h->pf_lay,
                          n_tokens, k, c.n_expert, c.n_embd, c.n_ff, c.swiglu_clamp, ly.layout, (int)c.f16_ieee,
-                         h->d_status, h->phase_events_set ? h->phase_events : nullptr, hc, before_sum};
+                         h->d_status, h->phase_events_set ? h->phase_events : nullptr, hc, before_sum, row_ptr};
         n += launch_prefill_experts(st, p);
         return check_launch(h, what, n);
     }
@@ -644,6 +644,10 @@ static int expert_ffn_impl(dsmoe_handle *h, cudaStream_t st, const dsmoe_layer_s
     if (before_sum) cudaStreamWaitEvent(st, before_sum, 0);
     if (hc && hc->out_hc) {
         launch_hc_expand(st, out, c.n_embd, n_tokens, *hc);
+        n += 1;
+    }
+    if (row_ptr) {  // the decode kernels wrote `out`; the rows go to their destinations with a copy kernel
+        launch_scatter_rows(st, out, row_ptr, c.n_embd, n_tokens);
         n += 1;
     }
     return check_launch(h, what, n);
@@ -871,6 +875,12 @@ int dsmoe_ep_last_recv_rows(dsmoe_handle *h, int32_t *rows_per_rank)
     return ep_last_recv_rows(h->ep, rows_per_rank);
 }
 
+int dsmoe_ep_combine_is_fused(dsmoe_handle *h)
+{
+    if (!h || !h->ep) return 0;
+    return ep_p2p_combine(h->ep);
+}
+
 int dsmoe_ep_set_phase_events(dsmoe_handle *h, void **events, int n_events)
 {
     DSMOE_ENTER(h);
@@ -909,6 +919,21 @@ int dsmoe_moe_forward_ep(dsmoe_handle *h, dsmoe_stream stream, uint32_t layer, c
                               h->ep_events_set ? h->ep_events : nullptr);
     if (rc != DSMOE_OK) return fail(h, rc, "%s", ep_last_error(h->ep));
     return check_launch(h, "moe_forward_ep", n);
+}
+
+// Internal (expert parallel): dsmoe_expert_ffn for a k = 1 handle whose result rows go to row_ptr[i] instead of a local
+// array; `out` ([n_tokens][n_embd]) is scratch for the case that the decode kernels run. Not part of the C ABI.
+int dsmoe_expert_ffn_rows(dsmoe_handle *h, cudaStream_t st, uint32_t layer, const uint8_t *xq, const int32_t *selected,
+                          const float *weights, uint32_t n_tokens, float *out, float *const *row_ptr)
+{
+    DSMOE_ENTER(h);
+    const dsmoe_config &c = h->cfg;
+    const uint32_t L = c.max_layers ? c.max_layers : 1;
+    if (layer >= L || !h->layers[layer].set) return fail(h, DSMOE_ERR_STATE, "expert_ffn: layer %u not registered", layer);
+    if (n_tokens > c.max_tokens) return fail(h, DSMOE_ERR_BOUNDS, "expert_ffn: n_tokens %u exceeds max_tokens %u", n_tokens, c.max_tokens);
+    if (c.n_expert_used != 1) return fail(h, DSMOE_ERR_STATE, "expert_ffn_rows: needs a handle with n_expert_used = 1");
+    if (n_tokens == 0) return DSMOE_OK;
+    return expert_ffn_impl(h, st, h->layers[layer], xq, selected, weights, n_tokens, out, 0, "expert_ffn", nullptr, nullptr, row_ptr);
 }
 
 int dsmoe_host_synchronize(dsmoe_handle *h)

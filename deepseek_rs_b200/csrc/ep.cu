@@ -7,6 +7,13 @@
 //             of 16 KB of f32) plus its expert id local to the owner and its router weight;
 //   combine   the owner returns the pair's down-projection row (f32 [n_embd]); the source sums a token's k rows in
 //             slot order straight from the receive buffer, so the result does not depend on arrival order.
+//             By default the combine is FUSED into the owner's down-projection kernel: every rank maps the others'
+//             receive buffers (CUDA IPC, exchanged once at set-up) and the grouped GEMM's epilogue stores each finished
+//             row straight into its source rank's buffer with plain global stores over NVLink, so the rows travel while
+//             the GEMM is still running and no separate transfer follows it. A four-byte all-gather after the kernel is
+//             the only synchronisation: when it completes on a rank, every peer's GEMM (which precedes the peer's
+//             all-gather in stream order) has finished writing. No TMA and no multicast is involved.
+//             DSMOE_EP_NO_P2P=1, or a failed IPC mapping, falls back to grouped ncclSend / ncclRecv of the rows.
 // Experts named by dsmoe_ep_set_replicas are held by every rank: their pairs stay on the rank that routed them.
 //
 // Everything between the router and the slot sum is device work on the caller's stream: the pairs are counted and
@@ -21,6 +28,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <vector>
@@ -181,6 +189,28 @@ __global__ void __launch_bounds__(256) ep_gather_kernel(EpRoute r, const uint32_
     }
 }
 
+// row_ptr[i] for received row i: where its result goes in the buffer of the rank it came from. seg_end[s] = end of
+// the rows received from rank s, dst_base[s] = first slot of this rank's segment in rank s's send order.
+struct EpRowMap {
+    float *peer_back[16];
+    uint32_t seg_end[16], dst_base[16];
+    uint32_t world, n_embd;
+};
+__global__ void __launch_bounds__(256) ep_row_ptr_kernel(EpRowMap m, uint32_t n_rows, float **__restrict__ row_ptr)
+{
+    const uint32_t i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= n_rows) return;
+    uint32_t s = 0, begin = 0;
+    while (s + 1 < m.world && i >= m.seg_end[s]) begin = m.seg_end[s], ++s;
+    row_ptr[i] = m.peer_back[s] + (size_t)(m.dst_base[s] + (i - begin)) * m.n_embd;
+}
+
+// expert_ffn of the owner-side handle with per-row destinations (api.cu; not part of the C ABI)
+}  // namespace dsmoe
+extern "C" int dsmoe_expert_ffn_rows(dsmoe_handle *h, cudaStream_t st, uint32_t layer, const uint8_t *xq, const int32_t *selected,
+                          const float *weights, uint32_t n_tokens, float *out, float *const *row_ptr);
+namespace dsmoe {
+
 // ---- host side ----------------------------------------------------------------------------------------------------
 struct EpState {
     const NcclApi *nccl = nullptr;
@@ -196,6 +226,11 @@ struct EpState {
     unsigned long long *hist = nullptr;
     uint8_t *send_xq = nullptr, *recv_xq = nullptr;
     float *send_w = nullptr, *recv_w = nullptr, *rows = nullptr, *back = nullptr;
+    // fused combine: the peers' `back` buffers mapped into this process, and per received row its destination
+    bool p2p = false;
+    float *peer_back[16] = {};
+    float **row_ptr = nullptr;
+    int32_t *token = nullptr;  // [1 + world] ints for the completion all-gather
     // pinned host
     int32_t *h_matrix = nullptr;
     std::vector<int32_t> last_recv;  // rows received from each rank in the most recent step
@@ -216,7 +251,10 @@ const char *ep_last_error(const EpState *s) { return s ? s->err : ""; }
 void ep_destroy(EpState *s)
 {
     if (!s) return;
+    for (int i = 0; i < s->world && i < 16; ++i)
+        if (s->p2p && i != s->rank && s->peer_back[i]) cudaIpcCloseMemHandle(s->peer_back[i]);
     if (s->comm && s->own_comm && s->nccl) s->nccl->CommDestroy(s->comm);
+    cudaFree(s->row_ptr), cudaFree(s->token);
     if (s->owner) dsmoe_destroy(s->owner);
     cudaFree(s->replica_slot), cudaFree(s->send_counts), cudaFree(s->count_matrix), cudaFree(s->pos), cudaFree(s->send_sel);
     cudaFree(s->recv_sel), cudaFree(s->order), cudaFree(s->hist), cudaFree(s->send_xq), cudaFree(s->recv_xq);
@@ -293,6 +331,61 @@ int ep_create(const dsmoe_config &cfg, int device, const uint8_t *id128, void *a
         return fail_early(DSMOE_ERR_NOMEM, "ep_init: device allocation failed");
     }
     s->last_recv.assign(W, 0);
+    // Fused combine: exchange CUDA IPC handles of the `back` buffers through the communicator and map the peers'. Any
+    // failure leaves p2p off on EVERY rank (the decision is agreed through a second all-gather), and the combine then
+    // goes through NCCL.
+    {
+        const char *no_p2p = getenv("DSMOE_EP_NO_P2P");
+        int want = world <= 16 && !(no_p2p && no_p2p[0] == '1') ? 1 : 0;
+        uint8_t *d_handles = nullptr;
+        int32_t *d_flags = nullptr;
+        ok = cudaMalloc((void **)&s->row_ptr, C * sizeof(float *)) == cudaSuccess &&
+             cudaMalloc((void **)&s->token, (1 + W) * sizeof(int32_t)) == cudaSuccess &&
+             cudaMemset(s->token, 0, (1 + W) * sizeof(int32_t)) == cudaSuccess &&
+             cudaMalloc((void **)&d_handles, (W + 1) * sizeof(cudaIpcMemHandle_t)) == cudaSuccess &&
+             cudaMalloc((void **)&d_flags, (W + 1) * sizeof(int32_t)) == cudaSuccess;
+        std::vector<cudaIpcMemHandle_t> handles(W);
+        cudaIpcMemHandle_t mine;
+        memset(&mine, 0, sizeof(mine));
+        if (ok && want && cudaIpcGetMemHandle(&mine, s->back) != cudaSuccess) want = 0;
+        cudaGetLastError();
+        if (ok) {
+            ok = cudaMemcpy(d_handles + W * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice) == cudaSuccess &&
+                 api->AllGather(d_handles + W * sizeof(mine), d_handles, sizeof(mine), NCCL_UINT8, s->comm, nullptr) == 0 &&
+                 cudaStreamSynchronize(nullptr) == cudaSuccess &&
+                 cudaMemcpy(handles.data(), d_handles, W * sizeof(mine), cudaMemcpyDeviceToHost) == cudaSuccess;
+        }
+        if (ok && want) {
+            for (int i = 0; i < world; ++i) {
+                if (i == rank) {
+                    s->peer_back[i] = s->back;
+                } else if (cudaIpcOpenMemHandle((void **)&s->peer_back[i], handles[(size_t)i], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+                    cudaGetLastError();
+                    s->peer_back[i] = nullptr;
+                    want = 0;
+                }
+            }
+        }
+        std::vector<int32_t> flags(W, 0);
+        if (ok) {
+            ok = cudaMemcpy(d_flags + W, &want, sizeof(int32_t), cudaMemcpyHostToDevice) == cudaSuccess &&
+                 api->AllGather(d_flags + W, d_flags, 1, NCCL_INT32, s->comm, nullptr) == 0 &&
+                 cudaStreamSynchronize(nullptr) == cudaSuccess &&
+                 cudaMemcpy(flags.data(), d_flags, W * sizeof(int32_t), cudaMemcpyDeviceToHost) == cudaSuccess;
+        }
+        cudaFree(d_handles), cudaFree(d_flags);
+        if (!ok) {
+            cudaGetLastError();
+            ep_destroy(s);
+            return fail_early(DSMOE_ERR_CUDA, "ep_init: exchange of the peer-buffer handles failed");
+        }
+        bool all = want != 0;
+        for (size_t i = 0; i < W; ++i) all = all && flags[i] != 0;
+        if (!all)
+            for (int i = 0; i < world; ++i)
+                if (i != rank && s->peer_back[i]) cudaIpcCloseMemHandle(s->peer_back[i]), s->peer_back[i] = nullptr;
+        s->p2p = all;
+    }
     *out = s;
     return DSMOE_OK;
 }
@@ -300,6 +393,7 @@ int ep_create(const dsmoe_config &cfg, int device, const uint8_t *id128, void *a
 dsmoe_handle *ep_owner(EpState *s) { return s->owner; }
 int ep_rank(const EpState *s) { return s->rank; }
 int ep_world(const EpState *s) { return s->world; }
+int ep_p2p_combine(const EpState *s) { return s->p2p ? 1 : 0; }
 
 int ep_set_replicas(EpState *s, uint32_t n_expert, const int32_t *ids, uint32_t n)
 {
@@ -398,13 +492,42 @@ int ep_forward(EpState *s, cudaStream_t st, uint32_t layer, const uint8_t *xq, c
     EP_NCCL(s->nccl->GroupEnd(), "dispatch");
     mark(2);
     // 4. the owner's compute: every received row is one (token, slot) pair of one local expert
-    if (R) {
+    if (R && s->p2p) {
+        // fused combine: the down projection's epilogue stores every row where its source rank will sum it
+        EpRowMap m = {};
+        m.world = W, m.n_embd = n_embd;
+        for (uint32_t src = 0; src < W; ++src) {
+            m.peer_back[src] = s->peer_back[src];
+            m.seg_end[src] = (uint32_t)roff[src + 1];
+            uint32_t base = 0;
+            for (uint32_t d = 0; d < (uint32_t)s->rank; ++d) base += (uint32_t)M[src * W + d];
+            m.dst_base[src] = base;
+        }
+        ep_row_ptr_kernel<<<((uint32_t)R + 255) / 256, 256, 0, st>>>(m, (uint32_t)R, s->row_ptr);
+        const uint64_t before = dsmoe_launch_count(s->owner);
+        const int rc = dsmoe_expert_ffn_rows(s->owner, st, layer, s->recv_xq, s->recv_sel, s->recv_w, (uint32_t)R, s->rows, s->row_ptr);
+        if (rc != DSMOE_OK) return ep_fail(s, rc, "moe_forward_ep: owner compute: %s", dsmoe_last_error(s->owner));
+        *n_launched += 1 + (int)(dsmoe_launch_count(s->owner) - before);
+    } else if (R) {
         const uint64_t before = dsmoe_launch_count(s->owner);
         const int rc = dsmoe_expert_ffn(s->owner, st, layer, s->recv_xq, s->recv_sel, s->recv_w, (uint32_t)R, s->rows);
         if (rc != DSMOE_OK) return ep_fail(s, rc, "moe_forward_ep: owner compute: %s", dsmoe_last_error(s->owner));
         *n_launched += (int)(dsmoe_launch_count(s->owner) - before);
     }
     mark(3);
+    if (s->p2p) {
+        // completion: a rank's all-gather follows its GEMM in stream order, so when this one completes here every peer
+        // has finished storing into this rank's buffer
+        EP_NCCL(s->nccl->AllGather(s->token, s->token + 1, 1, NCCL_INT32, s->comm, st), "combine completion");
+        mark(4);
+        if (P) {
+            launch_moe_sum(st, s->back, s->pos, out, n_embd, k, n_tokens);
+            EP_CUDA(cudaGetLastError(), "slot sum");
+            *n_launched += 1;
+        }
+        mark(5);
+        return DSMOE_OK;
+    }
     // 5. combine: the rows travel back along the same splits and land in send order
     EP_NCCL(s->nccl->GroupStart(), "combine");
     for (uint32_t peer = 0; peer < W; ++peer) {

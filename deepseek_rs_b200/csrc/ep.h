@@ -20,6 +20,7 @@ const char *ep_last_error(const EpState *s);
 dsmoe_handle *ep_owner(EpState *s);
 int ep_rank(const EpState *s);
 int ep_world(const EpState *s);
+int ep_p2p_combine(const EpState *s);  // 1: the combine is fused into the owner's down projection (peer stores)
 int ep_set_replicas(EpState *s, uint32_t n_expert, const int32_t *ids, uint32_t n);
 int ep_expert_counts(EpState *s, cudaStream_t st, uint32_t n_expert, uint64_t *host_out, int reset);
 int ep_last_recv_rows(const EpState *s, int32_t *per_rank_out);

@@ -87,6 +87,8 @@ void launch_moe_sum(cudaStream_t st, const float *down, const int32_t *pos, floa
                     uint32_t n_tokens, const HcEpilogue *hc = nullptr);
 void launch_hc_expand(cudaStream_t st, const float *block_add, uint32_t n_embd, uint32_t n_tokens, const HcEpilogue &hc);
 void launch_bf16_to_f32(cudaStream_t st, const uint16_t *in, float *out, uint64_t n);
+// dst[i][0 .. n_embd) = rows[i][0 .. n_embd) for i < n_rows; the destinations may lie in another GPU's memory.
+void launch_scatter_rows(cudaStream_t st, const float *rows, float *const *dst, uint32_t n_embd, uint32_t n_rows);
 // dst[i] = src[i] < hi ? src[i] : 0, recording DEV_ERR_INDEX_RANGE in *status on a replacement (checked build).
 void launch_sanitize_indices(cudaStream_t st, const int32_t *src, int32_t *dst, uint64_t n, int32_t hi, int *status);
 // hc_split_weighted_sum_norm_fused (engine/src/kernels/hc.rs:313-394), n_hc = 4: split [n_rows][24], out and norm_out
@@ -164,6 +166,7 @@ struct PrefillArgs {
     cudaEvent_t *phase_events;         // optional, 6 events: start, grouped+gathered, gate/up, q8k+gather, down, sum
     const HcEpilogue *hc;              // optional: hc_expand fused into the slot sum
     cudaEvent_t before_sum;            // optional: the stream waits for this event before the slot sum (shared expert done)
+    float *const *row_ptr;             // optional (k == 1): row_ptr[pair] receives the pair's down row; no slot sum then
 };
 // Everything after the router and the Q8_K of x. Returns the number of kernels launched.
 int launch_prefill_experts(cudaStream_t st, const PrefillArgs &p);

@@ -265,6 +265,8 @@ struct PfGemmArgs {
     const uint32_t *sorted, *tile_expert, *tile_start, *tile_rows, *tile_boff, *plan;
     const float *weights;    // IQ2: router weight per pair
     float *out;              // IQ2: mid [pair][out_dim]; Q2K: per-pair down rows [pair][out_dim]
+    float *const *row_ptr;   // Q2K, optional: row_ptr[pair] is where that pair's down row goes instead (it may point into
+                             // another GPU's memory: the expert-parallel combine fused into this kernel's epilogue)
     uint32_t out_dim, kblocks;
     float clamp;
     int ieee, layout;
@@ -748,9 +750,17 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
                         const uint4 t = *reinterpret_cast<const uint4 *>(sP + acol0 + i0 + 4 * q);
                         pr[4 * q] = t.x, pr[4 * q + 1] = t.y, pr[4 * q + 2] = t.z, pr[4 * q + 3] = t.w;
                     }
+                    if (a.row_ptr != nullptr) {
+                        // plain stores through the row's own pointer: the 32 lanes of a warp write 128 contiguous bytes
+                        // of one row, local or across NVLink
 #pragma unroll
-                    for (int k = 0; k < 8; ++k)
-                        if (acol0 + i0 + k < rows) orow[(size_t)pr[k] * a.out_dim] = acc[i0 + k];
+                        for (int k = 0; k < 8; ++k)
+                            if (acol0 + i0 + k < rows) a.row_ptr[pr[k]][mt * 128 + arow] = acc[i0 + k];
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            if (acol0 + i0 + k < rows) orow[(size_t)pr[k] * a.out_dim] = acc[i0 + k];
+                    }
                 }
             }
         }
@@ -1047,13 +1057,15 @@ int launch_prefill_experts(cudaStream_t st, const PrefillArgs &p)
     d.w0 = p.down, d.w1 = nullptr, d.expert_bytes = (uint64_t)p.n_embd * mb * Q2K_BYTES;
     d.B = w + L.bm, d.S = reinterpret_cast<const float *>(w + L.sm), d.BS = reinterpret_cast<const __half *>(w + L.bs);
     d.weights = nullptr, d.out = reinterpret_cast<float *>(w + L.down_pair), d.out_dim = p.n_embd, d.kblocks = mb;
+    d.row_ptr = p.row_ptr;
     pf_grouped_gemm_kernel<PF_Q2K><<<sms, PF_THREADS, PF_SMEM_TOTAL, st>>>(d);
     mark(4);
-    // 6. slots summed in slot order
+    // 6. slots summed in slot order (not when the rows went to their own destinations: the receiver sums them)
     if (p.before_sum) cudaStreamWaitEvent(st, p.before_sum, 0);
-    launch_moe_sum(st, reinterpret_cast<const float *>(w + L.down_pair), nullptr, p.out, p.n_embd, p.k, p.n_tokens, p.hc);
+    if (!p.row_ptr)
+        launch_moe_sum(st, reinterpret_cast<const float *>(w + L.down_pair), nullptr, p.out, p.n_embd, p.k, p.n_tokens, p.hc);
     mark(5);
-    return n + 6;
+    return n + (p.row_ptr ? 5 : 6);
 }
 
 }  // namespace dsmoe

@@ -610,6 +610,23 @@ void launch_sanitize_indices(cudaStream_t st, const int32_t *src, int32_t *dst, 
     sanitize_indices_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(src, dst, n, hi, status);
 }
 
+// Copies row i to dst[i] (expert-parallel combine on the decode path: plain 16-byte stores, possibly across NVLink).
+__global__ void __launch_bounds__(256) scatter_rows_kernel(const float *__restrict__ rows, float *const *__restrict__ dst,
+                                                            uint32_t n_embd, uint32_t n_rows)
+{
+    const uint32_t row = blockIdx.x;
+    if (row >= n_rows) return;
+    const float4 *src = reinterpret_cast<const float4 *>(rows + (size_t)row * n_embd);
+    float4 *d = reinterpret_cast<float4 *>(dst[row]);
+    for (uint32_t i = threadIdx.x; i < n_embd / 4; i += 256) d[i] = src[i];
+}
+
+void launch_scatter_rows(cudaStream_t st, const float *rows, float *const *dst, uint32_t n_embd, uint32_t n_rows)
+{
+    if (n_rows == 0) return;
+    scatter_rows_kernel<<<n_rows, 256, 0, st>>>(rows, dst, n_embd, n_rows);
+}
+
 // bf16 -> f32, exact (the bf16 bit pattern is the upper half of the f32 one)
 __global__ void __launch_bounds__(256) bf16_to_f32_kernel(const uint16_t *__restrict__ in, float *__restrict__ out, uint64_t n)
 {

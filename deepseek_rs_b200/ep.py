@@ -72,6 +72,11 @@ class ExpertParallelHandle:
         self.k._check(self.k.lib.dsmoe_ep_expert_counts(self.k.h, stream, C.c_void_p(out.data_ptr()), int(reset)))
         return out
 
+    @property
+    def combine_is_fused(self) -> bool:
+        """True when the owner's down projection stores its rows straight into the source ranks' buffers (peer memory)."""
+        return bool(self.k.lib.dsmoe_ep_combine_is_fused(self.k.h))
+
     def last_recv_rows(self) -> list:
         import ctypes as C
 

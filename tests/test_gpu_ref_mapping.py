@@ -85,3 +85,24 @@ def test_per_token_loop_matches_oracle_layer(torch_cuda, oracle, refmap):
                   xq, mid, midq, out, 4096, 2048, T, 10.0)
     torch.cuda.synchronize()
     assert np.array_equal(out.cpu().numpy(), want)
+
+
+def test_batched_sorted_form_matches_oracle_layer(torch_cuda, oracle, refmap):
+    """The reference's unused batched formulation (count / prefix / scatter of pairs into expert order, sorted gate/up
+    and down kernels, slot sum; engine/src/kernels/moe.rs:299-362, 721-916, 983-1005): the atomic scatter makes the
+    order inside an expert arbitrary, the result does not depend on it and equals the oracle bit for bit."""
+    torch = torch_cuda
+    n_e, T = 16, 9
+    lw = F.ExpertLayer(seed=23, n_expert=n_e)
+    rng = np.random.default_rng(24)
+    x = F.bf16_round(rng.standard_normal((T, 4096)).astype(np.float32))
+    logits = rng.standard_normal((T, n_e)).astype(np.float32)
+    want, sel, w = oracle.moe_layer(x, logits, lw.gate, lw.up, lw.down, k=6)
+    out = torch.empty((T, 4096), device="cuda")
+    scratch = refmap.batched(dev(torch, lw.gate), dev(torch, lw.up), dev(torch, lw.down), dev(torch, x), dev(torch, sel),
+                             dev(torch, w), out, 4096, 2048, T, 10.0)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), want)
+    sorted_pairs = scratch[4][770:770 + T * 6].cpu().numpy()
+    assert sorted(sorted_pairs.tolist()) == list(range(T * 6))
+    assert np.all(np.diff(sel.reshape(-1)[sorted_pairs]) >= 0)  # grouped by expert
