@@ -59,6 +59,10 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 }
 
 void launch_q8k_quantize(cudaStream_t st, const float *x, uint8_t *out, uint32_t in_dim, uint32_t n_rows);
+// mid = swiglu(clamped gate, clamped up) * weight[row] (engine/src/kernels/moe.rs:692-710) quantised to Q8_K on the fly
+// (quantize.rs:309-417): gate / up f32 [n_rows][in_dim], weight f32 [n_rows], out Q8_K [n_rows][in_dim / 256].
+void launch_swiglu_q8k(cudaStream_t st, const float *gate, const float *up, const float *weight, uint8_t *out,
+                       uint32_t in_dim, uint32_t n_rows, float clamp);
 
 void launch_router_select(cudaStream_t st, const float *logits, const float *bias, const int32_t *hash,
                           const int32_t *tokens, float *probs, int32_t *selected, float *weights, int32_t token_scalar,
@@ -143,7 +147,7 @@ int launch_down_tma(cudaStream_t st, const DownArgs &a, int *status);
 // Batched path (tcgen05 grouped GEMM). Scratch is one device buffer carved up by prefill_scratch_bytes().
 struct PrefillScratch {
     uint32_t r_cap, tile_cap;
-    size_t counts, offsets, sorted, tile_expert, tile_start, tile_rows, tile_boff, plan, bx, sx, bm, sm, bs, down_pair;
+    size_t counts, offsets, sorted, tile_expert, tile_start, tile_rows, tile_boff, plan, bx, sx, bm, sm, bs, down_pair, up_rows;
 };
 size_t prefill_scratch_bytes(uint32_t max_tokens, uint32_t k, uint32_t n_expert, uint32_t n_embd, uint32_t n_ff,
                              PrefillScratch *lay);

@@ -12,8 +12,8 @@
 // Pipeline (all on the caller's stream, no host synchronisation):
 //   1 pair_count / pair_plan / pair_place   stable counting sort of (token, slot) pairs by expert + token-tile list
 //   2 gather_acts                           Q8_K rows of each tile -> f16 operand tiles in the tensor-core layout
-//   3 grouped_gemm<IQ2>                     gate & up (64 + 64 rows per tile) -> clamp, SwiGLU, weight -> mid f32
-//   4 q8k_quantize(mid), gather_acts        as in decode
+//   3 grouped_gemm<IQ2>                     gate & up (64 + 64 rows per tile) -> gate and up row totals f32
+//   4 swiglu_q8k, gather_acts               clamp, SwiGLU, router weight, Q8_K of mid in one pass; tiles of it
 //   5 grouped_gemm<Q2K>                     down, min-term as a second K=16 MMA -> per-pair rows
 //   6 moe_sum                               slots summed in slot order
 #include <cuda_fp16.h>
@@ -264,7 +264,8 @@ struct PfGemmArgs {
     uint32_t r_cap;
     const uint32_t *sorted, *tile_expert, *tile_start, *tile_rows, *tile_boff, *plan;
     const float *weights;    // IQ2: router weight per pair
-    float *out;              // IQ2: mid [pair][out_dim]; Q2K: per-pair down rows [pair][out_dim]
+    float *out;              // IQ2: gate row totals [pair][out_dim]; Q2K: per-pair down rows [pair][out_dim]
+    float *out_u;            // IQ2: up row totals [pair][out_dim]
     float *const *row_ptr;   // Q2K, optional: row_ptr[pair] is where that pair's down row goes instead (it may point into
                              // another GPU's memory: the expert-parallel combine fused into this kernel's epilogue)
     uint32_t out_dim, kblocks;
@@ -505,11 +506,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
             const uint8_t *srow = pf_tile_row<KIND>(a, ebase, mt, arow, row_bytes);  // the row whose scales apply here
 
             // per-item tables: activation scales, this tile's weight scales (raw bits: IQ2 d as f16, Q2K d | dmin << 16),
-            // pair ids, router weights. They are rewritten once every warp is done with the previous item's.
+            // pair ids. They are rewritten once every warp is done with the previous item's.
             float *sS = reinterpret_cast<float *>(smem + PF_SMEM_S);
             uint32_t *sD = reinterpret_cast<uint32_t *>(smem + PF_SMEM_D);
             uint32_t *sP = reinterpret_cast<uint32_t *>(smem + PF_SMEM_P);
-            float *sW = reinterpret_cast<float *>(smem + PF_SMEM_W);
             ok = named_barrier_and(1, 32 * PF_DRAIN_WARPS, ok);
             if (!ok) break;  // the same decision in all consumer warps
             if ((uint32_t)(tid & (PF_TN - 1)) < rows16)
@@ -524,7 +524,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
             if ((uint32_t)tid < rows) {
                 const uint32_t pair = a.sorted[start + tid];
                 sP[tid] = pair;
-                if (KIND == PF_IQ2) sW[tid] = a.weights[pair];
+
             }
             named_barrier_sync(1, 32 * PF_DRAIN_WARPS);
 
@@ -703,41 +703,22 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
 
             // the item's result
             if (KIND == PF_IQ2) {
-                // lanes 2r / 2r+1 hold gate / up of output row r; the even lane finishes columns 0-31 of this warp's
-                // column half, the odd lane columns 32-63, each receiving the other input from its neighbour
-                const bool odd = (lane & 1) != 0;
-                const uint32_t orow = mt * 64 + (arow >> 1);
-                // eight columns at a time; pair ids and router weights are fetched first and everything but the store
-                // is unconditional, so that the eight dependency chains interleave
-                const uint32_t ecol0 = acol0 + (odd ? PF_COLS / 2 : 0);
+                // Lanes 2r / 2r+1 hold gate / up of output row r. The row totals go out as they are, gate rows to
+                // a.out and up rows to a.out_u: clamp, SwiGLU, router weight and the Q8_K quantisation of the result
+                // run in the kernel that follows (swiglu_q8k_kernel), at full occupancy instead of on these eight warps.
+                float *dst = ((lane & 1) ? a.out_u : a.out) + mt * 64 + (arow >> 1);
 #pragma unroll
-                for (int i0 = 0; i0 < PF_COLS / 2; i0 += 8) {
-                    if (acol0 + i0 >= rows) break;  // warp-uniform: the odd lanes' columns lie 32 further on
+                for (int i0 = 0; i0 < PF_COLS; i0 += 8) {
+                    if (acol0 + i0 >= rows) break;
                     uint32_t pr[8];
-                    float wr[8], r[8];
 #pragma unroll
                     for (int q = 0; q < 2; ++q) {
-                        const uint4 t = *reinterpret_cast<const uint4 *>(sP + ecol0 + i0 + 4 * q);
-                        const float4 w4 = *reinterpret_cast<const float4 *>(sW + ecol0 + i0 + 4 * q);
+                        const uint4 t = *reinterpret_cast<const uint4 *>(sP + acol0 + i0 + 4 * q);
                         pr[4 * q] = t.x, pr[4 * q + 1] = t.y, pr[4 * q + 2] = t.z, pr[4 * q + 3] = t.w;
-                        wr[4 * q] = w4.x, wr[4 * q + 1] = w4.y, wr[4 * q + 2] = w4.z, wr[4 * q + 3] = w4.w;
-                    }
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        const int i = i0 + k;
-                        const float send = odd ? acc[i] : acc[PF_COLS / 2 + i];
-                        const float recv = __shfl_xor_sync(FULL, send, 1);
-                        float g = odd ? recv : acc[i], u = odd ? acc[PF_COLS / 2 + i] : recv;
-                        if (a.clamp > 1.0e-6f) {
-                            if (g > a.clamp) g = a.clamp;
-                            if (u > a.clamp) u = a.clamp;
-                            if (u < -a.clamp) u = -a.clamp;
-                        }
-                        r[k] = swiglu_weighted(g, u, wr[k]);
                     }
 #pragma unroll
                     for (int k = 0; k < 8; ++k)
-                        if (ecol0 + i0 + k < rows) a.out[(size_t)pr[k] * a.out_dim + orow] = r[k];
+                        if (acol0 + i0 + k < rows) dst[(size_t)pr[k] * a.out_dim] = acc[i0 + k];
                 }
             } else {
                 float *orow = a.out + mt * 128 + arow;
@@ -978,6 +959,7 @@ size_t prefill_scratch_bytes(uint32_t max_tokens, uint32_t k, uint32_t n_expert,
     L.sm = take(r_cap * (size_t)(n_ff / QK_K) * 4);
     L.bs = take(r_cap * (size_t)(n_ff / QK_K) * 16 * 2);
     L.down_pair = take(P * (size_t)n_embd * 4);
+    L.up_rows = take(P * (size_t)n_ff * 4);
     if (lay) *lay = L;
     return off;
 }
@@ -1041,12 +1023,13 @@ int launch_prefill_experts(cudaStream_t st, const PrefillArgs &p)
     g.B = w + L.bx, g.S = reinterpret_cast<const float *>(w + L.sx), g.BS = nullptr, g.r_cap = L.r_cap;
     g.sorted = u32p(L.sorted), g.tile_expert = u32p(L.tile_expert), g.tile_start = u32p(L.tile_start);
     g.tile_rows = u32p(L.tile_rows), g.tile_boff = u32p(L.tile_boff), g.plan = u32p(L.plan);
-    g.weights = p.weights, g.out = p.mid, g.out_dim = p.n_ff, g.kblocks = xb, g.clamp = p.clamp, g.ieee = p.ieee;
+    g.weights = p.weights, g.out = p.mid, g.out_u = reinterpret_cast<float *>(w + L.up_rows), g.out_dim = p.n_ff, g.kblocks = xb;
+    g.clamp = p.clamp, g.ieee = p.ieee;
     g.layout = p.layout, g.status = p.status;
     pf_grouped_gemm_kernel<PF_IQ2><<<sms, PF_THREADS, PF_SMEM_TOTAL, st>>>(g);
     mark(2);
-    // 4. Q8_K of mid, tiles of it (with bsums)
-    launch_q8k_quantize(st, p.mid, p.midq, p.n_ff, P);
+    // 4. clamp, SwiGLU, router weight and Q8_K of the result in one pass over the gate / up rows; tiles of it (with bsums)
+    launch_swiglu_q8k(st, p.mid, reinterpret_cast<const float *>(w + L.up_rows), p.weights, p.midq, p.n_ff, P, p.clamp);
     pf_gather_kernel<<<ggrid, 256, 0, st>>>(p.midq, mb, 1, u32p(L.sorted), u32p(L.tile_start), u32p(L.tile_rows),
                                             u32p(L.tile_boff), u32p(L.plan), w + L.bm,
                                             reinterpret_cast<float *>(w + L.sm), reinterpret_cast<__half *>(w + L.bs),

@@ -13,11 +13,9 @@ namespace dsmoe {
 // maxima the element with the smallest bit-reversed index wins; using (|x|, bit-reversed index) as the reduction key
 // reproduces that choice (and hence the sign of d) in any reduction order.
 // ---------------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ void q8k_quantize_block(const float *__restrict__ xb, uint8_t *__restrict__ yb, int lane)
+// v: the lane's eight elements 8 lane .. 8 lane + 7 of the block
+__device__ __forceinline__ void q8k_quantize_vals(const float (&v)[8], uint8_t *__restrict__ yb, int lane)
 {
-    const float4 *src = reinterpret_cast<const float4 *>(xb + 8 * lane);
-    float4 v0 = src[0], v1 = src[1];
-    float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
 
     float best_abs = -1.0f, best_val = 0.0f;
     uint32_t best_rev = 0xFFFFFFFFu;
@@ -69,6 +67,52 @@ __device__ __forceinline__ void q8k_quantize_block(const float *__restrict__ xb,
               ((uint32_t)(q[7] & 255) << 24);
     s += __shfl_xor_sync(FULL, s, 1);  // bsums cover 16 elements = two lanes
     if ((lane & 1) == 0) reinterpret_cast<int16_t *>(yb + 260)[lane >> 1] = (int16_t)s;
+}
+
+__device__ __forceinline__ void q8k_quantize_block(const float *__restrict__ xb, uint8_t *__restrict__ yb, int lane)
+{
+    const float4 *src = reinterpret_cast<const float4 *>(xb + 8 * lane);
+    const float4 v0 = src[0], v1 = src[1];
+    const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    q8k_quantize_vals(v, yb, lane);
+}
+
+// The batched path's step between its two grouped GEMMs: the gate and up row totals become mid = silu(gate) * up * w with
+// the reference's clamps and operation order (engine/src/kernels/moe.rs:692-710), and mid is quantised to Q8_K in the
+// same warp without ever being stored as f32. One warp per 256-element block.
+__global__ void __launch_bounds__(256) swiglu_q8k_kernel(const float *__restrict__ gate, const float *__restrict__ up,
+                                                          const float *__restrict__ weight, uint8_t *__restrict__ out,
+                                                          uint32_t blocks_per_row, uint64_t n_blocks_total, float clamp)
+{
+    const int lane = threadIdx.x & 31;
+    const uint64_t blk = (uint64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (blk >= n_blocks_total) return;
+    const uint64_t row = blk / blocks_per_row;
+    const float w = weight[row];
+    const float4 *gs = reinterpret_cast<const float4 *>(gate + blk * QK_K + 8 * lane);
+    const float4 *us = reinterpret_cast<const float4 *>(up + blk * QK_K + 8 * lane);
+    const float4 g0 = gs[0], g1 = gs[1], u0 = us[0], u1 = us[1];
+    const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float gg = g[i], uu = u[i];
+        if (clamp > 1.0e-6f) {
+            if (gg > clamp) gg = clamp;
+            if (uu > clamp) uu = clamp;
+            if (uu < -clamp) uu = -clamp;
+        }
+        v[i] = swiglu_weighted(gg, uu, w);
+    }
+    q8k_quantize_vals(v, out + blk * Q8K_BYTES, lane);
+}
+
+void launch_swiglu_q8k(cudaStream_t st, const float *gate, const float *up, const float *weight, uint8_t *out,
+                       uint32_t in_dim, uint32_t n_rows, float clamp)
+{
+    const uint64_t nb = (uint64_t)(in_dim / QK_K) * n_rows;
+    if (nb == 0) return;
+    swiglu_q8k_kernel<<<(unsigned)((nb + 7) / 8), 256, 0, st>>>(gate, up, weight, out, in_dim / QK_K, nb, clamp);
 }
 
 __global__ void __launch_bounds__(256) q8k_quantize_kernel(const float *__restrict__ x, uint8_t *__restrict__ out,
