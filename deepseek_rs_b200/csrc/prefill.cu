@@ -167,7 +167,8 @@ __global__ void __launch_bounds__(256) pf_gather_kernel(const uint8_t *__restric
                                                          const uint32_t *__restrict__ tile_rows,
                                                          const uint32_t *__restrict__ tile_boff,
                                                          const uint32_t *__restrict__ plan, uint8_t *__restrict__ B,
-                                                         float *__restrict__ S, __half *__restrict__ BS, uint32_t r_cap)
+                                                         float *__restrict__ S, __half *__restrict__ BS, uint32_t r_cap,
+                                                         uint32_t perm)
 {
     const uint32_t n_tiles = plan[0];
     // one warp per (tile, group of 8 padded rows, Q8_K block): lane = (row of the group r8, quarter q); in round j the
@@ -200,9 +201,13 @@ __global__ void __launch_bounds__(256) pf_gather_kernel(const uint8_t *__restric
                     __half2 v = __hsub2(*reinterpret_cast<__half2 *>(&h[i]), off);
                     op[i] = *reinterpret_cast<uint32_t *>(&v);
                 }
-                // element k = 256 kb + 8 c: stage 2 kb + c / 16, core column c % 16
-                const size_t off_b = tile_base + (size_t)(2 * kb + (c >> 4)) * rows16 * 256 + (size_t)g8 * PF_SBO + (c & 15) * 128 +
-                                     r8 * 16;
+                // element k = 256 kb + 8 c. Plain order: stage 2 kb + c / 16, core column c % 16. Interleaved order
+                // (perm, for the IQ2_XXS GEMM): the superblock's eight 32-element groups g = c / 4 alternate between its
+                // two stages, group g in stage g % 2 at position g / 2, so that the two groups a decoding thread needs in
+                // one superblock (2 j and 2 j + 1) are 16 adjacent bytes of the packed row. The order inside a superblock
+                // does not matter to the contraction: its products are exact integers.
+                const uint32_t st_half = perm ? ((c >> 2) & 1u) : (c >> 4), col = perm ? (4u * (c >> 3) + (c & 3u)) : (c & 15u);
+                const size_t off_b = tile_base + (size_t)(2 * kb + st_half) * rows16 * 256 + (size_t)g8 * PF_SBO + col * 128 + r8 * 16;
                 *reinterpret_cast<uint4 *>(B + off_b) = o;
             }
             if (q == 0) S[(size_t)kb * r_cap + boff + r] = valid ? *reinterpret_cast<const float *>(blk) : 0.0f;
@@ -318,9 +323,9 @@ __device__ __forceinline__ uint32_t pf_hmul2(uint32_t a, uint32_t b)
 template <int KIND>
 __device__ __forceinline__ uint2 pf_load_packed(const uint8_t *row, int layout, uint32_t kb, uint32_t half, uint32_t c)
 {
-    if (KIND == PF_IQ2) {
-        if (layout == DSMOE_LAYOUT_ROWSOA) return *reinterpret_cast<const uint2 *>(row + 32 + 64 * kb + 8 * (4 * half + c));
-        const uint16_t *p = reinterpret_cast<const uint16_t *>(row + IQ2XXS_BYTES * kb + 2 + 8 * (4 * half + c));
+    if (KIND == PF_IQ2) {  // stage `half` of a superblock holds groups half, 2 + half, 4 + half, 6 + half (see pf_gather_kernel)
+        if (layout == DSMOE_LAYOUT_ROWSOA) return *reinterpret_cast<const uint2 *>(row + 32 + 64 * kb + 8 * (2 * c + half));
+        const uint16_t *p = reinterpret_cast<const uint16_t *>(row + IQ2XXS_BYTES * kb + 2 + 8 * (2 * c + half));
         return make_uint2((uint32_t)p[0] | ((uint32_t)p[1] << 16), (uint32_t)p[2] | ((uint32_t)p[3] << 16));
     }
     if (layout == DSMOE_LAYOUT_ROWSOA) return *reinterpret_cast<const uint2 *>(row + 128 + 64 * kb + 32 * half + 8 * c);
@@ -822,8 +827,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
                 const uint8_t *nrow = j + 1 < a.kblocks ? drow : drow_next;
                 if (nrow != nullptr) {
                     const uint32_t kbn = pf_visit_block<KIND>(a.kblocks, j + 1 < a.kblocks ? j + 1 : 0);
-                    n0 = pf_load_packed<KIND>(nrow, a.layout, kbn, 0, dc);
-                    n1 = pf_load_packed<KIND>(nrow, a.layout, kbn, 1, dc);
+                    if (KIND == PF_IQ2 && a.layout == DSMOE_LAYOUT_ROWSOA) {  // both stages' groups in one 16-byte load
+                        const uint4 t = *reinterpret_cast<const uint4 *>(nrow + 32 + 64 * kbn + 16 * dc);
+                        n0 = make_uint2(t.x, t.y), n1 = make_uint2(t.z, t.w);
+                    } else {
+                        n0 = pf_load_packed<KIND>(nrow, a.layout, kbn, 0, dc);
+                        n1 = pf_load_packed<KIND>(nrow, a.layout, kbn, 1, dc);
+                    }
                     if (KIND == PF_Q2K) sc_nxt = pf_load_q2k_scales16(nrow, a.layout, kbn);
                 }
                 return stage(2 * j, c0, sc_cur) && stage(2 * j + 1, c1, sc_cur);
@@ -1015,7 +1025,7 @@ int launch_prefill_experts(cudaStream_t st, const PrefillArgs &p)
     const dim3 ggrid(32, (unsigned)(L.tile_cap < 1024u ? L.tile_cap : 1024u));
     pf_gather_kernel<<<ggrid, 256, 0, st>>>(p.xq, xb, p.k, u32p(L.sorted), u32p(L.tile_start), u32p(L.tile_rows),
                                             u32p(L.tile_boff), u32p(L.plan), w + L.bx,
-                                            reinterpret_cast<float *>(w + L.sx), nullptr, L.r_cap);
+                                            reinterpret_cast<float *>(w + L.sx), nullptr, L.r_cap, 1u);
     mark(1);
     // 3. gate / up / SwiGLU
     PfGemmArgs g = {};
@@ -1033,7 +1043,7 @@ int launch_prefill_experts(cudaStream_t st, const PrefillArgs &p)
     pf_gather_kernel<<<ggrid, 256, 0, st>>>(p.midq, mb, 1, u32p(L.sorted), u32p(L.tile_start), u32p(L.tile_rows),
                                             u32p(L.tile_boff), u32p(L.plan), w + L.bm,
                                             reinterpret_cast<float *>(w + L.sm), reinterpret_cast<__half *>(w + L.bs),
-                                            L.r_cap);
+                                            L.r_cap, 0u);
     mark(3);
     // 5. down
     PfGemmArgs d = g;
