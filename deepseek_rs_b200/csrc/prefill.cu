@@ -284,7 +284,7 @@ constexpr int PF_SMEM_A = 0;                                          // Q2K: 2 
 constexpr uint32_t PF_TMEM_X = 256, PF_TMEM_A = 384;                    // IQ2: TMEM columns of spill set X and of the weight ring
 constexpr uint32_t PF_TMEM_A_STAGE = PF_KS / 2;                          // 64 columns: 128 f16 per row
 constexpr int PF_SMEM_B = PF_A_STAGES * PF_STAGE_A;                   // 3 x 32 KB activations
-constexpr int PF_SMEM_LUT = PF_SMEM_B + PF_B_STAGES * PF_STAGE_A;     // IQ2: codebook magnitudes as bytes (32 KB: 16 copies of 256 entries)
+constexpr int PF_SMEM_LUT = PF_SMEM_B + PF_B_STAGES * PF_STAGE_A;     // IQ2: codebook magnitudes as f16 (32 KB: 8 copies of 256 entries)
 constexpr int PF_SMEM_A2 = PF_SMEM_LUT;                               // Q2K (no tables): 2 x 4 KB sc_hi tile, one per TMEM buffer
 constexpr int PF_SMEM_B2 = PF_SMEM_A2 + 8192;                         // Q2K: 2 x 4 KB bsums tile
 constexpr int PF_SMEM_S = PF_SMEM_LUT + 49152;                        // per-item tables: 16 x 128 f32 activation scales,
@@ -350,31 +350,26 @@ __device__ __forceinline__ uint4 pf_load_q2k_scales16(const uint8_t *row, int la
 }
 
 // IQ2_XXS for the tensor-memory ring: decode one 32-weight group into 16 words (f16 pairs in K order).
-// Magnitudes: one 8-byte codebook lookup per 8 weights (the table holds 16 copies of every entry, entry stride 128
-// bytes, copy = lane & 15, so the 16 lanes of a 64-bit shared-memory wavefront never share a bank). A byte b becomes the
-// f16 1024 + b by placing it under the exponent byte 0x64; one fused multiply-add (1024 + b) * ls - 1024 * ls then gives
-// ls * b exactly (at most 1333, an integer below 2048, rounded once). Signs are computed: the sign byte of a 7-bit index
-// is the index with its parity as bit 7 (engine/src/kernels/quantize.rs:693-708), and one multiplication by
-// 2^(15-2i) + 2^(30-2i) moves bits 2i and 2i+1 of that byte to the f16 sign positions 15 and 31 of word i, where a
-// single logic operation flips the two magnitudes.
-__device__ __forceinline__ void pf_decode_iq2_regs(uint2 pk, uint32_t (&w)[16], const uint2 *lut_grid, uint32_t lane15)
+// Magnitudes: one 16-byte lookup per 8 weights in a table of f16 magnitudes (8 copies of every entry, entry stride 128
+// bytes, copy = lane & 7, so the eight lanes of a 128-bit shared-memory wavefront never share a bank group), scaled by
+// ls with one packed multiply per two weights. Signs are computed: the sign byte of a 7-bit index is the index with
+// its parity as bit 7 (engine/src/kernels/quantize.rs:693-708), and one multiplication by 2^(15-2i) + 2^(30-2i) moves
+// bits 2i and 2i+1 of that byte to the f16 sign positions 15 and 31 of word i, where one logic operation flips the two
+// magnitudes. (A byte-wide table with a PRMT + fused multiply-add conversion reads a quarter of the shared-memory
+// wavefronts but costs four more instructions per 8 weights; the kernel is bound by instruction issue, so this form wins.)
+__device__ __forceinline__ void pf_decode_iq2_regs(uint2 pk, uint32_t (&w)[16], const uint4 *lut_grid, uint32_t lane7)
 {
     const uint32_t aux0 = pk.x, aux1 = pk.y;
-    const float lsf = (float)(2u * (aux1 >> 28) + 1u);
-    const __half2 ls = __float2half2_rn(lsf), nc = __float2half2_rn(-1024.0f * lsf);
+    const __half2 ls = __float2half2_rn((float)(2u * (aux1 >> 28) + 1u));
+    const uint32_t ls2 = *reinterpret_cast<const uint32_t *>(&ls);
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-        const uint2 g = lut_grid[((aux0 >> (8 * u)) & 255u) * 16 + lane15];
+        const uint4 g = lut_grid[((aux0 >> (8 * u)) & 255u) * 8 + lane7];
         const uint32_t idx = (aux1 >> (7 * u)) & 127u, sb = idx | ((__popc(idx) & 1u) << 7);
-        uint32_t h[4] = {__byte_perm(g.x, 0x64646464u, 0x4140u), __byte_perm(g.x, 0x64646464u, 0x4342u),
-                         __byte_perm(g.y, 0x64646464u, 0x4140u), __byte_perm(g.y, 0x64646464u, 0x4342u)};
-        const uint32_t sm[4] = {(sb * 0x40008000u) & 0x80008000u, (sb * 0x10002000u) & 0x80008000u,
-                                (sb * 0x04000800u) & 0x80008000u, (sb * 0x01000200u) & 0x80008000u};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const __half2 v = __hfma2(*reinterpret_cast<__half2 *>(&h[i]), ls, nc);
-            w[4 * u + i] = *reinterpret_cast<const uint32_t *>(&v) ^ sm[i];
-        }
+        w[4 * u + 0] = pf_hmul2(g.x, ls2) ^ ((sb * 0x40008000u) & 0x80008000u);
+        w[4 * u + 1] = pf_hmul2(g.y, ls2) ^ ((sb * 0x10002000u) & 0x80008000u);
+        w[4 * u + 2] = pf_hmul2(g.z, ls2) ^ ((sb * 0x04000800u) & 0x80008000u);
+        w[4 * u + 3] = pf_hmul2(g.w, ls2) ^ ((sb * 0x01000200u) & 0x80008000u);
     }
 }
 
@@ -456,7 +451,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
     uint64_t *bar_acc_full = bar_a_full + 10;                                  // [2] superblock contracted
     uint64_t *bar_acc_free = bar_a_full + 12;                                  // [2] accumulator drained (8 warps)
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_a_full + 14);
-    uint2 *lut_grid = reinterpret_cast<uint2 *>(smem + PF_SMEM_LUT);
+    uint4 *lut_grid = reinterpret_cast<uint4 *>(smem + PF_SMEM_LUT);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     constexpr uint32_t TMEM_COLS = 512u;
@@ -464,9 +459,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
     const bool ieee = a.ieee != 0;
 
     if (KIND == PF_IQ2) {
-        for (int i = tid; i < 256 * 16; i += PF_THREADS) {
-            const uint64_t g = c_iq2xxs_grid[i >> 4];
-            lut_grid[i] = make_uint2((uint32_t)g, (uint32_t)(g >> 32));
+        for (int i = tid; i < 256 * 8; i += PF_THREADS) {
+            const uint64_t g = c_iq2xxs_grid[i >> 3];
+            lut_grid[i] = pf_bytes_to_f16x8((uint32_t)g, (uint32_t)(g >> 32));
         }
     }
     if (warp == 0) tc05_alloc(tmem_slot, TMEM_COLS);
@@ -799,7 +794,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_grouped_gemm_kernel(PfGemmAr
                 if (KIND == PF_IQ2) {
                     // group dc of the stage -> K elements 32 dc .. 32 dc + 31 -> 16 columns of this row's TMEM lane
                     uint32_t wreg[16];
-                    pf_decode_iq2_regs(cur, wreg, lut_grid, lane & 15u);
+                    pf_decode_iq2_regs(cur, wreg, lut_grid, dr8);
                     tc05_st16_u32(tmem + ((32u * (warp & 3u)) << 16) + PF_TMEM_A + b * PF_TMEM_A_STAGE + 16u * dc, wreg);
                     tc05_wait_st();
                     tc05_fence_before_sync();
