@@ -484,7 +484,8 @@ static int shared_expert_impl(dsmoe_handle *h, cudaStream_t st, const uint8_t *g
     const dsmoe_config &c = h->cfg;
     int n = 0;
     if (shared_fused_eligible(c.n_embd, c.n_ff, n_tokens) && n_tokens <= h->sh_chunk) {
-        n = launch_shared_fused(st, gate_w, up_w, down_w, x, h->sh_mid, out, c.n_embd, c.n_ff, n_tokens, c.swiglu_clamp);
+        n = launch_shared_fused(st, gate_w, up_w, down_w, x, h->sh_mid, out, c.n_embd, c.n_ff, n_tokens, c.swiglu_clamp,
+                                h->d_status);
         return check_launch(h, "shared_expert", n);
     }
     for (uint32_t t0 = 0; t0 < n_tokens; t0 += h->sh_chunk) {

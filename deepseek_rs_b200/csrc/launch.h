@@ -110,7 +110,8 @@ void launch_swiglu(cudaStream_t st, const float *gate, const float *up, float *o
 // The shared expert in two launches for up to 4 tokens (mid: f32 [n_tokens][n_ff] scratch). Returns the launch count.
 bool shared_fused_eligible(uint32_t n_embd, uint32_t n_ff, uint32_t n_tokens);
 int launch_shared_fused(cudaStream_t st, const uint8_t *gate_w, const uint8_t *up_w, const uint8_t *down_w, const float *x,
-                        float *mid, float *out, uint32_t n_embd, uint32_t n_ff, uint32_t n_tokens, float clamp);
+                        float *mid, float *out, uint32_t n_embd, uint32_t n_ff, uint32_t n_tokens, float clamp,
+                        int *status);
 void launch_matmul_f16(cudaStream_t st, const uint16_t *w, const float *x, float *out, uint64_t in_dim, uint64_t out_dim,
                        uint64_t n_tok);
 

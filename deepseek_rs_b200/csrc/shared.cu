@@ -196,6 +196,51 @@ __global__ void __launch_bounds__(64) matmul_f16_kernel(const uint16_t *__restri
     if (lane == 0) out[tok * out_dim + row] = __fadd_rn(p[0], p[1]);  // stride 1
 }
 
+// The common shape (rows of at most 4096 values, a multiple of 256, 16-byte aligned): every weight load of the row is
+// requested at once, and the CTA's four rows share one copy of the token's activations in shared memory. Same
+// partial sums and tree as above.
+constexpr int MF_MAX_IN = 4096;
+
+__global__ void __launch_bounds__(128) matmul_f16_staged_kernel(const uint16_t *__restrict__ w, const float *__restrict__ x,
+                                                                float *__restrict__ out, uint32_t in_dim, uint32_t out_dim)
+{
+    __shared__ __align__(16) float s_x[MF_MAX_IN];
+    const uint32_t lane = threadIdx.x & 31, row = blockIdx.x * 4 + (threadIdx.x >> 5), tok = blockIdx.y;
+    const uint32_t rounds = in_dim / 256;
+    const bool has = row < out_dim;
+    const uint16_t *wr = w + (size_t)(has ? row : 0) * in_dim + 8 * lane;
+    uint4 wv[MF_MAX_IN / 256];
+#pragma unroll
+    for (int u = 0; u < MF_MAX_IN / 256; ++u)
+        if (has && (uint32_t)u < rounds) wv[u] = *reinterpret_cast<const uint4 *>(wr + 256 * u);
+    const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)tok * in_dim);
+    for (uint32_t i = threadIdx.x; i < in_dim / 4; i += 128) reinterpret_cast<float4 *>(s_x)[i] = xr[i];
+    __syncthreads();
+    if (!has) return;
+    float p[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) p[k] = 0.0f;
+#pragma unroll
+    for (int u = 0; u < MF_MAX_IN / 256; ++u) {
+        if ((uint32_t)u >= rounds) break;
+        const float4 xa = *reinterpret_cast<const float4 *>(s_x + 256 * u + 8 * lane);
+        const float4 xb = *reinterpret_cast<const float4 *>(s_x + 256 * u + 8 * lane + 4);
+        const uint32_t ww[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
+        const float xs[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            p[k] = __fadd_rn(p[k], __fmul_rn(f16_bits_to_f32((ww[k >> 1] >> (16 * (k & 1))) & 0xFFFFu, false), xs[k]));
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) p[k] = __fadd_rn(p[k], __shfl_down_sync(FULL, p[k], m));
+#pragma unroll
+    for (int k = 0; k < 4; ++k) p[k] = __fadd_rn(p[k], p[k + 4]);
+    p[0] = __fadd_rn(p[0], p[2]), p[1] = __fadd_rn(p[1], p[3]);
+    if (lane == 0) out[(size_t)tok * out_dim + row] = __fadd_rn(p[0], p[1]);
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // Small batches: the shared expert in two launches instead of six. Every CTA quantises the token's activation row to
 // Q8_0 itself, into shared memory (the same arithmetic as quantize_q8_0_kernel, so the same codes), and then its eight
@@ -315,14 +360,201 @@ __global__ void __launch_bounds__(256) shared_fused_kernel(const uint8_t *__rest
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The same two launches with the weight rows staged through shared memory by bulk asynchronous copies: a warp's two
+// rows (gate row r and up row r; or two adjacent down rows) arrive as whole 16-byte-aligned rows while the CTA
+// quantises the activations, instead of as 4-byte loads at a 34-byte lane stride. All TOK tokens of the call share
+// one pass over the weights. The second launch requests its rows before it waits for the first launch to finish
+// (the weights are never written by these kernels). Needs 16-byte aligned tensors and in_dim a multiple of 256.
+// Lane partials over ascending blocks and the xor butterfly are those of the kernels above: same bits.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int SHS_MAX_TOK = 8;
+
+template <bool FIRST, int TOK>
+__global__ void __launch_bounds__(256) shared_staged_kernel(const uint8_t *__restrict__ w0, const uint8_t *__restrict__ w1,
+                                                             const float *__restrict__ x, float *__restrict__ out,
+                                                             uint32_t in_dim, uint32_t out_dim, uint32_t n_tok, float clamp,
+                                                             int *status)
+{
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, blocks = in_dim / 32;
+    const uint32_t row_bytes = blocks * Q8_0_BYTES;
+    uint8_t *wst = smem + (size_t)warp * 2 * row_bytes;
+    int8_t *s_xq = reinterpret_cast<int8_t *>(smem + (size_t)16 * row_bytes);
+    float *s_xs = reinterpret_cast<float *>(s_xq + (size_t)TOK * in_dim);
+    uint64_t *bar = reinterpret_cast<uint64_t *>(s_xs + (size_t)TOK * blocks) + warp;
+    // FIRST: rows r of both tensors; otherwise rows r, r + 1 of the one tensor (adjacent in memory: one copy)
+    const uint32_t row = FIRST ? blockIdx.x * 8 + warp : blockIdx.x * 16 + 2 * warp;
+    const uint32_t n_rows = row >= out_dim ? 0u : (FIRST ? 2u : (out_dim - row < 2u ? out_dim - row : 2u));
+    if (lane == 0) {
+        mbar_init(bar, 1);
+        fence_async_smem();
+    }
+    auto request_rows = [&]() {
+        if (lane != 0 || n_rows == 0) return;
+        mbar_expect_tx(bar, n_rows * row_bytes);
+        if (FIRST) {
+            bulk_g2s(wst, w0 + (size_t)row * row_bytes, row_bytes, bar);
+            bulk_g2s(wst + row_bytes, w1 + (size_t)row * row_bytes, row_bytes, bar);
+        } else {
+            bulk_g2s(wst, w0 + (size_t)row * row_bytes, n_rows * row_bytes, bar);
+        }
+    };
+    if (!FIRST) request_rows();
+    pdl_launch_dependents();
+    pdl_wait();
+    if (FIRST) request_rows();
+    // quantize_q8_0 of every token's row: a thread takes 16 adjacent values, two neighbouring lanes share a block
+    // (its largest magnitude is the larger of the two halves'; the maximum does not depend on the order)
+    {
+        const uint32_t halves = in_dim / 16, total = n_tok * halves;
+        for (uint32_t base = 0; base < total; base += 256) {
+            const uint32_t u = base + threadIdx.x;
+            const bool active = u < total;
+            const uint32_t t = active ? u / halves : 0, h = active ? u - t * halves : 0;
+            const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)t * in_dim + h * 16);
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float4 f = active ? src[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                v[4 * i] = f.x, v[4 * i + 1] = f.y, v[4 * i + 2] = f.z, v[4 * i + 3] = f.w;
+            }
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float m = v[i] < 0.0f ? -v[i] : v[i];
+                amax = m > amax ? m : amax;
+            }
+            const float o = __shfl_xor_sync(FULL, amax, 1);
+            amax = o > amax ? o : amax;
+            const float d = __fdiv_rn(amax, 127.0f), id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+            uint32_t pk[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                pk[i] = 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float raw = __fmul_rn(v[4 * i + j], id);
+                    int q = raw >= 0.0f ? (int)__fadd_rn(raw, 0.5f) : (int)__fsub_rn(raw, 0.5f);
+                    q = q > 127 ? 127 : (q < -128 ? -128 : q);
+                    pk[i] |= ((uint32_t)q & 0xFFu) << (8 * j);
+                }
+            }
+            if (active) {
+                *reinterpret_cast<uint4 *>(s_xq + (size_t)t * in_dim + h * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                if (!(h & 1)) s_xs[t * blocks + (h >> 1)] = d;
+            }
+        }
+    }
+    __syncthreads();
+    if (n_rows == 0) return;
+    if (!mbar_wait_bounded(bar, 0, status)) return;
+    float acc[2][TOK];
+#pragma unroll
+    for (int t = 0; t < TOK; ++t) acc[0][t] = acc[1][t] = 0.0f;
+    for (uint32_t b = lane; b < blocks; b += 32) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            if ((uint32_t)r >= n_rows) break;
+            // A block starts on a 2-byte boundary: nine aligned words from its first 4-byte boundary at or after the
+            // scale's, shifted by 16 bits when the block itself is aligned (its int8 data then starts mid-word). No
+            // branch on the block's parity, which alternates across the lanes. The ninth word of a block that is not
+            // aligned belongs to whatever follows it in shared memory and is shifted out.
+            const uint8_t *blk = wst + (size_t)r * row_bytes + (size_t)b * Q8_0_BYTES;
+            const uint32_t odd = (uint32_t)(b & 1);  // rows start 16-byte aligned and a block has 34 bytes
+            const uint32_t *aw = reinterpret_cast<const uint32_t *>(blk + 2 * odd);
+            const uint32_t shift = odd ? 0u : 16u;
+            uint32_t raw[9], wq[8];
+#pragma unroll
+            for (int i = 0; i < 9; ++i) raw[i] = aw[i];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) wq[i] = __funnelshift_r(raw[i], raw[i + 1], shift);
+            const float sw = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(blk), false);
+#pragma unroll
+            for (int t = 0; t < TOK; ++t) {
+                if ((uint32_t)t >= n_tok) break;
+                const int dot = q8_0_dot32(wq, s_xq + (size_t)t * in_dim + b * 32);
+                acc[r][t] = __fadd_rn(acc[r][t], __fmul_rn(__fmul_rn(sw, s_xs[t * blocks + b]), (float)dot));
+            }
+        }
+    }
+    // after the xor butterfly every lane holds the sums; lane t keeps token t's pair and finishes it
+    float g = 0.0f, u = 0.0f;
+#pragma unroll
+    for (int t = 0; t < TOK; ++t) {
+        if ((uint32_t)t >= n_tok) break;
+        float a0 = acc[0][t], a1 = acc[1][t];
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) {
+            a0 = __fadd_rn(a0, __shfl_xor_sync(FULL, a0, m));
+            a1 = __fadd_rn(a1, __shfl_xor_sync(FULL, a1, m));
+        }
+        if (lane == (uint32_t)t) g = a0, u = a1;
+    }
+    if (lane >= n_tok || lane >= (uint32_t)TOK) return;
+    if (FIRST) {
+        if (clamp > 1.0e-6f) {
+            if (g > clamp) g = clamp;
+            if (u > clamp) u = clamp;
+            if (u < -clamp) u = -clamp;
+        }
+        out[(size_t)lane * out_dim + row] = swiglu_weighted(g, u, 1.0f);
+    } else {
+        out[(size_t)lane * out_dim + row] = g;
+        if (n_rows == 2) out[(size_t)lane * out_dim + row + 1] = u;
+    }
+}
+
+static size_t shared_staged_smem(uint32_t in_dim, int tok)
+{
+    const size_t blocks = in_dim / 32;
+    return 16 * blocks * Q8_0_BYTES + (size_t)tok * in_dim + (size_t)tok * blocks * 4 + 8 * sizeof(uint64_t);
+}
+
+template <int TOK>
+static void launch_shared_staged(cudaStream_t st, const uint8_t *gate_w, const uint8_t *up_w, const uint8_t *down_w,
+                                 const float *x, float *mid, float *out, uint32_t n_embd, uint32_t n_ff, uint32_t n_tokens,
+                                 float clamp, int *status)
+{
+    static OncePerDevice attr;  // one per template instance
+    if (attr.first()) {
+        cudaFuncSetAttribute(shared_staged_kernel<true, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)shared_staged_smem(SHF_MAX_IN, TOK));
+        cudaFuncSetAttribute(shared_staged_kernel<false, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)shared_staged_smem(SHF_MAX_IN, TOK));
+    }
+    launch_pdl(shared_staged_kernel<true, TOK>, dim3((n_ff + 7) / 8), dim3(256), shared_staged_smem(n_embd, TOK), st, gate_w,
+               up_w, x, mid, n_embd, n_ff, n_tokens, clamp, status);
+    launch_pdl(shared_staged_kernel<false, TOK>, dim3((n_embd + 15) / 16), dim3(256), shared_staged_smem(n_ff, TOK), st, down_w,
+               (const uint8_t *)nullptr, (const float *)mid, out, n_ff, n_embd, n_tokens, clamp, status);
+}
+
+// The staged form needs whole rows that bulk copies can take: 16-byte aligned tensors, rows a multiple of 16 bytes.
+static bool shared_staged_eligible(const uint8_t *gate_w, const uint8_t *up_w, const uint8_t *down_w, const float *x,
+                                   const float *mid, uint32_t n_embd, uint32_t n_ff, uint32_t n_tokens)
+{
+    return n_tokens <= (uint32_t)SHS_MAX_TOK && n_embd % 256 == 0 && n_ff % 256 == 0 && n_embd <= (uint32_t)SHF_MAX_IN &&
+           n_ff <= (uint32_t)SHF_MAX_IN &&
+           ((reinterpret_cast<uintptr_t>(gate_w) | reinterpret_cast<uintptr_t>(up_w) | reinterpret_cast<uintptr_t>(down_w) |
+             reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(mid)) & 15) == 0;
+}
+
 bool shared_fused_eligible(uint32_t n_embd, uint32_t n_ff, uint32_t n_tokens)
 {
-    return n_tokens <= 4 && n_embd % 32 == 0 && n_ff % 32 == 0 && n_embd <= (uint32_t)SHF_MAX_IN && n_ff <= (uint32_t)SHF_MAX_IN;
+    return n_tokens <= (uint32_t)SHS_MAX_TOK && n_embd % 32 == 0 && n_ff % 32 == 0 && n_embd <= (uint32_t)SHF_MAX_IN &&
+           n_ff <= (uint32_t)SHF_MAX_IN;
 }
 
 int launch_shared_fused(cudaStream_t st, const uint8_t *gate_w, const uint8_t *up_w, const uint8_t *down_w, const float *x,
-                        float *mid, float *out, uint32_t n_embd, uint32_t n_ff, uint32_t n_tokens, float clamp)
+                        float *mid, float *out, uint32_t n_embd, uint32_t n_ff, uint32_t n_tokens, float clamp, int *status)
 {
+    if (shared_staged_eligible(gate_w, up_w, down_w, x, mid, n_embd, n_ff, n_tokens)) {
+        if (n_tokens == 1) launch_shared_staged<1>(st, gate_w, up_w, down_w, x, mid, out, n_embd, n_ff, n_tokens, clamp, status);
+        else if (n_tokens == 2) launch_shared_staged<2>(st, gate_w, up_w, down_w, x, mid, out, n_embd, n_ff, n_tokens, clamp, status);
+        else if (n_tokens <= 4) launch_shared_staged<4>(st, gate_w, up_w, down_w, x, mid, out, n_embd, n_ff, n_tokens, clamp, status);
+        else launch_shared_staged<8>(st, gate_w, up_w, down_w, x, mid, out, n_embd, n_ff, n_tokens, clamp, status);
+        return 2;
+    }
     launch_pdl(shared_fused_kernel<true>, dim3((n_ff + 7) / 8, n_tokens), dim3(256), 0, st, gate_w, up_w, x, mid, n_embd, n_ff,
                clamp);
     launch_pdl(shared_fused_kernel<false>, dim3((n_embd + 7) / 8, n_tokens), dim3(256), 0, st, down_w,
@@ -358,6 +590,12 @@ void launch_matmul_f16(cudaStream_t st, const uint16_t *w, const float *x, float
                        uint64_t n_tok)
 {
     if (out_dim == 0 || n_tok == 0) return;
+    if (in_dim <= (uint64_t)MF_MAX_IN && in_dim % 256 == 0 && out_dim < (1ull << 31) &&
+        ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x)) & 15) == 0) {
+        matmul_f16_staged_kernel<<<dim3((unsigned)((out_dim + 3) / 4), (unsigned)n_tok), 128, 0, st>>>(w, x, out, (uint32_t)in_dim,
+                                                                                                     (uint32_t)out_dim);
+        return;
+    }
     matmul_f16_kernel<<<dim3((unsigned)((out_dim + 1) / 2), (unsigned)n_tok), 64, 0, st>>>(w, x, out, in_dim, out_dim, n_tok);
 }
 

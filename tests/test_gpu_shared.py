@@ -75,7 +75,7 @@ def test_swiglu_bit_exact(torch_cuda, oracle, K):
         assert np.array_equal(out.cpu().numpy().view(np.uint32), oracle.swiglu(g, u, clamp, weight).view(np.uint32))
 
 
-@pytest.mark.parametrize("T,in_dim,out_dim", [(1, 4096, 256), (7, 4096, 32), (2, 1000, 10)])
+@pytest.mark.parametrize("T,in_dim,out_dim", [(1, 4096, 256), (7, 4096, 32), (2, 1000, 10), (3, 2048, 6), (2, 4352, 9)])
 def test_matmul_f16_router_logits_bit_exact(torch_cuda, oracle, K, T, in_dim, out_dim):
     torch = torch_cuda
     rng = np.random.default_rng(out_dim)
@@ -88,10 +88,12 @@ def test_matmul_f16_router_logits_bit_exact(torch_cuda, oracle, K, T, in_dim, ou
     assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
 
 
-@pytest.mark.parametrize("T", [1, 3, 1300])
-def test_shared_expert_whole(torch_cuda, oracle, K, T):
-    """The one-call shared expert against the oracle's four steps: 1 and 3 tokens take the fused two-launch kernels, 1300
-    tokens the six-launch path across the library's 1024-token chunks."""
+@pytest.mark.parametrize("T,shift", [(1, 0), (2, 0), (3, 0), (5, 0), (8, 0), (1, 4), (3, 4), (9, 0), (1300, 0)])
+def test_shared_expert_whole(torch_cuda, oracle, K, T, shift):
+    """The one-call shared expert against the oracle's four steps. Up to 8 tokens take the two-launch kernels: with
+    16-byte aligned tensors the form that stages whole weight rows in shared memory by bulk copies, with tensors that
+    start 4 bytes off such a boundary (shift) the form that loads words; 9 and 1300 tokens take the six-launch path, the
+    latter across the library's 1024-token chunks."""
     torch = torch_cuda
     rng = np.random.default_rng(T)
     n_embd, n_ff = 4096, 2048
@@ -106,7 +108,14 @@ def test_shared_expert_whole(torch_cuda, oracle, K, T):
     mq, ms = oracle.quantize_q8_0(mid)
     want = oracle.matmul_q8_0(dw, mq, ms, n_ff, n_embd)
     out = torch.empty((T, n_embd), device="cuda")
-    K.shared_expert(dev(torch, gw), dev(torch, uw), dev(torch, dw), dev(torch, x), T, out)
+    def place(w):  # the tensor's bytes at `shift` bytes past a 256-byte aligned allocation
+        buf = torch.empty(w.size + 16, dtype=torch.uint8, device="cuda")
+        view = buf[shift:shift + w.size]
+        view.copy_(torch.from_numpy(w.reshape(-1)))
+        assert view.data_ptr() % 16 == shift
+        return view
+
+    K.shared_expert(place(gw), place(uw), place(dw), dev(torch, x), T, out)
     torch.cuda.synchronize()
     assert K.device_status() == 0
     assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
