@@ -39,6 +39,7 @@ WORKLOADS = {
     "moe_decode_b1": dict(tokens=1, layers=8, zipf=False),
     "moe_decode_b8": dict(tokens=8, layers=4, zipf=False),
     "moe_decode_b64": dict(tokens=64, layers=2, zipf=False),
+    "moe_decode_b16": dict(tokens=16, layers=4, zipf=False),
     # prefill chunk: router logits N(0,1) - 1.1 ln(rank) (Zipf s = 1.1 expert popularity), tcgen05 grouped GEMM
     "moe_prefill_4096": dict(tokens=4096, layers=2, zipf=True),
     # FP8 E4M3 block-scaled dense projection (no counterpart in the reference), all six (M, N) shapes in one line

@@ -33,6 +33,7 @@ struct dsmoe_handle {
     // library-owned scratch for the tier-2 call, sized by cfg.max_tokens
     float *probs, *weights, *mid;
     int32_t *selected;
+    int32_t *pair_order;  // pairs sorted by expert for the decode gate/up kernel at 16 tokens and more
     uint8_t *xq, *midq;
     // staging for the host-buffer call
     cudaStream_t hstream;
@@ -183,6 +184,7 @@ int dsmoe_create(const dsmoe_config *cfg, int device, dsmoe_handle **out)
     ok = ok && dev_alloc(&h->probs, T * cfg->n_expert) == cudaSuccess;
     ok = ok && dev_alloc(&h->weights, T * k) == cudaSuccess;
     ok = ok && dev_alloc(&h->selected, T * k) == cudaSuccess;
+    ok = ok && dev_alloc(&h->pair_order, T * k) == cudaSuccess;
     ok = ok && dev_alloc(&h->xq, T * (cfg->n_embd / QK_K) * Q8K_BYTES) == cudaSuccess;
     ok = ok && dev_alloc(&h->mid, T * k * cfg->n_ff) == cudaSuccess;
     ok = ok && dev_alloc(&h->midq, T * k * (cfg->n_ff / QK_K) * Q8K_BYTES) == cudaSuccess;
@@ -247,6 +249,7 @@ int dsmoe_destroy(dsmoe_handle *h)
     cudaFree(h->probs);
     cudaFree(h->weights);
     cudaFree(h->selected);
+    cudaFree(h->pair_order);
     cudaFree(h->xq);
     cudaFree(h->mid);
     cudaFree(h->midq);
@@ -360,8 +363,15 @@ int dsmoe_gate_up_mid(dsmoe_handle *h, dsmoe_stream stream, const uint8_t *gate_
                     gate_row_bytes, xq_blocks, expert_mid_dim, n_expert_used, n_tokens, clamp, layout,
                     (int)h->cfg.f16_ieee};
     DSMOE_REQUIRE(h, (uint64_t)n_tokens * n_expert_used <= 65535u, "gate_up_mid: n_tokens*k exceeds 65535");
-    int n = (h->use_tma && gate_up_tma_eligible(a)) ? launch_gate_up_mid_tma((cudaStream_t)stream, a, h->d_status)
-                                                    : launch_gate_up_mid((cudaStream_t)stream, a);
+    const bool tma = h->use_tma && gate_up_tma_eligible(a);
+    int n = 0;
+    // the same pair sorting as in the whole-layer call, when the handle's buffer holds this many pairs
+    if (tma && n_tokens >= 16 && (uint64_t)n_tokens * n_expert_used <= (uint64_t)h->cfg.max_tokens * h->cfg.n_expert_used &&
+        launch_pair_order((cudaStream_t)stream, selected, n_tokens * n_expert_used, h->cfg.n_expert, h->pair_order)) {
+        a.order = h->pair_order;
+        n += 1;
+    }
+    n += tma ? launch_gate_up_mid_tma((cudaStream_t)stream, a, h->d_status) : launch_gate_up_mid((cudaStream_t)stream, a);
     return check_launch(h, "gate_up_mid", n);
 }
 
@@ -632,8 +642,13 @@ static int expert_ffn_impl(dsmoe_handle *h, cudaStream_t st, const dsmoe_layer_s
     if ((uint64_t)n_tokens * k > 65535u) return fail(h, DSMOE_ERR_BOUNDS, "%s: n_tokens*k exceeds 65535 on the decode kernels", what);
     GateUpArgs g = {ly.gate, ly.up, xq, sel, wts, nullptr, nullptr, h->mid, (uint64_t)c.n_ff * xb * IQ2XXS_BYTES,
                     (uint64_t)xb * IQ2XXS_BYTES, xb, c.n_ff, k, n_tokens, c.swiglu_clamp, ly.layout, (int)c.f16_ieee};
-    n += ((h->use_tma && gate_up_tma_eligible(g)) ? launch_gate_up_mid_tma(st, g, h->d_status)
-                                                  : launch_gate_up_mid(st, g));
+    const bool gu_tma = h->use_tma && gate_up_tma_eligible(g);
+    // from 16 tokens on, experts repeat among the pairs often enough to pay for sorting them (one small launch)
+    if (gu_tma && n_tokens >= 16 && launch_pair_order(st, sel, n_tokens * k, c.n_expert, h->pair_order)) {
+        g.order = h->pair_order;
+        n += 1;
+    }
+    n += gu_tma ? launch_gate_up_mid_tma(st, g, h->d_status) : launch_gate_up_mid(st, g);
     if (int rc = check_launch(h, what, n)) return rc;
     n = 1;
     launch_q8k_quantize(st, h->mid, h->midq, c.n_ff, n_tokens * k);

@@ -42,7 +42,7 @@ constexpr int GU_STAGE_BYTES = 2 * GU_ROW_BYTES; // gate row + up row of one out
 constexpr int GU_GRID_TABLE_BYTES = DSMOE_IQ2XXS_GRID_ENTRIES * 256;  // 65536
 constexpr int GU_SIGN_TABLE_BYTES = DSMOE_IQ2_SIGN_ENTRIES * 128;     // 16384
 constexpr int GU_TABLE_BYTES = GU_GRID_TABLE_BYTES + GU_SIGN_TABLE_BYTES;
-constexpr int GU_MAX_WARPS = 14;  // register file: 14 warps x 146 registers; 80 KB tables + 14 rings of 2 x 4224 B
+constexpr int GU_MAX_WARPS = 16;  // register file: 16 warps x 128 registers; 80 KB tables + 16 rings of 2 x 4224 B
 
 // Integer dot of one 32-weight group; tables addressed as described above. lane8 = 8 * lane,
 // sbase = GU_GRID_TABLE_BYTES + 8 * (lane & 15). Signs by the identity sum(+/-g*q) = dp4a(g^m, q) - dp4a(m, q).
@@ -103,7 +103,8 @@ __global__ void __launch_bounds__(32 * GU_MAX_WARPS, 1)
                            const uint8_t *__restrict__ xq, const int32_t *__restrict__ selected,
                            const float *__restrict__ weights, float *__restrict__ gate_out, float *__restrict__ up_out,
                            float *__restrict__ mid_out, uint64_t expert_bytes, uint32_t mid_dim, uint32_t k,
-                           uint32_t n_items, float clamp, int ieee_i, int *status)
+                           uint32_t n_items, float clamp, int ieee_i, int *status, const int32_t *__restrict__ order,
+                           uint32_t parts)
 {
     extern __shared__ __align__(128) uint8_t smem[];
     const int wpc = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -131,105 +132,127 @@ __global__ void __launch_bounds__(32 * GU_MAX_WARPS, 1)
     pdl_wait();
     __syncthreads();
 
-    // this warp's run of items; item i covers rows 2i, 2i+1 of the flattened [pair][row] space (mid_dim is even)
+    // Items: item i covers rows 2i, 2i+1 of the flattened [pair position][row] space (mid_dim is even). Without `order`
+    // a warp takes one contiguous run of items and pair position = pair. With `order` (pair positions sorted by expert,
+    // order[position] = pair) every pair's items are cut into `parts` runs at the same rows, run = task, and warps take
+    // tasks position-major: pairs of one expert stream the same rows at the same time, so the second one finds them
+    // in L2 instead of reading DRAM again.
     const uint32_t n_warps = gridDim.x * wpc, gw = blockIdx.x * wpc + warp;
-    const uint32_t chunk = (n_items + n_warps - 1) / n_warps;
-    const uint32_t begin = min(n_items, gw * chunk), end = min(n_items, begin + chunk);
-    if (begin >= end) return;
     const bool ieee = ieee_i != 0;
     const uint32_t lane8 = 8u * lane, sbase = GU_GRID_TABLE_BYTES + 8u * (lane & 15);
     const int sub = lane >> 4, blk = lane & 15, rot = blk >> 1;
     const uint32_t items_per_pair = mid_dim / GU_ITEM_ROWS;
-
-    uint32_t f_item = begin, f_pair = begin / items_per_pair, f_row = (begin - f_pair * items_per_pair) * GU_ITEM_ROWS;
-    auto issue_next = [&](int stage) {
-        if (lane == 0) {
-            const int32_t e = selected[f_pair];
-            const uint64_t off = (e < 0 ? 0u : (uint64_t)e) * expert_bytes + (uint64_t)f_row * GU_ROW_BYTES;
-            uint8_t *dst = ring + stage * GU_ITEM_BYTES;
-            mbar_expect_tx(&bars[stage], GU_ITEM_BYTES);
-            // rows f_row and f_row+1 are adjacent in each tensor: one copy per tensor; gate rows first, then up rows
-            bulk_g2s(dst, gate_base + off, GU_ITEM_ROWS * GU_ROW_BYTES, &bars[stage]);
-            bulk_g2s(dst + GU_ITEM_ROWS * GU_ROW_BYTES, up_base + off, GU_ITEM_ROWS * GU_ROW_BYTES, &bars[stage]);
-        }
-        ++f_item;
-        f_row += GU_ITEM_ROWS;
-        if (f_row == mid_dim) {
-            f_row = 0;
-            ++f_pair;
-        }
-    };
-#pragma unroll
-    for (int j = 0; j < GU_STAGES - 1; ++j)
-        if (f_item < end) issue_next(j);
-
+    const uint32_t n_tasks = order ? (n_items / items_per_pair) * parts : 1u;
     int q[64];  // activations of block blk, 16-byte pieces in rotated order: q[16j ..] belongs to piece (j + rot) & 3
     float yd = 0.0f;
-    uint32_t pair = begin / items_per_pair, row = (begin - pair * items_per_pair) * GU_ITEM_ROWS, cur_tok = 0xFFFFFFFFu;
-    float keep_g = 0.0f, keep_u = 0.0f;  // lane L keeps row (2 * flush_base + L) of the flattened output
-    uint32_t flush_base = begin;
-    uint32_t it = 0;
-    for (uint32_t item = begin; item < end; ++item, ++it) {
-        const int stage = it % GU_STAGES;
-        const uint32_t tok = pair / k;
-        if (tok != cur_tok) {  // new token: reload this lane's block of its Q8_K row
-            cur_tok = tok;
-            const uint8_t *xb = xq + ((size_t)tok * 16 + blk) * Q8K_BYTES;
-            yd = *reinterpret_cast<const float *>(xb);
+    uint32_t cur_tok = 0xFFFFFFFFu;
+    uint32_t it = 0;  // items consumed so far: ring stage and mbarrier phase follow it across tasks
+
+    // tasks go to the CTAs round-robin, so that when there are fewer tasks than warps every SM keeps about as many
+    for (uint32_t task = order ? warp * gridDim.x + blockIdx.x : 0u; task < n_tasks; task += n_warps) {
+        uint32_t begin, end;
+        if (order) {
+            const uint32_t pos = task / parts, part = task - pos * parts;
+            begin = pos * items_per_pair + (uint32_t)(((uint64_t)part * items_per_pair) / parts);
+            end = pos * items_per_pair + (uint32_t)(((uint64_t)(part + 1) * items_per_pair) / parts);
+        } else {
+            const uint32_t chunk = (n_items + n_warps - 1) / n_warps;
+            begin = min(n_items, gw * chunk), end = min(n_items, begin + chunk);
+        }
+        if (begin >= end) continue;
+
+        uint32_t f_item = begin, f_pair = begin / items_per_pair, f_row = (begin - f_pair * items_per_pair) * GU_ITEM_ROWS;
+        auto issue_next = [&](int stage) {
+            if (lane == 0) {
+                const int32_t e = selected[order ? (uint32_t)order[f_pair] : f_pair];
+                const uint64_t off = (e < 0 ? 0u : (uint64_t)e) * expert_bytes + (uint64_t)f_row * GU_ROW_BYTES;
+                uint8_t *dst = ring + stage * GU_ITEM_BYTES;
+                mbar_expect_tx(&bars[stage], GU_ITEM_BYTES);
+                // rows f_row and f_row+1 are adjacent in each tensor: one copy per tensor; gate rows first, then up rows
+                bulk_g2s(dst, gate_base + off, GU_ITEM_ROWS * GU_ROW_BYTES, &bars[stage]);
+                bulk_g2s(dst + GU_ITEM_ROWS * GU_ROW_BYTES, up_base + off, GU_ITEM_ROWS * GU_ROW_BYTES, &bars[stage]);
+            }
+            ++f_item;
+            f_row += GU_ITEM_ROWS;
+            if (f_row == mid_dim) {
+                f_row = 0;
+                ++f_pair;
+            }
+        };
+        if (it > 0) fence_async_smem();  // the stages were read by the task before
+#pragma unroll
+        for (int j = 0; j < GU_STAGES - 1; ++j)
+            if (f_item < end) issue_next((it + j) % GU_STAGES);
+
+        uint32_t pos = begin / items_per_pair, row = (begin - pos * items_per_pair) * GU_ITEM_ROWS;
+        uint32_t pair = order ? (uint32_t)order[pos] : pos;
+        float keep_g = 0.0f, keep_u = 0.0f;  // lane L keeps row (2 * flush_base + L) of the flattened [position][row] space
+        uint32_t flush_base = begin;
+        for (uint32_t item = begin; item < end; ++item, ++it) {
+            const int stage = it % GU_STAGES;
+            const uint32_t tok = pair / k;
+            if (tok != cur_tok) {  // new token: reload this lane's block of its Q8_K row
+                cur_tok = tok;
+                const uint8_t *xb = xq + ((size_t)tok * 16 + blk) * Q8K_BYTES;
+                yd = *reinterpret_cast<const float *>(xb);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int *pq = reinterpret_cast<const int *>(xb + 4 + 64 * ((j + rot) & 3));
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) q[16 * j + i] = pq[i];
+                }
+            }
+            if (f_item < end) {  // refill the stage consumed one iteration ago
+                fence_async_smem();
+                issue_next((it + GU_STAGES - 1) % GU_STAGES);
+            }
+            if (!mbar_wait_bounded(&bars[stage], (it / GU_STAGES) & 1, status)) return;
+            const uint8_t *grow = ring + stage * GU_ITEM_BYTES + sub * GU_ROW_BYTES;
+            const uint8_t *urow = grow + GU_ITEM_ROWS * GU_ROW_BYTES;
+            int sg = 0, su = 0;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const int *pq = reinterpret_cast<const int *>(xb + 4 + 64 * ((j + rot) & 3));
-#pragma unroll
-                for (int i = 0; i < 16; ++i) q[16 * j + i] = pq[i];
+                const int c = (j + rot) & 3;
+                const uint4 gp = gu_smem_piece<LAYOUT>(grow, blk, c), up = gu_smem_piece<LAYOUT>(urow, blk, c);
+                sg += iq2_group_dot_rep(gp.x, gp.y, q + 16 * j, smem, lane8, sbase);
+                sg += iq2_group_dot_rep(gp.z, gp.w, q + 16 * j + 8, smem, lane8, sbase);
+                su += iq2_group_dot_rep(up.x, up.y, q + 16 * j, smem, lane8, sbase);
+                su += iq2_group_dot_rep(up.z, up.w, q + 16 * j + 8, smem, lane8, sbase);
             }
-        }
-        if (f_item < end) {  // refill the stage consumed one iteration ago
-            fence_async_smem();
-            issue_next((it + GU_STAGES - 1) % GU_STAGES);
-        }
-        if (!mbar_wait_bounded(&bars[stage], (it / GU_STAGES) & 1, status)) return;
-        const uint8_t *grow = ring + stage * GU_ITEM_BYTES + sub * GU_ROW_BYTES;
-        const uint8_t *urow = grow + GU_ITEM_ROWS * GU_ROW_BYTES;
-        int sg = 0, su = 0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int c = (j + rot) & 3;
-            const uint4 gp = gu_smem_piece<LAYOUT>(grow, blk, c), up = gu_smem_piece<LAYOUT>(urow, blk, c);
-            sg += iq2_group_dot_rep(gp.x, gp.y, q + 16 * j, smem, lane8, sbase);
-            sg += iq2_group_dot_rep(gp.z, gp.w, q + 16 * j + 8, smem, lane8, sbase);
-            su += iq2_group_dot_rep(up.x, up.y, q + 16 * j, smem, lane8, sbase);
-            su += iq2_group_dot_rep(up.z, up.w, q + 16 * j + 8, smem, lane8, sbase);
-        }
-        const uint32_t dstep = LAYOUT == DSMOE_LAYOUT_ROWSOA ? 2 : IQ2XXS_BYTES;
-        const uint32_t dg = ld_u16(grow + dstep * blk), du = ld_u16(urow + dstep * blk);
-        __syncwarp();  // every lane has finished reading the stage
-        const float g = gu_row_total(iq2_block_scale(dg, yd, sg, ieee));  // all 16 lanes of the half hold the row total
-        const float u = gu_row_total(iq2_block_scale(du, yd, su, ieee));
-        const float g_o = __shfl_xor_sync(FULL, g, 16), u_o = __shfl_xor_sync(FULL, u, 16);
-        if ((uint32_t)(lane >> 1) == item - flush_base) {  // lane L keeps sub-row L & 1 of this item
-            keep_g = (lane & 1) == sub ? g : g_o;
-            keep_u = (lane & 1) == sub ? u : u_o;
-        }
-        if (item - flush_base == 15 || item + 1 == end) {
-            // clamp + SwiGLU + stores for up to 32 finished rows at once, one per lane
-            const uint32_t mine = GU_ITEM_ROWS * flush_base + lane;  // flattened [pair][row] output index
-            if (mine < GU_ITEM_ROWS * (item + 1)) {
-                float gg = keep_g, uu = keep_u;
-                if (clamp > 1.0e-6f) {
-                    if (gg > clamp) gg = clamp;
-                    if (uu > clamp) uu = clamp;
-                    if (uu < -clamp) uu = -clamp;
+            const uint32_t dstep = LAYOUT == DSMOE_LAYOUT_ROWSOA ? 2 : IQ2XXS_BYTES;
+            const uint32_t dg = ld_u16(grow + dstep * blk), du = ld_u16(urow + dstep * blk);
+            __syncwarp();  // every lane has finished reading the stage
+            const float g = gu_row_total(iq2_block_scale(dg, yd, sg, ieee));  // all 16 lanes of the half hold the row total
+            const float u = gu_row_total(iq2_block_scale(du, yd, su, ieee));
+            const float g_o = __shfl_xor_sync(FULL, g, 16), u_o = __shfl_xor_sync(FULL, u, 16);
+            if ((uint32_t)(lane >> 1) == item - flush_base) {  // lane L keeps sub-row L & 1 of this item
+                keep_g = (lane & 1) == sub ? g : g_o;
+                keep_u = (lane & 1) == sub ? u : u_o;
+            }
+            if (item - flush_base == 15 || item + 1 == end) {
+                // clamp + SwiGLU + stores for up to 32 finished rows at once, one per lane
+                const uint32_t mine = GU_ITEM_ROWS * flush_base + lane;  // flattened [position][row] index
+                if (mine < GU_ITEM_ROWS * (item + 1)) {
+                    float gg = keep_g, uu = keep_u;
+                    if (clamp > 1.0e-6f) {
+                        if (gg > clamp) gg = clamp;
+                        if (uu > clamp) uu = clamp;
+                        if (uu < -clamp) uu = -clamp;
+                    }
+                    const uint32_t mpos = mine / mid_dim, mpair = order ? (uint32_t)order[mpos] : mpos;
+                    const size_t dst = (size_t)mpair * mid_dim + (mine - mpos * mid_dim);
+                    if (gate_out) gate_out[dst] = gg;
+                    if (up_out) up_out[dst] = uu;
+                    mid_out[dst] = swiglu_weighted(gg, uu, weights[mpair]);
                 }
-                if (gate_out) gate_out[mine] = gg;
-                if (up_out) up_out[mine] = uu;
-                mid_out[mine] = swiglu_weighted(gg, uu, weights[mine / mid_dim]);
+                flush_base = item + 1;
             }
-            flush_base = item + 1;
-        }
-        row += GU_ITEM_ROWS;
-        if (row == mid_dim) {
-            row = 0;
-            ++pair;
+            row += GU_ITEM_ROWS;
+            if (row == mid_dim) {
+                row = 0;
+                ++pos;
+                if (item + 1 < end) pair = order ? (uint32_t)order[pos] : pos;
+            }
         }
     }
 }
@@ -265,8 +288,10 @@ __global__ void __launch_bounds__(256, 2) down_m8_tma_kernel(const uint8_t *__re
     float *s_part = reinterpret_cast<float *>(smem + (size_t)k * (rows_per_cta * DN_ROW_BYTES + DN_ACT_BYTES));
     uint64_t *bars = reinterpret_cast<uint64_t *>(s_part + MAX_K * DN_ROWS_MAX) + slot * DN_STAGES;
 
-    const uint32_t tok = blockIdx.y, pair = tok * k + slot;
-    const uint32_t row_begin = blockIdx.x * rows_per_cta;
+    // tokens run fastest over the grid: the CTAs resident at one time cover every token at a few row groups, so tokens
+    // that share an expert ask for the same rows at the same time and all but the first are served by L2
+    const uint32_t tok = blockIdx.x, pair = tok * k + slot;
+    const uint32_t row_begin = blockIdx.y * rows_per_cta;
     const uint32_t n_rows = min((uint32_t)rows_per_cta, out_dim - row_begin);
     pdl_launch_dependents();
     pdl_wait();
@@ -374,19 +399,80 @@ bool gate_up_tma_eligible(const GateUpArgs &a)
            (((uintptr_t)a.gate_base | (uintptr_t)a.up_base | a.expert_bytes) & 15) == 0;
 }
 
+// Pair positions sorted by expert for the gate/up kernel: order[position] = pair. One CTA: counts in shared memory,
+// an exclusive scan, placement (the order inside an expert's run does not matter: every pair is computed on its own).
+constexpr int PO_MAX_EXPERTS = 4096;
+
+__global__ void __launch_bounds__(1024) pair_order_kernel(const int32_t *__restrict__ selected, uint32_t n_pairs,
+                                                           uint32_t n_expert, int32_t *__restrict__ order)
+{
+    extern __shared__ uint32_t po_count[];  // n_expert counts, then n_expert cursors
+    uint32_t *cursor = po_count + n_expert;
+    pdl_launch_dependents();
+    for (uint32_t e = threadIdx.x; e < n_expert; e += blockDim.x) po_count[e] = 0;
+    pdl_wait();
+    __syncthreads();
+    auto bin = [&](uint32_t p) {
+        const int32_t e = selected[p];
+        return e < 0 ? 0u : ((uint32_t)e < n_expert ? (uint32_t)e : n_expert - 1);
+    };
+    for (uint32_t p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicAdd(&po_count[bin(p)], 1u);
+    __syncthreads();
+    if (threadIdx.x < 32) {  // exclusive scan by one warp, 32 experts per round
+        uint32_t run = 0;
+        for (uint32_t e0 = 0; e0 < n_expert; e0 += 32) {
+            const uint32_t e = e0 + threadIdx.x, c = e < n_expert ? po_count[e] : 0u;
+            uint32_t inc = c;
+#pragma unroll
+            for (int m = 1; m < 32; m <<= 1) {
+                const uint32_t o = __shfl_up_sync(FULL, inc, m);
+                if ((int)threadIdx.x >= m) inc += o;
+            }
+            if (e < n_expert) cursor[e] = run + inc - c;
+            run += __shfl_sync(FULL, inc, 31);
+        }
+    }
+    __syncthreads();
+    for (uint32_t p = threadIdx.x; p < n_pairs; p += blockDim.x) order[atomicAdd(&cursor[bin(p)], 1u)] = (int32_t)p;
+}
+
+int launch_pair_order(cudaStream_t st, const int32_t *selected, uint32_t n_pairs, uint32_t n_expert, int32_t *order)
+{
+    if (n_pairs == 0 || n_expert == 0 || n_expert > (uint32_t)PO_MAX_EXPERTS) return 0;
+    launch_pdl(pair_order_kernel, dim3(1), dim3(1024), (size_t)2 * n_expert * sizeof(uint32_t), st, selected, n_pairs, n_expert,
+               order);
+    return 1;
+}
+
 template <int LAYOUT>
 static void launch_gu_tma(cudaStream_t st, const GateUpArgs &a, int *status)
 {
-    const uint32_t n_items = a.n_tokens * a.k * (a.mid_dim / GU_ITEM_ROWS);
+    const uint32_t items_per_pair = a.mid_dim / GU_ITEM_ROWS, n_pairs = a.n_tokens * a.k;
+    const uint32_t n_items = n_pairs * items_per_pair;
     const int sms = sm_count_current();
-    // warps per CTA: as many as fit, unless a smaller count wastes clearly fewer warp-slots in the last round of items
-    auto eff_of = [&](int w) {
-        const uint32_t nw = (uint32_t)sms * w, chunk = (n_items + nw - 1) / nw;
-        return (double)n_items / ((double)chunk * nw);
-    };
     int best_w = GU_MAX_WARPS;
-    for (int w = GU_MAX_WARPS - 1; w >= 8; --w)
-        if (eff_of(w) > eff_of(best_w) + 0.08) best_w = w;
+    uint32_t parts = 1;
+    if (a.order) {
+        // warps per CTA and runs per pair: the fewest items for the busiest warp, a run's start (an empty ring to
+        // fill) counted as eight items; ties go to more warps, fewer runs
+        uint64_t best_cost = ~0ull;
+        for (int w = GU_MAX_WARPS; w >= 8; --w) {
+            const uint32_t nw = (uint32_t)sms * w;
+            for (uint32_t pr = 1; pr <= items_per_pair && pr <= 256; ++pr) {
+                const uint64_t tasks = (uint64_t)n_pairs * pr, rounds = (tasks + nw - 1) / nw;
+                const uint64_t cost = rounds * ((items_per_pair + pr - 1) / pr + 8);
+                if (cost < best_cost) best_cost = cost, best_w = w, parts = pr;
+            }
+        }
+    } else {
+        // warps per CTA: as many as fit, unless a smaller count wastes clearly fewer warp-slots in the last round of items
+        auto eff_of = [&](int w) {
+            const uint32_t nw = (uint32_t)sms * w, chunk = (n_items + nw - 1) / nw;
+            return (double)n_items / ((double)chunk * nw);
+        };
+        for (int w = GU_MAX_WARPS - 1; w >= 8; --w)
+            if (eff_of(w) > eff_of(best_w) + 0.08) best_w = w;
+    }
     const size_t smem = GU_TABLE_BYTES + (size_t)best_w * GU_STAGES * GU_ITEM_BYTES + (size_t)best_w * GU_STAGES * 8;
     static OncePerDevice attr;  // one per template instance
     if (attr.first())
@@ -396,7 +482,7 @@ static void launch_gu_tma(cudaStream_t st, const GateUpArgs &a, int *status)
     const uint32_t grid = want < (uint32_t)sms ? want : (uint32_t)sms;
     launch_pdl(gate_up_x16_tma_kernel<LAYOUT>, dim3(grid), dim3(32 * best_w), smem, st, a.gate_base, a.up_base, a.xq,
                a.selected, a.weights, a.gate_out, a.up_out, a.mid_out, a.expert_bytes, a.mid_dim, a.k, n_items, a.clamp,
-               a.ieee, status);
+               a.ieee, status, a.order, parts);
 }
 
 int launch_gate_up_mid_tma(cudaStream_t st, const GateUpArgs &a, int *status)
@@ -423,7 +509,7 @@ static void launch_dn_tma(cudaStream_t st, const DownArgs &a, int *status)
     if (attr.first())
         cudaFuncSetAttribute(down_m8_tma_kernel<LAYOUT, SUM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              MAX_K * (DN_ROWS_MAX * DN_ROW_BYTES + DN_ACT_BYTES) + MAX_K * DN_ROWS_MAX * 4 + MAX_K * DN_STAGES * 8);
-    dim3 grid((a.out_dim + rows_per_cta - 1) / rows_per_cta, a.n_tokens);
+    dim3 grid(a.n_tokens, (a.out_dim + rows_per_cta - 1) / rows_per_cta);
     launch_pdl(down_m8_tma_kernel<LAYOUT, SUM>, grid, dim3(32 * a.k), smem, st, a.down_base, a.midq, a.selected, a.out,
                a.expert_bytes, a.out_dim, a.k, a.ieee, rows_per_cta, status);
 }

@@ -124,9 +124,14 @@ struct GateUpArgs {
     uint32_t xq_blocks, mid_dim, k, n_tokens;
     float clamp;
     int layout, ieee;
+    // TMA kernel only, optional: the pairs sorted by expert (order[position] = pair, from launch_pair_order); pairs of
+    // one expert are then streamed together and the second one finds the weights in L2. Results do not depend on it.
+    const int32_t *order = nullptr;
 };
 // Returns the number of kernels launched.
 int launch_gate_up_mid(cudaStream_t st, const GateUpArgs &a);
+// order[position] = pair, positions sorted by selected[pair]; 0 launches (and `order` untouched) above 4096 experts.
+int launch_pair_order(cudaStream_t st, const int32_t *selected, uint32_t n_pairs, uint32_t n_expert, int32_t *order);
 
 struct DownArgs {
     const uint8_t *down_base, *midq;
