@@ -493,7 +493,10 @@ static int shared_expert_impl(dsmoe_handle *h, cudaStream_t st, const uint8_t *g
 {
     const dsmoe_config &c = h->cfg;
     int n = 0;
-    if (shared_fused_eligible(c.n_embd, c.n_ff, n_tokens) && n_tokens <= h->sh_chunk) {
+    // up to four tokens every CTA quantises the activations itself (two launches); above that, when the tensors can be
+    // staged by bulk copies, quantising once and working through tiles of eight tokens is cheaper (four launches)
+    const bool tiles = shared_tiles_eligible(gate_w, up_w, down_w, h->sh_xq, h->sh_xscale, c.n_embd, c.n_ff);
+    if (n_tokens <= (tiles ? 4u : 8u) && shared_fused_eligible(c.n_embd, c.n_ff, n_tokens) && n_tokens <= h->sh_chunk) {
         n = launch_shared_fused(st, gate_w, up_w, down_w, x, h->sh_mid, out, c.n_embd, c.n_ff, n_tokens, c.swiglu_clamp,
                                 h->d_status);
         return check_launch(h, "shared_expert", n);
@@ -501,6 +504,11 @@ static int shared_expert_impl(dsmoe_handle *h, cudaStream_t st, const uint8_t *g
     for (uint32_t t0 = 0; t0 < n_tokens; t0 += h->sh_chunk) {
         const uint32_t T = n_tokens - t0 < h->sh_chunk ? n_tokens - t0 : h->sh_chunk;
         const float *xc = x + (size_t)t0 * c.n_embd;
+        if (tiles) {
+            n += launch_shared_tiles(st, gate_w, up_w, down_w, xc, h->sh_xq, h->sh_xscale, h->sh_mid, out + (size_t)t0 * c.n_embd,
+                                     c.n_embd, c.n_ff, T, c.swiglu_clamp, h->d_status);
+            continue;
+        }
         launch_quantize_q8_0(st, xc, h->sh_xq, h->sh_xscale, c.n_embd, T);
         launch_matmul_q8_0(st, gate_w, h->sh_xq, h->sh_xscale, h->sh_gate, c.n_embd, c.n_ff, T);
         launch_matmul_q8_0(st, up_w, h->sh_xq, h->sh_xscale, h->sh_up, c.n_embd, c.n_ff, T);

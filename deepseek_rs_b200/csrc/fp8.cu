@@ -36,6 +36,16 @@ __device__ __forceinline__ float fp8_decode(uint8_t c)
     return __half2float(*reinterpret_cast<const __half *>(&h));
 }
 
+// Four e4m3 codes (byte 0 first) to f32, two per conversion instruction; the values are exact.
+__device__ __forceinline__ void fp8x4_decode(uint32_t c, float *f)
+{
+    const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(c & 0xFFFFu), __NV_E4M3);
+    const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(c >> 16), __NV_E4M3);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&lo));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&hi));
+    f[0] = a.x, f[1] = a.y, f[2] = b.x, f[3] = b.y;
+}
+
 // rows_per_block == 1: one warp per (row, 128-column block). rows_per_block == 128: one CTA (256 threads) per block.
 __global__ void __launch_bounds__(256) fp8_quantize_kernel(const float *__restrict__ x, uint8_t *__restrict__ codes,
                                                             float *__restrict__ scales, uint32_t rows, uint32_t cols,
@@ -97,7 +107,7 @@ void launch_fp8_quantize(cudaStream_t st, const float *x, uint8_t *codes, float 
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int FP8_MV_MAX_M = 8;
 
-__global__ void __launch_bounds__(256) fp8_matvec_kernel(const uint8_t *__restrict__ a, const float *__restrict__ a_scale,
+__global__ void __launch_bounds__(256, 4) fp8_matvec_kernel(const uint8_t *__restrict__ a, const float *__restrict__ a_scale,
                                                           const uint8_t *__restrict__ w, const float *__restrict__ w_scale,
                                                           __nv_bfloat16 *__restrict__ out, uint32_t M, uint32_t N, uint32_t K)
 {
@@ -108,23 +118,32 @@ __global__ void __launch_bounds__(256) fp8_matvec_kernel(const uint8_t *__restri
     float acc[FP8_MV_MAX_M];
 #pragma unroll
     for (int m = 0; m < FP8_MV_MAX_M; ++m) acc[m] = 0.0f;
-    for (uint32_t k0 = 16 * lane; k0 < K; k0 += 512) {
-        const uint32_t kb = k0 >> 7;
-        const uint4 wv = ld_stream_16B(w + (size_t)n * K + k0);
-        const float sw = w_scale[(size_t)(n >> 7) * kbn + kb];
-        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-        float wf[16];
+    // four 512-byte stretches of the row per round, all requested before any is used (four CTAs per SM: the 512 CTAs
+    // of a 4096-feature projection are resident at once)
+    for (uint32_t kr = 16 * lane; kr < K; kr += 4 * 512) {
+        uint4 wq[4];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) wf[i] = fp8_decode((uint8_t)(ww[i >> 2] >> (8 * (i & 3))));
+        for (int u = 0; u < 4; ++u)
+            if (kr + 512 * u < K) wq[u] = ld_stream_16B(w + (size_t)n * K + kr + 512 * u);
 #pragma unroll
-        for (int m = 0; m < FP8_MV_MAX_M; ++m) {
-            if (m < (int)M) {
-                const uint4 av = *reinterpret_cast<const uint4 *>(a + (size_t)m * K + k0);
-                const uint32_t aw[4] = {av.x, av.y, av.z, av.w};
-                float p = 0.0f;
+        for (int u = 0; u < 4; ++u) {
+            const uint32_t k0 = kr + 512 * u;
+            if (k0 >= K) break;
+            const uint32_t kb = k0 >> 7;
+            const float sw = w_scale[(size_t)(n >> 7) * kbn + kb];
+            float wf[16];
+            fp8x4_decode(wq[u].x, wf), fp8x4_decode(wq[u].y, wf + 4), fp8x4_decode(wq[u].z, wf + 8), fp8x4_decode(wq[u].w, wf + 12);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) p = fmaf(fp8_decode((uint8_t)(aw[i >> 2] >> (8 * (i & 3)))), wf[i], p);
-                acc[m] = fmaf(a_scale[(size_t)m * kbn + kb] * sw, p, acc[m]);
+            for (int m = 0; m < FP8_MV_MAX_M; ++m) {
+                if (m < (int)M) {
+                    const uint4 av = *reinterpret_cast<const uint4 *>(a + (size_t)m * K + k0);
+                    float af[16];
+                    fp8x4_decode(av.x, af), fp8x4_decode(av.y, af + 4), fp8x4_decode(av.z, af + 8), fp8x4_decode(av.w, af + 12);
+                    float p = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) p = fmaf(af[i], wf[i], p);
+                    acc[m] = fmaf(a_scale[(size_t)m * kbn + kb] * sw, p, acc[m]);
+                }
             }
         }
     }

@@ -112,6 +112,13 @@ bool shared_fused_eligible(uint32_t n_embd, uint32_t n_ff, uint32_t n_tokens);
 int launch_shared_fused(cudaStream_t st, const uint8_t *gate_w, const uint8_t *up_w, const uint8_t *down_w, const float *x,
                         float *mid, float *out, uint32_t n_embd, uint32_t n_ff, uint32_t n_tokens, float clamp,
                         int *status);
+// More than eight tokens (any count): quantise, gate + up + SwiGLU, quantise, down, the two matrix kernels with weight
+// rows and activation tiles staged in shared memory by bulk copies. Needs what shared_tiles_eligible checks. 4 launches.
+bool shared_tiles_eligible(const uint8_t *gate_w, const uint8_t *up_w, const uint8_t *down_w, const int8_t *xq,
+                           const float *xs, uint32_t n_embd, uint32_t n_ff);
+int launch_shared_tiles(cudaStream_t st, const uint8_t *gate_w, const uint8_t *up_w, const uint8_t *down_w, const float *x,
+                        int8_t *xq, float *xs, float *mid, float *out, uint32_t n_embd, uint32_t n_ff, uint32_t n_tokens,
+                        float clamp, int *status);
 void launch_matmul_f16(cudaStream_t st, const uint16_t *w, const float *x, float *out, uint64_t in_dim, uint64_t out_dim,
                        uint64_t n_tok);
 

@@ -370,10 +370,14 @@ __global__ void __launch_bounds__(256) shared_fused_kernel(const uint8_t *__rest
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int SHS_MAX_TOK = 8;
 
-template <bool FIRST, int TOK>
+// PREQ: the activations arrive quantised (xq, xs in global memory, from quantize_q8_0_kernel) and the CTA takes the
+// tile of TOK tokens blockIdx.y, fetched by two more bulk copies instead of being quantised here; this is the form
+// for more than SHS_MAX_TOK tokens, where quantising in every CTA would cost more than the weights.
+template <bool FIRST, int TOK, bool PREQ>
 __global__ void __launch_bounds__(256) shared_staged_kernel(const uint8_t *__restrict__ w0, const uint8_t *__restrict__ w1,
-                                                             const float *__restrict__ x, float *__restrict__ out,
-                                                             uint32_t in_dim, uint32_t out_dim, uint32_t n_tok, float clamp,
+                                                             const float *__restrict__ x, const int8_t *__restrict__ xq,
+                                                             const float *__restrict__ xs, float *__restrict__ out,
+                                                             uint32_t in_dim, uint32_t out_dim, uint32_t n_tok_all, float clamp,
                                                              int *status)
 {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -382,12 +386,15 @@ __global__ void __launch_bounds__(256) shared_staged_kernel(const uint8_t *__res
     uint8_t *wst = smem + (size_t)warp * 2 * row_bytes;
     int8_t *s_xq = reinterpret_cast<int8_t *>(smem + (size_t)16 * row_bytes);
     float *s_xs = reinterpret_cast<float *>(s_xq + (size_t)TOK * in_dim);
-    uint64_t *bar = reinterpret_cast<uint64_t *>(s_xs + (size_t)TOK * blocks) + warp;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(s_xs + (size_t)TOK * blocks), *bar = bars + warp, *tile_bar = bars + 8;
+    const uint32_t tok0 = PREQ ? blockIdx.y * TOK : 0u;
+    const uint32_t n_tok = n_tok_all - tok0 < (uint32_t)TOK ? n_tok_all - tok0 : (uint32_t)TOK;
     // FIRST: rows r of both tensors; otherwise rows r, r + 1 of the one tensor (adjacent in memory: one copy)
     const uint32_t row = FIRST ? blockIdx.x * 8 + warp : blockIdx.x * 16 + 2 * warp;
     const uint32_t n_rows = row >= out_dim ? 0u : (FIRST ? 2u : (out_dim - row < 2u ? out_dim - row : 2u));
     if (lane == 0) {
         mbar_init(bar, 1);
+        if (PREQ && warp == 0) mbar_init(tile_bar, 1);
         fence_async_smem();
     }
     auto request_rows = [&]() {
@@ -404,9 +411,15 @@ __global__ void __launch_bounds__(256) shared_staged_kernel(const uint8_t *__res
     pdl_launch_dependents();
     pdl_wait();
     if (FIRST) request_rows();
-    // quantize_q8_0 of every token's row: a thread takes 16 adjacent values, two neighbouring lanes share a block
-    // (its largest magnitude is the larger of the two halves'; the maximum does not depend on the order)
-    {
+    if (PREQ) {
+        if (threadIdx.x == 0) {
+            mbar_expect_tx(tile_bar, n_tok * in_dim + n_tok * blocks * 4);
+            bulk_g2s(s_xq, xq + (size_t)tok0 * in_dim, n_tok * in_dim, tile_bar);
+            bulk_g2s(s_xs, xs + (size_t)tok0 * blocks, n_tok * blocks * 4, tile_bar);
+        }
+    } else {
+        // quantize_q8_0 of every token's row: a thread takes 16 adjacent values, two neighbouring lanes share a block
+        // (its largest magnitude is the larger of the two halves'; the maximum does not depend on the order)
         const uint32_t halves = in_dim / 16, total = n_tok * halves;
         for (uint32_t base = 0; base < total; base += 256) {
             const uint32_t u = base + threadIdx.x;
@@ -448,6 +461,7 @@ __global__ void __launch_bounds__(256) shared_staged_kernel(const uint8_t *__res
     }
     __syncthreads();
     if (n_rows == 0) return;
+    if (PREQ && !mbar_wait_bounded(tile_bar, 0, status)) return;
     if (!mbar_wait_bounded(bar, 0, status)) return;
     float acc[2][TOK];
 #pragma unroll
@@ -498,17 +512,17 @@ __global__ void __launch_bounds__(256) shared_staged_kernel(const uint8_t *__res
             if (u > clamp) u = clamp;
             if (u < -clamp) u = -clamp;
         }
-        out[(size_t)lane * out_dim + row] = swiglu_weighted(g, u, 1.0f);
+        out[(size_t)(tok0 + lane) * out_dim + row] = swiglu_weighted(g, u, 1.0f);
     } else {
-        out[(size_t)lane * out_dim + row] = g;
-        if (n_rows == 2) out[(size_t)lane * out_dim + row + 1] = u;
+        out[(size_t)(tok0 + lane) * out_dim + row] = g;
+        if (n_rows == 2) out[(size_t)(tok0 + lane) * out_dim + row + 1] = u;
     }
 }
 
 static size_t shared_staged_smem(uint32_t in_dim, int tok)
 {
     const size_t blocks = in_dim / 32;
-    return 16 * blocks * Q8_0_BYTES + (size_t)tok * in_dim + (size_t)tok * blocks * 4 + 8 * sizeof(uint64_t);
+    return 16 * blocks * Q8_0_BYTES + (size_t)tok * in_dim + (size_t)tok * blocks * 4 + 16 * sizeof(uint64_t);
 }
 
 template <int TOK>
@@ -518,15 +532,49 @@ static void launch_shared_staged(cudaStream_t st, const uint8_t *gate_w, const u
 {
     static OncePerDevice attr;  // one per template instance
     if (attr.first()) {
-        cudaFuncSetAttribute(shared_staged_kernel<true, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(shared_staged_kernel<true, TOK, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)shared_staged_smem(SHF_MAX_IN, TOK));
-        cudaFuncSetAttribute(shared_staged_kernel<false, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(shared_staged_kernel<false, TOK, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)shared_staged_smem(SHF_MAX_IN, TOK));
     }
-    launch_pdl(shared_staged_kernel<true, TOK>, dim3((n_ff + 7) / 8), dim3(256), shared_staged_smem(n_embd, TOK), st, gate_w,
-               up_w, x, mid, n_embd, n_ff, n_tokens, clamp, status);
-    launch_pdl(shared_staged_kernel<false, TOK>, dim3((n_embd + 15) / 16), dim3(256), shared_staged_smem(n_ff, TOK), st, down_w,
-               (const uint8_t *)nullptr, (const float *)mid, out, n_ff, n_embd, n_tokens, clamp, status);
+    launch_pdl(shared_staged_kernel<true, TOK, false>, dim3((n_ff + 7) / 8), dim3(256), shared_staged_smem(n_embd, TOK), st,
+               gate_w, up_w, x, (const int8_t *)nullptr, (const float *)nullptr, mid, n_embd, n_ff, n_tokens, clamp, status);
+    launch_pdl(shared_staged_kernel<false, TOK, false>, dim3((n_embd + 15) / 16), dim3(256), shared_staged_smem(n_ff, TOK), st,
+               down_w, (const uint8_t *)nullptr, (const float *)mid, (const int8_t *)nullptr, (const float *)nullptr, out, n_ff,
+               n_embd, n_tokens, clamp, status);
+}
+
+// More than SHS_MAX_TOK tokens: quantise, gate + up + SwiGLU over tiles of eight tokens, quantise, down over tiles.
+bool shared_tiles_eligible(const uint8_t *gate_w, const uint8_t *up_w, const uint8_t *down_w, const int8_t *xq,
+                           const float *xs, uint32_t n_embd, uint32_t n_ff)
+{
+    return n_embd % 256 == 0 && n_ff % 256 == 0 && n_embd <= (uint32_t)SHF_MAX_IN && n_ff <= (uint32_t)SHF_MAX_IN &&
+           ((reinterpret_cast<uintptr_t>(gate_w) | reinterpret_cast<uintptr_t>(up_w) | reinterpret_cast<uintptr_t>(down_w) |
+             reinterpret_cast<uintptr_t>(xq) | reinterpret_cast<uintptr_t>(xs)) & 15) == 0;
+}
+
+int launch_shared_tiles(cudaStream_t st, const uint8_t *gate_w, const uint8_t *up_w, const uint8_t *down_w, const float *x,
+                        int8_t *xq, float *xs, float *mid, float *out, uint32_t n_embd, uint32_t n_ff, uint32_t n_tokens,
+                        float clamp, int *status)
+{
+    constexpr int TOK = SHS_MAX_TOK;
+    static OncePerDevice attr;
+    if (attr.first()) {
+        cudaFuncSetAttribute(shared_staged_kernel<true, TOK, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)shared_staged_smem(SHF_MAX_IN, TOK));
+        cudaFuncSetAttribute(shared_staged_kernel<false, TOK, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)shared_staged_smem(SHF_MAX_IN, TOK));
+    }
+    const unsigned tiles = (n_tokens + TOK - 1) / TOK;
+    launch_quantize_q8_0(st, x, xq, xs, n_embd, n_tokens);
+    launch_pdl(shared_staged_kernel<true, TOK, true>, dim3((n_ff + 7) / 8, tiles), dim3(256), shared_staged_smem(n_embd, TOK), st,
+               gate_w, up_w, (const float *)nullptr, (const int8_t *)xq, (const float *)xs, mid, n_embd, n_ff, n_tokens, clamp,
+               status);
+    launch_quantize_q8_0(st, mid, xq, xs, n_ff, n_tokens);
+    launch_pdl(shared_staged_kernel<false, TOK, true>, dim3((n_embd + 15) / 16, tiles), dim3(256), shared_staged_smem(n_ff, TOK),
+               st, down_w, (const uint8_t *)nullptr, (const float *)nullptr, (const int8_t *)xq, (const float *)xs, out, n_ff,
+               n_embd, n_tokens, clamp, status);
+    return 4;
 }
 
 // The staged form needs whole rows that bulk copies can take: 16-byte aligned tensors, rows a multiple of 16 bytes.

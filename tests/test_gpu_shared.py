@@ -88,7 +88,7 @@ def test_matmul_f16_router_logits_bit_exact(torch_cuda, oracle, K, T, in_dim, ou
     assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
 
 
-@pytest.mark.parametrize("T,shift", [(1, 0), (2, 0), (3, 0), (5, 0), (8, 0), (1, 4), (3, 4), (9, 0), (1300, 0)])
+@pytest.mark.parametrize("T,shift", [(1, 0), (2, 0), (3, 0), (5, 0), (8, 0), (1, 4), (3, 4), (9, 0), (64, 0), (9, 4), (1300, 0)])
 def test_shared_expert_whole(torch_cuda, oracle, K, T, shift):
     """The one-call shared expert against the oracle's four steps. Up to 8 tokens take the two-launch kernels: with
     16-byte aligned tensors the form that stages whole weight rows in shared memory by bulk copies, with tensors that
