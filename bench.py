@@ -635,6 +635,7 @@ def run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, 
     L, V = 2, 4
     K = MoeKernels(device=local_rank, max_tokens=T, max_layers=L)
     ep = ExpertParallelHandle(K, rank, world, max_replicas=R, recv_capacity_rows=3 * T * TOP_K)
+    ep_fused = ep.combine_is_fused()
     g_exp, d_exp = GATE_EXPERT_BYTES, DOWN_EXPERT_BYTES
     shards = []
     for il in range(L):  # shard of layer il in ROWSOA order, with R empty replica slots behind the rank's own experts
@@ -799,7 +800,9 @@ def run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, 
                    "top_k": TOP_K, "n_expert": N_EXPERT, "experts_per_gpu": per, "replicated_hot_experts": R,
                    "replicas_chosen_from": "running counts of `selected` inside the library over the unreplicated steps",
                    "n_embd": N_EMBD, "n_ff": N_FF, "layout": "rowsoa", "router": "Zipf s=1.1 expert popularity",
-                   "parallelism": f"ep{world}: dsmoe_moe_forward_ep, NCCL send/recv dispatch (Q8_K rows) + combine (f32 rows)",
+                   "parallelism": f"ep{world}: dsmoe_moe_forward_ep, " + (
+                       "dispatch (Q8_K rows) and combine (f32 rows) as kernel stores into peer-mapped buffers over NVLink"
+                       if ep_fused else "grouped ncclSend / ncclRecv dispatch (Q8_K rows) and combine (f32 rows)"),
                    "l2": f"inputs rotate over {L} layers x {V} routings",
                    "routing_bit_exact_vs_single_gpu": bool(int(flags[0].item())),
                    "outputs_match_single_gpu": bool(int(flags[1].item())), "outputs_max_diff_of_scale": out_maxdiff,

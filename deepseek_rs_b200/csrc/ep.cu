@@ -189,6 +189,38 @@ __global__ void __launch_bounds__(256) ep_gather_kernel(EpRoute r, const uint32_
     }
 }
 
+// The same gather with the rows stored straight into the receive buffers of their destination ranks (peer-mapped;
+// plain stores over NVLink, never loads): send_end[d] = end of destination d's segment in send order, recv_base[d] =
+// first slot of this rank's segment in rank d's receive buffers. One warp per row.
+struct EpPeerDst {
+    uint8_t *xq[16];
+    int32_t *sel[16];
+    float *w[16];
+    uint32_t send_end[16], recv_base[16];
+    uint32_t world;
+};
+__global__ void __launch_bounds__(256) ep_gather_p2p_kernel(EpRoute r, const uint32_t *__restrict__ order,
+                                                             const uint8_t *__restrict__ xq, const float *__restrict__ weights,
+                                                             uint32_t k, uint32_t row_bytes, EpPeerDst dst)
+{
+    const uint32_t lane = threadIdx.x & 31, i = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (i >= r.n_pairs) return;
+    uint32_t d = 0, begin = 0;
+    while (d + 1 < dst.world && i >= dst.send_end[d]) begin = dst.send_end[d], ++d;
+    const size_t slot = (size_t)dst.recv_base[d] + (i - begin);
+    const uint32_t p = order[i];
+    const uint4 *src = reinterpret_cast<const uint4 *>(xq + (size_t)(p / k) * row_bytes);
+    uint4 *out = reinterpret_cast<uint4 *>(dst.xq[d] + slot * row_bytes);
+    for (uint32_t j = lane; j < row_bytes / 16; j += 32) out[j] = src[j];
+    if (lane == 0) {
+        uint32_t dest;
+        int32_t local;
+        ep_route(r, p, &dest, &local);
+        dst.sel[d][slot] = local;
+        dst.w[d][slot] = weights[p];
+    }
+}
+
 // row_ptr[i] for received row i: where its result goes in the buffer of the rank it came from. seg_end[s] = end of
 // the rows received from rank s, dst_base[s] = first slot of this rank's segment in rank s's send order.
 struct EpRowMap {
@@ -229,6 +261,10 @@ struct EpState {
     // fused combine: the peers' `back` buffers mapped into this process, and per received row its destination
     bool p2p = false;
     float *peer_back[16] = {};
+    // fused dispatch: recv_xq, recv_sel and recv_w are carved out of one allocation (recv_blob) whose peers' copies are
+    // mapped here, so that the gather kernel stores every row where its owner will read it
+    uint8_t *recv_blob = nullptr, *peer_blob[16] = {};
+    size_t blob_sel_off = 0, blob_w_off = 0;
     float **row_ptr = nullptr;
     int32_t *token = nullptr;  // [1 + world] ints for the completion all-gather
     // pinned host
@@ -252,13 +288,16 @@ void ep_destroy(EpState *s)
 {
     if (!s) return;
     for (int i = 0; i < s->world && i < 16; ++i)
-        if (s->p2p && i != s->rank && s->peer_back[i]) cudaIpcCloseMemHandle(s->peer_back[i]);
+        if (s->p2p && i != s->rank) {
+            if (s->peer_back[i]) cudaIpcCloseMemHandle(s->peer_back[i]);
+            if (s->peer_blob[i]) cudaIpcCloseMemHandle(s->peer_blob[i]);
+        }
     if (s->comm && s->own_comm && s->nccl) s->nccl->CommDestroy(s->comm);
     cudaFree(s->row_ptr), cudaFree(s->token);
     if (s->owner) dsmoe_destroy(s->owner);
     cudaFree(s->replica_slot), cudaFree(s->send_counts), cudaFree(s->count_matrix), cudaFree(s->pos), cudaFree(s->send_sel);
-    cudaFree(s->recv_sel), cudaFree(s->order), cudaFree(s->hist), cudaFree(s->send_xq), cudaFree(s->recv_xq);
-    cudaFree(s->send_w), cudaFree(s->recv_w), cudaFree(s->rows), cudaFree(s->back);
+    cudaFree(s->order), cudaFree(s->hist), cudaFree(s->send_xq), cudaFree(s->recv_blob);
+    cudaFree(s->send_w), cudaFree(s->rows), cudaFree(s->back);
     if (s->h_matrix) cudaFreeHost(s->h_matrix);
     delete s;
 }
@@ -319,8 +358,16 @@ int ep_create(const dsmoe_config &cfg, int device, const uint8_t *id128, void *a
     bool ok = true;
     auto alloc = [&](auto **p, size_t n) { ok = ok && cudaMalloc((void **)p, n * sizeof(**p)) == cudaSuccess; };
     alloc(&s->replica_slot, cfg.n_expert), alloc(&s->send_counts, W), alloc(&s->count_matrix, W * W), alloc(&s->pos, P);
-    alloc(&s->order, P), alloc(&s->hist, cfg.n_expert), alloc(&s->send_sel, P), alloc(&s->recv_sel, C);
-    alloc(&s->send_xq, P * s->row_bytes), alloc(&s->recv_xq, C * s->row_bytes), alloc(&s->send_w, P), alloc(&s->recv_w, C);
+    alloc(&s->order, P), alloc(&s->hist, cfg.n_expert), alloc(&s->send_sel, P);
+    alloc(&s->send_xq, P * s->row_bytes), alloc(&s->send_w, P);
+    s->blob_sel_off = (C * s->row_bytes + 255) & ~(size_t)255;
+    s->blob_w_off = (s->blob_sel_off + C * sizeof(int32_t) + 255) & ~(size_t)255;
+    alloc(&s->recv_blob, s->blob_w_off + C * sizeof(float));
+    if (ok) {
+        s->recv_xq = s->recv_blob;
+        s->recv_sel = reinterpret_cast<int32_t *>(s->recv_blob + s->blob_sel_off);
+        s->recv_w = reinterpret_cast<float *>(s->recv_blob + s->blob_w_off);
+    }
     alloc(&s->rows, C * cfg.n_embd), alloc(&s->back, P * cfg.n_embd);
     ok = ok && cudaMallocHost((void **)&s->h_matrix, W * W * sizeof(int32_t)) == cudaSuccess;
     ok = ok && cudaMemset(s->replica_slot, 0xFF, cfg.n_expert * sizeof(int32_t)) == cudaSuccess;
@@ -344,28 +391,33 @@ int ep_create(const dsmoe_config &cfg, int device, const uint8_t *id128, void *a
              cudaMemset(s->token, 0, (1 + W) * sizeof(int32_t)) == cudaSuccess &&
              cudaMalloc((void **)&d_handles, (W + 1) * sizeof(cudaIpcMemHandle_t)) == cudaSuccess &&
              cudaMalloc((void **)&d_flags, (W + 1) * sizeof(int32_t)) == cudaSuccess;
-        std::vector<cudaIpcMemHandle_t> handles(W);
-        cudaIpcMemHandle_t mine;
-        memset(&mine, 0, sizeof(mine));
-        if (ok && want && cudaIpcGetMemHandle(&mine, s->back) != cudaSuccess) want = 0;
-        cudaGetLastError();
-        if (ok) {
-            ok = cudaMemcpy(d_handles + W * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice) == cudaSuccess &&
-                 api->AllGather(d_handles + W * sizeof(mine), d_handles, sizeof(mine), NCCL_UINT8, s->comm, nullptr) == 0 &&
-                 cudaStreamSynchronize(nullptr) == cudaSuccess &&
-                 cudaMemcpy(handles.data(), d_handles, W * sizeof(mine), cudaMemcpyDeviceToHost) == cudaSuccess;
-        }
-        if (ok && want) {
-            for (int i = 0; i < world; ++i) {
-                if (i == rank) {
-                    s->peer_back[i] = s->back;
-                } else if (cudaIpcOpenMemHandle((void **)&s->peer_back[i], handles[(size_t)i], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
-                    cudaGetLastError();
-                    s->peer_back[i] = nullptr;
-                    want = 0;
+        // one round per exported buffer: all-gather its handle, open the peers'
+        auto exchange = [&](void *mine_ptr, void **peers) {
+            std::vector<cudaIpcMemHandle_t> handles(W);
+            cudaIpcMemHandle_t mine;
+            memset(&mine, 0, sizeof(mine));
+            if (ok && want && cudaIpcGetMemHandle(&mine, mine_ptr) != cudaSuccess) want = 0;
+            cudaGetLastError();
+            if (ok) {
+                ok = cudaMemcpy(d_handles + W * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice) == cudaSuccess &&
+                     api->AllGather(d_handles + W * sizeof(mine), d_handles, sizeof(mine), NCCL_UINT8, s->comm, nullptr) == 0 &&
+                     cudaStreamSynchronize(nullptr) == cudaSuccess &&
+                     cudaMemcpy(handles.data(), d_handles, W * sizeof(mine), cudaMemcpyDeviceToHost) == cudaSuccess;
+            }
+            if (ok && want) {
+                for (int i = 0; i < world; ++i) {
+                    if (i == rank) {
+                        peers[i] = mine_ptr;
+                    } else if (cudaIpcOpenMemHandle(&peers[i], handles[(size_t)i], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+                        cudaGetLastError();
+                        peers[i] = nullptr;
+                        want = 0;
+                    }
                 }
             }
-        }
+        };
+        exchange(s->back, reinterpret_cast<void **>(s->peer_back));
+        exchange(s->recv_blob, reinterpret_cast<void **>(s->peer_blob));
         std::vector<int32_t> flags(W, 0);
         if (ok) {
             ok = cudaMemcpy(d_flags + W, &want, sizeof(int32_t), cudaMemcpyHostToDevice) == cudaSuccess &&
@@ -383,7 +435,10 @@ int ep_create(const dsmoe_config &cfg, int device, const uint8_t *id128, void *a
         for (size_t i = 0; i < W; ++i) all = all && flags[i] != 0;
         if (!all)
             for (int i = 0; i < world; ++i)
-                if (i != rank && s->peer_back[i]) cudaIpcCloseMemHandle(s->peer_back[i]), s->peer_back[i] = nullptr;
+                if (i != rank) {
+                    if (s->peer_back[i]) cudaIpcCloseMemHandle(s->peer_back[i]), s->peer_back[i] = nullptr;
+                    if (s->peer_blob[i]) cudaIpcCloseMemHandle(s->peer_blob[i]), s->peer_blob[i] = nullptr;
+                }
         s->p2p = all;
     }
     *out = s;
@@ -452,10 +507,11 @@ int ep_forward(EpState *s, cudaStream_t st, uint32_t layer, const uint8_t *xq, c
     EP_CUDA(cudaMemcpyAsync(s->h_matrix, s->count_matrix, (size_t)W * W * sizeof(int32_t), cudaMemcpyDeviceToHost, st), "count read");
     if (P) {
         ep_place_kernel<<<W, 256, 0, st>>>(r, s->send_counts, s->pos, s->order);
-        ep_gather_kernel<<<(P + 7) / 8, 256, 0, st>>>(r, s->order, xq, weights, k, s->row_bytes, s->send_xq, s->send_sel, s->send_w);
+        if (!s->p2p)
+            ep_gather_kernel<<<(P + 7) / 8, 256, 0, st>>>(r, s->order, xq, weights, k, s->row_bytes, s->send_xq, s->send_sel, s->send_w);
     }
     EP_CUDA(cudaGetLastError(), "plan launch");
-    *n_launched += P ? 3 : 1;
+    *n_launched += P ? (s->p2p ? 2 : 3) : 1;
     EP_CUDA(cudaStreamSynchronize(st), "count read");
     mark(1);
     // 2. sizes; every rank evaluates every rank's receive total, so an overflow is reported by all of them alike
@@ -475,6 +531,28 @@ int ep_forward(EpState *s, cudaStream_t st, uint32_t layer, const uint8_t *xq, c
     }
     const size_t R = roff[W];
     // 3. dispatch
+    if (s->p2p) {
+        // fused with the gather: every row is stored where its owner reads it. A rank's completion all-gather follows
+        // its gather in stream order, so when it completes here every peer has finished storing into this rank's
+        // buffers. (The buffers are free: the step before ended with an all-gather that followed every rank's GEMM.)
+        if (P) {
+            EpPeerDst dst = {};
+            dst.world = W;
+            for (uint32_t d = 0; d < W; ++d) {
+                dst.xq[d] = s->peer_blob[d];
+                dst.sel[d] = reinterpret_cast<int32_t *>(s->peer_blob[d] + s->blob_sel_off);
+                dst.w[d] = reinterpret_cast<float *>(s->peer_blob[d] + s->blob_w_off);
+                dst.send_end[d] = (uint32_t)soff[d + 1];
+                uint32_t base = 0;
+                for (uint32_t src = 0; src < (uint32_t)s->rank; ++src) base += (uint32_t)M[src * W + d];
+                dst.recv_base[d] = base;
+            }
+            ep_gather_p2p_kernel<<<(P + 7) / 8, 256, 0, st>>>(r, s->order, xq, weights, k, s->row_bytes, dst);
+            EP_CUDA(cudaGetLastError(), "dispatch launch");
+            *n_launched += 1;
+        }
+        EP_NCCL(s->nccl->AllGather(s->token, s->token + 1, 1, NCCL_INT32, s->comm, st), "dispatch completion");
+    } else {
     EP_NCCL(s->nccl->GroupStart(), "dispatch");
     for (uint32_t peer = 0; peer < W; ++peer) {
         const size_t sc = soff[peer + 1] - soff[peer], rc = roff[peer + 1] - roff[peer];
@@ -490,6 +568,7 @@ int ep_forward(EpState *s, cudaStream_t st, uint32_t layer, const uint8_t *xq, c
         }
     }
     EP_NCCL(s->nccl->GroupEnd(), "dispatch");
+    }
     mark(2);
     // 4. the owner's compute: every received row is one (token, slot) pair of one local expert
     if (R && s->p2p) {

@@ -107,6 +107,7 @@ void launch_fp8_quantize(cudaStream_t st, const float *x, uint8_t *codes, float 
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int FP8_MV_MAX_M = 8;
 
+template <int MM, int DEPTH>  // MM: rows handled (M <= MM); DEPTH: 512-byte stretches of the weight row in flight
 __global__ void __launch_bounds__(256, 4) fp8_matvec_kernel(const uint8_t *__restrict__ a, const float *__restrict__ a_scale,
                                                           const uint8_t *__restrict__ w, const float *__restrict__ w_scale,
                                                           __nv_bfloat16 *__restrict__ out, uint32_t M, uint32_t N, uint32_t K)
@@ -115,18 +116,18 @@ __global__ void __launch_bounds__(256, 4) fp8_matvec_kernel(const uint8_t *__res
     const uint32_t n = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (n >= N) return;
     const uint32_t kbn = K / 128;
-    float acc[FP8_MV_MAX_M];
+    float acc[MM];
 #pragma unroll
-    for (int m = 0; m < FP8_MV_MAX_M; ++m) acc[m] = 0.0f;
-    // four 512-byte stretches of the row per round, all requested before any is used (four CTAs per SM: the 512 CTAs
-    // of a 4096-feature projection are resident at once)
-    for (uint32_t kr = 16 * lane; kr < K; kr += 4 * 512) {
-        uint4 wq[4];
+    for (int m = 0; m < MM; ++m) acc[m] = 0.0f;
+    // DEPTH stretches of the row per round, all requested before any is used; four CTAs per SM, so that the 512 CTAs
+    // of a 4096-feature projection are resident at once
+    for (uint32_t kr = 16 * lane; kr < K; kr += DEPTH * 512) {
+        uint4 wq[DEPTH];
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < DEPTH; ++u)
             if (kr + 512 * u < K) wq[u] = ld_stream_16B(w + (size_t)n * K + kr + 512 * u);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < DEPTH; ++u) {
             const uint32_t k0 = kr + 512 * u;
             if (k0 >= K) break;
             const uint32_t kb = k0 >> 7;
@@ -134,7 +135,7 @@ __global__ void __launch_bounds__(256, 4) fp8_matvec_kernel(const uint8_t *__res
             float wf[16];
             fp8x4_decode(wq[u].x, wf), fp8x4_decode(wq[u].y, wf + 4), fp8x4_decode(wq[u].z, wf + 8), fp8x4_decode(wq[u].w, wf + 12);
 #pragma unroll
-            for (int m = 0; m < FP8_MV_MAX_M; ++m) {
+            for (int m = 0; m < MM; ++m) {
                 if (m < (int)M) {
                     const uint4 av = *reinterpret_cast<const uint4 *>(a + (size_t)m * K + k0);
                     float af[16];
@@ -148,7 +149,7 @@ __global__ void __launch_bounds__(256, 4) fp8_matvec_kernel(const uint8_t *__res
         }
     }
 #pragma unroll
-    for (int m = 0; m < FP8_MV_MAX_M; ++m) {
+    for (int m = 0; m < MM; ++m) {
         float v = acc[m];
 #pragma unroll
         for (int s = 16; s > 0; s >>= 1) v += __shfl_xor_sync(FULL, v, s);
@@ -558,7 +559,8 @@ int launch_fp8_linear(cudaStream_t st, const uint8_t *a, const float *a_scale, c
     if (M == 0 || N == 0) return 0;
     __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(out_bf16);
     if (M <= FP8_MV_MAX_M) {
-        fp8_matvec_kernel<<<(N + 7) / 8, 256, 0, st>>>(a, a_scale, w, w_scale, out, M, N, K);
+        if (M == 1) fp8_matvec_kernel<1, 8><<<(N + 7) / 8, 256, 0, st>>>(a, a_scale, w, w_scale, out, M, N, K);
+        else fp8_matvec_kernel<FP8_MV_MAX_M, 4><<<(N + 7) / 8, 256, 0, st>>>(a, a_scale, w, w_scale, out, M, N, K);
         return 1;
     }
     static OncePerDevice attr;

@@ -364,11 +364,13 @@ DSMOE_API int dsmoe_ep_set_replicas(dsmoe_handle *h, const int32_t *expert_ids, 
 DSMOE_API int dsmoe_ep_expert_counts(dsmoe_handle *h, dsmoe_stream stream, uint64_t *counts_host, int reset);
 /* Rows this rank received from each rank in its most recent dsmoe_moe_forward_ep (int32 [world]). */
 DSMOE_API int dsmoe_ep_last_recv_rows(dsmoe_handle *h, int32_t *rows_per_rank);
-/* 1 when the combine is fused into the owner's down-projection kernel: at dsmoe_ep_init every rank maps the others'
- * receive buffers (CUDA IPC) and the grouped GEMM's epilogue stores each finished row straight into its source rank's
- * buffer over NVLink (plain global stores, no TMA, no multicast), followed by a four-byte all-gather as the completion
- * signal. 0: the rows travel by grouped ncclSend / ncclRecv after the kernel (DSMOE_EP_NO_P2P=1 in the environment at
- * dsmoe_ep_init, or an IPC mapping failed on some rank - the ranks agree on the mode). Results are identical. */
+/* 1 when dispatch and combine go over peer-mapped memory: at dsmoe_ep_init every rank maps the others' receive and
+ * return buffers (CUDA IPC). Dispatch is then the row-gather kernel itself, storing each pair's Q8_K row, local expert
+ * id and router weight where its owner reads them; combine is the owner's down-projection epilogue, storing each
+ * finished row straight into its source rank's buffer. Both are plain global stores over NVLink (no loads from peer
+ * memory, no TMA, no multicast), each followed by a four-byte all-gather as the completion signal. 0: rows travel both
+ * ways by grouped ncclSend / ncclRecv (DSMOE_EP_NO_P2P=1 in the environment at dsmoe_ep_init, or an IPC mapping failed
+ * on some rank - the ranks agree on the mode). Results are identical. */
 DSMOE_API int dsmoe_ep_combine_is_fused(dsmoe_handle *h);
 /* Measurement aid: six cudaEvent_t recorded at start, plan done, dispatch done, owner compute done, combine done, slot
  * sum done. NULL / 0 clears. */
