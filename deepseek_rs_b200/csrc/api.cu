@@ -34,6 +34,7 @@ struct dsmoe_handle {
     float *probs, *weights, *mid;
     int32_t *selected;
     int32_t *pair_order;  // pairs sorted by expert for the decode gate/up kernel at 16 tokens and more
+    uint32_t *blk_rows;   // rows stored so far per 256-row block of mid (decode gate/up kernel); zero between calls
     uint8_t *xq, *midq;
     // staging for the host-buffer call
     cudaStream_t hstream;
@@ -185,6 +186,8 @@ int dsmoe_create(const dsmoe_config *cfg, int device, dsmoe_handle **out)
     ok = ok && dev_alloc(&h->weights, T * k) == cudaSuccess;
     ok = ok && dev_alloc(&h->selected, T * k) == cudaSuccess;
     ok = ok && dev_alloc(&h->pair_order, T * k) == cudaSuccess;
+    ok = ok && dev_alloc(&h->blk_rows, T * k * (cfg->n_ff / QK_K) + 1) == cudaSuccess &&
+         cudaMemset(h->blk_rows, 0, (T * k * (cfg->n_ff / QK_K) + 1) * sizeof(uint32_t)) == cudaSuccess;
     ok = ok && dev_alloc(&h->xq, T * (cfg->n_embd / QK_K) * Q8K_BYTES) == cudaSuccess;
     ok = ok && dev_alloc(&h->mid, T * k * cfg->n_ff) == cudaSuccess;
     ok = ok && dev_alloc(&h->midq, T * k * (cfg->n_ff / QK_K) * Q8K_BYTES) == cudaSuccess;
@@ -250,6 +253,7 @@ int dsmoe_destroy(dsmoe_handle *h)
     cudaFree(h->weights);
     cudaFree(h->selected);
     cudaFree(h->pair_order);
+    cudaFree(h->blk_rows);
     cudaFree(h->xq);
     cudaFree(h->mid);
     cudaFree(h->midq);
@@ -293,7 +297,13 @@ int dsmoe_device_status(dsmoe_handle *h, dsmoe_stream stream, int *code_out)
     if (e != cudaSuccess) return fail(h, DSMOE_ERR_CUDA, "device_status: %s", cudaGetErrorString(e));
     if (*code_out == DEV_ERR_INDEX_RANGE)
         return fail(h, DSMOE_ERR_BOUNDS, "an expert index outside the layer was replaced by 0 (checked build, code %d)", *code_out);
-    if (*code_out != 0) return fail(h, DSMOE_ERR_TIMEOUT, "a bounded device-side wait expired (code %d)", *code_out);
+    if (*code_out != 0) {
+        // a kernel that gave up may have left the row counters of its unfinished blocks behind
+        if (h->blk_rows)
+            cudaMemsetAsync(h->blk_rows, 0, ((size_t)h->cfg.max_tokens * h->cfg.n_expert_used * (h->cfg.n_ff / QK_K) + 1) * sizeof(uint32_t),
+                            (cudaStream_t)stream);
+        return fail(h, DSMOE_ERR_TIMEOUT, "a bounded device-side wait expired (code %d)", *code_out);
+    }
     return DSMOE_OK;
 }
 uint64_t dsmoe_launch_count(const dsmoe_handle *h) { return h ? h->launches : 0; }
@@ -656,12 +666,16 @@ static int expert_ffn_impl(dsmoe_handle *h, cudaStream_t st, const dsmoe_layer_s
         g.order = h->pair_order;
         n += 1;
     }
+    // the TMA kernel quantises mid itself (a block as soon as its last row is stored): one launch less
+    const bool fused_q8k = gu_tma && c.n_ff % QK_K == 0;
+    if (fused_q8k) g.midq_out = h->midq, g.blk_rows = h->blk_rows;
     n += gu_tma ? launch_gate_up_mid_tma(st, g, h->d_status) : launch_gate_up_mid(st, g);
     if (int rc = check_launch(h, what, n)) return rc;
-    n = 1;
-    launch_q8k_quantize(st, h->mid, h->midq, c.n_ff, n_tokens * k);
-    if (int rc = check_launch(h, what, n)) return rc;
     n = 0;
+    if (!fused_q8k) {
+        launch_q8k_quantize(st, h->mid, h->midq, c.n_ff, n_tokens * k);
+        if (int rc = check_launch(h, what, 1)) return rc;
+    }
     DownArgs d = {ly.down, h->midq, sel, out, (uint64_t)c.n_embd * mb * Q2K_BYTES, (uint64_t)mb * Q2K_BYTES, mb,
                   c.n_embd, k, n_tokens, ly.layout, (int)c.f16_ieee, 1};
     n += ((h->use_tma && down_tma_eligible(d)) ? launch_down_tma(st, d, h->d_status) : launch_down(st, d));

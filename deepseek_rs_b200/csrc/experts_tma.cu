@@ -26,6 +26,7 @@
 #include "async.cuh"
 #include "common.cuh"
 #include "launch.h"
+#include "q8k.cuh"
 
 namespace dsmoe {
 
@@ -104,7 +105,7 @@ __global__ void __launch_bounds__(32 * GU_MAX_WARPS, 1)
                            const float *__restrict__ weights, float *__restrict__ gate_out, float *__restrict__ up_out,
                            float *__restrict__ mid_out, uint64_t expert_bytes, uint32_t mid_dim, uint32_t k,
                            uint32_t n_items, float clamp, int ieee_i, int *status, const int32_t *__restrict__ order,
-                           uint32_t parts)
+                           uint32_t parts, uint8_t *__restrict__ midq_out, uint32_t *__restrict__ blk_rows)
 {
     extern __shared__ __align__(128) uint8_t smem[];
     const int wpc = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -232,7 +233,9 @@ __global__ void __launch_bounds__(32 * GU_MAX_WARPS, 1)
             if (item - flush_base == 15 || item + 1 == end) {
                 // clamp + SwiGLU + stores for up to 32 finished rows at once, one per lane
                 const uint32_t mine = GU_ITEM_ROWS * flush_base + lane;  // flattened [position][row] index
-                if (mine < GU_ITEM_ROWS * (item + 1)) {
+                const bool wrote = mine < GU_ITEM_ROWS * (item + 1);
+                size_t dst = 0;
+                if (wrote) {
                     float gg = keep_g, uu = keep_u;
                     if (clamp > 1.0e-6f) {
                         if (gg > clamp) gg = clamp;
@@ -240,10 +243,40 @@ __global__ void __launch_bounds__(32 * GU_MAX_WARPS, 1)
                         if (uu < -clamp) uu = -clamp;
                     }
                     const uint32_t mpos = mine / mid_dim, mpair = order ? (uint32_t)order[mpos] : mpos;
-                    const size_t dst = (size_t)mpair * mid_dim + (mine - mpos * mid_dim);
+                    dst = (size_t)mpair * mid_dim + (mine - mpos * mid_dim);
                     if (gate_out) gate_out[dst] = gg;
                     if (up_out) up_out[dst] = uu;
                     mid_out[dst] = swiglu_weighted(gg, uu, weights[mpair]);
+                }
+                if (midq_out) {
+                    // Q8_K of mid, block by block as the blocks fill up: the rows just stored are counted into their
+                    // 256-row blocks (32 adjacent rows touch at most two), and the warp whose rows complete a block
+                    // quantises it (mid_dim is a multiple of 256, so a block never spans two pairs). The counter goes
+                    // back to 0 for the next call. Nobody waits: whoever arrives last does the work.
+                    __threadfence();
+                    const uint32_t gb = wrote ? (uint32_t)(dst >> 8) : 0xFFFFFFFFu;
+                    const uint32_t any = __ballot_sync(FULL, wrote);
+                    const uint32_t gb_a = __shfl_sync(FULL, gb, __ffs(any) - 1);
+                    const uint32_t in_b = __ballot_sync(FULL, wrote && gb != gb_a);
+                    const uint32_t gb_b = in_b ? __shfl_sync(FULL, gb, __ffs(in_b) - 1) : 0xFFFFFFFFu;
+                    uint32_t done = 0;
+                    if (lane == 0) {
+                        const uint32_t n_a = __popc(any & ~in_b), n_b = __popc(in_b);
+                        if (atomicAdd(&blk_rows[gb_a], n_a) + n_a == 256u) done |= 1u;
+                        if (in_b && atomicAdd(&blk_rows[gb_b], n_b) + n_b == 256u) done |= 2u;
+                    }
+                    done = __shfl_sync(FULL, done, 0);
+#pragma unroll
+                    for (int which = 0; which < 2; ++which) {
+                        if (!(done & (1u << which))) continue;
+                        const uint32_t b = which ? gb_b : gb_a;
+                        __threadfence();
+                        const float4 *src = reinterpret_cast<const float4 *>(mid_out + (size_t)b * QK_K + 8 * lane);
+                        const float4 v0 = __ldcg(src), v1 = __ldcg(src + 1);
+                        const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                        q8k_quantize_vals(v, midq_out + (size_t)b * Q8K_BYTES, lane);
+                        if (lane == 0) blk_rows[b] = 0;
+                    }
                 }
                 flush_base = item + 1;
             }
@@ -482,7 +515,7 @@ static void launch_gu_tma(cudaStream_t st, const GateUpArgs &a, int *status)
     const uint32_t grid = want < (uint32_t)sms ? want : (uint32_t)sms;
     launch_pdl(gate_up_x16_tma_kernel<LAYOUT>, dim3(grid), dim3(32 * best_w), smem, st, a.gate_base, a.up_base, a.xq,
                a.selected, a.weights, a.gate_out, a.up_out, a.mid_out, a.expert_bytes, a.mid_dim, a.k, n_items, a.clamp,
-               a.ieee, status, a.order, parts);
+               a.ieee, status, a.order, parts, a.midq_out, a.blk_rows);
 }
 
 int launch_gate_up_mid_tma(cudaStream_t st, const GateUpArgs &a, int *status)

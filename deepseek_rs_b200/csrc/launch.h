@@ -134,6 +134,11 @@ struct GateUpArgs {
     // TMA kernel only, optional: the pairs sorted by expert (order[position] = pair, from launch_pair_order); pairs of
     // one expert are then streamed together and the second one finds the weights in L2. Results do not depend on it.
     const int32_t *order = nullptr;
+    // TMA kernel only, optional: the kernel also writes Q8_K(mid) ([pair][mid_dim / 256] blocks), each block by the warp
+    // that stores its last row; blk_rows is one zeroed counter per block, which the kernel leaves zeroed. mid_dim must
+    // be a multiple of 256.
+    uint8_t *midq_out = nullptr;
+    uint32_t *blk_rows = nullptr;
 };
 // Returns the number of kernels launched.
 int launch_gate_up_mid(cudaStream_t st, const GateUpArgs &a);

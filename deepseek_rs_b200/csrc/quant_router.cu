@@ -2,6 +2,7 @@
 #include "async.cuh"
 #include "common.cuh"
 #include "launch.h"
+#include "q8k.cuh"
 
 namespace dsmoe {
 
@@ -13,62 +14,6 @@ namespace dsmoe {
 // maxima the element with the smallest bit-reversed index wins; using (|x|, bit-reversed index) as the reduction key
 // reproduces that choice (and hence the sign of d) in any reduction order.
 // ---------------------------------------------------------------------------------------------------------------
-// v: the lane's eight elements 8 lane .. 8 lane + 7 of the block
-__device__ __forceinline__ void q8k_quantize_vals(const float (&v)[8], uint8_t *__restrict__ yb, int lane)
-{
-
-    float best_abs = -1.0f, best_val = 0.0f;
-    uint32_t best_rev = 0xFFFFFFFFu;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        float a = v[i] < 0.0f ? -v[i] : v[i];
-        uint32_t rev = __brev((uint32_t)(8 * lane + i)) >> 24;
-        if (a > best_abs || (a == best_abs && rev < best_rev)) {
-            best_abs = a;
-            best_val = v[i];
-            best_rev = rev;
-        }
-    }
-#pragma unroll
-    for (int m = 16; m > 0; m >>= 1) {
-        float oa = __shfl_xor_sync(FULL, best_abs, m);
-        float ov = __shfl_xor_sync(FULL, best_val, m);
-        uint32_t orv = __shfl_xor_sync(FULL, best_rev, m);
-        if (oa > best_abs || (oa == best_abs && orv < best_rev)) {
-            best_abs = oa;
-            best_val = ov;
-            best_rev = orv;
-        }
-    }
-
-    uint32_t *qdst = reinterpret_cast<uint32_t *>(yb + 4 + 8 * lane);
-    if (!(best_abs > 0.0f)) {  // amax == 0 (or no finite maximum): all-zero block
-        if (lane == 0) *reinterpret_cast<float *>(yb) = 0.0f;
-        qdst[0] = 0u;
-        qdst[1] = 0u;
-        if (lane < 16) reinterpret_cast<uint16_t *>(yb + 260)[lane] = 0;
-        return;
-    }
-    const float iscale = __fdiv_rn(-127.0f, best_val);
-    if (lane == 0) *reinterpret_cast<float *>(yb) = __fdiv_rn(1.0f, iscale);
-
-    int q[8], s = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        float raw = __fmul_rn(iscale, v[i]);
-        int qi = raw >= 0.0f ? __float2int_rz(__fadd_rn(raw, 0.5f)) : __float2int_rz(__fadd_rn(raw, -0.5f));
-        qi = max(-128, min(127, qi));
-        q[i] = qi;
-        s += qi;
-    }
-    qdst[0] = (uint32_t)(q[0] & 255) | ((uint32_t)(q[1] & 255) << 8) | ((uint32_t)(q[2] & 255) << 16) |
-              ((uint32_t)(q[3] & 255) << 24);
-    qdst[1] = (uint32_t)(q[4] & 255) | ((uint32_t)(q[5] & 255) << 8) | ((uint32_t)(q[6] & 255) << 16) |
-              ((uint32_t)(q[7] & 255) << 24);
-    s += __shfl_xor_sync(FULL, s, 1);  // bsums cover 16 elements = two lanes
-    if ((lane & 1) == 0) reinterpret_cast<int16_t *>(yb + 260)[lane >> 1] = (int16_t)s;
-}
-
 __device__ __forceinline__ void q8k_quantize_block(const float *__restrict__ xb, uint8_t *__restrict__ yb, int lane)
 {
     const float4 *src = reinterpret_cast<const float4 *>(xb + 8 * lane);
@@ -246,9 +191,10 @@ void launch_router_select(cudaStream_t st, const float *logits, const float *bia
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Router and Q8_K of the same token in one launch (no bias, no hash table): one 256-thread CTA per token, one expert
-// per thread, so the double-precision exp/ln of all experts run side by side; the eight warps then quantise the
-// token's hidden row. Same results as router_select_kernel + q8k_quantize_kernel.
+// Router and Q8_K of the same token in one launch (no bias, no hash table): per token one 256-thread CTA routes, one
+// expert per thread, so the double-precision exp/ln of all experts run side by side, and the CTAs beside it
+// (blockIdx.y = 1 ..) quantise the token's hidden row, one block per warp, at the same time. Same results as
+// router_select_kernel + q8k_quantize_kernel.
 // Selection key: order-preserving integer image of the score in the high word, inverted expert index in the low
 // word, so an integer maximum picks the highest score and, among equals, the lowest index; key 0 = not selectable.
 // ---------------------------------------------------------------------------------------------------------------
@@ -273,6 +219,12 @@ __global__ void __launch_bounds__(256) router_q8k_fused_kernel(const float *__re
     pdl_wait();
     const uint32_t t = blockIdx.x;
     const int e = threadIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (blockIdx.y > 0) {  // CTAs 1.. of a token quantise its row, eight blocks each, beside CTA 0's routing
+        const uint32_t n_blocks = n_embd / QK_K, b = (blockIdx.y - 1) * 8 + warp;
+        if (b < n_blocks)
+            q8k_quantize_block(x + (size_t)t * n_embd + (size_t)b * QK_K, xq + ((size_t)t * n_blocks + b) * Q8K_BYTES, lane);
+        return;
+    }
     float p = 0.0f;
     unsigned long long key = 0ull;
     if (e < n_expert) {
@@ -314,9 +266,6 @@ __global__ void __launch_bounds__(256) router_q8k_fused_kernel(const float *__re
             weights[(size_t)t * k + j] = __fdiv_rn(s_w[j], div);
         }
     }
-    const uint32_t n_blocks = n_embd / QK_K;
-    for (uint32_t b = warp; b < n_blocks; b += 8)
-        q8k_quantize_block(x + (size_t)t * n_embd + (size_t)b * QK_K, xq + ((size_t)t * n_blocks + b) * Q8K_BYTES, lane);
 }
 
 void launch_router_q8k_fused(cudaStream_t st, const float *logits, const float *x, float *probs, int32_t *selected,
@@ -324,8 +273,9 @@ void launch_router_q8k_fused(cudaStream_t st, const float *logits, const float *
                              float route_scale)
 {
     if (n_tokens == 0) return;
-    router_q8k_fused_kernel<<<n_tokens, 256, 0, st>>>(logits, x, probs, selected, weights, xq, k, n_expert, n_embd,
-                                                      route_scale);
+    const unsigned q_ctas = (n_embd / QK_K + 7) / 8;
+    router_q8k_fused_kernel<<<dim3(n_tokens, 1 + q_ctas), 256, 0, st>>>(logits, x, probs, selected, weights, xq, k, n_expert,
+                                                                        n_embd, route_scale);
 }
 
 // ---------------------------------------------------------------------------------------------------------------

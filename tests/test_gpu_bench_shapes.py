@@ -104,3 +104,34 @@ def test_decode_layer_256_experts(torch_cuda, oracle, device_layer, T):
     got = out.cpu().numpy()
     assert np.array_equal(got.view(np.uint32), ref.view(np.uint32)), f"max abs err {np.abs(got - ref).max()}"
     K.close()
+
+
+@pytest.mark.parametrize("T,layout", [(16, "rowsoa"), (40, "native"), (100, "rowsoa")])
+def test_decode_layer_skewed_routing_twice(torch_cuda, oracle, device_layer, T, layout):
+    """Decode kernels with many tokens on the same few experts (Zipf s = 1.1 popularity): from 16 tokens on the pairs are
+    sorted by expert and walked in aligned runs, and the gate/up kernel quantises mid block by block as the blocks fill
+    up. Bit-identical to the oracle, and the same again from a second call on the same handle (the block counters must
+    come back to zero)."""
+    torch = torch_cuda
+    from deepseek_rs_b200.kernels import LAYOUT_NATIVE, LAYOUT_ROWSOA, MoeKernels, MoeLayer
+
+    rng = np.random.default_rng(900 + T)
+    x = F.bf16_round(rng.standard_normal((T, N_EMBD)).astype(np.float32))
+    logits = F.zipf_logits(rng, T, N_E, s=1.1)
+    K = MoeKernels(device=0, max_tokens=128)
+    layer = MoeLayer(K, *device_layer, layout=LAYOUT_ROWSOA if layout == "rowsoa" else LAYOUT_NATIVE)
+    sel = torch.zeros((T, K_USED), dtype=torch.int32, device="cuda")
+    wts = torch.zeros((T, K_USED), dtype=torch.float32, device="cuda")
+    xd, ld = torch.from_numpy(x).cuda(), torch.from_numpy(logits).cuda()
+    out1 = layer.forward(xd, ld, selected_out=sel, weights_out=wts).clone()
+    out2 = layer.forward(xd, ld, selected_out=sel, weights_out=wts).clone()
+    assert K.device_status() == 0
+    sel_h, wts_h = sel.cpu().numpy(), wts.cpu().numpy()
+    _, ref_sel, ref_w = oracle.router_select(logits, k=K_USED)
+    assert np.array_equal(sel_h, ref_sel) and np.array_equal(wts_h, ref_w)
+    assert np.bincount(sel_h.reshape(-1), minlength=N_E).max() >= T // 3, "the routing should pile tokens on one expert"
+    ref, _ = _oracle_sample(oracle, torch, device_layer, x, sel_h, wts_h, np.arange(T))
+    got1, got2 = out1.cpu().numpy(), out2.cpu().numpy()
+    assert np.array_equal(got1.view(np.uint32), ref.view(np.uint32)), f"max abs err {np.abs(got1 - ref).max()}"
+    assert np.array_equal(got2.view(np.uint32), got1.view(np.uint32))
+    K.close()
