@@ -635,7 +635,7 @@ def run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, 
     L, V = 2, 4
     K = MoeKernels(device=local_rank, max_tokens=T, max_layers=L)
     ep = ExpertParallelHandle(K, rank, world, max_replicas=R, recv_capacity_rows=3 * T * TOP_K)
-    ep_fused = ep.combine_is_fused()
+    ep_fused = bool(ep.combine_is_fused)
     g_exp, d_exp = GATE_EXPERT_BYTES, DOWN_EXPERT_BYTES
     shards = []
     for il in range(L):  # shard of layer il in ROWSOA order, with R empty replica slots behind the rank's own experts
