@@ -18,6 +18,7 @@ semantics; the reference's Rust cannot be built here) on the host cores.
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -1012,6 +1013,22 @@ def run_decode(args, torch, dist, K, layers, layout, device, rank, world, sample
 
 
 
+def start_watchdog(args, rank: int, world: int):
+    """Multi-rank runs only. A collective whose peer never arrives blocks inside a library call; this thread lets the
+    job end with a line that says so (value null: nothing was measured) instead of hanging until someone kills it."""
+
+    def give_up():
+        time.sleep(args.watchdog_s)
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": None, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                              "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+                              "error": f"the {world}-rank run did not finish within {args.watchdog_s} s "
+                                       "(a rank or a collective never arrived); nothing was measured"}), flush=True)
+        os._exit(4)
+
+    threading.Thread(target=give_up, daemon=True).start()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1025,6 +1042,8 @@ def main():
     ap.add_argument("--no-decode-block", action="store_true", help="prefill workload: skip the batch 1 / 8 / 64 decode block")
     ap.add_argument("--ep-replicate", type=int, default=32, choices=[0, 32, 64],
                     help="N > 1: this many of the most popular experts are held by every rank (0 = pure sharding)")
+    ap.add_argument("--watchdog-s", type=int, default=420, help="N > 1: give up (error line, exit 4) when the run has not "
+                    "finished after this many seconds, instead of waiting on a collective for ever")
     ap.add_argument("--layers", type=int, default=0, help="layers to rotate over (0 = the workload's default; 1 keeps "
                     "device memory small for profiler captures)")
     args = ap.parse_args()
@@ -1050,7 +1069,11 @@ def main():
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        # The exchanges here are kernel stores into peer memory plus tiny all-gathers, so NCCL's in-switch (NVLS) paths
+        # buy nothing; leaving them off keeps communicator set-up independent of the switch's multicast state.
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        start_watchdog(args, rank, world)
+        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=args.watchdog_s))
 
     sampler = ClockSampler(local_rank)
     sampler.start()  # started early (nvidia-smi takes a while to come up); samples are filtered to the load window
