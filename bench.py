@@ -637,6 +637,7 @@ def run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, 
     K = MoeKernels(device=local_rank, max_tokens=T, max_layers=L)
     ep = ExpertParallelHandle(K, rank, world, max_replicas=R, recv_capacity_rows=3 * T * TOP_K)
     ep_fused = bool(ep.combine_is_fused)
+    progress(rank, f"library communicator up, peer-mapped exchanges: {ep_fused}")
     g_exp, d_exp = GATE_EXPERT_BYTES, DOWN_EXPERT_BYTES
     shards = []
     for il in range(L):  # shard of layer il in ROWSOA order, with R empty replica slots behind the rank's own experts
@@ -688,8 +689,10 @@ def run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, 
         return float(t.item())
 
     t_load0 = time.time()
+    progress(rank, "shards and inputs ready; unreplicated steps")
     # pure sharding first: its time is reported, and its steps fill the running per-expert counts
     ms_unreplicated = timed(min(args.steps, 10))
+    progress(rank, f"unreplicated {ms_unreplicated:.3f} ms per step; installing replicas")
     max_recv_unrep = torch.tensor([float(sum(ep.last_recv_rows()))], dtype=torch.float64, device=device)
     dist.all_reduce(max_recv_unrep, op=dist.ReduceOp.MAX)
     hot = []
@@ -708,6 +711,7 @@ def run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, 
         ep.set_replicas(hot)
 
     # correctness before timing: routing against the single-GPU router, outputs against a single-GPU run of the layer
+    progress(rank, "replicas installed; checking routing and outputs against one GPU")
     K_solo = MoeKernels(device=local_rank, max_tokens=T, max_layers=1)
     probs = torch.empty((T, N_EXPERT), device=device)
     sel_solo, w_solo = torch.empty_like(sel), torch.empty((T, TOP_K), device=device)
@@ -746,8 +750,10 @@ def run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, 
         raise SystemExit(f"expert-parallel output differs from the single-GPU layer (max diff {out_maxdiff} of scale)")
 
     # timed: weak scaling (the line's value), then strong scaling (one chunk split over the ranks)
+    progress(rank, "checks done; timed weak-scaling steps")
     l0 = K.launch_count
     ms_step = timed(args.steps)
+    progress(rank, f"weak {ms_step:.3f} ms per step; strong-scaling steps")
     launches = K.launch_count - l0  # the route-side handle; the owner-side launches are counted inside the library call
     recv_rows = float(sum(ep.last_recv_rows()))
     ms_strong = timed(args.steps, T // world)
@@ -769,6 +775,7 @@ def run_prefill_ep(args, torch, dist, device, rank, world, local_rank, sampler, 
     ep.set_phase_events(None)
 
     # end to end: pinned host slices in, result back on the host, every step
+    progress(rank, "phases done; end-to-end steps")
     xh = [t.cpu().pin_memory() for t in xl]
     lh = [t.cpu().pin_memory() for t in ll]
     oh = torch.empty((T, N_EMBD)).pin_memory()
@@ -1013,6 +1020,15 @@ def run_decode(args, torch, dist, K, layers, layout, device, rank, world, sample
 
 
 
+T_START = time.time()
+
+
+def progress(rank: int, msg: str):
+    """Stage marks of a multi-rank run on stderr (the JSON line owns stdout): if a run stops, its log says where."""
+    if rank == 0:
+        print(f"[bench {time.time() - T_START:6.1f}s] {msg}", file=sys.stderr, flush=True)
+
+
 def start_watchdog(args, rank: int, world: int):
     """Multi-rank runs only. A collective whose peer never arrives blocks inside a library call; this thread lets the
     job end with a line that says so (value null: nothing was measured) instead of hanging until someone kills it."""
@@ -1073,7 +1089,9 @@ def main():
         # buy nothing; leaving them off keeps communicator set-up independent of the switch's multicast state.
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         start_watchdog(args, rank, world)
+        progress(rank, f"starting the process group ({world} ranks)")
         dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=args.watchdog_s))
+        progress(rank, "process group up")
 
     sampler = ClockSampler(local_rank)
     sampler.start()  # started early (nvidia-smi takes a while to come up); samples are filtered to the load window
