@@ -1058,7 +1058,7 @@ def main():
     ap.add_argument("--no-decode-block", action="store_true", help="prefill workload: skip the batch 1 / 8 / 64 decode block")
     ap.add_argument("--ep-replicate", type=int, default=32, choices=[0, 32, 64],
                     help="N > 1: this many of the most popular experts are held by every rank (0 = pure sharding)")
-    ap.add_argument("--watchdog-s", type=int, default=420, help="N > 1: give up (error line, exit 4) when the run has not "
+    ap.add_argument("--watchdog-s", type=int, default=240, help="N > 1: give up (error line, exit 4) when the run has not "
                     "finished after this many seconds, instead of waiting on a collective for ever")
     ap.add_argument("--layers", type=int, default=0, help="layers to rotate over (0 = the workload's default; 1 keeps "
                     "device memory small for profiler captures)")

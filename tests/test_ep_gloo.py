@@ -105,3 +105,40 @@ def test_expert_parallel_two_ranks_matches_single_rank():
     for rank, ok, sent, pairs in results:
         assert ok, f"rank {rank}: sharded result differs from the single-rank layer"
         assert sent == pairs  # every pair was dispatched exactly once
+
+
+def test_peer_store_slots_equal_an_all_to_all():
+    """The peer-store exchanges address the destination's buffer directly: send position i of rank r, lying in the
+    segment for destination d, goes to slot recv_base[r][d] + (i - send_begin[r][d]) of rank d, with recv_base[r][d] =
+    sum of M[s][d] over s < r (M[s][d] = rows rank s sends to rank d). This replays that arithmetic (csrc/ep.cu, the
+    gather's EpPeerDst and the combine's EpRowMap) on random count matrices and checks it against what an all-to-all
+    with the same splits delivers: every destination's slots are filled exactly once, grouped by source rank in rank
+    order, in send order inside a group; and the return path lands every result row on the position it was sent from."""
+    rng = np.random.default_rng(5)
+    for world in (1, 2, 4, 8, 16):
+        M = rng.integers(0, 50, size=(world, world))
+        M[rng.integers(0, world), :] = 0  # a rank that sends nothing
+        M[:, rng.integers(0, world)] = 0  # a rank that receives nothing
+        send_end = np.cumsum(M, axis=1)                       # [r][d]: end of d's segment in r's send order
+        send_begin = send_end - M
+        recv_base = np.cumsum(M, axis=0) - M                  # [r][d]: first slot of r's segment at d
+        recv = [[None] * int(M[:, d].sum()) for d in range(world)]
+        for r in range(world):
+            for i in range(int(M[r].sum())):
+                d = 0
+                while d + 1 < world and i >= send_end[r][d]:  # the kernels' linear search over destinations
+                    d += 1
+                slot = int(recv_base[r][d] + (i - send_begin[r][d]))
+                assert recv[d][slot] is None
+                recv[d][slot] = (r, i)
+        for d in range(world):
+            want = [(r, int(send_begin[r][d]) + j) for r in range(world) for j in range(int(M[r][d]))]
+            assert recv[d] == want                            # = all_to_all_single with these splits
+            seg_end = np.cumsum(M[:, d])                      # combine: received row j came from rank s, position ...
+            for j, (r, i) in enumerate(recv[d]):
+                s = 0
+                while s + 1 < world and j >= seg_end[s]:
+                    s += 1
+                begin = int(seg_end[s] - M[s][d])
+                dst_base = int(M[s][:d].sum())                # first slot of d's segment in s's send order
+                assert (s, dst_base + (j - begin)) == (r, i)
